@@ -1,0 +1,122 @@
+/* C ABI of the B200 (sm_100a) Pyramid-Sparse-Attention kernels.
+ *
+ * Every entry point takes raw device pointers, sizes and a cudaStream_t (passed as void*), enqueues
+ * its kernels on that stream and returns a status code without synchronising.  Nothing here allocates
+ * device memory unless the comment of the entry point says otherwise: outputs and scratch are the
+ * caller's.  All tensors are contiguous; "[BH, S, D]" means batch*heads major, token, channel.
+ * dtype codes: 0 = float32, 1 = float16, 2 = bfloat16.
+ *
+ * Each declaration cites the part of ziplab/Pyramid-Sparse-Attention it stands in for
+ * (paths relative to that project).
+ */
+#ifndef PSA_B200_H_
+#define PSA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PSA_OK 0
+#define PSA_ERR_ARG 1          /* bad argument (shape, alignment, null pointer) */
+#define PSA_ERR_UNSUPPORTED 2  /* valid request this build has no kernel for */
+#define PSA_ERR_CUDA 3         /* a CUDA runtime/driver call or launch failed */
+#define PSA_ERR_TIMEOUT 4      /* a bounded device-side wait expired (reported through a status word) */
+
+#define PSA_F32 0
+#define PSA_F16 1
+#define PSA_BF16 2
+
+#define PSA_MAX_LEVELS 8
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* psa_last_error_string(void);
+
+/* Library version / build info string. */
+const char* psa_build_info(void);
+
+/* Pyramid K/V builder.  Replaces pad_to_multiple + pooling chain,
+ * src/psa_triton/kernels/psa_kernel.py:318-349 and its call site :381-388 (legacy twin
+ * src/psa_triton/kernels/psa_kernel_legacy.py:806-834, 868-875).
+ * k, v: [BH, S, D].  Outputs x2/x4/x8: [BH, S_pad/l, D] with S_pad = ceil(S/block_n)*block_n; tokens past
+ * S replicate token S-1; each level is the pairwise mean of the previous ROUNDED level (fp32 add, one
+ * rounding to dtype).  One pass over K and V; the never-read level 16 is not built. */
+int psa_pyramid_kv(const void* k, const void* v, void* k2, void* k4, void* k8, void* v2, void* v4, void* v8,
+                   int64_t bh, int64_t seq, int head_dim, int block_n, int dtype, void* stream);
+
+/* Block-importance scores.  Replaces _random_sample_tokens' gather + replicate padding
+ * (src/psa_triton/attention.py:128-137, 195-196, 214-215), attn_with_pooling_optimized
+ * (src/psa_triton/kernels/attn_pooling_kernel.py:119-431) and the slice at attention.py:223.
+ * q: [BH, seq_q, D], k: [BH, seq_k, D]; idx_q: [BH, block_m/4], idx_k: [BH, block_n/4] int32 = the
+ * in-block token offsets drawn by topk(rand) on the host side.  po: [BH, ceil(seq_q/block_m),
+ * ceil(seq_k/block_n)] in dtype.  scratch: psa_block_scores_scratch_bytes() bytes, 256-byte aligned.
+ * impl: 0 = pick (tensor-core kernel for f16/bf16, else scalar), 1 = scalar fp32 kernel, 2 = tcgen05 kernel. */
+size_t psa_block_scores_scratch_bytes(int64_t bh, int64_t seq_q, int64_t seq_k, int block_m, int block_n, int dtype);
+int psa_block_scores(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* po,
+                     void* scratch, size_t scratch_bytes, int64_t bh, int64_t seq_q, int64_t seq_k, int head_dim,
+                     int block_m, int block_n, int dtype, int impl, void* stream);
+
+/* Level assignment.  Replaces transfer_attn_to_mask, all four modes,
+ * src/psa_triton/utils/transfer_attn_to_mask.py:6-507.
+ * po: [rows, nk] scores in dtype (rows = B*H*Mq).  mask: int32 [rows, nk + n_levels] (newtype) or [rows, nk].
+ * Sort is descending with equal scores in ascending index order.
+ * threshold_mode 0 (topk*): starts/ends[n_levels] are the rank intervals, computed by the caller with the
+ *   reference's Python arithmetic (:63-120 / :282-351); an empty interval has start == end.
+ * threshold_mode 1 (thresholdbound*): levels must be in ascending end_ratio order; thresholds[i] is
+ *   end_ratio+1e-6 already rounded to dtype; aligns[i] = ceil(level/(block_n/tile_n)); min_index =
+ *   min(nk, int(nk*min_full_attn_ratio)+1) applies to level 1 (:225-232, :454-461).
+ * text_blocks > 0 (old format only): the last text_blocks columns are forced to 1 (:40-45).
+ * level_values/starts/ends/thresholds/aligns are HOST arrays of n_levels <= PSA_MAX_LEVELS entries. */
+int psa_assign_levels(const void* po, int32_t* mask, int64_t rows, int nk, int dtype, int threshold_mode,
+                      int newtype, int n_levels, const int32_t* level_values, const int32_t* starts,
+                      const int32_t* ends, const float* thresholds, const int32_t* aligns, int min_index,
+                      int text_blocks, void* stream);
+
+/* Mask density.  Replaces calc_density_newtype / calc_density,
+ * src/psa_triton/utils/transfer_attn_to_mask.py:510-622.  per_bh: float32 [BH], the mean density of
+ * each (batch, head); no host synchronisation. */
+int psa_density(const int32_t* mask, float* per_bh, int64_t bh, int64_t mq, int width, int newtype, void* stream);
+
+/* K-similarity cap.  Replaces calc_k_similarity_triton, src/psa_triton/kernels/calc_ksim_kernel.py:6-225
+ * (and its PyTorch twin :227-265) together with the replicate padding at src/psa_triton/attention.py:196.
+ * k: [BH, seq, D]; out: int32 [BH, ceil(seq/block_n)] in {1,2,4,8}. */
+int psa_ksim(const void* k, int32_t* out, int64_t bh, int64_t seq, int head_dim, int block_n, float t2, float t4,
+             float t8, int dtype, void* stream);
+
+/* Multi-level block-sparse attention forward on the separator-format mask.  Replaces _fwd_kernel /
+ * _forward, src/psa_triton/kernels/psa_kernel.py:24-316, 351-432 (pyramid tensors come from
+ * psa_pyramid_kv).  q/out: [BH, seq_q, D]; k, v: [BH, seq_k, D]; k2..v8 as produced by psa_pyramid_kv;
+ * mask: int32 [BH, ceil(seq_q/block_m), mask_width], per row: level-1 block indices, -1, level-2, -1,
+ * level-4, -1, level-8, -1, rest ignored.  compat_quirk != 0 reproduces the reference's handling of levels
+ * whose pooled block is narrower than half a tile (:261-278): each merged pair also attends pooled tokens
+ * [2P, tile_n) of that level.  impl: 0 = pick, 1 = scalar kernel, 2 = tcgen05 kernel (f16/bf16, block_m 128).
+ * status: device int32 word, written non-zero if a bounded wait inside the kernel expired (may be NULL). */
+int psa_fwd(const void* q, const void* k, const void* v, const void* k2, const void* k4, const void* k8,
+            const void* v2, const void* v4, const void* v8, const int32_t* mask, void* out, int64_t bh,
+            int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width,
+            float sm_scale, int compat_quirk, int impl, int dtype, int32_t* status, void* stream);
+
+/* Legacy forward on the dense old-format mask, optional causal.  Replaces _fwd_kernel / _forward,
+ * src/psa_triton/kernels/psa_kernel_legacy.py:415-799, 837-938 (block sizes fixed 128/32/128, :1333-1351).
+ * mask: int32 [BH, ceil(seq/128), mask_cols] in {0,1,2,4,8}; lse: float32 [BH, seq] = M + ln(max(L,1e-8))
+ * (:931), may be NULL. */
+int psa_legacy_fwd(const void* q, const void* k, const void* v, const void* k2, const void* k4, const void* k8,
+                   const void* v2, const void* v4, const void* v8, const int32_t* mask, void* out, float* lse,
+                   int64_t bh, int64_t seq, int head_dim, int mask_cols, float sm_scale, int causal, int dtype,
+                   void* stream);
+
+/* Legacy backward.  Replaces _sparse_attention.backward and its kernels/helpers,
+ * src/psa_triton/kernels/psa_kernel_legacy.py:947-1320.  dq/dk/dv: [BH, seq, D] in dtype; delta: float32
+ * [BH, seq] scratch.  Gradients follow the reference's rule (causality on original key positions of the
+ * repeat-expanded pooled K/V, :1139-1150). */
+int psa_legacy_bwd(const void* q, const void* k, const void* v, const void* k2, const void* k4, const void* k8,
+                   const void* v2, const void* v4, const void* v8, const int32_t* mask, const void* out,
+                   const float* lse, const void* dout, void* dq, void* dk, void* dv, float* delta, int64_t bh,
+                   int64_t seq, int head_dim, int mask_cols, float sm_scale, int causal, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PSA_B200_H_ */

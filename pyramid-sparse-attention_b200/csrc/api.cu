@@ -1,0 +1,75 @@
+// extern "C" surface shared by all kernels: error text, build info and the attention entry points that
+// choose between the scalar and the tcgen05 kernels.
+#include <stdarg.h>
+#include <string.h>
+
+#include "psa_common.cuh"
+#include "fwd.h"
+
+namespace psa {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+}  // namespace psa
+
+extern "C" const char* psa_last_error_string(void) { return psa::g_err; }
+
+extern "C" const char* psa_build_info(void) {
+  return "psa_b200 sm_100a (pyramid, block scores, level assignment, multi-level forward, legacy fwd/bwd); "
+         "built " __DATE__ " " __TIME__;
+}
+
+extern "C" int psa_fwd(const void* q, const void* k, const void* v, const void* k2, const void* k4, const void* k8,
+                       const void* v2, const void* v4, const void* v8, const int32_t* mask, void* out, int64_t bh,
+                       int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width,
+                       float sm_scale, int compat_quirk, int impl, int dtype, int32_t* status, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(q && k && v && k2 && k4 && k8 && v2 && v4 && v8 && mask && out, PSA_ERR_ARG, "psa_fwd: null pointer");
+  PSA_REQUIRE(head_dim == 64 || head_dim == 128, PSA_ERR_ARG, "psa_fwd: head_dim=%d (must be 64 or 128)", head_dim);
+  PSA_REQUIRE(block_n == 32 || block_n == 64 || block_n == 128, PSA_ERR_ARG, "psa_fwd: block_n=%d (32/64/128)", block_n);
+  PSA_REQUIRE(tile_n == 32, PSA_ERR_UNSUPPORTED, "psa_fwd: tile_n=%d (only 32, the value every preset uses)", tile_n);
+  PSA_REQUIRE(block_m == 32 || block_m == 64 || block_m == 128, PSA_ERR_ARG, "psa_fwd: block_m=%d (32/64/128)", block_m);
+  PSA_REQUIRE(bh > 0 && bh < 65536 && seq_q > 0 && seq_k > 0, PSA_ERR_ARG, "psa_fwd: bad shape");
+  PSA_REQUIRE(mask_width >= 1 && mask_width <= 16384, PSA_ERR_ARG, "psa_fwd: mask_width=%d", mask_width);
+  PSA_REQUIRE(impl >= 0 && impl <= 2, PSA_ERR_ARG, "psa_fwd: impl=%d", impl);
+  const int64_t s_pad = cdiv64(seq_k, block_n) * block_n;
+  const void* kl[4] = {k, k2, k4, k8};
+  const void* vl[4] = {v, v2, v4, v8};
+  const int64_t nl[4] = {seq_k, s_pad / 2, s_pad / 4, s_pad / 8};
+  cudaStream_t st = (cudaStream_t)stream;
+  FwdArgs a;
+  a.q = q; a.mask = mask; a.out = out; a.status = status;
+  for (int i = 0; i < 4; ++i) { a.k[i] = kl[i]; a.v[i] = vl[i]; a.n[i] = nl[i]; }
+  a.bh = bh; a.seq_q = seq_q; a.seq_k = seq_k; a.D = head_dim; a.bm = block_m; a.bn = block_n; a.tn = tile_n;
+  a.width = mask_width; a.scale = sm_scale; a.quirk = compat_quirk; a.dtype = dtype;
+  const bool tc_ok = fwd_tc_supported(a);
+  if (impl == 2) PSA_REQUIRE(tc_ok, PSA_ERR_UNSUPPORTED, "psa_fwd: the tcgen05 kernel needs f16/bf16, block_m=128");
+  if (impl == 2 || (impl == 0 && tc_ok)) return fwd_tc_launch(a, st);
+  return fwd_simt_dispatch(q, kl, vl, nl, mask, out, bh, seq_q, head_dim, block_m, block_n, tile_n, mask_width, sm_scale,
+                           compat_quirk, dtype, st);
+}
+
+extern "C" int psa_legacy_fwd(const void* q, const void* k, const void* v, const void* k2, const void* k4,
+                              const void* k8, const void* v2, const void* v4, const void* v8, const int32_t* mask,
+                              void* out, float* lse, int64_t bh, int64_t seq, int head_dim, int mask_cols, float sm_scale,
+                              int causal, int dtype, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(q && k && v && k2 && k4 && k8 && v2 && v4 && v8 && mask && out, PSA_ERR_ARG, "psa_legacy_fwd: null pointer");
+  PSA_REQUIRE(head_dim == 64 || head_dim == 128, PSA_ERR_ARG, "psa_legacy_fwd: head_dim=%d (must be 64 or 128)", head_dim);
+  PSA_REQUIRE(bh > 0 && bh < 65536 && seq > 0, PSA_ERR_ARG, "psa_legacy_fwd: bad shape");
+  PSA_REQUIRE(mask_cols >= cdiv64(seq, 128), PSA_ERR_ARG, "psa_legacy_fwd: mask has %d columns, needs %lld", mask_cols,
+              (long long)cdiv64(seq, 128));
+  const int64_t s_pad = cdiv64(seq, 128) * 128;
+  const void* kl[4] = {k, k2, k4, k8};
+  const void* vl[4] = {v, v2, v4, v8};
+  const int64_t nl[4] = {seq, s_pad / 2, s_pad / 4, s_pad / 8};
+  return legacy_fwd_simt_dispatch(q, kl, vl, nl, mask, out, lse, bh, seq, head_dim, mask_cols, sm_scale, causal, dtype,
+                                  (cudaStream_t)stream);
+}

@@ -1,0 +1,103 @@
+// Pyramid K/V builder: levels 2/4/8 of the mean-pooled K and V in ONE pass over HBM.
+//
+// HBM-bound.  Algorithmic bytes per call: read K and V once (2*N*e), write levels 2, 4, 8
+// (2*N*e*(1/2+1/4+1/8)) = 3.75*N*e with N = BH*S*D elements of e bytes.
+//
+// Each thread owns one 16-byte channel chunk of 8 consecutive tokens: it loads 8 x 16 B (rows 8j..8j+7,
+// clamped to S-1 = replicate padding), forms level 2 (4 rows), level 4 (2 rows) and level 8 (1 row) in
+// registers, rounding to the element type after every level exactly like a chain of means over a
+// size-2 dimension does, and stores 7 x 16 B.  Consecutive threads take consecutive 16-byte chunks of
+// the same token group, so every warp access covers whole 128-byte lines.
+#include "psa_common.cuh"
+
+namespace psa {
+
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+
+template <typename T>
+__device__ __forceinline__ void pair_mean(const uint4& a, const uint4& b, uint4& o) {
+  constexpr int N = Vec16<T>::N;
+  const T* pa = reinterpret_cast<const T*>(&a);
+  const T* pb = reinterpret_cast<const T*>(&b);
+  T* po = reinterpret_cast<T*>(&o);
+#pragma unroll
+  for (int i = 0; i < N; ++i) po[i] = Elem<T>::from_f((Elem<T>::to_f(pa[i]) + Elem<T>::to_f(pb[i])) * 0.5f);
+}
+
+// grid.x: chunks of work items; grid.y: 0 = K, 1 = V.
+template <typename T>
+__global__ void __launch_bounds__(256) pyramid_kernel(const T* __restrict__ k, const T* __restrict__ v,
+                                                      T* __restrict__ k2, T* __restrict__ k4, T* __restrict__ k8,
+                                                      T* __restrict__ v2, T* __restrict__ v4, T* __restrict__ v8,
+                                                      int64_t bh, int64_t S, int64_t n8, int cpr /*16B chunks per row*/) {
+  const T* x = blockIdx.y ? v : k;
+  T* x2 = blockIdx.y ? v2 : k2;
+  T* x4 = blockIdx.y ? v4 : k4;
+  T* x8 = blockIdx.y ? v8 : k8;
+  const int64_t total = bh * n8 * cpr;
+  const int64_t row_u4 = cpr;  // uint4 per token row
+  for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(w % cpr);
+    const int64_t g = w / cpr;  // token group index over all heads
+    const int64_t head = g / n8;
+    const int64_t j = g % n8;
+    const uint4* src = reinterpret_cast<const uint4*>(x) + head * S * row_u4 + c;
+    uint4 r[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      int64_t tok = j * 8 + t;
+      tok = tok < S ? tok : S - 1;
+      r[t] = __ldg(src + tok * row_u4);
+    }
+    uint4 a[4], b[2], d;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) pair_mean<T>(r[2 * t], r[2 * t + 1], a[t]);
+    pair_mean<T>(a[0], a[1], b[0]);
+    pair_mean<T>(a[2], a[3], b[1]);
+    pair_mean<T>(b[0], b[1], d);
+    uint4* d2 = reinterpret_cast<uint4*>(x2) + (head * n8 * 4 + j * 4) * row_u4 + c;
+    uint4* d4 = reinterpret_cast<uint4*>(x4) + (head * n8 * 2 + j * 2) * row_u4 + c;
+    uint4* d8 = reinterpret_cast<uint4*>(x8) + (head * n8 + j) * row_u4 + c;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) d2[t * row_u4] = a[t];
+    d4[0] = b[0];
+    d4[row_u4] = b[1];
+    d8[0] = d;
+  }
+}
+
+template <typename T>
+static int launch_pyramid(const void* k, const void* v, void* k2, void* k4, void* k8, void* v2, void* v4, void* v8,
+                          int64_t bh, int64_t S, int D, int block_n, cudaStream_t st) {
+  const int64_t s_pad = cdiv64(S, block_n) * block_n;
+  const int64_t n8 = s_pad / 8;
+  const int cpr = D * (int)sizeof(T) / 16;
+  const int64_t total = bh * n8 * cpr;
+  int64_t blocks = cdiv64(total, 256);
+  const int64_t cap = 148 * 16;  // a few resident CTAs per SM, grid-stride beyond that
+  if (blocks > cap) blocks = cap;
+  dim3 grid((unsigned)blocks, 2);
+  pyramid_kernel<T><<<grid, 256, 0, st>>>((const T*)k, (const T*)v, (T*)k2, (T*)k4, (T*)k8, (T*)v2, (T*)v4, (T*)v8,
+                                          bh, S, n8, cpr);
+  PSA_CHECK_LAUNCH("psa_pyramid_kv");
+  return PSA_OK;
+}
+
+}  // namespace psa
+
+extern "C" int psa_pyramid_kv(const void* k, const void* v, void* k2, void* k4, void* k8, void* v2, void* v4,
+                              void* v8, int64_t bh, int64_t seq, int head_dim, int block_n, int dtype, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(k && v && k2 && k4 && k8 && v2 && v4 && v8, PSA_ERR_ARG, "psa_pyramid_kv: null pointer");
+  PSA_REQUIRE(bh > 0 && seq > 0, PSA_ERR_ARG, "psa_pyramid_kv: empty tensor (bh=%lld seq=%lld)", (long long)bh,
+              (long long)seq);
+  PSA_REQUIRE(block_n > 0 && block_n % 8 == 0, PSA_ERR_ARG, "psa_pyramid_kv: block_n=%d must be a multiple of 8", block_n);
+  PSA_REQUIRE(head_dim > 0 && head_dim % 8 == 0, PSA_ERR_ARG, "psa_pyramid_kv: head_dim=%d must be a multiple of 8",
+              head_dim);
+  const void* ptrs[8] = {k, v, k2, k4, k8, v2, v4, v8};
+  for (int i = 0; i < 8; ++i)
+    PSA_REQUIRE(((uintptr_t)ptrs[i] & 15) == 0, PSA_ERR_ARG, "psa_pyramid_kv: pointer %d is not 16-byte aligned", i);
+  cudaStream_t st = (cudaStream_t)stream;
+  PSA_DISPATCH_DTYPE(dtype, T, return launch_pyramid<T>(k, v, k2, k4, k8, v2, v4, v8, bh, seq, head_dim, block_n, st));
+  return PSA_OK;
+}

@@ -1,0 +1,200 @@
+// Block-importance scores on sampled tokens.
+//
+// Stage A (cell maxima): for every sampled query row i and every K cell c (block_n/4 consecutive sampled
+// key rows) R[i,c] = max_{j in c}(q_i . k_j) * (D^-0.5 * log2 e), stored in the element type, and the row
+// maximum m_i of the UNROUNDED values.  The sampled rows are gathered on the fly from Q/K through the
+// per-head index lists (token = min(block*blk + idx[t], S-1): replicate padding of the tail block; sample
+// rows past the end replicate the last sample: the reference pads the sample matrices to a multiple of 64).
+// Stage B (pooling + normalisation): Po[r,c] = max_{i in group r} exp2(R[i,c] - m_i) rounded to the element
+// type, divided by the row sum over ALL cells (padded cells included), sliced to [Mq, Nk].
+//
+// This file holds the scalar fp32 stage A (any dtype; exact fp32 dot products) and stage B.  The tcgen05
+// stage A for f16/bf16 lives in scores_tc.cu.
+#include "psa_common.cuh"
+#include "scores.h"
+
+namespace psa {
+
+// ---------------------------------------------------------------- stage A, scalar -----------------
+// CTA: 64 sampled q rows x all K cells; 256 threads as 16x16, each 4x4 outputs of a 64x64 tile.
+template <typename T>
+__global__ void __launch_bounds__(256) scores_cellmax_simt(const T* __restrict__ q, const T* __restrict__ k,
+                                                           const int32_t* __restrict__ idx_q,
+                                                           const int32_t* __restrict__ idx_k, T* __restrict__ R,
+                                                           float* __restrict__ rowmax, ScoreDims d) {
+  __shared__ float Qs[64][33];
+  __shared__ float Ks[64][33];
+  __shared__ int64_t qtok[64];
+  __shared__ int64_t ktok[64];
+  const int bh = blockIdx.y;
+  const int row0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const T* qh = q + (int64_t)bh * d.seq_q * d.D;
+  const T* kh = k + (int64_t)bh * d.seq_k * d.D;
+  if (threadIdx.x < 64) {
+    int i = row0 + threadIdx.x;
+    i = i < d.nq_s ? i : d.nq_s - 1;
+    int64_t tok = (int64_t)(i / d.kq) * d.bm + idx_q[bh * d.kq + (i % d.kq)];
+    qtok[threadIdx.x] = tok < d.seq_q ? tok : d.seq_q - 1;
+  }
+  float run_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  const int cells_per_tile = 64 / d.kk;
+  for (int col0 = 0; col0 < d.nk_cols; col0 += 64) {
+    __syncthreads();
+    if (threadIdx.x < 64) {
+      int j = col0 + threadIdx.x;
+      j = j < d.nk_s ? j : d.nk_s - 1;
+      int64_t tok = (int64_t)(j / d.kk) * d.bn + idx_k[bh * d.kk + (j % d.kk)];
+      ktok[threadIdx.x] = tok < d.seq_k ? tok : d.seq_k - 1;
+    }
+    float acc[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+    for (int d0 = 0; d0 < d.D; d0 += 32) {
+      __syncthreads();
+      for (int e = threadIdx.x; e < 64 * 32; e += 256) {
+        int r = e >> 5, c = e & 31;
+        Qs[r][c] = Elem<T>::to_f(qh[qtok[r] * d.D + d0 + c]);
+        Ks[r][c] = Elem<T>::to_f(kh[ktok[r] * d.D + d0 + c]);
+      }
+      __syncthreads();
+#pragma unroll 8
+      for (int c = 0; c < 32; ++c) {
+        float qa[4], kb[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) qa[a] = Qs[ty * 4 + a][c];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) kb[b] = Ks[tx * 4 + b][c];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(qa[a], kb[b], acc[a][b]);
+      }
+    }
+    // cell maxima: a thread's 4 columns sit inside one cell (kk is a multiple of 4); reduce over the
+    // kk/4 neighbouring tx lanes.
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      float mx = fmaxf(fmaxf(acc[a][0], acc[a][1]), fmaxf(acc[a][2], acc[a][3]));
+      for (int off = 1; off < d.kk / 4; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      mx *= d.qk_scale;
+      run_max[a] = fmaxf(run_max[a], mx);
+      const int row = row0 + ty * 4 + a;
+      if ((tx % (d.kk / 4)) == 0 && row < d.nq_s) {
+        const int cell = col0 / d.kk + (tx * 4) / d.kk;
+        if (cell < d.n_d) R[((int64_t)bh * d.nq_s + row) * d.n_d + cell] = Elem<T>::from_f(mx);
+      }
+    }
+    (void)cells_per_tile;
+  }
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    float mx = run_max[a];
+    for (int off = 1; off < 16; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    const int row = row0 + ty * 4 + a;
+    if (tx == 0 && row < d.nq_s) rowmax[(int64_t)bh * d.nq_s + row] = mx;
+  }
+}
+
+// ---------------------------------------------------------------- stage B -------------------------
+// CTA per (query block r, bh).  Dynamic smem: n_d floats.
+template <typename T>
+__global__ void __launch_bounds__(256) scores_pool_normalise(const T* __restrict__ R, const float* __restrict__ rowmax,
+                                                            T* __restrict__ po, ScoreDims d) {
+  extern __shared__ float sm_po[];
+  __shared__ float red[8];
+  __shared__ float s_rowmax[64];
+  const int r = blockIdx.x, bh = blockIdx.y;
+  const int64_t rbase = (int64_t)bh * d.nq_s + (int64_t)r * d.kq;
+  if (threadIdx.x < d.kq) s_rowmax[threadIdx.x] = rowmax[rbase + threadIdx.x];
+  __syncthreads();
+  float part = 0.f;
+  for (int c = threadIdx.x; c < d.n_d; c += blockDim.x) {
+    float best = 0.f;
+    for (int t = 0; t < d.kq; ++t) {
+      float x = Elem<T>::to_f(R[(rbase + t) * d.n_d + c]);
+      best = fmaxf(best, exp2f(x - s_rowmax[t]));
+    }
+    best = Elem<T>::round(best);
+    sm_po[c] = best;
+    part += best;
+  }
+  for (int off = 16; off; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
+  __syncthreads();
+  float sum = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) sum += red[w];
+  sum = Elem<T>::round(sum);
+  T* dst = po + ((int64_t)bh * d.Mq + r) * d.Nk;
+  for (int c = threadIdx.x; c < d.Nk; c += blockDim.x) dst[c] = Elem<T>::from_f(sm_po[c] / sum);
+}
+
+template <typename T>
+static int launch_scores(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* po,
+                         void* scratch, const ScoreDims& d, int64_t bh, int impl, cudaStream_t st) {
+  T* R = (T*)scratch;
+  const size_t r_bytes = ((size_t)bh * d.nq_s * d.n_d * sizeof(T) + 255) & ~(size_t)255;
+  float* rowmax = (float*)((char*)scratch + r_bytes);
+  bool use_tc = (impl == 2) || (impl == 0 && sizeof(T) == 2 && scores_tc_supported(d));
+  if (use_tc) {
+    int rc = launch_scores_cellmax_tc(q, k, idx_q, idx_k, R, rowmax, d, bh, sizeof(T) == 4 ? PSA_F32 :
+                                      (std::is_same<T, __half>::value ? PSA_F16 : PSA_BF16), st);
+    if (rc != PSA_OK) return rc;
+  } else {
+    dim3 grid((unsigned)cdiv64(d.nq_s, 64), (unsigned)bh);
+    scores_cellmax_simt<T><<<grid, 256, 0, st>>>((const T*)q, (const T*)k, idx_q, idx_k, R, rowmax, d);
+    PSA_CHECK_LAUNCH("psa_block_scores(stage A)");
+  }
+  dim3 gridb((unsigned)d.Mq, (unsigned)bh);
+  scores_pool_normalise<T><<<gridb, 256, d.n_d * sizeof(float), st>>>(R, rowmax, (T*)po, d);
+  PSA_CHECK_LAUNCH("psa_block_scores(stage B)");
+  return PSA_OK;
+}
+
+int make_score_dims(ScoreDims& d, int64_t seq_q, int64_t seq_k, int D, int bm, int bn) {
+  PSA_REQUIRE(bm >= 16 && bm <= 256 && bm % 16 == 0, PSA_ERR_ARG, "block_m=%d unsupported (16..256, multiple of 16)", bm);
+  PSA_REQUIRE(bn == 32 || bn == 64 || bn == 128, PSA_ERR_ARG, "block_n=%d unsupported (32/64/128)", bn);
+  PSA_REQUIRE(D == 64 || D == 128, PSA_ERR_ARG, "head_dim=%d unsupported (64/128)", D);
+  PSA_REQUIRE(seq_q > 0 && seq_k > 0, PSA_ERR_ARG, "empty sequence");
+  d.seq_q = seq_q; d.seq_k = seq_k; d.D = D; d.bm = bm; d.bn = bn;
+  d.kq = bm / 4; d.kk = bn / 4;
+  d.Mq = (int)cdiv64(seq_q, bm); d.Nk = (int)cdiv64(seq_k, bn);
+  d.nq_s = d.Mq * d.kq; d.nk_s = d.Nk * d.kk;
+  d.nk_cols = (int)(cdiv64(d.nk_s, 64) * 64);
+  d.n_d = d.nk_cols / d.kk;
+  PSA_REQUIRE(d.kq <= 64, PSA_ERR_ARG, "block_m too large");
+  const float sm_scale = (float)(1.0 / sqrt((double)D));
+  d.qk_scale = sm_scale * 1.44269504f;
+  return PSA_OK;
+}
+
+}  // namespace psa
+
+extern "C" size_t psa_block_scores_scratch_bytes(int64_t bh, int64_t seq_q, int64_t seq_k, int block_m, int block_n,
+                                                 int dtype) {
+  psa::ScoreDims d;
+  if (psa::make_score_dims(d, seq_q, seq_k, 64, block_m, block_n) != PSA_OK) return 0;
+  const size_t es = dtype == PSA_F32 ? 4 : 2;
+  const size_t r_bytes = ((size_t)bh * d.nq_s * d.n_d * es + 255) & ~(size_t)255;
+  return r_bytes + (size_t)bh * d.nq_s * sizeof(float) + 256;
+}
+
+extern "C" int psa_block_scores(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* po,
+                                void* scratch, size_t scratch_bytes, int64_t bh, int64_t seq_q, int64_t seq_k,
+                                int head_dim, int block_m, int block_n, int dtype, int impl, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(q && k && idx_q && idx_k && po && scratch, PSA_ERR_ARG, "psa_block_scores: null pointer");
+  PSA_REQUIRE(bh > 0 && bh < 65536, PSA_ERR_ARG, "psa_block_scores: bh=%lld out of range", (long long)bh);
+  PSA_REQUIRE(((uintptr_t)scratch & 255) == 0, PSA_ERR_ARG, "psa_block_scores: scratch must be 256-byte aligned");
+  ScoreDims d;
+  int rc = make_score_dims(d, seq_q, seq_k, head_dim, block_m, block_n);
+  if (rc != PSA_OK) return rc;
+  PSA_REQUIRE(scratch_bytes >= psa_block_scores_scratch_bytes(bh, seq_q, seq_k, block_m, block_n, dtype), PSA_ERR_ARG,
+              "psa_block_scores: scratch too small (%zu bytes)", scratch_bytes);
+  PSA_REQUIRE(impl >= 0 && impl <= 2, PSA_ERR_ARG, "psa_block_scores: impl=%d", impl);
+  cudaStream_t st = (cudaStream_t)stream;
+  PSA_DISPATCH_DTYPE(dtype, T, return launch_scores<T>(q, k, idx_q, idx_k, po, scratch, d, bh, impl, st));
+  return PSA_OK;
+}

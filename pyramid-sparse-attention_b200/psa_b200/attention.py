@@ -1,0 +1,111 @@
+"""Plug-and-play PSA module: same names, fields, validation and call contract as
+src/psa_triton/attention.py (PSAConfig :36-104, PSAAttention :226-310, psa_attention :314-367).
+The work is done by the sm_100a kernels; nothing here falls back to PyTorch math."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import ops
+from .kernels import legacy_sparse_attention_factory, sparse_attention_factory
+
+
+@dataclass
+class PSAConfig:
+    """Configuration for PSA attention; defaults give ~85% sparsity."""
+    block_m: int = 128
+    block_n: int = 64
+    tile_n: int = 32
+    mask_ratios: Dict[int, Tuple[float, float]] = field(default_factory=lambda: {
+        1: (0.0, 0.1), 2: (0.1, 0.15), 4: (0.15, 0.15), 8: (0.15, 0.35), 0: (0.35, 1.0)})
+    mask_mode: str = 'topk'
+    use_sim_mask: bool = False
+    sim_2x_threshold: float = 0.0
+    sim_4x_threshold: float = 0.0
+    sim_8x_threshold: float = -1.0
+    rearrange_method: str = None
+    attn_impl: str = "new_mask_type"
+
+    def __post_init__(self):
+        if self.attn_impl == "new_mask_type" and self.use_sim_mask:
+            raise ValueError(
+                "Incompatible configuration: 'new_mask_type' does not support 'use_sim_mask=True'.\n"
+                "Please choose one of the following options:\n"
+                "  1. Set 'use_sim_mask=False' to disable similarity mask\n"
+                "  2. Use 'attn_impl=\"old_mask_type\"' with block_size config (m=128, n=128, tile_n=32)")
+        if self.attn_impl == "old_mask_type":
+            if self.block_m != 128 or self.block_n != 128:
+                raise ValueError(
+                    f"attn_impl='old_mask_type' only supports block_m=128 and block_n=128.\n"
+                    f"Got block_m={self.block_m}, block_n={self.block_n}.\n"
+                    f"Use attn_impl='new_mask_type' for flexible block sizes (128/64/32).")
+        if self.attn_impl == "new_mask_type":
+            if self.block_n not in [128, 64, 32]:
+                raise ValueError(
+                    f"attn_impl='new_mask_type' only supports block_n in [128, 64, 32].\n"
+                    f"Got block_n={self.block_n}.")
+
+
+def compute_block_mask(q, k, config, text_length: int = 0, idx_q=None, idx_k=None):
+    """Scores -> level mask (-> similarity cap), the no-grad half of PSAAttention.forward
+    (src/psa_triton/attention.py:178-223, 276-299).  Returns (mask, scores, sim_mask).
+    The sample offsets are drawn from torch's generator of q's device, Q first and K second, exactly as
+    the reference does; tests may pass them in instead."""
+    B, H = q.shape[0], q.shape[1]
+    sim = None
+    if config.use_sim_mask:
+        sim = ops.k_similarity(k, config.block_n, float(config.sim_2x_threshold), float(config.sim_4x_threshold),
+                               float(config.sim_8x_threshold))
+    if idx_q is None:
+        idx_q = ops.draw_sample_indices(B, H, config.block_m, config.block_m // 4, q.device)
+    if idx_k is None:
+        idx_k = ops.draw_sample_indices(B, H, config.block_n, config.block_n // 4, q.device)
+    po = ops.block_scores(q, k, idx_q, idx_k, config.block_m, config.block_n)
+    if config.attn_impl == "old_mask_type":
+        mode = config.mask_mode
+    else:
+        mode = f"{config.mask_mode}_newtype"
+    mask = ops.assign_levels(po, config.mask_ratios, mode, config.block_n, config.tile_n, text_length=text_length)
+    if config.use_sim_mask and sim is not None:
+        mask = torch.min(sim.unsqueeze(-2).to(mask.dtype), mask)
+    return mask, po, sim
+
+
+class PSAAttention(nn.Module):
+    """Drop-in attention: ``out = PSAAttention(config)(q, k, v)`` with q, k, v of shape [B, H, L, D]."""
+
+    def __init__(self, config: PSAConfig = None):
+        super().__init__()
+        self.config = config if config is not None else PSAConfig()
+        if self.config.attn_impl == "old_mask_type":
+            self.sparse_attention_fn = legacy_sparse_attention_factory(self.config.block_m, self.config.tile_n,
+                                                                       self.config.block_n)
+        else:
+            self.sparse_attention_fn = sparse_attention_factory(self.config.block_m, self.config.tile_n,
+                                                                self.config.block_n)
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, idx_q=None, idx_k=None) -> torch.Tensor:
+        config = self.config
+        with torch.no_grad():
+            mask, _, _ = compute_block_mask(q, k, config, text_length=0, idx_q=idx_q, idx_k=idx_k)
+        return self.sparse_attention_fn(q.contiguous(), k.contiguous(), v.contiguous(), mask, None)
+
+
+def psa_attention(q, k, v, *, config: PSAConfig = None, mask_ratios=None, mask_mode: str = None, block_m: int = None,
+                  block_n: int = None) -> torch.Tensor:
+    """Functional form (src/psa_triton/attention.py:314-367); a block_n override also sets tile_n=min(32, block_n)."""
+    if config is None:
+        config = PSAConfig()
+    if mask_ratios is not None:
+        config.mask_ratios = mask_ratios
+    if mask_mode is not None:
+        config.mask_mode = mask_mode
+    if block_m is not None:
+        config.block_m = block_m
+    if block_n is not None:
+        config.block_n = block_n
+        config.tile_n = min(32, block_n)
+    return PSAAttention(config)(q, k, v)

@@ -1,0 +1,267 @@
+"""Tensor-level wrappers around the C-ABI kernels.  torch is used for device memory and streams only."""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+_DT = {torch.float32: _lib.PSA_F32, torch.float16: _lib.PSA_F16, torch.bfloat16: _lib.PSA_BF16}
+
+IMPL_AUTO, IMPL_SCALAR, IMPL_TENSOR = 0, 1, 2
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("psa_b200 kernels need CUDA tensors; there is no CPU path in this package")
+
+
+def _stream(t: torch.Tensor):
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype not in _DT:
+        raise ValueError(f"unsupported dtype {t.dtype}; use float32, float16 or bfloat16")
+    return _DT[t.dtype]
+
+
+def _flat_bh(x: torch.Tensor) -> torch.Tensor:
+    return x if x.is_contiguous() else x.contiguous()
+
+
+# ------------------------------------------------------------------------------------------------
+def pyramid_kv(k: torch.Tensor, v: torch.Tensor, block_n: int):
+    """Levels 2/4/8 of the mean-pooled K and V ([B,H,S,D] -> [B,H,S_pad/l,D]) in one pass.
+    Mirrors pad_to_multiple + pooling, src/psa_triton/kernels/psa_kernel.py:318-349,381-388."""
+    _need_cuda(k, v)
+    assert k.shape == v.shape and k.dtype == v.dtype
+    k, v = _flat_bh(k), _flat_bh(v)
+    B, H, S, D = k.shape
+    s_pad = -(-S // block_n) * block_n
+    with torch.cuda.device(k.device):
+        outs = [torch.empty((B, H, s_pad // l, D), dtype=k.dtype, device=k.device) for l in (2, 4, 8) for _ in (0, 1)]
+        k2, v2, k4, v4, k8, v8 = outs
+        rc = lib.psa_pyramid_kv(_ptr(k), _ptr(v), _ptr(k2), _ptr(k4), _ptr(k8), _ptr(v2), _ptr(v4), _ptr(v8),
+                                B * H, S, D, block_n, _dt(k), _stream(k))
+    check(rc, "psa_pyramid_kv")
+    return (k2, k4, k8), (v2, v4, v8)
+
+
+def draw_sample_indices(B: int, H: int, block: int, keep: int, device) -> torch.Tensor:
+    """topk(rand(B,H,1,block), keep).indices: the same two torch calls, in the same order on the same
+    generator, as _random_sample_tokens (src/psa_triton/attention.py:132-133)."""
+    rand_vals = torch.rand(B, H, 1, block, device=device)
+    _, idx = torch.topk(rand_vals, keep, dim=3)
+    return idx.view(B, H, keep)
+
+
+def block_scores(q, k, idx_q, idx_k, block_m: int, block_n: int, impl: int = IMPL_AUTO) -> torch.Tensor:
+    """Block-importance scores Po [B,H,Mq,Nk] (q.dtype).  idx_q [B,H,block_m/4], idx_k [B,H,block_n/4]."""
+    _need_cuda(q, k, idx_q, idx_k)
+    q, k = _flat_bh(q), _flat_bh(k)
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    assert idx_q.shape == (B, H, block_m // 4) and idx_k.shape == (B, H, block_n // 4)
+    iq = idx_q.to(torch.int32).contiguous()
+    ik = idx_k.to(torch.int32).contiguous()
+    Mq, Nk = -(-Sq // block_m), -(-Sk // block_n)
+    with torch.cuda.device(q.device):
+        po = torch.empty((B, H, Mq, Nk), dtype=q.dtype, device=q.device)
+        nbytes = lib.psa_block_scores_scratch_bytes(B * H, Sq, Sk, block_m, block_n, _dt(q))
+        if nbytes == 0:
+            raise ValueError(f"psa_block_scores: unsupported block sizes m={block_m} n={block_n}")
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        rc = lib.psa_block_scores(_ptr(q), _ptr(k), _ptr(iq), _ptr(ik), _ptr(po), _ptr(scratch), nbytes, B * H, Sq, Sk,
+                                  D, block_m, block_n, _dt(q), impl, _stream(q))
+    check(rc, "psa_block_scores")
+    return po
+
+
+# ------------------------------------------------------------------------------------------------
+def _align_multiple(level: int, block_n: int, tile_n: int, topk: bool) -> int:
+    if level == 0 and topk:
+        return 1
+    return math.ceil(level / (block_n // tile_n))
+
+
+def topk_intervals(nk: int, ratios: Dict[int, Tuple[float, float]], block_n: int, tile_n: int, newtype: bool):
+    """Rank interval of every level in dict order, with the reference's Python arithmetic
+    (src/psa_triton/utils/transfer_attn_to_mask.py:63-120 old format, :282-351 new format)."""
+    out = []
+    last_end = 0
+    for level, (_, end_ratio) in ratios.items():
+        a = _align_multiple(level, block_n, tile_n, True)
+        start = last_end
+        init_end = min(nk, int(nk * end_ratio))
+        length = init_end - start
+        if a > 1 and length > 0:
+            rem = length % a
+            aligned = length + (a - rem) if rem else length
+            end = min(start + aligned, nk)
+            if end == nk:
+                end = start + ((end - start) // a) * a
+        else:
+            end = init_end
+        if start < end:
+            out.append((level, start, end))
+            last_end = end
+        else:
+            out.append((level, start, start))   # empty: new format still gets its separator
+            if newtype:
+                last_end = start
+    return out
+
+
+def _round_to_dtype(x: float, dtype: torch.dtype) -> float:
+    return float(torch.tensor(x, dtype=torch.float64).to(dtype).to(torch.float64))
+
+
+def assign_levels(po: torch.Tensor, mask_ratios: Dict[int, Tuple[float, float]], mode: str, block_n: int,
+                  tile_n: int, text_length: int = 0, min_full_attn_ratio: float = 0.06) -> torch.Tensor:
+    """Score rows -> level mask.  Same modes, argument meaning and errors as transfer_attn_to_mask
+    (src/psa_triton/utils/transfer_attn_to_mask.py:6-507)."""
+    if mask_ratios is None:
+        raise ValueError("mask_ratios must be provided")
+    if mode not in ("topk", "thresholdbound", "topk_newtype", "thresholdbound_newtype"):
+        raise ValueError(f"Unknown mode: {mode}. Must be 'topk' or 'thresholdbound'")
+    _need_cuda(po)
+    po = _flat_bh(po)
+    B, H, Mq, Nk = po.shape
+    newtype = mode.endswith("_newtype")
+    threshold = mode.startswith("thresholdbound")
+    n = len(mask_ratios)
+    if n > 8:
+        raise ValueError("at most 8 levels")
+    I32 = C.c_int32 * n
+    F32 = C.c_float * n
+    if threshold:
+        items = sorted(mask_ratios.items(), key=lambda x: x[1][1])
+        levels = I32(*[int(l) for l, _ in items])
+        thr = F32(*[_round_to_dtype(r[1] + 1e-6, po.dtype) for _, r in items])
+        aligns = I32(*[_align_multiple(int(l), block_n, tile_n, False) for l, _ in items])
+        starts = ends = None
+        min_index = min(Nk, int(Nk * min_full_attn_ratio) + 1)
+    else:
+        iv = topk_intervals(Nk, mask_ratios, block_n, tile_n, newtype)
+        levels = I32(*[int(l) for l, _, _ in iv])
+        starts = I32(*[s for _, s, _ in iv])
+        ends = I32(*[e for _, _, e in iv])
+        thr = aligns = None
+        min_index = 0
+    text_blocks = 0 if (newtype or text_length == 0) else (text_length + block_n - 1) // block_n
+    width = Nk + n if newtype else Nk
+    with torch.cuda.device(po.device):
+        mask = torch.empty((B, H, Mq, width), dtype=torch.int32, device=po.device)
+        rc = lib.psa_assign_levels(_ptr(po), _ptr(mask), B * H * Mq, Nk, _dt(po), int(threshold), int(newtype), n,
+                                   levels, starts, ends, thr, aligns, min_index, text_blocks, _stream(po))
+    check(rc, "psa_assign_levels")
+    return mask
+
+
+def density(mask: torch.Tensor, newtype: bool) -> torch.Tensor:
+    """Per-(batch, head) mean density [B,H] float32 on the device (no host sync).
+    calc_density_newtype / calc_density, src/psa_triton/utils/transfer_attn_to_mask.py:510-622."""
+    _need_cuda(mask)
+    mask = _flat_bh(mask)
+    B, H, Mq, W = mask.shape
+    with torch.cuda.device(mask.device):
+        out = torch.empty((B, H), dtype=torch.float32, device=mask.device)
+        rc = lib.psa_density(_ptr(mask), _ptr(out), B * H, Mq, W, int(newtype), _stream(mask))
+    check(rc, "psa_density")
+    return out
+
+
+def k_similarity(k: torch.Tensor, block_n: int, t2: float, t4: float, t8: float) -> torch.Tensor:
+    """[B,H,ceil(S/block_n)] int32 in {1,2,4,8}; calc_k_similarity_triton on the replicate-padded K
+    (src/psa_triton/kernels/calc_ksim_kernel.py:160-225, src/psa_triton/attention.py:196-204)."""
+    _need_cuda(k)
+    k = _flat_bh(k)
+    B, H, S, D = k.shape
+    assert block_n % 8 == 0, "blocksize must be divisible by 8"
+    with torch.cuda.device(k.device):
+        out = torch.empty((B, H, -(-S // block_n)), dtype=torch.int32, device=k.device)
+        rc = lib.psa_ksim(_ptr(k), _ptr(out), B * H, S, D, block_n, t2, t4, t8, _dt(k), _stream(k))
+    check(rc, "psa_ksim")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+def psa_forward(q, k, v, mask, block_m: int, block_n: int, tile_n: int, sm_scale: Optional[float] = None,
+                compat_quirk: bool = True, impl: int = IMPL_AUTO, pyramid=None, out=None) -> torch.Tensor:
+    """Multi-level block-sparse forward on the separator-format mask
+    (_forward, src/psa_triton/kernels/psa_kernel.py:351-432)."""
+    _need_cuda(q, k, v, mask)
+    assert q.shape[-1] == k.shape[-1] == v.shape[-1]
+    assert k.shape[2] == v.shape[2]
+    assert q.shape[-1] in [64, 128]
+    q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _flat_bh(mask)
+    if mask.dtype != torch.int32:
+        mask = mask.to(torch.int32)
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    if pyramid is None:
+        pyramid = pyramid_kv(k, v, block_n)
+    (k2, k4, k8), (v2, v4, v8) = pyramid
+    with torch.cuda.device(q.device):
+        o = out if out is not None else torch.empty_like(q)
+        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        rc = lib.psa_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(k2), _ptr(k4), _ptr(k8), _ptr(v2), _ptr(v4), _ptr(v8),
+                         _ptr(mask), _ptr(o), B * H, Sq, Sk, D, block_m, block_n, tile_n, mask.shape[-1],
+                         float(sm_scale), int(compat_quirk), impl, _dt(q), _ptr(status), _stream(q))
+    check(rc, "psa_fwd")
+    o._psa_status = status     # read lazily by callers that want to check for an expired device wait
+    return o
+
+
+def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float] = None, need_lse: bool = False,
+                   pyramid=None):
+    """Legacy forward on the dense old-format mask (_forward, src/psa_triton/kernels/psa_kernel_legacy.py:837-938)."""
+    _need_cuda(q, k, v, mask)
+    assert q.shape[-1] == k.shape[-1] == v.shape[-1]
+    assert k.shape[2] == v.shape[2]
+    assert q.shape[-1] in [64, 128]
+    q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _flat_bh(mask)
+    if mask.dtype != torch.int32:
+        mask = mask.to(torch.int32)
+    B, H, S, D = q.shape
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    if pyramid is None:
+        pyramid = pyramid_kv(k, v, 128)
+    (k2, k4, k8), (v2, v4, v8) = pyramid
+    with torch.cuda.device(q.device):
+        o = torch.empty_like(q)
+        lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if need_lse else None
+        rc = lib.psa_legacy_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(k2), _ptr(k4), _ptr(k8), _ptr(v2), _ptr(v4), _ptr(v8),
+                                _ptr(mask), _ptr(o), _ptr(lse), B * H, S, D, mask.shape[-1], float(sm_scale), int(causal),
+                                _dt(q), _stream(q))
+    check(rc, "psa_legacy_fwd")
+    return o, lse, pyramid
+
+
+def legacy_backward(q, k, v, mask, o, lse, do, causal: bool, sm_scale: float, pyramid):
+    """dQ, dK, dV of the legacy kernel (_sparse_attention.backward, psa_kernel_legacy.py:947-1069)."""
+    _need_cuda(q, k, v, mask, o, lse, do)
+    do = _flat_bh(do)
+    B, H, S, D = q.shape
+    (k2, k4, k8), (v2, v4, v8) = pyramid
+    with torch.cuda.device(q.device):
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        delta = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
+        rc = lib.psa_legacy_bwd(_ptr(q), _ptr(k), _ptr(v), _ptr(k2), _ptr(k4), _ptr(k8), _ptr(v2), _ptr(v4), _ptr(v8),
+                                _ptr(mask), _ptr(o), _ptr(lse), _ptr(do), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(delta),
+                                B * H, S, D, mask.shape[-1], float(sm_scale), int(causal), _dt(q), _stream(q))
+    check(rc, "psa_legacy_bwd")
+    return dq, dk, dv

@@ -1,0 +1,196 @@
+"""GPU: every CUDA entry point (through the C ABI) against the CPU oracle and the reference's fixtures."""
+import numpy as np
+import pytest
+import torch
+
+import cases as C
+from oracle import psa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+# tolerance of the attention outputs (north-star bar): max-abs <= 2e-2, cosine >= 0.999
+ATOL_OUT, COS_OUT = 2e-2, 0.999
+
+
+def t(a):
+    return torch.from_numpy(np.asarray(a))
+
+
+def cosine(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float((a @ b) / (a.norm() * b.norm() + 1e-30))
+
+
+@pytest.fixture(scope="module")
+def P():
+    import psa_b200
+    assert torch.cuda.is_available()
+    return psa_b200
+
+
+# ------------------------------------------------------------------ pyramid: bit exact ------------
+@pytest.mark.parametrize("dt", ["fp32", "bf16", "fp16"])
+@pytest.mark.parametrize("S,D,bn", [(333, 64, 64), (1000, 128, 32), (257, 64, 128), (64, 128, 64), (1, 64, 32)])
+def test_pyramid(P, dt, S, D, bn):
+    k = C.randn(11, (2, 3, S, D), C.DT[dt])
+    v = C.randn(12, (2, 3, S, D), C.DT[dt])
+    (k2, k4, k8), (v2, v4, v8) = P.ops.pyramid_kv(k.to(DEV), v.to(DEV), bn)
+    ok, ov = O.pyramid_kv(k, bn), O.pyramid_kv(v, bn)
+    for l, a, b in ((2, k2, v2), (4, k4, v4), (8, k8, v8)):
+        assert torch.equal(a.cpu(), ok[l]) and torch.equal(b.cpu(), ov[l])
+
+
+def test_pyramid_golden(P, golden):
+    for dt in ("fp32", "bf16", "fp16"):
+        x = C.randn(11, (1, 2, 333, 64), C.DT[dt]).to(DEV)
+        (k2, k4, k8), _ = P.ops.pyramid_kv(x, x, 64)
+        for l, a in ((2, k2), (4, k4), (8, k8)):
+            assert torch.equal(a.float().cpu(), t(golden[f"pyramid_{dt}_l{l}"]))
+
+
+# ------------------------------------------------------------------ block scores ---------------------
+@pytest.mark.parametrize("case", C.SCORE_CASES, ids=lambda c: c[0])
+def test_block_scores_golden(P, golden, case):
+    name, S, D, H, bm, bn, dt = case
+    q, k, _ = C.qkv(100, 1, H, S, D, C.DT[dt])
+    iq, ik = C.sample_idx(7, 1, H, bm, bm // 4), C.sample_idx(8, 1, H, bn, bn // 4)
+    po = P.ops.block_scores(q.to(DEV), k.to(DEV), iq.to(DEV), ik.to(DEV), bm, bn, impl=P.ops.IMPL_SCALAR).float().cpu()
+    ref = t(golden[f"scores_{name}"])
+    tol = 1e-6 if dt == "fp32" else 2e-3      # fp16: one rounding step of R can move a cell by 2^-11 relative
+    assert float((po - ref).abs().max()) <= tol * float(ref.max()) * 10
+
+
+@pytest.mark.parametrize("dt,S,D,bm,bn", [("bf16", 1500, 128, 128, 64), ("fp16", 900, 64, 128, 32), ("bf16", 2048, 64, 128, 128),
+                                           ("fp32", 777, 64, 64, 64)])
+def test_block_scores_oracle(P, dt, S, D, bm, bn):
+    q, k, _ = C.qkv(150, 1, 2, S, D, C.DT[dt])
+    iq, ik = C.sample_idx(9, 1, 2, bm, bm // 4), C.sample_idx(10, 1, 2, bn, bn // 4)
+    po = P.ops.block_scores(q.to(DEV), k.to(DEV), iq.to(DEV), ik.to(DEV), bm, bn, impl=P.ops.IMPL_SCALAR).float().cpu()
+    ref = O.block_scores(q, k, iq, ik, bm, bn).float()
+    assert po.shape == ref.shape
+    # the scores feed a sort: compare within a few ulps of the element type, relative to the row scale
+    eps = {"fp32": 1e-6, "fp16": 2e-3, "bf16": 1.6e-2}[dt]
+    assert float(((po - ref).abs() / ref.amax(-1, keepdim=True)).max()) <= eps
+    assert float((po != ref).float().mean()) < (0.02 if dt != "fp32" else 1.0)
+
+
+# ------------------------------------------------------------------ level assignment: bit exact --------
+@pytest.mark.parametrize("case", C.ASSIGN_CASES, ids=lambda c: c[0])
+def test_assign_levels_golden(P, golden, case):
+    name, Mq, Nk, bn, tn, mode, rn, dt, text, ties = case
+    po = C.scores_like(sum(map(ord, name)), 1, 2, Mq, Nk, C.DT[dt], ties=ties)
+    mask = P.ops.assign_levels(po.to(DEV), getattr(C, rn), mode, bn, tn, text_length=text)
+    ref = t(golden[f"assign_{name}"])
+    assert torch.equal(mask.cpu(), ref)
+    key = f"density_{name}"
+    if key in golden.files:
+        d = P.ops.density(mask, mode.endswith("newtype")).cpu()
+        assert np.allclose(d[0].numpy(), golden[key][1:], atol=1e-6)
+
+
+@pytest.mark.parametrize("dt", ["fp32", "bf16"])
+@pytest.mark.parametrize("mode", ["topk_newtype", "thresholdbound_newtype", "topk", "thresholdbound"])
+@pytest.mark.parametrize("Nk,bn", [(512, 64), (1182, 64), (2363, 32), (1, 64), (5, 128)])
+def test_assign_levels_oracle_large(P, dt, mode, Nk, bn):
+    po = C.scores_like(Nk + len(mode), 1, 2, 4, Nk, C.DT[dt], ties=True)
+    ratios = C.RATIOS_THR2 if mode.startswith("threshold") else C.RATIOS_90
+    mask = P.ops.assign_levels(po.to(DEV), ratios, mode, bn, 32)
+    assert torch.equal(mask.cpu(), O.assign_levels(po, ratios, mode, bn, 32))
+
+
+def test_device_sort_of_the_host_library_is_index_stable():
+    """torch.sort on CUDA (the call the reference makes on a GPU) orders equal scores by ascending index,
+    i.e. the rule the assignment kernel and the oracle implement."""
+    x = torch.randint(0, 5, (7, 600), device=DEV).float()
+    _, o = torch.sort(x, dim=-1, descending=True)
+    _, o2 = torch.sort(x.cpu(), dim=-1, descending=True, stable=True)
+    assert torch.equal(o.cpu(), o2)
+
+
+# ------------------------------------------------------------------ new-mask forward -------------------
+def run_fwd(P, q, k, v, mask, bm, bn, tn, impl, quirk=True):
+    fn = P.sparse_attention_factory(bm, tn, bn, compat_quirk=quirk, impl=impl)
+    return fn(q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), None)
+
+
+@pytest.mark.parametrize("case", C.FWD_CASES, ids=lambda c: c[0])
+def test_forward_scalar_golden_fp32(P, golden, case):
+    name, S, D, H, bm, bn, tn, mode, rn = case
+    q, k, v = C.qkv(200, 1, H, S, D)
+    mask = t(golden[f"{name}_mask"])
+    out = run_fwd(P, q, k, v, mask, bm, bn, tn, P.ops.IMPL_SCALAR).cpu()
+    ref = t(golden[f"{name}_out"])
+    assert float((C.sub(out) - ref).abs().max()) < 2e-5
+    clean = run_fwd(P, q, k, v, mask, bm, bn, tn, P.ops.IMPL_SCALAR, quirk=False).cpu()
+    assert float((clean - O.psa_forward_newmask(q, k, v, mask, bm, bn, tn, quirk=False)).abs().max()) < 2e-5
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+@pytest.mark.parametrize("case", C.FWD_CASES, ids=lambda c: c[0])
+def test_forward_scalar_half(P, golden, case, dt):
+    name, S, D, H, bm, bn, tn, mode, rn = case
+    q, k, v = C.qkv(200, 1, H, S, D, C.DT[dt])
+    mask = t(golden[f"{name}_mask"])
+    out = run_fwd(P, q, k, v, mask, bm, bn, tn, P.ops.IMPL_SCALAR).float().cpu()
+    ref = O.psa_forward_newmask(q, k, v, mask, bm, bn, tn).float()
+    assert float((out - ref).abs().max()) <= ATOL_OUT and cosine(out, ref) >= COS_OUT
+
+
+# ------------------------------------------------------------------ legacy forward -------------------
+@pytest.mark.parametrize("case", C.LEGACY_CASES, ids=lambda c: c[0])
+def test_legacy_forward_golden(P, golden, case):
+    name, S, D, H, B, causal, diag1 = case
+    q, k, v = C.qkv(400, B, H, S, D)
+    mask = C.legacy_mask(405, B, H, S, causal, diag1)
+    o, lse, _ = P.ops.legacy_forward(q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), causal, need_lse=True)
+    assert float((C.sub(o.cpu()) - t(golden[f"{name}_out"])).abs().max()) < 2e-5
+    _, lse_ref = O.legacy_forward(q, k, v, mask, causal)
+    assert float((lse.cpu() - lse_ref).abs().max()) < 1e-4
+
+
+# ------------------------------------------------------------------ K similarity ---------------------
+@pytest.mark.parametrize("case", C.KSIM_CASES, ids=lambda c: c[0])
+def test_ksim_golden(P, golden, case):
+    from test_oracle_golden import ksim_input
+    name, S, D, H, bn = case
+    k = ksim_input(S, D, H)
+    out = P.ops.k_similarity(k.to(DEV), bn, 0.7, 0.65, 0.6).cpu()
+    assert torch.equal(out, t(golden[name]))
+
+
+# ------------------------------------------------------------------ plug-and-play call -----------------
+@pytest.mark.parametrize("case", C.E2E_CASES, ids=lambda c: c[0])
+def test_end_to_end_golden(P, golden, case):
+    """PSAAttention with the oracle's sample offsets: mask vs the reference's mask, output vs its output."""
+    name, S, D, H, kw, seed = case
+    kw = dict(kw)
+    if "mask_ratios" in kw:
+        kw["mask_ratios"] = getattr(C, kw["mask_ratios"])
+    cfg = P.PSAConfig(**kw)
+    q, k, v = C.qkv(600, 1, H, S, D)
+    torch.manual_seed(seed)
+    iq = O.draw_sample_indices(1, H, cfg.block_m, cfg.block_m // 4)
+    ik = O.draw_sample_indices(1, H, cfg.block_n, cfg.block_n // 4)
+    mask, po, _ = P.compute_block_mask(q.to(DEV), k.to(DEV), cfg, idx_q=iq.to(DEV), idx_k=ik.to(DEV))
+    ref_mask = t(golden[f"{name}_mask"])
+    agree = float((mask.cpu() == ref_mask).float().mean())
+    assert agree > 0.98, f"mask agreement {agree}"     # fp32 scores differ in the last bits (summation order)
+    out = P.PSAAttention(cfg)(q.to(DEV), k.to(DEV), v.to(DEV), idx_q=iq.to(DEV), idx_k=ik.to(DEV)).cpu()
+    if agree == 1.0:
+        assert float((C.sub(out) - t(golden[f"{name}_out"])).abs().max()) < 2e-5
+    else:
+        ref = t(golden[f"{name}_out"])
+        assert cosine(C.sub(out), ref) > 0.999
+
+
+def test_psa_attention_draws_indices_like_the_reference(P):
+    """Without explicit offsets the module consumes torch's device generator: Q draw first, K second."""
+    q, k, v = (x.to(DEV) for x in C.qkv(700, 1, 2, 640, 64, torch.bfloat16))
+    torch.manual_seed(77)
+    a = P.PSAAttention()(q, k, v)
+    torch.manual_seed(77)
+    iq = P.ops.draw_sample_indices(1, 2, 128, 32, q.device)
+    ik = P.ops.draw_sample_indices(1, 2, 64, 16, q.device)
+    b = P.PSAAttention()(q, k, v, idx_q=iq, idx_k=ik)
+    assert torch.equal(a, b)
