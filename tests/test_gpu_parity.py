@@ -194,3 +194,59 @@ def test_psa_attention_draws_indices_like_the_reference(P):
     ik = P.ops.draw_sample_indices(1, 2, 64, 16, q.device)
     b = P.PSAAttention()(q, k, v, idx_q=iq, idx_k=ik)
     assert torch.equal(a, b)
+
+
+# ------------------------------------------------------------------ tcgen05 forward -------------------
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+@pytest.mark.parametrize("case", C.FWD_CASES, ids=lambda c: c[0])
+def test_forward_tensor_core_vs_oracle(P, golden, case, dt):
+    name, S, D, H, bm, bn, tn, mode, rn = case
+    q, k, v = C.qkv(200, 1, H, S, D, C.DT[dt])
+    mask = t(golden[f"{name}_mask"])
+    out = run_fwd(P, q, k, v, mask, bm, bn, tn, P.ops.IMPL_TENSOR)
+    assert int(out._psa_status.item()) == 0
+    out = out.float().cpu()
+    ref = O.psa_forward_newmask(q, k, v, mask, bm, bn, tn).float()
+    assert float((out - ref).abs().max()) <= ATOL_OUT and cosine(out, ref) >= COS_OUT
+    # "clean" mode (without the reference's extra columns) must differ from the reference where the quirk bites
+    clean = run_fwd(P, q, k, v, mask, bm, bn, tn, P.ops.IMPL_TENSOR, quirk=False).float().cpu()
+    ref_clean = O.psa_forward_newmask(q, k, v, mask, bm, bn, tn, quirk=False).float()
+    assert float((clean - ref_clean).abs().max()) <= ATOL_OUT
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+@pytest.mark.parametrize("S,D,bn,mode,rn", [(4096, 128, 64, "topk", "RATIOS_90"), (3000, 64, 32, "thresholdbound", "RATIOS_THR"),
+                                            (2500, 128, 128, "topk", "DEFAULT_RATIOS"), (130, 64, 64, "topk", "RATIOS_DENSE"),
+                                            (5000, 128, 32, "topk", "DEFAULT_RATIOS")])
+def test_forward_tensor_core_vs_scalar_kernel(P, dt, S, D, bn, mode, rn):
+    """Larger ragged shapes: the tcgen05 kernel against the scalar fp32 kernel on the same mask, twice (bitwise
+    repeatable), through the whole module path."""
+    H = 3
+    q, k, v = (x.to(DEV) for x in C.qkv(900, 1, H, S, D, C.DT[dt]))
+    cfg = P.PSAConfig(block_n=bn, mask_mode=mode, mask_ratios=getattr(C, rn))
+    iq, ik = C.sample_idx(1, 1, H, 128, 32).to(DEV), C.sample_idx(2, 1, H, bn, bn // 4).to(DEV)
+    mask, _, _ = P.compute_block_mask(q, k, cfg, idx_q=iq, idx_k=ik)
+    a = P.ops.psa_forward(q, k, v, mask, 128, bn, 32, impl=P.ops.IMPL_TENSOR)
+    b = P.ops.psa_forward(q, k, v, mask, 128, bn, 32, impl=P.ops.IMPL_TENSOR)
+    ref = P.ops.psa_forward(q, k, v, mask, 128, bn, 32, impl=P.ops.IMPL_SCALAR)
+    assert int(a._psa_status.item()) == 0
+    assert torch.equal(a, b)
+    assert float((a.float() - ref.float()).abs().max()) <= ATOL_OUT and cosine(a.float(), ref.float()) >= COS_OUT
+
+
+def test_forward_empty_and_dense_rows(P):
+    """A row that selects nothing gives NaN like the reference (0/0); a row that selects every block at level 1
+    equals dense attention."""
+    S, D, bn = 512, 64, 64
+    q, k, v = (x.to(DEV) for x in C.qkv(950, 1, 1, S, D, torch.bfloat16))
+    Nk = S // bn
+    mask = torch.zeros(1, 1, S // 128, Nk + 5, dtype=torch.int32)
+    mask[0, 0, 0, :5] = -1                                     # empty
+    for m in range(1, S // 128):
+        mask[0, 0, m, :Nk] = torch.arange(Nk, dtype=torch.int32)
+        mask[0, 0, m, Nk:] = -1
+    for impl in (P.ops.IMPL_SCALAR, P.ops.IMPL_TENSOR):
+        o = P.ops.psa_forward(q, k, v, mask.to(DEV), 128, bn, 32, impl=impl).float().cpu()
+        assert torch.isnan(o[0, 0, :128]).all()
+        dense = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float()).cpu()
+        assert float((o[0, 0, 128:] - dense[0, 0, 128:]).abs().max()) < 1e-2
