@@ -1,0 +1,343 @@
+#!/usr/bin/env python
+"""PSA attention-layer benchmark on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+A "step" is one Pyramid-Sparse-Attention layer call (pyramid K/V builder -> block scores -> level assignment ->
+multi-level sparse forward) on a Wan2.1-14B-shaped attention layer (B=1, 40 heads x 128, S=75600 video tokens on a
+21x45x80 latent grid, bf16, ~90% block sparsity; other shapes via --workload).  Inputs are seeded synthetic
+structured fields (psa_b200/synthetic.py).
+
+N GPUs: heads are sharded across ranks (strong scaling, total work fixed).  Activations start sequence-sharded
+([S/N, H, D] per rank, as a sequence-parallel DiT holds them) and are reshuffled to head-sharded with one NCCL
+all-to-all before the layer and one after it; both are inside the timed region.
+
+Prints ONE JSON line (rank 0).  `value` = dense-equivalent TFLOP/s of the whole job (4*B*H*S^2*D / step time) with
+inputs resident in HBM; `e2e` = the same through the public module call with pinned HOST q/k/v in and O back out.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "pyramid-sparse-attention_b200"))
+sys.path.insert(0, ROOT)
+
+import torch
+
+RATIOS_90 = {1: (0.0, 0.05), 2: (0.05, 0.1), 4: (0.1, 0.15), 8: (0.15, 0.25), 0: (0.25, 1.0)}
+DEFAULT_RATIOS = {1: (0.0, 0.1), 2: (0.1, 0.15), 4: (0.15, 0.15), 8: (0.15, 0.35), 0: (0.35, 1.0)}
+BLOCK_M, BLOCK_N, TILE_N = 128, 64, 32
+CPU_SAMPLE_TOKENS = 32768
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], bf16_tflops_sustained=d.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def oracle_sample_time(workload, ratios, steps, warmup):
+    """Time the CPU restatement of the same layer on a bounded sample (head 0, first CPU_SAMPLE_TOKENS tokens).
+    Returns (dense-equivalent TFLOP/s, seconds per call, description)."""
+    from oracle import psa_oracle as O
+    from psa_b200 import synthetic
+    S = min(synthetic.seq_len(workload), CPU_SAMPLE_TOKENS)
+    D = workload["head_dim"]
+    q, k, v = synthetic.make_qkv(workload, 1000, torch.float32, "cpu", head_range=(0, 1), token_range=(0, S))
+    times = []
+    for i in range(warmup + steps):
+        torch.manual_seed(2000)
+        t0 = time.perf_counter()
+        O.psa_attention(q, k, v, block_m=BLOCK_M, block_n=BLOCK_N, tile_n=TILE_N, mask_ratios=ratios, mask_mode="topk")
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    f_dense = 4.0 * S * S * D
+    return f_dense / sec / 1e12, sec, f"head 0 of {workload['heads']}, first {S} tokens, fp32 inputs, fp64 softmax"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="wan2.1-14b-attn-layer")
+    ap.add_argument("--sparsity", default="90", choices=["90", "85"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    from psa_b200 import synthetic
+    workload = synthetic.WORKLOADS[args.workload]
+    ratios = RATIOS_90 if args.sparsity == "90" else DEFAULT_RATIOS
+    H, D, S = workload["heads"], workload["head_dim"], synthetic.seq_len(workload)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    f_dense = 4.0 * H * float(S) * S * D
+    cfg_json = {"workload": workload["name"], "B": 1, "heads": H, "head_dim": D, "seq_len": S, "grid": list(workload["grid"]),
+                "text_tokens": workload["text"], "block_m": BLOCK_M, "block_n": BLOCK_N, "tile_n": TILE_N,
+                "mask_mode": "topk", "mask_ratios": {str(k): list(v) for k, v in ratios.items()},
+                "parallelism": f"heads/{max(world, 1)}" + ("+all_to_all" if world > 1 else ""),
+                "l2": "inputs (q,k,v) larger than L2"}
+
+    # ------------------------------------------------------------------ reference arm: the CPU restatement
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        tf, sec, sample = oracle_sample_time(workload, ratios, args.steps, args.warmup)
+        print(json.dumps({
+            "impl": "reference", "metric": "psa_attn_dense_equiv_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg_json,
+            "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    # ------------------------------------------------------------------ our arm
+    import torch.distributed as dist
+    import psa_b200
+    from psa_b200 import ops
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        assert H % world == 0 and S % world == 0, "heads and tokens must divide by the number of GPUs"
+    hp = H // world
+    h0 = rank * hp
+    dtype = torch.bfloat16
+    cfg = psa_b200.PSAConfig(block_m=BLOCK_M, block_n=BLOCK_N, tile_n=TILE_N, mask_ratios=ratios, mask_mode="topk")
+
+    if world == 1:
+        q, k, v = synthetic.make_qkv(workload, 1000, dtype, dev)
+        seq_shard = None
+    else:
+        # what a sequence-parallel DiT holds: this rank's tokens, all heads -> [3, S/N, H, D]
+        sl = S // world
+        qs, ks, vs = synthetic.make_qkv(workload, 1000, dtype, dev, token_range=(rank * sl, (rank + 1) * sl))
+        seq_shard = torch.stack([qs[0], ks[0], vs[0]]).permute(0, 2, 1, 3).contiguous()       # [3, S/N, H, D]
+        del qs, ks, vs
+        q = k = v = None
+
+    def draw_indices():
+        torch.manual_seed(2000)                      # same draw on every rank, sliced by head
+        iq = ops.draw_sample_indices(1, H, BLOCK_M, BLOCK_M // 4, dev)[:, h0:h0 + hp]
+        ik = ops.draw_sample_indices(1, H, BLOCK_N, BLOCK_N // 4, dev)[:, h0:h0 + hp]
+        return iq.contiguous(), ik.contiguous()
+
+    def to_head_sharded(x):
+        """[3, S/N, H, D] on every rank -> [3, H/N, S, D] (NCCL all-to-all + local reorder)."""
+        sl = x.shape[1]
+        send = x.view(3, sl, world, hp, D).permute(2, 0, 3, 1, 4).contiguous()                 # [N_dst, 3, hp, S/N, D]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send)
+        return recv.permute(1, 2, 0, 3, 4).reshape(3, hp, world * sl, D)                          # [3, hp, S, D]
+
+    def to_seq_sharded(o):
+        """[H/N, S, D] -> [H, S/N, D] on every rank."""
+        sl = S // world
+        send = o.view(hp, world, sl, D).permute(1, 0, 2, 3).contiguous()                         # [N_dst, hp, S/N, D]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send)
+        return recv.view(world * hp, sl, D)
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    stage_names = ["a2a_in", "sample", "pyramid", "scores", "assign", "forward", "a2a_out"]
+
+    def layer_step(record=None):
+        marks = []
+        mark = (lambda: marks.append(ev()) or marks[-1].record()) if record is not None else (lambda: None)
+        mark()
+        if world > 1:
+            x = to_head_sharded(seq_shard)
+            qq, kk, vv = x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0)
+        else:
+            qq, kk, vv = q, k, v
+        mark()
+        iq, ik = draw_indices()
+        mark()
+        pyr = ops.pyramid_kv(kk, vv, BLOCK_N)
+        mark()
+        po = ops.block_scores(qq, kk, iq, ik, BLOCK_M, BLOCK_N)
+        mark()
+        mask = ops.assign_levels(po, ratios, "topk_newtype", BLOCK_N, TILE_N)
+        mark()
+        out = ops.psa_forward(qq, kk, vv, mask, BLOCK_M, BLOCK_N, TILE_N, pyramid=pyr)
+        mark()
+        if world > 1:
+            out_final = to_seq_sharded(out[0])
+        else:
+            out_final = out
+        mark()
+        if record is not None:
+            record.append(marks)
+        return out_final, mask, out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        out_final, mask, out = layer_step()
+    barrier()
+    status = int(out._psa_status.item())
+    dens = float(ops.density(mask, True).mean().item())
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    records = []
+    barrier()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(args.steps):
+        layer_step(records)
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = e0.elapsed_time(e1)
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    stage_ms = {n: sum(r[i].elapsed_time(r[i + 1]) for r in records) / len(records) for i, n in enumerate(stage_names)}
+
+    # ------------------------------------------------------------------ end to end: host buffers in, O back out
+    e2e = None
+    if not args.no_e2e:
+        if world == 1:
+            hq, hk, hv = (x.cpu().pin_memory() for x in (q, k, v))
+        else:
+            hx = seq_shard.cpu().pin_memory()
+        module = psa_b200.PSAAttention(cfg)
+        h_out = None
+
+        def e2e_step():
+            nonlocal h_out
+            if world == 1:
+                dq, dk, dv = (x.to(dev, non_blocking=True) for x in (hq, hk, hv))
+            else:
+                x = to_head_sharded(hx.to(dev, non_blocking=True))
+                dq, dk, dv = x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0)
+            iq, ik = draw_indices()
+            o = module(dq, dk, dv, idx_q=iq, idx_k=ik)
+            if world > 1:
+                o = to_seq_sharded(o[0])
+            if h_out is None:
+                h_out = torch.empty(o.shape, dtype=o.dtype).pin_memory()
+            h_out.copy_(o, non_blocking=True)
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        a0, a1 = ev(), ev()
+        a0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        a1.record()
+        barrier()
+        te = torch.tensor([a0.elapsed_time(a1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        ms_e2e = float(te.item()) / args.steps
+        esz = 2
+        per_rank_in = 3 * (S // world) * H * D * esz
+        per_rank_out = (S // world) * H * D * esz
+        e2e = {"value": f_dense / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": per_rank_in * world, "d2h_bytes_per_step": per_rank_out * world}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    # dominant kernel: the tcgen05 forward.  Algorithmic FLOPs per launch = 4*hp*S^2*D*density (surviving blocks).
+    f_surv_launch = 4.0 * hp * float(S) * S * D * dens
+    fwd_tflops = f_surv_launch / (stage_ms["forward"] * 1e-3) / 1e12
+    peak_tf = peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]
+    n_elem = hp * S * D
+    line = {
+        "metric": "psa_attn_dense_equiv_tflops", "value": f_dense / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg_json,
+        "ms_per_layer": ms_step, "stage_ms": stage_ms, "density": dens, "sparsity": 1.0 - dens,
+        "surviving_tflops_forward": fwd_tflops, "kernel_status": status,
+        "gpu_launches": 5 * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "psa_fwd_tc_kernel", "achieved": fwd_tflops, "peak": peak_tf,
+                     "unit": "TFLOP/s", "frac": fwd_tflops / peak_tf, "traffic": None,
+                     "peak_source": f"{peaks['source']} (sustained bf16: kernel timed inside a long step)",
+                     "pyramid_gbs": 3.75 * n_elem * 2 / (stage_ms["pyramid"] * 1e-3) / 1e9,
+                     "pyramid_frac_of_hbm": 3.75 * n_elem * 2 / (stage_ms["pyramid"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+        "clocks": clocks, "e2e": e2e,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        tf, sec, sample = oracle_sample_time(workload, ratios, 1, 1)
+        line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": sample, "seconds": sec}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
