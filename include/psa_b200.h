@@ -58,6 +58,23 @@ int psa_block_scores(const void* q, const void* k, const int32_t* idx_q, const i
                      void* scratch, size_t scratch_bytes, int64_t bh, int64_t seq_q, int64_t seq_k, int head_dim,
                      int block_m, int block_n, int dtype, int impl, void* stream);
 
+/* Block-importance scores for callers that cannot allocate device memory.  (No counterpart in the reference, which
+ * allocates its R / Po buffers with torch on every call.)
+ * Same arguments, result and kernels as psa_block_scores, minus the scratch pointer: the scratch is a built-in
+ * device array of PSA_STATIC_SCRATCH_BYTES (64 MiB) that every GPU loading this library holds until the process
+ * exits.  The entry point calls no cudaMalloc/cudaFree and no allocating library routine; the caller still owns
+ * q, k, idx_q, idx_k and po.  A call whose psa_block_scores_scratch_bytes() exceeds the capacity is rejected with
+ * PSA_ERR_ARG and a message naming both sizes (split it over fewer heads).
+ * The first call on a device resolves the array's device address (cudaGetSymbolAddress, with that device current);
+ * make that first call outside any stream capture.  All calls on a device share the one array, which keeps the last
+ * call's contents: every element a call reads it has written before, so nothing needs clearing, but two calls that
+ * overlap on the GPU (different streams, or threads) race on it - serialise them. */
+#define PSA_STATIC_SCRATCH_BYTES (64u << 20)
+size_t psa_block_scores_static_capacity(void);
+int psa_block_scores_static(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* po,
+                            int64_t bh, int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int dtype,
+                            int impl, void* stream);
+
 /* Level assignment.  Replaces transfer_attn_to_mask, all four modes,
  * src/psa_triton/utils/transfer_attn_to_mask.py:6-507.
  * po: [rows, nk] scores in dtype (rows = B*H*Mq).  mask: int32 [rows, nk + n_levels] (newtype) or [rows, nk].

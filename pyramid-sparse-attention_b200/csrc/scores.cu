@@ -10,6 +10,8 @@
 //
 // This file holds the scalar fp32 stage A (any dtype; exact fp32 dot products) and stage B.  The tcgen05
 // stage A for f16/bf16 lives in scores_tc.cu.
+#include <mutex>
+
 #include "psa_common.cuh"
 #include "scores.h"
 
@@ -194,6 +196,66 @@ extern "C" int psa_block_scores(const void* q, const void* k, const int32_t* idx
   PSA_REQUIRE(scratch_bytes >= psa_block_scores_scratch_bytes(bh, seq_q, seq_k, block_m, block_n, dtype), PSA_ERR_ARG,
               "psa_block_scores: scratch too small (%zu bytes)", scratch_bytes);
   PSA_REQUIRE(impl >= 0 && impl <= 2, PSA_ERR_ARG, "psa_block_scores: impl=%d", impl);
+  cudaStream_t st = (cudaStream_t)stream;
+  PSA_DISPATCH_DTYPE(dtype, T, return launch_scores<T>(q, k, idx_q, idx_k, po, scratch, d, bh, impl, st));
+  return PSA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free variant.  Some hosts of this library may not allocate device memory at call time: code that
+// runs with a fixed memory budget handed out at start-up (an inference server that has given every byte to its own
+// pools), a plug-in that is only given input and output buffers, or a caller inside a region where cudaMalloc is
+// forbidden.  For them the stage-A/stage-B scratch lives in this file-scope device array, which every GPU that loads
+// the library keeps until the process exits.
+namespace psa {
+
+constexpr size_t kStaticScratchBytes = PSA_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scores_scratch[kStaticScratchBytes];
+
+// Device address of the array, resolved once per device.  In host code the array's name is only a handle for the
+// runtime, not a device address, so it must go through cudaGetSymbolAddress with the target device current.
+static int static_scratch_ptr(void** out) {
+  constexpr int kMaxDevices = 64;
+  static void* cached[kMaxDevices] = {nullptr};
+  static std::mutex mu;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  PSA_REQUIRE(e == cudaSuccess && dev >= 0 && dev < kMaxDevices, PSA_ERR_CUDA, "psa_block_scores_static: cudaGetDevice failed: %s",
+              cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_static_scores_scratch);
+    PSA_REQUIRE(e == cudaSuccess && ptr != nullptr, PSA_ERR_CUDA,
+                "psa_block_scores_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return PSA_OK;
+}
+
+}  // namespace psa
+
+extern "C" size_t psa_block_scores_static_capacity(void) { return psa::kStaticScratchBytes; }
+
+extern "C" int psa_block_scores_static(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* po,
+                                       int64_t bh, int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n,
+                                       int dtype, int impl, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(q && k && idx_q && idx_k && po, PSA_ERR_ARG, "psa_block_scores_static: null pointer");
+  PSA_REQUIRE(bh > 0 && bh < 65536, PSA_ERR_ARG, "psa_block_scores_static: bh=%lld out of range", (long long)bh);
+  PSA_REQUIRE(impl >= 0 && impl <= 2, PSA_ERR_ARG, "psa_block_scores_static: impl=%d", impl);
+  ScoreDims d;
+  int rc = make_score_dims(d, seq_q, seq_k, head_dim, block_m, block_n);
+  if (rc != PSA_OK) return rc;
+  const size_t need = psa_block_scores_scratch_bytes(bh, seq_q, seq_k, block_m, block_n, dtype);
+  PSA_REQUIRE(need <= kStaticScratchBytes, PSA_ERR_ARG,
+              "psa_block_scores_static: this call needs %zu bytes of scratch but the built-in scratch holds %zu; "
+              "split the call over fewer heads or use psa_block_scores with caller-provided scratch",
+              need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  rc = static_scratch_ptr(&scratch);
+  if (rc != PSA_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
   PSA_DISPATCH_DTYPE(dtype, T, return launch_scores<T>(q, k, idx_q, idx_k, po, scratch, d, bh, impl, st));
   return PSA_OK;

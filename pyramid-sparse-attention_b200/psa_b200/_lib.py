@@ -31,6 +31,8 @@ SIGNATURES = {
     "psa_pyramid_kv": (_i, [_p] * 8 + [_i64, _i64, _i, _i, _i, _p]),
     "psa_block_scores_scratch_bytes": (_sz, [_i64, _i64, _i64, _i, _i, _i]),
     "psa_block_scores": (_i, [_p] * 6 + [_sz, _i64, _i64, _i64, _i, _i, _i, _i, _i, _p]),
+    "psa_block_scores_static_capacity": (_sz, []),
+    "psa_block_scores_static": (_i, [_p] * 5 + [_i64, _i64, _i64, _i, _i, _i, _i, _i, _p]),
     "psa_assign_levels": (_i, [_p, _p, _i64, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _i, _i, _p]),
     "psa_density": (_i, [_p, _p, _i64, _i64, _i, _i, _p]),
     "psa_ksim": (_i, [_p, _p, _i64, _i64, _i, _i, _f, _f, _f, _i, _p]),
