@@ -139,9 +139,11 @@ static int launch_scores(const void* q, const void* k, const int32_t* idx_q, con
   T* R = (T*)scratch;
   const size_t r_bytes = ((size_t)bh * d.nq_s * d.n_d * sizeof(T) + 255) & ~(size_t)255;
   float* rowmax = (float*)((char*)scratch + r_bytes);
+  const size_t m_bytes = ((size_t)bh * d.nq_s * sizeof(float) + 255) & ~(size_t)255;
+  void* extra = (char*)scratch + r_bytes + m_bytes;
   bool use_tc = (impl == 2) || (impl == 0 && sizeof(T) == 2 && scores_tc_supported(d));
   if (use_tc) {
-    int rc = launch_scores_cellmax_tc(q, k, idx_q, idx_k, R, rowmax, d, bh, sizeof(T) == 4 ? PSA_F32 :
+    int rc = launch_scores_cellmax_tc(q, k, idx_q, idx_k, R, rowmax, extra, d, bh, sizeof(T) == 4 ? PSA_F32 :
                                       (std::is_same<T, __half>::value ? PSA_F16 : PSA_BF16), st);
     if (rc != PSA_OK) return rc;
   } else {
@@ -177,10 +179,12 @@ int make_score_dims(ScoreDims& d, int64_t seq_q, int64_t seq_k, int D, int bm, i
 extern "C" size_t psa_block_scores_scratch_bytes(int64_t bh, int64_t seq_q, int64_t seq_k, int block_m, int block_n,
                                                  int dtype) {
   psa::ScoreDims d;
-  if (psa::make_score_dims(d, seq_q, seq_k, 64, block_m, block_n) != PSA_OK) return 0;
+  if (psa::make_score_dims(d, seq_q, seq_k, 128, block_m, block_n) != PSA_OK) return 0;   // sized for head_dim 128
   const size_t es = dtype == PSA_F32 ? 4 : 2;
   const size_t r_bytes = ((size_t)bh * d.nq_s * d.n_d * es + 255) & ~(size_t)255;
-  return r_bytes + (size_t)bh * d.nq_s * sizeof(float) + 256;
+  const size_t m_bytes = ((size_t)bh * d.nq_s * sizeof(float) + 255) & ~(size_t)255;
+  const size_t extra = dtype == PSA_F32 ? 0 : psa::scores_tc_extra_scratch(d, bh);
+  return r_bytes + m_bytes + extra;
 }
 
 extern "C" int psa_block_scores(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* po,

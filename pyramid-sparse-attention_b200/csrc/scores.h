@@ -21,7 +21,9 @@ int make_score_dims(ScoreDims& d, int64_t seq_q, int64_t seq_k, int D, int bm, i
 
 // tcgen05 stage A (scores_tc.cu)
 bool scores_tc_supported(const ScoreDims& d);
+// bytes of scratch the tcgen05 path needs beyond R and rowmax (compacted sample matrices)
+size_t scores_tc_extra_scratch(const ScoreDims& d, int64_t bh);
 int launch_scores_cellmax_tc(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* R,
-                             float* rowmax, const ScoreDims& d, int64_t bh, int dtype, cudaStream_t st);
+                             float* rowmax, void* extra, const ScoreDims& d, int64_t bh, int dtype, cudaStream_t st);
 
 }  // namespace psa

@@ -61,12 +61,17 @@ def test_block_scores_golden(P, golden, case):
     assert float((po - ref).abs().max()) <= tol * float(ref.max()) * 10
 
 
+@pytest.mark.parametrize("impl", ["scalar", "tensor"])
 @pytest.mark.parametrize("dt,S,D,bm,bn", [("bf16", 1500, 128, 128, 64), ("fp16", 900, 64, 128, 32), ("bf16", 2048, 64, 128, 128),
-                                           ("fp32", 777, 64, 64, 64)])
-def test_block_scores_oracle(P, dt, S, D, bm, bn):
+                                           ("fp32", 777, 64, 64, 64), ("fp16", 5000, 128, 128, 64), ("bf16", 300, 128, 128, 32),
+                                           ("bf16", 4100, 64, 128, 64)])
+def test_block_scores_oracle(P, dt, S, D, bm, bn, impl):
+    if impl == "tensor" and dt == "fp32":
+        pytest.skip("the tcgen05 score kernel takes 16-bit inputs")
     q, k, _ = C.qkv(150, 1, 2, S, D, C.DT[dt])
     iq, ik = C.sample_idx(9, 1, 2, bm, bm // 4), C.sample_idx(10, 1, 2, bn, bn // 4)
-    po = P.ops.block_scores(q.to(DEV), k.to(DEV), iq.to(DEV), ik.to(DEV), bm, bn, impl=P.ops.IMPL_SCALAR).float().cpu()
+    po = P.ops.block_scores(q.to(DEV), k.to(DEV), iq.to(DEV), ik.to(DEV), bm, bn,
+                            impl=P.ops.IMPL_SCALAR if impl == "scalar" else P.ops.IMPL_TENSOR).float().cpu()
     ref = O.block_scores(q, k, iq, ik, bm, bn).float()
     assert po.shape == ref.shape
     # the scores feed a sort: compare within a few ulps of the element type, relative to the row scale
