@@ -1,18 +1,20 @@
 // Multi-level block-sparse flash-attention forward on tcgen05 tensor cores (f16/bf16, block_m = 128).
 //
-// One CTA per (128-row query block, batch*head), 6 warps:
+// One CTA per (128-row query block, batch*head), 10 warps:
 //   warp 0      producer: walks the block's index list and gathers the selected K/V blocks of every pyramid level
-//               with TMA (128-byte swizzle, one {64 ch, P tokens} box per block and 64-channel slab, no multicast)
-//               into 128-token tiles, PACKING blocks of different levels into the same tile; it also writes the
-//               per-column logit bias (log2 of the level, -inf for columns that do not exist).
-//   warp 1      MMA issuer: S = Q K^T into one of two TMEM score buffers, then O += P V (V read MN-major from the
-//               same swizzled tile), software-pipelined so that the next tile's S is in flight while the softmax
-//               warps work on the current one.
-//   warps 2-5   softmax: thread = query row.  Two passes over the TMEM row (max, then exp2), probabilities rounded
-//               to the element type into a swizzled shared-memory tile (the A operand of P V), running sum in fp32.
+//               with TMA (128-byte swizzle, one {64 ch, P tokens} box per block and 64-channel slab, no multicast;
+//               lanes 0..3 each issue one of the four copies of a block) into 128-token tiles, PACKING blocks of
+//               different levels into the same tile; it also writes the per-column logit bias (log2 of the level,
+//               -inf for columns that do not exist).
+//   warp 1      MMA issuer: S = Q K^T (operands in shared memory) into one of two TMEM score buffers, then
+//               O += P V with P read from TMEM and V read MN-major from the same swizzled tile; software-pipelined
+//               so that the next tile's S is in flight while the softmax warps work on the current one.
+//   warps 2-9   softmax: two threads per query row, 64 columns each.  One TMEM read of the row half into registers
+//               (the score buffer is released at once), row maximum exchanged through shared memory, exp2, running
+//               sum in fp32, probabilities rounded to the element type and stored to one of two TMEM P buffers.
 //               The running maximum is only raised when the new maximum exceeds it by more than 2^8 ("lazy"
 //               rescale); raising it rescales the O accumulator in TMEM.  Epilogue: O / sum -> global.
-// Accumulators live in TMEM: S0 [0,128), S1 [128,256), O [256,256+D) of a 512-column allocation.
+// TMEM (512 columns): S0 [0,128), S1 [128,256), O [256,256+D), P0 [384,448), P1 [448,512).
 //
 // Every mbarrier wait is bounded; on expiry the CTA records PSA_ERR_TIMEOUT in the status word, lets copies in
 // flight land, frees its TMEM and returns.
@@ -24,9 +26,10 @@ namespace psa {
 
 namespace {
 
-constexpr int kMaxWidth = 4096;      // longest index list (entries) the kernel stages in shared memory
+constexpr int kMaxWidth = 4096;        // longest index list (entries) the kernel stages in shared memory
 constexpr int kSlabBytes = 128 * 128;  // 128 rows x 128 B (64 16-bit channels)
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kSoftmaxThreads = 256;
 
 struct TmapPack {
   CUtensorMap q;
@@ -49,18 +52,17 @@ template <int D> struct Cfg {
   static constexpr int NST = D == 64 ? 4 : 2;
   static constexpr int Q_BYTES = SLABS * kSlabBytes;
   static constexpr int KV_BYTES = 2 * SLABS * kSlabBytes;   // K then V of one stage
-  static constexpr int P_BYTES = 2 * kSlabBytes;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_KV = OFF_Q + Q_BYTES;
-  static constexpr int OFF_P = OFF_KV + NST * KV_BYTES;
-  static constexpr int OFF_BIAS = OFF_P + P_BYTES;
-  static constexpr int OFF_ROW = OFF_BIAS + NST * 128 * 4;
+  static constexpr int OFF_BIAS = OFF_KV + NST * KV_BYTES;
+  static constexpr int OFF_XCH = OFF_BIAS + NST * 128 * 4;
+  static constexpr int OFF_ROW = OFF_XCH + 2 * 2 * 128 * 4;
   static constexpr int OFF_CTRL = OFF_ROW + kMaxWidth * 4;
   static constexpr int SMEM_BYTES = OFF_CTRL + 512 + 1024;   // + alignment slack
 };
 
 struct Ctrl {
-  uint64_t full[4], empty[4], s_full[2], s_empty[2], p_full, pv_done, q_full;
+  uint64_t full[4], empty[4], s_full[2], s_empty[2], p_full[2], pv_done[2], q_full;
   uint32_t tmem_base;
   int abort_flag;
   int n_sep;
@@ -92,8 +94,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   unsigned char* sQ = smem + C::OFF_Q;
   unsigned char* sKV = smem + C::OFF_KV;
-  unsigned char* sP = smem + C::OFF_P;
   float* sBias = reinterpret_cast<float*>(smem + C::OFF_BIAS);
+  float* sXch = reinterpret_cast<float*>(smem + C::OFF_XCH);      // [tile parity][half][row]
   int32_t* sRow = reinterpret_cast<int32_t*>(smem + C::OFF_ROW);
   Ctrl* ctl = reinterpret_cast<Ctrl*>(smem + C::OFF_CTRL);
   volatile int* abort_flag = &ctl->abort_flag;
@@ -106,9 +108,12 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   // ---------------------------------------------------------------- setup
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::NST; ++i) { tc::mbar_init(&ctl->full[i], 1); tc::mbar_init(&ctl->empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { tc::mbar_init(&ctl->s_full[i], 1); tc::mbar_init(&ctl->s_empty[i], 128); }
-    tc::mbar_init(&ctl->p_full, 128);
-    tc::mbar_init(&ctl->pv_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&ctl->s_full[i], 1);
+      tc::mbar_init(&ctl->s_empty[i], kSoftmaxThreads);
+      tc::mbar_init(&ctl->p_full[i], kSoftmaxThreads);
+      tc::mbar_init(&ctl->pv_done[i], 1);
+    }
     tc::mbar_init(&ctl->q_full, 1);
     ctl->abort_flag = 0;
     ctl->n_sep = 0;
@@ -134,22 +139,19 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       while (b >= 0 && ctl->sep[b] > v) { ctl->sep[b + 1] = ctl->sep[b]; --b; }
       ctl->sep[b + 1] = v;
     }
-    int prev = -1, tokens = 0, last_small_P = 0;
+    int prev = -1, tokens = 0;
     for (int li = 0; li < 4; ++li) {
       int end = li < ns ? ctl->sep[li] : p.width;
       int start = prev + 1;
-      int cnt = end > start ? end - start : 0;
-      if (li > ns) cnt = 0;                       // the row ended before this level's segment
+      int cnt = end > start ? end - start : 0;      // a row that ended early leaves later segments empty
       ctl->seg_start[li] = start;
       ctl->seg_cnt[li] = cnt;
       const int P = p.bn >> li;
       int items = cnt;
       if (p.quirk && P < p.tn && cnt >= 2) items += p.tn / P - 2;
       tokens += items * P;
-      if (items > 0 && P < 16) last_small_P = P;
       prev = end;
     }
-    (void)last_small_P;
     const int padded = (tokens + 15) & ~15;
     ctl->n_tiles = (padded + 127) / 128;
     ctl->last_cols = padded - (ctl->n_tiles - 1) * 128;
@@ -160,7 +162,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   const int n_tiles = ctl->n_tiles;
   const int last_cols = ctl->last_cols;
   const uint32_t tmem = ctl->tmem_base;
-  const uint32_t tS[2] = {tmem, tmem + 128};
   const uint32_t tO = tmem + 256;
 
   if (n_tiles > 0) {
@@ -175,6 +176,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       uint32_t bytes = 0;
       bool ok = true;
       int last_li = 0;
+      const int op_is_v = lane / C::SLABS, op_slab = lane % C::SLABS;   // lanes 0 .. 2*SLABS-1 each own one copy
       auto emit = [&](int li, int blk, float bias2) {
         if (!ok) return;
         const int stage = tile % C::NST;
@@ -184,15 +186,10 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           if (!ok) return;
         }
         const int P = p.bn >> li;
-        unsigned char* kdst = sKV + stage * C::KV_BYTES + fill * 128;
-        unsigned char* vdst = kdst + C::SLABS * kSlabBytes;
-        if (lane == 0) {
-          for (int s = 0; s < C::SLABS; ++s) {
-            tc::tma_load_3d(kdst + s * kSlabBytes, &maps.k[li], &ctl->full[stage], s * 64, blk * P, bh);
-            tc::tma_load_3d(vdst + s * kSlabBytes, &maps.v[li], &ctl->full[stage], s * 64, blk * P, bh);
-          }
+        if (lane < 2 * C::SLABS) {
+          unsigned char* dst = sKV + stage * C::KV_BYTES + (op_is_v * C::SLABS + op_slab) * kSlabBytes + fill * 128;
+          tc::tma_load_3d(dst, op_is_v ? &maps.v[li] : &maps.k[li], &ctl->full[stage], op_slab * 64, blk * P, bh);
         }
-        __syncwarp();
         bytes += 2u * C::SLABS * P * 128u;
         const int64_t t0 = (int64_t)blk * P;
         for (int c = lane; c < P; c += 32) sBias[stage * 128 + fill + c] = (t0 + c < p.n[li]) ? bias2 : -INFINITY;
@@ -228,7 +225,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       if (lane == 0) {
         bool ok = tc::mbar_wait(&ctl->q_full, 0, abort_flag);
         const uint32_t idesc_pv = tc::make_idesc(FMT, 128, D, 0, 1);
-        const uint32_t q_addr = tc::smem_u32(sQ), p_addr = tc::smem_u32(sP);
+        const uint32_t q_addr = tc::smem_u32(sQ);
         for (int j = 0; ok && j <= n_tiles; ++j) {
           if (j < n_tiles) {
             const int stage = j % C::NST, b = j & 1;
@@ -243,32 +240,32 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
               const uint32_t off = (ks >> 2) * kSlabBytes + (ks & 3) * 32;
-              tc::umma_ss(tS[b], tc::make_smem_desc(q_addr + off, 16, 1024), tc::make_smem_desc(k_addr + off, 16, 1024),
-                          idesc_qk, ks > 0);
+              tc::umma_ss(tmem + b * 128, tc::make_smem_desc(q_addr + off, 16, 1024),
+                          tc::make_smem_desc(k_addr + off, 16, 1024), idesc_qk, ks > 0);
             }
             tc::umma_commit(&ctl->s_full[b]);
           }
           if (j > 0) {
             const int t = j - 1;
-            const int stage = t % C::NST;
+            const int stage = t % C::NST, b = t & 1;
             const int ncols = t == n_tiles - 1 ? last_cols : 128;
-            ok = tc::mbar_wait(&ctl->p_full, t & 1, abort_flag);
+            ok = tc::mbar_wait(&ctl->p_full[b], (t >> 1) & 1, abort_flag);
             if (!ok) break;
             tc::tc_fence_after();
             const uint32_t v_addr = tc::smem_u32(sKV + stage * C::KV_BYTES + C::SLABS * kSlabBytes);
-            for (int ks = 0; ks < ncols / 16; ++ks) {
-              const uint32_t aoff = (ks >> 2) * kSlabBytes + (ks & 3) * 32;
-              tc::umma_ss(tO, tc::make_smem_desc(p_addr + aoff, 16, 1024),
-                          tc::make_smem_desc(v_addr + ks * 2048, kSlabBytes, 1024), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
-            }
+            const uint32_t tP = tmem + 384 + b * 64;
+            for (int ks = 0; ks < ncols / 16; ++ks)
+              tc::umma_ts(tO, tP + ks * 8, tc::make_smem_desc(v_addr + ks * 2048, kSlabBytes, 1024), idesc_pv,
+                          (t > 0 || ks > 0) ? 1u : 0u);
             tc::umma_commit(&ctl->empty[stage]);   // K/V stage may be refilled
-            tc::umma_commit(&ctl->pv_done);        // O and the P tile are consistent again
+            tc::umma_commit(&ctl->pv_done[b]);     // O is consistent again, P buffer b may be rewritten
           }
         }
       }
     } else {
-      // ============================================================ softmax / epilogue (4 warps, thread = row)
+      // ============================================================ softmax / epilogue (8 warps, 2 threads per row)
       const int quarter = warp & 3;                 // TMEM lanes this warp may touch
+      const int half = (warp - 2) >> 2;             // which 64 score columns / which half of the O channels
       const int r = quarter * 32 + lane;            // row inside the query block
       const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
       float m_run = -INFINITY, l_run = 0.f;
@@ -280,22 +277,41 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc::tc_fence_after();
-        const float* bias = sBias + stage * 128;
-        // pass 1: row maximum of the biased, scaled logits (log2 domain)
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 32) {
-          uint32_t v[32];
-          tc::tmem_ld32(tS[b] + lane_base + c0, v);
-          tc::tmem_wait_ld();
+        uint32_t v0[32], v1[32];
+        tc::tmem_ld32(tmem + b * 128 + lane_base + half * 64, v0);
+        tc::tmem_ld32(tmem + b * 128 + lane_base + half * 64 + 32, v1);
+        tc::tmem_wait_ld();
+        tc::tc_fence_before();
+        tc::mbar_arrive(&ctl->s_empty[b]);          // the score buffer is free for tile j+2
+        if (j == n_tiles - 1 && last_cols < 128) {  // columns the MMA did not write hold stale bits
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float bb = bias[c0 + i];
-            const float x = bb == -INFINITY ? -INFINITY : fmaf(__uint_as_float(v[i]), p.scale_log2, bb);
-            mx = fmaxf(mx, x);
+            if (half * 64 + i >= last_cols) v0[i] = 0u;
+            if (half * 64 + 32 + i >= last_cols) v1[i] = 0u;
           }
         }
-        // raise the running maximum only when it is far off (or still unset)
+        // biased, scaled logits (log2 domain) in place, and their maximum
+        const float4* bias4 = reinterpret_cast<const float4*>(sBias + stage * 128 + half * 64);
+        float mx = -INFINITY;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const float4 ba = bias4[g], bb = bias4[8 + g];
+          float x;
+          x = fmaf(__uint_as_float(v0[4 * g + 0]), p.scale_log2, ba.x); v0[4 * g + 0] = __float_as_uint(x); mx = fmaxf(mx, x);
+          x = fmaf(__uint_as_float(v0[4 * g + 1]), p.scale_log2, ba.y); v0[4 * g + 1] = __float_as_uint(x); mx = fmaxf(mx, x);
+          x = fmaf(__uint_as_float(v0[4 * g + 2]), p.scale_log2, ba.z); v0[4 * g + 2] = __float_as_uint(x); mx = fmaxf(mx, x);
+          x = fmaf(__uint_as_float(v0[4 * g + 3]), p.scale_log2, ba.w); v0[4 * g + 3] = __float_as_uint(x); mx = fmaxf(mx, x);
+          x = fmaf(__uint_as_float(v1[4 * g + 0]), p.scale_log2, bb.x); v1[4 * g + 0] = __float_as_uint(x); mx = fmaxf(mx, x);
+          x = fmaf(__uint_as_float(v1[4 * g + 1]), p.scale_log2, bb.y); v1[4 * g + 1] = __float_as_uint(x); mx = fmaxf(mx, x);
+          x = fmaf(__uint_as_float(v1[4 * g + 2]), p.scale_log2, bb.z); v1[4 * g + 2] = __float_as_uint(x); mx = fmaxf(mx, x);
+          x = fmaf(__uint_as_float(v1[4 * g + 3]), p.scale_log2, bb.w); v1[4 * g + 3] = __float_as_uint(x); mx = fmaxf(mx, x);
+        }
+        // the two threads of a row exchange their partial maxima
+        float* xch = sXch + (j & 1) * 256;
+        xch[half * 128 + r] = mx;
+        tc::named_bar_sync(1 + quarter, 64);
+        mx = fmaxf(mx, xch[(half ^ 1) * 128 + r]);
+        // raise the running maximum only when it is far off (or still unset); both threads of a row agree
         float alpha = 1.f;
         const bool raise = mx > m_run + 8.f;
         if (raise) {
@@ -303,70 +319,64 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           m_run = mx;
           l_run *= alpha;
         }
-        // the previous tile's P V must have finished before P is overwritten or O is rescaled
-        if (j > 0) {
-          ok = tc::mbar_wait(&ctl->pv_done, (j - 1) & 1, abort_flag);
+        // P buffer b was last read by the P V of tile j-2
+        ok = tc::mbar_wait(&ctl->pv_done[b], ((j >> 1) & 1) ^ 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (j > 0 && __any_sync(0xffffffffu, raise)) {
+          // O may only be touched between two P V products: wait for the one of tile j-1
+          ok = tc::mbar_wait(&ctl->pv_done[b ^ 1], ((j - 1) >> 1) & 1, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc::tc_fence_after();
-          if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < D; c0 += 32) {
-              uint32_t v[32];
-              tc::tmem_ld32(tO + lane_base + c0, v);
-              tc::tmem_wait_ld();
+          for (int c0 = 0; c0 < D / 2; c0 += 32) {
+            uint32_t o[32];
+            tc::tmem_ld32(tO + lane_base + half * (D / 2) + c0, o);
+            tc::tmem_wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-              tc::tmem_st32(tO + lane_base + c0, v);
-            }
-            tc::tmem_wait_st();
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tc::tmem_st32(tO + lane_base + half * (D / 2) + c0, o);
           }
+          tc::tmem_wait_st();
         }
-        // pass 2: probabilities -> swizzled P tile, running sum
+        // probabilities (rounded to the element type) -> TMEM, running sum
         const float m_use = m_run == -INFINITY ? 0.f : m_run;
         float lsum = 0.f;
-#pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 32) {
-          uint32_t v[32];
-          tc::tmem_ld32(tS[b] + lane_base + c0, v);
-          tc::tmem_wait_ld();
-          uint32_t pk[16];
+        uint32_t pk[32];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float b0 = bias[c0 + i], b1 = bias[c0 + i + 1];
-            const float x0 = b0 == -INFINITY ? -INFINITY : fmaf(__uint_as_float(v[i]), p.scale_log2, b0);
-            const float x1 = b1 == -INFINITY ? -INFINITY : fmaf(__uint_as_float(v[i + 1]), p.scale_log2, b1);
-            const float p0 = ex2(x0 - m_use), p1 = ex2(x1 - m_use);
-            lsum += p0 + p1;
-            pk[i >> 1] = pack2<FMT>(p0, p1);
-          }
-          unsigned char* prow = sP + (c0 >> 6) * kSlabBytes + r * 128;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int c16 = ((c0 & 32) >> 3) + i;
-            *reinterpret_cast<uint4*>(prow + ((c16 ^ (r & 7)) << 4)) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
-          }
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ex2(__uint_as_float(v0[i]) - m_use), p1 = ex2(__uint_as_float(v0[i + 1]) - m_use);
+          const float p2 = ex2(__uint_as_float(v1[i]) - m_use), p3 = ex2(__uint_as_float(v1[i + 1]) - m_use);
+          lsum += (p0 + p1) + (p2 + p3);
+          pk[i >> 1] = pack2<FMT>(p0, p1);
+          pk[16 + (i >> 1)] = pack2<FMT>(p2, p3);
         }
         l_run += lsum;
+        tc::tmem_st32(tmem + 384 + b * 64 + lane_base + half * 32, pk);
+        tc::tmem_wait_st();
         tc::tc_fence_before();
-        tc::mbar_arrive(&ctl->s_empty[b]);      // score buffer b may be overwritten
-        tc::fence_proxy_async();                // P tile visible to the tensor core
-        tc::mbar_arrive(&ctl->p_full);
+        tc::mbar_arrive(&ctl->p_full[b]);
       }
       // epilogue
       if (ok) {
-        ok = tc::mbar_wait(&ctl->pv_done, (n_tiles - 1) & 1, abort_flag);
+        const int t = n_tiles - 1;
+        ok = tc::mbar_wait(&ctl->pv_done[t & 1], (t >> 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
       }
       if (ok) {
         tc::tc_fence_after();
+        float* xch = sXch + (n_tiles & 1) * 256;
+        xch[half * 128 + r] = l_run;
+        tc::named_bar_sync(1 + quarter, 64);
+        const float l_tot = l_run + xch[(half ^ 1) * 128 + r];
         const int64_t qrow = (int64_t)m * 128 + r;
-        const float inv = 1.0f / l_run;     // empty row: 0/0 like the reference
-        uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D;
+        const float inv = 1.0f / l_tot;     // empty row: 0/0 like the reference
+        uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + half * (D / 2);
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = 0; c0 < D / 2; c0 += 32) {
           uint32_t v[32];
-          tc::tmem_ld32(tO + lane_base + c0, v);
+          tc::tmem_ld32(tO + lane_base + half * (D / 2) + c0, v);
           tc::tmem_wait_ld();
           if (qrow < p.seq_q) {
 #pragma unroll
@@ -384,11 +394,12 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     }
   } else if (warp >= 2) {
     // no block selected at all: the reference divides 0 by 0
+    const int half = (warp - 2) >> 2;
     const int64_t qrow = (int64_t)m * 128 + (warp & 3) * 32 + lane;
     if (qrow < p.seq_q) {
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + half * (D / 2);
       const uint32_t nan2 = pack2<FMT>(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
-      for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(nan2, nan2, nan2, nan2);
+      for (int c = 0; c < D / 2; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(nan2, nan2, nan2, nan2);
     }
   }
 
