@@ -1,23 +1,29 @@
 // Multi-level block-sparse flash-attention forward on tcgen05 tensor cores (f16/bf16, block_m = 128).
 //
-// One CTA per (128-row query block, batch*head), 10 warps:
-//   warp 0      producer: walks the block's index list and gathers the selected K/V blocks of every pyramid level
-//               with TMA (128-byte swizzle, one {64 ch, P tokens} box per block and 64-channel slab, no multicast;
-//               lanes 0..3 each issue one of the four copies of a block) into 128-token tiles, PACKING blocks of
-//               different levels into the same tile; it also writes the per-column logit bias (log2 of the level,
-//               -inf for columns that do not exist).
-//   warp 1      MMA issuer: S = Q K^T (operands in shared memory) into one of two TMEM score buffers, then
-//               O += P V with P read from TMEM and V read MN-major from the same swizzled tile; software-pipelined
-//               so that the next tile's S is in flight while the softmax warps work on the current one.
-//   warps 2-9   softmax: two threads per query row, 64 columns each.  One TMEM read of the row half into registers
-//               (the score buffer is released at once), row maximum exchanged through shared memory, exp2, running
-//               sum in fp32, probabilities rounded to the element type and stored to one of two TMEM P buffers.
-//               The running maximum is only raised when the new maximum exceeds it by more than 2^8 ("lazy"
-//               rescale); raising it rescales the O accumulator in TMEM.  Epilogue: O / sum -> global.
+// One CTA per (128-row query block, batch*head), 12 warps:
+//   warps 0-2   producers: walk the block's index list and gather the selected K/V blocks of every pyramid level into
+//               128-token tiles, PACKING blocks of different levels into the same tile.  A block is P = block_n/level
+//               contiguous pooled rows, fetched with one TMA box {64 ch, P rows} per 64-channel slab (128-byte
+//               swizzle, never multicast).  A TMA operation costs its issuing thread ~150 cycles whatever its size,
+//               so the blocks of a tile are dealt round-robin to the three warps, which issue concurrently.
+//               K tiles and V tiles live in separate rings (K is released after S = Q K^T, V after O += P V)
+//               and K runs one tile ahead of V.  Warp 0 also writes the per-column logit bias (log2 of the level,
+//               -inf for columns that do not exist) and loads the Q tile.
+//   warp 3      MMA issuer: S = Q K^T (operands in shared memory) into one of two TMEM score buffers, and
+//               O += P V with P read from TMEM and V read MN-major from its swizzled tile.  It polls both kinds of
+//               work and issues whichever is ready, so a K/V tile that is still in flight never delays a product
+//               whose operands are there.
+//   warps 4-11  softmax: two threads per query row, 64 columns each.  One TMEM read of the row half into registers,
+//               row maximum exchanged through shared memory, exp2, running sum in fp32, probabilities rounded to the
+//               element type and stored to one of two TMEM P buffers.  The running maximum is only raised when the
+//               new maximum exceeds it by more than 2^8 ("lazy" rescale); raising it rescales the O accumulator in
+//               TMEM.  Epilogue: O / sum -> global.
 // TMEM (512 columns): S0 [0,128), S1 [128,256), O [256,256+D), P0 [384,448), P1 [448,512).
 //
 // Every mbarrier wait is bounded; on expiry the CTA records PSA_ERR_TIMEOUT in the status word, lets copies in
 // flight land, frees its TMEM and returns.
+#include <cstddef>
+
 #include "psa_common.cuh"
 #include "fwd.h"
 #include "tc_common.cuh"
@@ -26,14 +32,18 @@ namespace psa {
 
 namespace {
 
-constexpr int kMaxWidth = 4096;        // longest index list (entries) the kernel stages in shared memory
+constexpr int kMaxWidth = 4064;        // longest index list (entries) the kernel handles
+constexpr int kMaxItems = 4096;        // item table capacity (entries + extra + padding blocks)
 constexpr int kSlabBytes = 128 * 128;  // 128 rows x 128 B (64 16-bit channels)
-constexpr int kThreads = 320;
+constexpr int kProducerWarps = 3;
+constexpr int kProducerThreads = kProducerWarps * 32;
 constexpr int kSoftmaxThreads = 256;
+constexpr int kThreads = kProducerThreads + 32 + kSoftmaxThreads;   // 384
+constexpr int kBiasSlots = 8;
 
 struct TmapPack {
   CUtensorMap q;
-  CUtensorMap k[4];
+  CUtensorMap k[4];   // levels 1, 2, 4, 8
   CUtensorMap v[4];
 };
 
@@ -49,26 +59,29 @@ struct TcParams {
 
 template <int D> struct Cfg {
   static constexpr int SLABS = D / 64;
-  static constexpr int NST = D == 64 ? 4 : 2;
-  static constexpr int Q_BYTES = SLABS * kSlabBytes;
-  static constexpr int KV_BYTES = 2 * SLABS * kSlabBytes;   // K then V of one stage
+  static constexpr int NK = D == 64 ? 4 : 3;   // K-tile ring
+  static constexpr int NV = D == 64 ? 4 : 2;   // V-tile ring
+  static constexpr int TILE_BYTES = SLABS * kSlabBytes;
   static constexpr int OFF_Q = 0;
-  static constexpr int OFF_KV = OFF_Q + Q_BYTES;
-  static constexpr int OFF_BIAS = OFF_KV + NST * KV_BYTES;
-  static constexpr int OFF_XCH = OFF_BIAS + NST * 128 * 4;
+  static constexpr int OFF_K = OFF_Q + TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + NK * TILE_BYTES;
+  static constexpr int OFF_BIAS = OFF_V + NV * TILE_BYTES;
+  static constexpr int OFF_XCH = OFF_BIAS + kBiasSlots * 128 * 4;
   static constexpr int OFF_ROW = OFF_XCH + 2 * 2 * 128 * 4;
-  static constexpr int OFF_CTRL = OFF_ROW + kMaxWidth * 4;
-  static constexpr int SMEM_BYTES = OFF_CTRL + 512 + 1024;   // + alignment slack
+  static constexpr int OFF_CTRL = OFF_ROW + kMaxItems * 4;
+  static constexpr int SMEM_BYTES = OFF_CTRL + 1024 + 1024;   // control block + alignment slack
 };
 
 struct Ctrl {
-  uint64_t full[4], empty[4], s_full[2], s_empty[2], p_full[2], pv_done[2], q_full;
+  uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4], b_full[kBiasSlots];
+  uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2], q_full;
   uint32_t tmem_base;
   int abort_flag;
   int n_sep;
   int sep[16];
-  int n_tiles, last_cols;
-  int seg_start[4], seg_cnt[4];
+  int n_tiles, last_cols, n_items;
+  int seg_start[4], seg_cnt[4], item_base[4], tok_base[4];
+  float qbias2[4];
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -87,16 +100,33 @@ template <> __device__ __forceinline__ uint32_t pack2<0>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Item table entry (one gathered block): bits 0-11 block index, 12-13 level index, 14 extra block of a narrow level
+// (reference compatibility), 15 inert padding block, 16-31 first tile column of the block counted from the start
+// of the row's token stream, in units of 4 tokens.
+constexpr uint32_t kItemQuirk = 1u << 14, kItemPad = 1u << 15;
+
+#ifdef PSA_FWD_PROFILE
+}  // namespace
+__device__ long long g_prof[64];
+namespace {
+#define PROF_T0() long long prof_t0 = clock64()
+#define PROF_ADD(slot) do { long long t1 = clock64(); prof_acc[slot] += t1 - prof_t0; prof_t0 = t1; } while (0)
+#else
+#define PROF_T0()
+#define PROF_ADD(slot)
+#endif
+
 template <int D, int FMT>
 __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_constant__ TmapPack maps, const TcParams p) {
   using C = Cfg<D>;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   unsigned char* sQ = smem + C::OFF_Q;
-  unsigned char* sKV = smem + C::OFF_KV;
+  unsigned char* sK = smem + C::OFF_K;
+  unsigned char* sV = smem + C::OFF_V;
   float* sBias = reinterpret_cast<float*>(smem + C::OFF_BIAS);
   float* sXch = reinterpret_cast<float*>(smem + C::OFF_XCH);      // [tile parity][half][row]
-  int32_t* sRow = reinterpret_cast<int32_t*>(smem + C::OFF_ROW);
+  uint32_t* sItems = reinterpret_cast<uint32_t*>(smem + C::OFF_ROW);
   Ctrl* ctl = reinterpret_cast<Ctrl*>(smem + C::OFF_CTRL);
   volatile int* abort_flag = &ctl->abort_flag;
 
@@ -107,7 +137,11 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
 
   // ---------------------------------------------------------------- setup
   if (threadIdx.x == 0) {
-    for (int i = 0; i < C::NST; ++i) { tc::mbar_init(&ctl->full[i], 1); tc::mbar_init(&ctl->empty[i], 1); }
+    for (int i = 0; i < 4; ++i) {
+      tc::mbar_init(&ctl->k_full[i], kProducerWarps); tc::mbar_init(&ctl->k_empty[i], 1);
+      tc::mbar_init(&ctl->v_full[i], kProducerWarps); tc::mbar_init(&ctl->v_empty[i], 1);
+    }
+    for (int i = 0; i < kBiasSlots; ++i) tc::mbar_init(&ctl->b_full[i], kProducerWarps);
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&ctl->s_full[i], 1);
       tc::mbar_init(&ctl->s_empty[i], kSoftmaxThreads);
@@ -119,15 +153,17 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     ctl->n_sep = 0;
     tc::fence_mbar_init();
   }
-  for (int i = threadIdx.x; i < p.width; i += kThreads) sRow[i] = mrow[i];
+  // the raw index list is staged in the (still unused) K ring; the item table built from it stays resident
+  int32_t* sTmp = reinterpret_cast<int32_t*>(sK);
+  for (int i = threadIdx.x; i < p.width; i += kThreads) sTmp[i] = mrow[i];
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 3) {
     tc::tmem_alloc(&ctl->tmem_base, 512);
     tc::tmem_relinquish();
   }
   // separators of the index list (their order is recovered by a tiny sort)
   for (int i = threadIdx.x; i < p.width; i += kThreads)
-    if (sRow[i] == -1) {
+    if (sTmp[i] == -1) {
       int slot = atomicAdd(&ctl->n_sep, 1);
       if (slot < 16) ctl->sep[slot] = i;
     }
@@ -139,22 +175,43 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       while (b >= 0 && ctl->sep[b] > v) { ctl->sep[b + 1] = ctl->sep[b]; --b; }
       ctl->sep[b + 1] = v;
     }
-    int prev = -1, tokens = 0;
+    int prev = -1, tokens = 0, n_items = 0, last_P = p.bn;
     for (int li = 0; li < 4; ++li) {
       int end = li < ns ? ctl->sep[li] : p.width;
       int start = prev + 1;
       int cnt = end > start ? end - start : 0;      // a row that ended early leaves later segments empty
       ctl->seg_start[li] = start;
       ctl->seg_cnt[li] = cnt;
+      ctl->item_base[li] = n_items;
+      ctl->tok_base[li] = tokens;
       const int P = p.bn >> li;
       int items = cnt;
-      if (p.quirk && P < p.tn && cnt >= 2) items += p.tn / P - 2;
+      const bool quirk = p.quirk && P < p.tn && cnt >= 2;
+      if (quirk) items += p.tn / P - 2;
+      ctl->qbias2[li] = quirk ? (float)li + log2f((float)(cnt / 2)) : 0.f;
+      if (items > 0) last_P = P;
       tokens += items * P;
+      n_items += items;
       prev = end;
     }
+    // inert padding blocks (block 0 of the last used level, bias -inf) up to a multiple of 16 columns
     const int padded = (tokens + 15) & ~15;
+    const int last_li = 31 - __clz(p.bn / last_P);
+    for (int t = tokens; t < padded; t += last_P)
+      sItems[n_items++] = (uint32_t)last_li << 12 | kItemPad | ((uint32_t)(t >> 2) << 16);
+    ctl->n_items = n_items;
     ctl->n_tiles = (padded + 127) / 128;
     ctl->last_cols = padded - (ctl->n_tiles - 1) * 128;
+  }
+  __syncthreads();
+  for (int li = 0; li < 4; ++li) {
+    const int P = p.bn >> li, cnt = ctl->seg_cnt[li], start = ctl->seg_start[li];
+    const int ib = ctl->item_base[li], tb = ctl->tok_base[li];
+    for (int e = threadIdx.x; e < cnt; e += kThreads)
+      sItems[ib + e] = ((uint32_t)sTmp[start + e] & 0xfffu) | (uint32_t)li << 12 | ((uint32_t)((tb + e * P) >> 2) << 16);
+    if (p.quirk && P < p.tn && cnt >= 2)
+      for (int j = 2 + threadIdx.x; j < p.tn / P; j += kThreads)
+        sItems[ib + cnt + j - 2] = (uint32_t)j | (uint32_t)li << 12 | kItemQuirk | ((uint32_t)((tb + (cnt + j - 2) * P) >> 2) << 16);
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -165,114 +222,190 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   const uint32_t tO = tmem + 256;
 
   if (n_tiles > 0) {
-    if (warp == 0) {
-      // ============================================================ producer
-      if (lane == 0) {
+    if (warp < kProducerWarps) {
+      // ============================================================ producers
+      if (warp == 0 && lane == 0) {
         tc::tma_prefetch_desc(&maps.q);
         for (int s = 0; s < C::SLABS; ++s) tc::tma_load_3d(sQ + s * kSlabBytes, &maps.q, &ctl->q_full, s * 64, m * 128, bh);
-        tc::mbar_arrive_expect_tx(&ctl->q_full, C::Q_BYTES);
+        tc::mbar_arrive_expect_tx(&ctl->q_full, C::TILE_BYTES);
       }
-      int tile = 0, fill = 0;
-      uint32_t bytes = 0;
+      const int n_items = ctl->n_items;
+#ifdef PSA_FWD_PROFILE
+      long long prof_acc[4] = {0, 0, 0, 0};
+#endif
+      PROF_T0();
+      // everything the per-block issue needs, as plain 32-bit shared addresses / 64-bit map addresses
+      const uint32_t ctl_a = tc::smem_u32(ctl);
+      const uint32_t k_full_a = ctl_a + (uint32_t)offsetof(Ctrl, k_full), k_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, k_empty);
+      const uint32_t v_full_a = ctl_a + (uint32_t)offsetof(Ctrl, v_full), v_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, v_empty);
+      const uint32_t b_full_a = ctl_a + (uint32_t)offsetof(Ctrl, b_full);
+      const uint32_t sK_a = tc::smem_u32(sK), sV_a = tc::smem_u32(sV);
+      const uint64_t kmap0 = reinterpret_cast<uint64_t>(&maps.k[0]), vmap0 = reinterpret_cast<uint64_t>(&maps.v[0]);
+      const int n0 = (int)p.n[0], n1 = (int)p.n[1], n2 = (int)p.n[2], n3 = (int)p.n[3];
+      const float qb0 = ctl->qbias2[0], qb1 = ctl->qbias2[1], qb2 = ctl->qbias2[2], qb3 = ctl->qbias2[3];
+      int ki = 0, vi = 0;              // next item of the K pass / V pass; item i is issued by warp i % 3
       bool ok = true;
-      int last_li = 0;
-      const int op_is_v = lane / C::SLABS, op_slab = lane % C::SLABS;   // lanes 0 .. 2*SLABS-1 each own one copy
-      auto emit = [&](int li, int blk, float bias2) {
-        if (!ok) return;
-        const int stage = tile % C::NST;
-        if (fill == 0) {
-          ok = tc::mbar_wait(&ctl->empty[stage], ((tile / C::NST) & 1) ^ 1, abort_flag);
+      // step s gathers K tile s and then V tile s-1: K runs one tile ahead of V
+      for (int step = 0; ok && step <= n_tiles; ++step) {
+        if (step < n_tiles) {
+          const int t = step, stage = t % C::NK, slot = t % kBiasSlots;
+          ok = tc::mbar_wait_a(k_empty_a + stage * 8, ((t / C::NK) & 1) ^ 1, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
-          if (!ok) return;
-        }
-        const int P = p.bn >> li;
-        if (lane < 2 * C::SLABS) {
-          unsigned char* dst = sKV + stage * C::KV_BYTES + (op_is_v * C::SLABS + op_slab) * kSlabBytes + fill * 128;
-          tc::tma_load_3d(dst, op_is_v ? &maps.v[li] : &maps.k[li], &ctl->full[stage], op_slab * 64, blk * P, bh);
-        }
-        bytes += 2u * C::SLABS * P * 128u;
-        const int64_t t0 = (int64_t)blk * P;
-        for (int c = lane; c < P; c += 32) sBias[stage * 128 + fill + c] = (t0 + c < p.n[li]) ? bias2 : -INFINITY;
-        fill += P;
-        last_li = li;
-        if (fill == 128) {
+          if (!ok) break;
+          PROF_ADD(0);
+          const uint32_t tile_a = sK_a + stage * C::TILE_BYTES, bar_a = k_full_a + stage * 8;
+          float* bias_row = sBias + slot * 128;
+          uint32_t bytes = 0;
+          for (; ki < n_items; ++ki) {
+            const uint32_t x = sItems[ki];
+            const int tok = (int)(x >> 16) << 2;
+            if ((tok >> 7) != t) break;
+            if (ki % kProducerWarps != warp) continue;
+            const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = tok & 127, row0 = blk * P;
+            if (lane == 0) {
+#pragma unroll
+              for (int sl = 0; sl < C::SLABS; ++sl)
+                tc::tma_load_3d_a(tile_a + sl * kSlabBytes + col * 128, kmap0 + (uint64_t)li * sizeof(CUtensorMap), bar_a, sl * 64, row0, bh);
+            }
+            bytes += (uint32_t)C::SLABS * P * 128u;
+            // logit bias of the block's columns (every producer warp writes the bias of the blocks it issues)
+            const int nl = li == 0 ? n0 : (li == 1 ? n1 : (li == 2 ? n2 : n3));
+            const float qb = li == 0 ? qb0 : (li == 1 ? qb1 : (li == 2 ? qb2 : qb3));
+            const float bias2 = (x & kItemPad) ? -INFINITY : ((x & kItemQuirk) ? qb : (float)li);
+            const int nvalid = nl - row0;
+            for (int c = lane; c < P; c += 32) bias_row[col + c] = c < nvalid ? bias2 : -INFINITY;
+          }
+          if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
+          if (t == n_tiles - 1 && warp == 0) for (int c = last_cols + lane; c < 128; c += 32) bias_row[c] = -INFINITY;
           __syncwarp();
-          if (lane == 0) tc::mbar_arrive_expect_tx(&ctl->full[stage], bytes);
-          ++tile; fill = 0; bytes = 0;
+          if (lane == 0) tc::mbar_arrive_a(b_full_a + slot * 8);
+          PROF_ADD(1);
         }
-      };
-      for (int li = 0; li < 4; ++li) {
-        const int P = p.bn >> li;
-        const int cnt = ctl->seg_cnt[li], start = ctl->seg_start[li];
-        const float bias2 = (float)li;   // log2(level)
-        for (int e = 0; e < cnt; ++e) emit(li, sRow[start + e], bias2);
-        if (p.quirk && P < p.tn && cnt >= 2) {
-          const float qb = bias2 + log2f((float)(cnt / 2));
-          for (int j = 2; j < p.tn / P; ++j) emit(li, j, qb);
+        if (step > 0) {
+          const int t = step - 1, stage = t % C::NV;
+          ok = tc::mbar_wait_a(v_empty_a + stage * 8, ((t / C::NV) & 1) ^ 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          PROF_ADD(2);
+          const uint32_t tile_a = sV_a + stage * C::TILE_BYTES, bar_a = v_full_a + stage * 8;
+          uint32_t bytes = 0;
+          for (; vi < n_items; ++vi) {
+            const uint32_t x = sItems[vi];
+            const int tok = (int)(x >> 16) << 2;
+            if ((tok >> 7) != t) break;
+            if (vi % kProducerWarps != warp) continue;
+            const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = tok & 127;
+            if (lane == 0) {
+#pragma unroll
+              for (int sl = 0; sl < C::SLABS; ++sl)
+                tc::tma_load_3d_a(tile_a + sl * kSlabBytes + col * 128, vmap0 + (uint64_t)li * sizeof(CUtensorMap), bar_a, sl * 64, blk * P, bh);
+            }
+            bytes += (uint32_t)C::SLABS * P * 128u;
+          }
+          if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
+          PROF_ADD(3);
         }
       }
-      if (ok && fill > 0) {
-        while (ok && (fill & 15)) emit(last_li, 0, -INFINITY);   // inert columns up to a multiple of 16
-        if (ok && fill > 0) {
-          const int stage = tile % C::NST;
-          for (int c = fill + lane; c < 128; c += 32) sBias[stage * 128 + c] = -INFINITY;
-          __syncwarp();
-          if (lane == 0) tc::mbar_arrive_expect_tx(&ctl->full[stage], bytes);
-        }
-      }
-    } else if (warp == 1) {
+#ifdef PSA_FWD_PROFILE
+      if (lane == 0 && blockIdx.x == 3 && blockIdx.y == 0) for (int i = 0; i < 4; ++i) g_prof[warp * 4 + i] = prof_acc[i];
+#endif
+    } else if (warp == 3) {
       // ============================================================ MMA issuer
       if (lane == 0) {
         bool ok = tc::mbar_wait(&ctl->q_full, 0, abort_flag);
+        // ready-made descriptors: per tile only the stage offset is added, per MMA only an immediate
         const uint32_t idesc_pv = tc::make_idesc(FMT, 128, D, 0, 1);
-        const uint32_t q_addr = tc::smem_u32(sQ);
-        for (int j = 0; ok && j <= n_tiles; ++j) {
-          if (j < n_tiles) {
-            const int stage = j % C::NST, b = j & 1;
-            const int ncols = j == n_tiles - 1 ? last_cols : 128;
-            ok = tc::mbar_wait(&ctl->full[stage], (j / C::NST) & 1, abort_flag);
-            if (!ok) break;
-            ok = tc::mbar_wait(&ctl->s_empty[b], ((j >> 1) & 1) ^ 1, abort_flag);
-            if (!ok) break;
-            tc::tc_fence_after();
-            const uint32_t k_addr = tc::smem_u32(sKV + stage * C::KV_BYTES);
-            const uint32_t idesc_qk = tc::make_idesc(FMT, 128, ncols, 0, 0);
+        const uint32_t idesc_qk_full = tc::make_idesc(FMT, 128, 128, 0, 0);
+        const uint64_t qdesc = tc::make_smem_desc(tc::smem_u32(sQ), 16, 1024);
+        const uint64_t kdesc0 = tc::make_smem_desc(tc::smem_u32(sK), 16, 1024);
+        const uint64_t vdesc0 = tc::make_smem_desc(tc::smem_u32(sV), kSlabBytes, 1024);
+        const uint32_t ctl_a = tc::smem_u32(ctl);
+        const uint32_t k_full_a = ctl_a + (uint32_t)offsetof(Ctrl, k_full), k_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, k_empty);
+        const uint32_t v_full_a = ctl_a + (uint32_t)offsetof(Ctrl, v_full), v_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, v_empty);
+        const uint32_t s_full_a = ctl_a + (uint32_t)offsetof(Ctrl, s_full), s_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, s_empty);
+        const uint32_t p_full_a = ctl_a + (uint32_t)offsetof(Ctrl, p_full), pv_done_a = ctl_a + (uint32_t)offsetof(Ctrl, pv_done);
+        int qk_next = 0, pv_next = 0;
+        uint32_t idle = 0;
+#ifdef PSA_FWD_PROFILE
+        long long prof_acc[4] = {0, 0, 0, 0};
+        long long n_idle = 0;
+#endif
+        PROF_T0();
+        while (ok && pv_next < n_tiles) {
+          bool progressed = false;
+          if (pv_next < qk_next) {
+            const int t = pv_next, b = t & 1, stage = t % C::NV;
+            if (tc::mbar_try_wait_a(p_full_a + b * 8, (t >> 1) & 1) && tc::mbar_try_wait_a(v_full_a + stage * 8, (t / C::NV) & 1)) {
+              tc::tc_fence_after();
+              const uint64_t vdesc = vdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
+              const uint32_t tP = tmem + 384 + b * 64;
+              if (t < n_tiles - 1 || last_cols == 128) {
+                tc::umma_ts(tO, tP, vdesc, idesc_pv, t > 0 ? 1u : 0u);
 #pragma unroll
-            for (int ks = 0; ks < D / 16; ++ks) {
-              const uint32_t off = (ks >> 2) * kSlabBytes + (ks & 3) * 32;
-              tc::umma_ss(tmem + b * 128, tc::make_smem_desc(q_addr + off, 16, 1024),
-                          tc::make_smem_desc(k_addr + off, 16, 1024), idesc_qk, ks > 0);
+                for (int ks = 1; ks < 8; ++ks) tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * (2048 >> 4)), idesc_pv, 1u);
+              } else {
+                for (int ks = 0; ks < last_cols / 16; ++ks)
+                  tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+              }
+              tc::umma_commit_a(v_empty_a + stage * 8);   // V tile may be refilled
+              tc::umma_commit_a(pv_done_a + b * 8);       // O is consistent again, P buffer b may be rewritten
+              ++pv_next;
+              progressed = true;
+              PROF_ADD(0);
             }
-            tc::umma_commit(&ctl->s_full[b]);
           }
-          if (j > 0) {
-            const int t = j - 1;
-            const int stage = t % C::NST, b = t & 1;
-            const int ncols = t == n_tiles - 1 ? last_cols : 128;
-            ok = tc::mbar_wait(&ctl->p_full[b], (t >> 1) & 1, abort_flag);
-            if (!ok) break;
-            tc::tc_fence_after();
-            const uint32_t v_addr = tc::smem_u32(sKV + stage * C::KV_BYTES + C::SLABS * kSlabBytes);
-            const uint32_t tP = tmem + 384 + b * 64;
-            for (int ks = 0; ks < ncols / 16; ++ks)
-              tc::umma_ts(tO, tP + ks * 8, tc::make_smem_desc(v_addr + ks * 2048, kSlabBytes, 1024), idesc_pv,
-                          (t > 0 || ks > 0) ? 1u : 0u);
-            tc::umma_commit(&ctl->empty[stage]);   // K/V stage may be refilled
-            tc::umma_commit(&ctl->pv_done[b]);     // O is consistent again, P buffer b may be rewritten
+          if (qk_next < n_tiles) {
+            const int t = qk_next, b = t & 1, stage = t % C::NK;
+            if (tc::mbar_try_wait_a(k_full_a + stage * 8, (t / C::NK) & 1) && tc::mbar_try_wait_a(s_empty_a + b * 8, ((t >> 1) & 1) ^ 1)) {
+              tc::tc_fence_after();
+              const uint64_t kdesc = kdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
+              const uint32_t idesc_qk = t == n_tiles - 1 ? tc::make_idesc(FMT, 128, last_cols, 0, 0) : idesc_qk_full;
+              const uint32_t tSb = tmem + b * 128;
+#pragma unroll
+              for (int ks = 0; ks < D / 16; ++ks) {
+                constexpr int dummy = 0; (void)dummy;
+                const uint32_t off = (uint32_t)(((ks >> 2) * kSlabBytes + (ks & 3) * 32) >> 4);
+                tc::umma_ss(tSb, qdesc + off, kdesc + off, idesc_qk, ks > 0 ? 1u : 0u);
+              }
+              tc::umma_commit_a(k_empty_a + stage * 8);   // K tile may be refilled
+              tc::umma_commit_a(s_full_a + b * 8);
+              ++qk_next;
+              progressed = true;
+              PROF_ADD(1);
+            }
           }
+          if (progressed) {
+            idle = 0;
+          } else if (++idle > (1u << 24) || ((idle & 255) == 255 && *abort_flag)) {
+            *abort_flag = 1;
+            ok = false;
+          }
+#ifdef PSA_FWD_PROFILE
+          if (!progressed) {
+            const bool pv_possible = pv_next < qk_next;
+            int slot = 2;
+            if (pv_possible && !tc::mbar_try_wait(&ctl->p_full[pv_next & 1], (pv_next >> 1) & 1)) slot = 2;
+            else if (pv_possible && !tc::mbar_try_wait(&ctl->v_full[pv_next % C::NV], (pv_next / C::NV) & 1)) slot = 3;
+            if (qk_next < n_tiles && !tc::mbar_try_wait(&ctl->k_full[qk_next % C::NK], (qk_next / C::NK) & 1)) ++n_idle;
+            PROF_ADD(slot);
+          }
+#endif
         }
+#ifdef PSA_FWD_PROFILE
+        if (blockIdx.x == 3 && blockIdx.y == 0) { for (int i = 0; i < 4; ++i) g_prof[16 + i] = prof_acc[i]; g_prof[20] = n_idle; g_prof[21] = n_tiles; g_prof[22] = ctl->n_items; }
+#endif
       }
     } else {
       // ============================================================ softmax / epilogue (8 warps, 2 threads per row)
       const int quarter = warp & 3;                 // TMEM lanes this warp may touch
-      const int half = (warp - 2) >> 2;             // which 64 score columns / which half of the O channels
+      const int half = (warp - 4) >> 2;             // which 64 score columns / which half of the O channels
       const int r = quarter * 32 + lane;            // row inside the query block
       const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
       float m_run = -INFINITY, l_run = 0.f;
       bool ok = true;
       for (int j = 0; j < n_tiles; ++j) {
-        const int stage = j % C::NST, b = j & 1;
-        ok = tc::mbar_wait(&ctl->full[stage], (j / C::NST) & 1, abort_flag);   // bias[] of this tile is visible
+        const int slot = j % kBiasSlots, b = j & 1;
+        ok = tc::mbar_wait(&ctl->b_full[slot], (j / kBiasSlots) & 1, abort_flag);   // bias[] of this tile is visible
         ok = ok && tc::mbar_wait(&ctl->s_full[b], (j >> 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -281,8 +414,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         tc::tmem_ld32(tmem + b * 128 + lane_base + half * 64, v0);
         tc::tmem_ld32(tmem + b * 128 + lane_base + half * 64 + 32, v1);
         tc::tmem_wait_ld();
-        tc::tc_fence_before();
-        tc::mbar_arrive(&ctl->s_empty[b]);          // the score buffer is free for tile j+2
         if (j == n_tiles - 1 && last_cols < 128) {  // columns the MMA did not write hold stale bits
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -291,21 +422,25 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           }
         }
         // biased, scaled logits (log2 domain) in place, and their maximum
-        const float4* bias4 = reinterpret_cast<const float4*>(sBias + stage * 128 + half * 64);
-        float mx = -INFINITY;
+        const float4* bias4 = reinterpret_cast<const float4*>(sBias + slot * 128 + half * 64);
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains, not one of 64
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           const float4 ba = bias4[g], bb = bias4[8 + g];
           float x;
-          x = fmaf(__uint_as_float(v0[4 * g + 0]), p.scale_log2, ba.x); v0[4 * g + 0] = __float_as_uint(x); mx = fmaxf(mx, x);
-          x = fmaf(__uint_as_float(v0[4 * g + 1]), p.scale_log2, ba.y); v0[4 * g + 1] = __float_as_uint(x); mx = fmaxf(mx, x);
-          x = fmaf(__uint_as_float(v0[4 * g + 2]), p.scale_log2, ba.z); v0[4 * g + 2] = __float_as_uint(x); mx = fmaxf(mx, x);
-          x = fmaf(__uint_as_float(v0[4 * g + 3]), p.scale_log2, ba.w); v0[4 * g + 3] = __float_as_uint(x); mx = fmaxf(mx, x);
-          x = fmaf(__uint_as_float(v1[4 * g + 0]), p.scale_log2, bb.x); v1[4 * g + 0] = __float_as_uint(x); mx = fmaxf(mx, x);
-          x = fmaf(__uint_as_float(v1[4 * g + 1]), p.scale_log2, bb.y); v1[4 * g + 1] = __float_as_uint(x); mx = fmaxf(mx, x);
-          x = fmaf(__uint_as_float(v1[4 * g + 2]), p.scale_log2, bb.z); v1[4 * g + 2] = __float_as_uint(x); mx = fmaxf(mx, x);
-          x = fmaf(__uint_as_float(v1[4 * g + 3]), p.scale_log2, bb.w); v1[4 * g + 3] = __float_as_uint(x); mx = fmaxf(mx, x);
+          x = fmaf(__uint_as_float(v0[4 * g + 0]), p.scale_log2, ba.x); v0[4 * g + 0] = __float_as_uint(x); mx0 = fmaxf(mx0, x);
+          x = fmaf(__uint_as_float(v0[4 * g + 1]), p.scale_log2, ba.y); v0[4 * g + 1] = __float_as_uint(x); mx1 = fmaxf(mx1, x);
+          x = fmaf(__uint_as_float(v0[4 * g + 2]), p.scale_log2, ba.z); v0[4 * g + 2] = __float_as_uint(x); mx2 = fmaxf(mx2, x);
+          x = fmaf(__uint_as_float(v0[4 * g + 3]), p.scale_log2, ba.w); v0[4 * g + 3] = __float_as_uint(x); mx3 = fmaxf(mx3, x);
+          x = fmaf(__uint_as_float(v1[4 * g + 0]), p.scale_log2, bb.x); v1[4 * g + 0] = __float_as_uint(x); mx0 = fmaxf(mx0, x);
+          x = fmaf(__uint_as_float(v1[4 * g + 1]), p.scale_log2, bb.y); v1[4 * g + 1] = __float_as_uint(x); mx1 = fmaxf(mx1, x);
+          x = fmaf(__uint_as_float(v1[4 * g + 2]), p.scale_log2, bb.z); v1[4 * g + 2] = __float_as_uint(x); mx2 = fmaxf(mx2, x);
+          x = fmaf(__uint_as_float(v1[4 * g + 3]), p.scale_log2, bb.w); v1[4 * g + 3] = __float_as_uint(x); mx3 = fmaxf(mx3, x);
         }
+        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        // score buffer and bias slot are consumed: tile j+2 may overwrite the scores
+        tc::tc_fence_before();
+        tc::mbar_arrive(&ctl->s_empty[b]);
         // the two threads of a row exchange their partial maxima
         float* xch = sXch + (j & 1) * 256;
         xch[half * 128 + r] = mx;
@@ -342,17 +477,18 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         }
         // probabilities (rounded to the element type) -> TMEM, running sum
         const float m_use = m_run == -INFINITY ? 0.f : m_run;
-        float lsum = 0.f;
+        float ls0 = 0.f, ls1 = 0.f;
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const float p0 = ex2(__uint_as_float(v0[i]) - m_use), p1 = ex2(__uint_as_float(v0[i + 1]) - m_use);
           const float p2 = ex2(__uint_as_float(v1[i]) - m_use), p3 = ex2(__uint_as_float(v1[i + 1]) - m_use);
-          lsum += (p0 + p1) + (p2 + p3);
+          ls0 += p0 + p1;
+          ls1 += p2 + p3;
           pk[i >> 1] = pack2<FMT>(p0, p1);
           pk[16 + (i >> 1)] = pack2<FMT>(p2, p3);
         }
-        l_run += lsum;
+        l_run += ls0 + ls1;
         tc::tmem_st32(tmem + 384 + b * 64 + lane_base + half * 32, pk);
         tc::tmem_wait_st();
         tc::tc_fence_before();
@@ -392,9 +528,9 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         }
       }
     }
-  } else if (warp >= 2) {
+  } else if (warp >= 4) {
     // no block selected at all: the reference divides 0 by 0
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 4) >> 2;
     const int64_t qrow = (int64_t)m * 128 + (warp & 3) * 32 + lane;
     if (qrow < p.seq_q) {
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + half * (D / 2);
@@ -411,7 +547,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     for (int i = 0; i < 64; ++i) __nanosleep(1000);   // let copies in flight land before the CTA retires
     __syncthreads();
   }
-  if (warp == 1) {
+  if (warp == 3) {
     __syncwarp();
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem, 512);
@@ -459,6 +595,7 @@ bool fwd_tc_supported(const FwdArgs& a) {
   if (a.D != 64 && a.D != 128) return false;
   if (a.width > kMaxWidth) return false;
   if (a.bh > 65535) return false;
+  if (!(a.scale > 0.f)) return false;
   const void* ptrs[] = {a.q, a.out, a.k[0], a.k[1], a.k[2], a.k[3], a.v[0], a.v[1], a.v[2], a.v[3]};
   for (const void* ptr : ptrs)
     if ((uintptr_t)ptr & 15) return false;
@@ -500,3 +637,9 @@ int fwd_tc_launch(const FwdArgs& a, cudaStream_t st) {
 }
 
 }  // namespace psa
+
+#ifdef PSA_FWD_PROFILE
+extern "C" int psa_debug_read_prof(long long* host64) {
+  return (int)cudaMemcpyFromSymbol(host64, psa::g_prof, sizeof(long long) * 64);
+}
+#endif
