@@ -258,3 +258,36 @@ def test_forward_empty_and_dense_rows(P):
         assert torch.isnan(o[0, 0, :128]).all()
         dense = torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float()).cpu()
         assert float((o[0, 0, 128:] - dense[0, 0, 128:]).abs().max()) < 1e-2
+
+
+# ------------------------------------------------------------------ legacy backward -------------------
+@pytest.mark.parametrize("case", C.LEGACY_CASES, ids=lambda c: c[0])
+def test_legacy_backward_golden(P, golden, case):
+    """dQ/dK/dV of the differentiable legacy factory against the reference's own gradients (fp32)."""
+    name, S, D, H, B, causal, diag1 = case
+    q, k, v = (x.to(DEV).requires_grad_(True) for x in C.qkv(400, B, H, S, D))
+    do = C.randn(404, (B, H, S, D)).to(DEV)
+    mask = C.legacy_mask(405, B, H, S, causal, diag1).to(DEV)
+    fn = P.legacy_sparse_attention_factory(128, 32, 128, causal=causal)
+    out = fn(q, k, v, mask, None)
+    out.backward(do)
+    assert float((C.sub(out.detach().cpu()) - t(golden[f"{name}_out"])).abs().max()) < 2e-5
+    for g, n in ((q.grad, "dq"), (k.grad, "dk"), (v.grad, "dv")):
+        err = float((C.sub(g.cpu()) - t(golden[f"{name}_{n}"])).abs().max())
+        assert err < 5e-5, (n, err)
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+def test_legacy_backward_half_vs_oracle(P, dt):
+    S, D, H, B, causal = 700, 64, 2, 1, True
+    q, k, v = C.qkv(410, B, H, S, D, C.DT[dt])
+    do = C.randn(414, (B, H, S, D), C.DT[dt])
+    mask = C.legacy_mask(415, B, H, S, causal, True)
+    qd, kd, vd = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    out = P.legacy_sparse_attention_factory(128, 32, 128, causal=causal)(qd, kd, vd, mask.to(DEV), None)
+    out.backward(do.to(DEV))
+    o_ref, lse_ref = O.legacy_forward(q, k, v, mask, causal)
+    dq, dk, dv = O.legacy_backward(q, k, v, mask, o_ref, lse_ref, do, causal)
+    for g, r in ((qd.grad, dq), (kd.grad, dk), (vd.grad, dv)):
+        g, r = g.float().cpu(), r.float()
+        assert cosine(g, r) >= COS_OUT and float((g - r).abs().max()) <= 2e-2 * max(1.0, float(r.abs().max()))
