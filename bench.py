@@ -57,7 +57,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                                           "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -184,21 +184,9 @@ def main():
         ik = ops.draw_sample_indices(1, H, BLOCK_N, BLOCK_N // 4, dev)[:, h0:h0 + hp]
         return iq.contiguous(), ik.contiguous()
 
-    def to_head_sharded(x):
-        """[3, S/N, H, D] on every rank -> [3, H/N, S, D] (NCCL all-to-all + local reorder)."""
-        sl = x.shape[1]
-        send = x.view(3, sl, world, hp, D).permute(2, 0, 3, 1, 4).contiguous()                 # [N_dst, 3, hp, S/N, D]
-        recv = torch.empty_like(send)
-        dist.all_to_all_single(recv, send)
-        return recv.permute(1, 2, 0, 3, 4).reshape(3, hp, world * sl, D)                          # [3, hp, S, D]
-
-    def to_seq_sharded(o):
-        """[H/N, S, D] -> [H, S/N, D] on every rank."""
-        sl = S // world
-        send = o.view(hp, world, sl, D).permute(1, 0, 2, 3).contiguous()                         # [N_dst, hp, S/N, D]
-        recv = torch.empty_like(send)
-        dist.all_to_all_single(recv, send)
-        return recv.view(world * hp, sl, D)
+    from psa_b200.parallel import HeadShard
+    shard = HeadShard(world, rank, H, S, D)
+    to_head_sharded, to_seq_sharded = shard.to_head_sharded, shard.to_seq_sharded
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     stage_names = ["a2a_in", "sample", "pyramid", "scores", "assign", "forward", "a2a_out"]

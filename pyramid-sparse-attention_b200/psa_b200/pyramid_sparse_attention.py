@@ -1,0 +1,142 @@
+"""Full-featured PSA module used by the video-model attention processors: same constructor, fields, call contract and
+warm-up rule as PyramidSparseAttention / AttentionConfig (src/psa_triton/pyramid_sparse_attention.py:28-83, 252-413).
+
+Differences, all outside the arithmetic: only the 'Gilbert' rearrangement is built (the k-means / STA / hybrid
+rearrangers are out of scope and raise NotImplementedError), and the sparsity log is an in-memory list (the reference's
+PSALogger writes JSONL files) fed from a device-side density kernel so that logging never forces a host sync per call.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import ops
+from .attention import compute_block_mask
+from .kernels import legacy_sparse_attention_factory, sparse_attention_factory
+from .rearrange import GilbertRearranger
+
+
+@dataclass
+class AttentionConfig:
+    width: int = 45
+    height: int = 30
+    depth: int = 13
+    text_length: int = 226
+    use_rearrange: bool = True
+    block_m: int = 32
+    block_n: int = 32
+    tile_n: int = 32
+    use_sim_mask: bool = True
+    mask_ratios: Dict[int, Tuple[float, float]] = None
+    mask_mode: str = 'topk'
+    warmup_steps: int = 12
+    tile_size: Optional[Tuple[int, int, int]] = None
+    rearrange_method: str = None
+    attn_impl: str = "new_mask_type"
+    verbose: bool = False
+    enable_logging: bool = True
+    log_dir: str = "./psa_logs/"
+    sim_2x_threshold: float = 0
+    sim_4x_threshold: float = 0
+    sim_8x_threshold: float = -1
+
+    def __post_init__(self):
+        if self.mask_ratios is None:
+            self.mask_ratios = {1: (0.0, 0.05), 2: (0.05, 0.15), 4: (0.15, 0.25), 8: (0.25, 0.5), 0: (0.5, 1.0)}
+        if self.attn_impl == "new_mask_type" and self.use_sim_mask:
+            raise ValueError(
+                "Incompatible configuration: 'new_mask_type' does not support 'use_sim_mask=True'.\n"
+                "Please choose one of the following options:\n"
+                "  1. Set 'use_sim_mask: false' to disable similarity mask\n"
+                "  2. Use 'attn_impl: old_mask_type' with block_size config (m=128, n=128, tile_n=32)")
+
+
+class SparsityLog:
+    """Stand-in for PSALogger: one record per forward; densities stay on the device until somebody reads them."""
+
+    def __init__(self):
+        self.records: List[dict] = []
+
+    def log_sparsity(self, **kw):
+        self.records.append(kw)
+
+    def close(self):
+        pass
+
+    def summary(self) -> dict:
+        dens = [float(r["density"].mean().item()) for r in self.records if r.get("density") is not None]
+        return {"calls": len(self.records), "sparse_calls": len(dens),
+                "mean_sparsity": 1.0 - sum(dens) / len(dens) if dens else 0.0}
+
+
+def adaptive_block_sparse_attn(q, k, v, config: AttentionConfig, sparse_attention_fn, compute_stats: bool = False):
+    """Scores -> mask (-> similarity cap) -> sparse attention (pyramid_sparse_attention.py:188-249).
+    Returns (out, density [B,H] device tensor or None, sim_mask)."""
+    if config.attn_impl not in ("old_mask_type", "new_mask_type"):
+        raise ValueError(f"Unknown attn_impl: {config.attn_impl}")
+    with torch.no_grad():
+        mask, _, sim = compute_block_mask(q, k, config, text_length=config.text_length)
+    out = sparse_attention_fn(q.contiguous(), k.contiguous(), v.contiguous(), mask, None)
+    dens = ops.density(mask, config.attn_impl == "new_mask_type") if compute_stats else None
+    return out, dens, sim
+
+
+class PyramidSparseAttention(nn.Module):
+    def __init__(self, config: AttentionConfig = None, inference_num=50, layer_num=42, model_type="wan"):
+        super().__init__()
+        self.config = config if config is not None else AttentionConfig()
+        config = self.config
+        self.model_type = model_type.lower()
+        self.gilbert_rearranger = None
+        if config.use_rearrange:
+            if config.rearrange_method == 'Gilbert':
+                self.gilbert_rearranger = GilbertRearranger(config.width, config.height, config.depth, config.text_length)
+            elif config.rearrange_method in ('SemanticAware', 'STA', 'Hybrid'):
+                raise NotImplementedError(f"rearrange_method={config.rearrange_method!r} is outside this library's scope "
+                                          "(no shipped preset selects it); use 'Gilbert' or use_rearrange=False")
+            else:
+                raise ValueError(f"Unknown rearrange_method: {config.rearrange_method}")
+        self.sparsity_counter = 0
+        self.use_rearrange = config.use_rearrange
+        self.inference_num = inference_num
+        self.layer_num = layer_num
+        if config.attn_impl == "old_mask_type":
+            self.sparse_attention_fn = legacy_sparse_attention_factory(config.block_m, config.tile_n, config.block_n)
+        elif config.attn_impl == "new_mask_type":
+            self.sparse_attention_fn = sparse_attention_factory(config.block_m, config.tile_n, config.block_n)
+        else:
+            raise ValueError(f"Unknown attn_impl: {config.attn_impl}")
+        self.logger = SparsityLog() if config.enable_logging else None
+
+    def get_current_time(self):
+        """Denoising step index: one call per layer for cogvideo / 4-step Wan, two (CFG) passes per step otherwise
+        (pyramid_sparse_attention.py:317-322)."""
+        if self.model_type == "cogvideo" or self.model_type == "wan2.1_1.3b_4steps":
+            return (self.sparsity_counter // self.layer_num) % self.inference_num
+        return (self.sparsity_counter // (2 * self.layer_num)) % self.inference_num
+
+    def forward(self, q, k, v, layer_idx):
+        if self.use_rearrange:
+            q_r, k_r, v_r = self.gilbert_rearranger.rearrange(q, k, v)
+        else:
+            q_r, k_r, v_r = q, k, v
+        is_warmup = self.get_current_time() < self.config.warmup_steps
+        compute_stats = self.config.verbose or self.logger is not None
+        dens = None
+        if is_warmup:
+            # dense warm-up steps, exactly what the reference runs (:353-357)
+            out_r = torch.nn.functional.scaled_dot_product_attention(q_r, k_r, v_r)
+        else:
+            out_r, dens, _ = adaptive_block_sparse_attn(q_r, k_r, v_r, self.config, self.sparse_attention_fn, compute_stats)
+        self.sparsity_counter += 1
+        if self.logger is not None:
+            self.logger.log_sparsity(layer_idx=layer_idx, density=dens, sequence_length=q.shape[2], batch_size=q.shape[0],
+                                     num_heads=q.shape[1], is_warmup=is_warmup)
+        return self.gilbert_rearranger.reversed_rearrange(out_r) if self.use_rearrange else out_r
+
+    def close_logger(self):
+        if self.logger is not None:
+            self.logger.close()

@@ -132,3 +132,12 @@ def legacy_mask(seed, B, H, S, causal, diag1):
     if causal:
         m = m * np.tril(np.ones((n, n), dtype=np.int32))
     return torch.from_numpy(m.astype(np.int32))
+
+
+GILBERT_SHAPES = [(4, 4, 4), (7, 5, 3), (1, 9, 2), (3, 17, 6), (10, 1, 1), (45, 30, 13), (52, 30, 21), (80, 45, 21)]
+
+
+def order_checksum(order) -> int:
+    """Position-weighted checksum of a visiting order (detects any transposition)."""
+    o = np.asarray(order, dtype=np.int64)
+    return int(((np.arange(o.size, dtype=np.int64) % 1000003) * (o % 999983)).sum() % (1 << 61))

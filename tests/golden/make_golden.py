@@ -31,6 +31,7 @@ os.environ["TRITON_INTERPRET"] = "1"
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "pyramid-sparse-attention_b200"))
 sys.path.insert(0, HERE)
 
 import numpy as np
@@ -205,6 +206,20 @@ def main():
         print(f"e2e {name}: oracle vs ref {maxdiff(mine, ref):.3e}")
         out[f"{name}_out"] = C.sub(ref.numpy())
         out[f"{name}_mask"] = mmask.numpy()
+
+    # ---- Gilbert curve order (src/psa_triton/utils/gilbert3d.py via GilbertRearranger) ----------------
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("ref_gilbert3d", os.path.join(args.ref, "src/psa_triton/utils/gilbert3d.py"))
+    g3 = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(g3)
+    from psa_b200.rearrange import gilbert_order
+    for (w, h, d) in C.GILBERT_SHAPES:
+        ref = np.array([x + w * (y + h * z) for x, y, z in g3.gilbert3d(w, h, d)], dtype=np.int64)
+        assert np.array_equal(ref, gilbert_order(w, h, d)), (w, h, d)
+        if ref.size <= 512:
+            out[f"gilbert_{w}x{h}x{d}"] = ref.astype(np.int32)
+        out[f"gilbert_sum_{w}x{h}x{d}"] = np.array([C.order_checksum(ref)], dtype=np.int64)
+    print("gilbert: own curve equals the reference's on", len(C.GILBERT_SHAPES), "grids")
 
     path = os.path.join(HERE, "reference_outputs.npz")
     np.savez_compressed(path, **out)

@@ -291,3 +291,50 @@ def test_legacy_backward_half_vs_oracle(P, dt):
     for g, r in ((qd.grad, dq), (kd.grad, dk), (vd.grad, dv)):
         g, r = g.float().cpu(), r.float()
         assert cosine(g, r) >= COS_OUT and float((g - r).abs().max()) <= 2e-2 * max(1.0, float(r.abs().max()))
+
+
+# ------------------------------------------------------------------ full module (processor-facing) ----------
+def test_pyramid_sparse_attention_module_warmup_then_sparse(P):
+    """PyramidSparseAttention: dense while in warm-up, then Gilbert reorder -> PSA -> inverse reorder; the sparse call
+    equals the oracle composed the same way (same sample offsets through torch's generator)."""
+    from psa_b200.pyramid_sparse_attention import AttentionConfig, PyramidSparseAttention
+    W, Hh, T, H, D = 12, 8, 8, 2, 64                      # 768 video tokens
+    cfg = AttentionConfig(width=W, height=Hh, depth=T, text_length=0, use_rearrange=True, rearrange_method="Gilbert",
+                          block_m=128, block_n=64, tile_n=32, use_sim_mask=False, mask_ratios=C.DEFAULT_RATIOS, mask_mode="topk",
+                          warmup_steps=1, attn_impl="new_mask_type")
+    mod = PyramidSparseAttention(cfg, inference_num=10, layer_num=1, model_type="cogvideo")
+    q, k, v = C.qkv(990, 1, H, W * Hh * T, D, torch.float32)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    dense = mod(qd, kd, vd, 0)                            # step 0: warm-up
+    ref_dense = torch.nn.functional.scaled_dot_product_attention(q, k, v)
+    assert float((dense.cpu() - ref_dense).abs().max()) < 1e-4
+    torch.manual_seed(123)
+    sparse = mod(qd, kd, vd, 0).cpu()                     # step 1: PSA
+    # oracle: same reorder, same draws (device generator -> read the offsets back)
+    torch.manual_seed(123)
+    iq = P.ops.draw_sample_indices(1, H, 128, 32, DEV).cpu()
+    ik = P.ops.draw_sample_indices(1, H, 64, 16, DEV).cpu()
+    qr, kr, vr = mod.gilbert_rearranger.rearrange(q, k, v)
+    o, mask, _ = O.psa_attention(qr, kr, vr, idx_q=iq, idx_k=ik)
+    ref = mod.gilbert_rearranger.reversed_rearrange(o)
+    assert cosine(sparse, ref) > 0.999
+    rec = mod.logger.records
+    assert rec[0]["is_warmup"] and not rec[1]["is_warmup"] and rec[1]["density"].shape == (1, H)
+    assert abs(float(rec[1]["density"].mean()) - O.density_newtype(mask)[0]) < 1e-6
+
+
+def test_old_mask_module_with_similarity_cap(P):
+    """old_mask_type preset path: thresholdbound mask, K-similarity cap (min), text blocks forced to level 1."""
+    from psa_b200.pyramid_sparse_attention import AttentionConfig, PyramidSparseAttention
+    cfg = AttentionConfig(width=8, height=8, depth=10, text_length=0, use_rearrange=False, block_m=128, block_n=128, tile_n=32,
+                          use_sim_mask=True, mask_ratios=C.RATIOS_THR, mask_mode="thresholdbound", warmup_steps=0,
+                          attn_impl="old_mask_type", sim_2x_threshold=0.7, sim_4x_threshold=0.65, sim_8x_threshold=0.6)
+    mod = PyramidSparseAttention(cfg, layer_num=1, model_type="wan")
+    q, k, v = (x.to(DEV) for x in C.qkv(991, 1, 2, 640, 64, torch.bfloat16))
+    torch.manual_seed(5)
+    out = mod(q, k, v, 0)
+    torch.manual_seed(5)
+    mask, po, sim = P.compute_block_mask(q, k, cfg)
+    assert sim is not None and int(mask.max()) <= 8 and int((mask > sim.unsqueeze(-2)).sum()) == 0
+    ref, _ = O.legacy_forward(q.cpu(), k.cpu(), v.cpu(), mask.cpu(), False)
+    assert cosine(out.float().cpu(), ref.float()) > 0.999
