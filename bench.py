@@ -121,6 +121,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="wan2.1-14b-attn-layer")
     ap.add_argument("--sparsity", default="90", choices=["90", "85"])
+    ap.add_argument("--chunks", type=int, default=5, help="head chunks per rank for all-to-all/compute overlap (N>1)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -191,33 +192,62 @@ def main():
     ev = lambda: torch.cuda.Event(enable_timing=True)
     stage_names = ["a2a_in", "sample", "pyramid", "scores", "assign", "forward", "a2a_out"]
 
-    def layer_step(record=None):
-        marks = []
-        mark = (lambda: marks.append(ev()) or marks[-1].record()) if record is not None else (lambda: None)
-        mark()
-        if world > 1:
-            x = to_head_sharded(seq_shard)
-            qq, kk, vv = x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0)
-        else:
-            qq, kk, vv = q, k, v
-        mark()
-        iq, ik = draw_indices()
-        mark()
-        pyr = ops.pyramid_kv(kk, vv, BLOCK_N)
-        mark()
-        po = ops.block_scores(qq, kk, iq, ik, BLOCK_M, BLOCK_N)
-        mark()
-        mask = ops.assign_levels(po, ratios, "topk_newtype", BLOCK_N, TILE_N)
-        mark()
-        out = ops.psa_forward(qq, kk, vv, mask, BLOCK_M, BLOCK_N, TILE_N, pyramid=pyr)
-        mark()
-        if world > 1:
-            out_final = to_seq_sharded(out[0])
-        else:
-            out_final = out
-        mark()
-        if record is not None:
-            record.append(marks)
+    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    chunk_list = shard.chunks(args.chunks) if world > 1 else [(0, hp)]
+
+    def timed(name, fn, rec, stream=None):
+        """Run fn; when rec is a list, bracket it with CUDA events on the stream its kernels are launched on."""
+        if rec is None:
+            return fn()
+        st = stream if stream is not None else torch.cuda.current_stream(dev)
+        a, b = ev(), ev()
+        a.record(st)
+        r = fn()
+        b.record(st)
+        rec.append((name, a, b))
+        return r
+
+    def layer_on(qq, kk, vv, iq, ik, rec):
+        pyr = timed("pyramid", lambda: ops.pyramid_kv(kk, vv, BLOCK_N), rec)
+        po = timed("scores", lambda: ops.block_scores(qq, kk, iq, ik, BLOCK_M, BLOCK_N), rec)
+        mask = timed("assign", lambda: ops.assign_levels(po, ratios, "topk_newtype", BLOCK_N, TILE_N), rec)
+        out = timed("forward", lambda: ops.psa_forward(qq, kk, vv, mask, BLOCK_M, BLOCK_N, TILE_N, pyramid=pyr), rec)
+        return out, mask
+
+    def layer_step(rec=None):
+        """One PSA layer.  N = 1: inputs are already [1, H, S, D].  N > 1: the rank's heads are processed in chunks; the
+        all-to-all of chunk c+1 (and the return of chunk c-1) runs on a second stream under the kernels of chunk c."""
+        iq, ik = timed("sample", draw_indices, rec)
+        if world == 1:
+            out, mask = layer_on(q, k, v, iq, ik, rec)
+            return out, mask, out
+        cur = torch.cuda.current_stream(dev)
+        out_final = torch.empty((H, S // world, D), dtype=dtype, device=dev)
+        comm_stream.wait_stream(cur)
+        arrived = []
+
+        def fetch(ci):
+            with torch.cuda.stream(comm_stream):
+                x = timed("a2a_in", lambda: shard.to_head_sharded_chunk(seq_shard, *chunk_list[ci]), rec, comm_stream)
+                e = ev(); e.record(comm_stream)
+                arrived.append((x, e))
+        fetch(0)
+        mask = out = None
+        for ci, (first, count) in enumerate(chunk_list):
+            if ci + 1 < len(chunk_list):
+                fetch(ci + 1)                                  # prefetch the next chunk's heads under this chunk's kernels
+            x, e_in = arrived[ci]
+            cur.wait_event(e_in)
+            out, mask = layer_on(x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0),
+                                 iq[:, first:first + count].contiguous(), ik[:, first:first + count].contiguous(), rec)
+            x.record_stream(cur)
+            e_done = ev(); e_done.record(cur)
+            with torch.cuda.stream(comm_stream):              # send this chunk's output back
+                comm_stream.wait_event(e_done)
+                o = out[0]
+                timed("a2a_out", lambda: shard.to_seq_sharded_chunk(o, first, out_final), rec, comm_stream)
+                o.record_stream(comm_stream)
+        cur.wait_stream(comm_stream)
         return out_final, mask, out
 
     def barrier():
@@ -248,7 +278,9 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t.item()) / args.steps
-    stage_ms = {n: sum(r[i].elapsed_time(r[i + 1]) for r in records) / len(records) for i, n in enumerate(stage_names)}
+    stage_ms = {n: 0.0 for n in stage_names}        # per step, summed over the chunks of this rank; overlapped stages add up to more than the step
+    for name, a, b in records:
+        stage_ms[name] += a.elapsed_time(b) / args.steps
 
     # ------------------------------------------------------------------ end to end: host buffers in, O back out
     e2e = None

@@ -44,3 +44,36 @@ class HeadShard:
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv, send)
         return recv.view(P * hp, sl, D)
+
+    # ------------------------------------------------------------------ chunked variants (for overlap)
+    def chunks(self, n_chunks: int):
+        """Split this rank's heads into n_chunks equal groups; returns [(first_local_head, heads_in_chunk), ...]."""
+        n_chunks = max(1, min(n_chunks, self.heads_per_rank))
+        while self.heads_per_rank % n_chunks:
+            n_chunks -= 1
+        hc = self.heads_per_rank // n_chunks
+        return [(c * hc, hc) for c in range(n_chunks)]
+
+    def to_head_sharded_chunk(self, x: torch.Tensor, first: int, count: int) -> torch.Tensor:
+        """Like to_head_sharded, but only local heads [first, first+count) of every rank: [n, S/P, H, D] -> [n, count, S, D]."""
+        n, sl, H, D = x.shape
+        hp, P = self.heads_per_rank, self.world
+        send = x.view(n, sl, P, hp, D)[:, :, :, first:first + count].permute(2, 0, 3, 1, 4).contiguous()   # [P, n, count, S/P, D]
+        if P == 1:
+            return send[0].reshape(n, count, sl, D)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send)
+        return recv.permute(1, 2, 0, 3, 4).reshape(n, count, P * sl, D)
+
+    def to_seq_sharded_chunk(self, o: torch.Tensor, first: int, out: torch.Tensor) -> None:
+        """[count, S, D] of local heads [first, first+count) -> rows of out [H, S/P, D] (every rank's same local heads)."""
+        count, S, D = o.shape
+        P, hp = self.world, self.heads_per_rank
+        sl = S // P
+        if P == 1:
+            out[first:first + count] = o
+            return
+        send = o.view(count, P, sl, D).permute(1, 0, 2, 3).contiguous()                 # [P_dst, count, S/P, D]
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send)
+        out.view(P, hp, sl, D)[:, first:first + count] = recv
