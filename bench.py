@@ -122,13 +122,17 @@ def main():
     ap.add_argument("--workload", default="wan2.1-14b-attn-layer")
     ap.add_argument("--sparsity", default="90", choices=["90", "85"])
     ap.add_argument("--chunks", type=int, default=5, help="head chunks per rank for all-to-all/compute overlap (N>1)")
+    ap.add_argument("--heads", type=int, default=0, help="override the head count (smaller captures for profilers)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
     from psa_b200 import synthetic
-    workload = synthetic.WORKLOADS[args.workload]
+    workload = dict(synthetic.WORKLOADS[args.workload])
+    if args.heads:
+        workload["heads"] = args.heads
+        workload["name"] += f"-{args.heads}heads"
     ratios = RATIOS_90 if args.sparsity == "90" else DEFAULT_RATIOS
     H, D, S = workload["heads"], workload["head_dim"], synthetic.seq_len(workload)
     rank = int(os.environ.get("RANK", "0"))
