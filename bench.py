@@ -212,7 +212,8 @@ def main():
         return r
 
     def layer_on(qq, kk, vv, iq, ik, rec):
-        pyr = timed("pyramid", lambda: ops.pyramid_kv(kk, vv, BLOCK_N), rec)
+        build = ops.pyramid_kv_images if ops.images_supported(kk, BLOCK_M, BLOCK_N, TILE_N) else ops.pyramid_kv
+        pyr = timed("pyramid", lambda: build(kk, vv, BLOCK_N), rec)
         po = timed("scores", lambda: ops.block_scores(qq, kk, iq, ik, BLOCK_M, BLOCK_N), rec)
         mask = timed("assign", lambda: ops.assign_levels(po, ratios, "topk_newtype", BLOCK_N, TILE_N), rec)
         out = timed("forward", lambda: ops.psa_forward(qq, kk, vv, mask, BLOCK_M, BLOCK_N, TILE_N, pyramid=pyr), rec)

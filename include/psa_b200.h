@@ -46,6 +46,16 @@ const char* psa_build_info(void);
 int psa_pyramid_kv(const void* k, const void* v, void* k2, void* k4, void* k8, void* v2, void* v4, void* v8,
                    int64_t bh, int64_t seq, int head_dim, int block_n, int dtype, void* stream);
 
+/* Pyramid K/V builder, tile-image form (f16/bf16, head_dim 64/128, block_n a multiple of 64).  Same source lines of
+ * the reference as psa_pyramid_kv; the output LAYOUT is this library's own: per operand one buffer of
+ * psa_kv_image_bytes() bytes (16-byte aligned) holding levels 1, 2, 4, 8 one after the other, each level as
+ * [BH][8-row group][64-channel slab][8 rows][128 B] with the 16-byte chunks of a row XOR-ed by (row & 7) - the image
+ * of the 128-byte-swizzled shared-memory tile the tensor cores read, so that a block of pooled rows is one contiguous
+ * range.  Values are those of psa_pyramid_kv (level 1 = the input rows, tail rows replicate the last token). */
+size_t psa_kv_image_bytes(int64_t bh, int64_t seq, int head_dim, int block_n);
+int psa_pyramid_kv_images(const void* k, const void* v, void* kimg, void* vimg, int64_t bh, int64_t seq, int head_dim,
+                          int block_n, int dtype, void* stream);
+
 /* Block-importance scores.  Replaces _random_sample_tokens' gather + replicate padding
  * (src/psa_triton/attention.py:128-137, 195-196, 214-215), attn_with_pooling_optimized
  * (src/psa_triton/kernels/attn_pooling_kernel.py:119-431) and the slice at attention.py:223.
@@ -114,6 +124,13 @@ int psa_fwd(const void* q, const void* k, const void* v, const void* k2, const v
             const void* v2, const void* v4, const void* v8, const int32_t* mask, void* out, int64_t bh,
             int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width,
             float sm_scale, int compat_quirk, int impl, int dtype, int32_t* status, void* stream);
+
+/* The same forward (tcgen05 kernel only) reading K/V from the tile images of psa_pyramid_kv_images: every selected
+ * block is fetched with one linear bulk copy per operand instead of one tensor-map TMA operation per 64-channel
+ * slab.  Replaces the same reference code as psa_fwd. */
+int psa_fwd_images(const void* q, const void* kimg, const void* vimg, const int32_t* mask, void* out, int64_t bh,
+                   int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width,
+                   float sm_scale, int compat_quirk, int dtype, int32_t* status, void* stream);
 
 /* Legacy forward on the dense old-format mask, optional causal.  Replaces _fwd_kernel / _forward,
  * src/psa_triton/kernels/psa_kernel_legacy.py:415-799, 837-938 (block sizes fixed 128/32/128, :1333-1351).

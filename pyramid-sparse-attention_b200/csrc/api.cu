@@ -45,7 +45,7 @@ extern "C" int psa_fwd(const void* q, const void* k, const void* v, const void* 
   const int64_t nl[4] = {seq_k, s_pad / 2, s_pad / 4, s_pad / 8};
   cudaStream_t st = (cudaStream_t)stream;
   FwdArgs a;
-  a.q = q; a.mask = mask; a.out = out; a.status = status;
+  a.q = q; a.mask = mask; a.out = out; a.status = status; a.kimg = nullptr; a.vimg = nullptr;
   for (int i = 0; i < 4; ++i) { a.k[i] = kl[i]; a.v[i] = vl[i]; a.n[i] = nl[i]; }
   a.bh = bh; a.seq_q = seq_q; a.seq_k = seq_k; a.D = head_dim; a.bm = block_m; a.bn = block_n; a.tn = tile_n;
   a.width = mask_width; a.scale = sm_scale; a.quirk = compat_quirk; a.dtype = dtype;
@@ -72,4 +72,24 @@ extern "C" int psa_legacy_fwd(const void* q, const void* k, const void* v, const
   const int64_t nl[4] = {seq, s_pad / 2, s_pad / 4, s_pad / 8};
   return legacy_fwd_simt_dispatch(q, kl, vl, nl, mask, out, lse, bh, seq, head_dim, mask_cols, sm_scale, causal, dtype,
                                   (cudaStream_t)stream);
+}
+
+extern "C" int psa_fwd_images(const void* q, const void* kimg, const void* vimg, const int32_t* mask, void* out, int64_t bh,
+                              int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width,
+                              float sm_scale, int compat_quirk, int dtype, int32_t* status, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(q && kimg && vimg && mask && out, PSA_ERR_ARG, "psa_fwd_images: null pointer");
+  PSA_REQUIRE(bh > 0 && bh < 65536 && seq_q > 0 && seq_k > 0, PSA_ERR_ARG, "psa_fwd_images: bad shape");
+  PSA_REQUIRE(block_n == 64 || block_n == 128, PSA_ERR_UNSUPPORTED, "psa_fwd_images: block_n=%d (64/128)", block_n);
+  PSA_REQUIRE(mask_width >= 1, PSA_ERR_ARG, "psa_fwd_images: mask_width=%d", mask_width);
+  const int64_t s_pad = cdiv64(seq_k, block_n) * block_n;
+  FwdArgs a;
+  a.q = q; a.mask = mask; a.out = out; a.status = status; a.kimg = kimg; a.vimg = vimg;
+  const int64_t nl[4] = {seq_k, s_pad / 2, s_pad / 4, s_pad / 8};
+  for (int i = 0; i < 4; ++i) { a.k[i] = q; a.v[i] = q; a.n[i] = nl[i]; }   // row-major levels are not read in image mode
+  a.bh = bh; a.seq_q = seq_q; a.seq_k = seq_k; a.D = head_dim; a.bm = block_m; a.bn = block_n; a.tn = tile_n;
+  a.width = mask_width; a.scale = sm_scale; a.quirk = compat_quirk; a.dtype = dtype;
+  PSA_REQUIRE(fwd_tc_supported(a), PSA_ERR_UNSUPPORTED,
+              "psa_fwd_images: needs f16/bf16, block_m=128, tile_n=32, head_dim 64/128, mask width <= 4064");
+  return fwd_tc_launch(a, (cudaStream_t)stream);
 }

@@ -5,11 +5,33 @@
 
 namespace psa {
 
+// Placement of the four levels inside one operand's tile-image buffer (see pyramid.cu): level li starts at off[li] and
+// holds, per (batch*head), groups[li] groups of 8 rows, each group = [64-channel slab][8 rows][128 B].
+struct ImgLevels {
+  int64_t off[4];
+  int64_t groups[4];
+};
+
+inline ImgLevels make_img_levels(int64_t bh, int64_t seq, int D, int block_n) {
+  ImgLevels L;
+  const int64_t s_pad = (seq + block_n - 1) / block_n * block_n;
+  int64_t off = 0;
+  for (int li = 0; li < 4; ++li) {
+    const int64_t rows = s_pad >> li;
+    L.groups[li] = (rows + 7) / 8;
+    L.off[li] = off;
+    off += bh * L.groups[li] * (int64_t)(D / 64) * 1024;
+  }
+  return L;
+}
+
 struct FwdArgs {
   const void* q;
   const void* k[4];  // levels 1, 2, 4, 8
   const void* v[4];
   int64_t n[4];      // tokens per head at each level
+  const void* kimg;  // tile images of K and V (all four levels), or null
+  const void* vimg;
   const int32_t* mask;
   void* out;
   int32_t* status;

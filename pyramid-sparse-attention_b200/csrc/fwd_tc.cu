@@ -55,6 +55,10 @@ struct TcParams {
   int64_t n[4];
   int mq, bn, tn, width, quirk;
   float scale_log2;   // sm_scale * log2(e)
+  // tile-image mode: K/V of all levels pre-laid-out as shared-memory images (one linear bulk copy per block)
+  const unsigned char* kimg;
+  const unsigned char* vimg;
+  ImgLevels img;
 };
 
 template <int D> struct Cfg {
@@ -73,8 +77,8 @@ template <int D> struct Cfg {
 };
 
 struct Ctrl {
-  uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4], b_full[kBiasSlots];
-  uint64_t s_full[2], s_empty[2], p_full[2], pv_done[2], q_full;
+  uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
+  uint64_t s_full[2], p_full[2], pv_done[2], q_full;
   uint32_t tmem_base;
   int abort_flag;
   int n_sep;
@@ -116,7 +120,9 @@ namespace {
 #define PROF_ADD(slot)
 #endif
 
-template <int D, int FMT>
+// IMG = true: K/V tiles use the image layout [8-row group][slab][8 rows][128 B] and are filled by linear bulk copies from
+// the tile-image buffers; IMG = false: [slab][128 rows][128 B] filled by tensor-map TMA boxes from row-major tensors.
+template <int D, int FMT, bool IMG>
 __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_constant__ TmapPack maps, const TcParams p) {
   using C = Cfg<D>;
   extern __shared__ unsigned char smem_dyn[];
@@ -141,10 +147,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       tc::mbar_init(&ctl->k_full[i], kProducerWarps); tc::mbar_init(&ctl->k_empty[i], 1);
       tc::mbar_init(&ctl->v_full[i], kProducerWarps); tc::mbar_init(&ctl->v_empty[i], 1);
     }
-    for (int i = 0; i < kBiasSlots; ++i) tc::mbar_init(&ctl->b_full[i], kProducerWarps);
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&ctl->s_full[i], 1);
-      tc::mbar_init(&ctl->s_empty[i], kSoftmaxThreads);
       tc::mbar_init(&ctl->p_full[i], kSoftmaxThreads);
       tc::mbar_init(&ctl->pv_done[i], 1);
     }
@@ -238,12 +242,14 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       const uint32_t ctl_a = tc::smem_u32(ctl);
       const uint32_t k_full_a = ctl_a + (uint32_t)offsetof(Ctrl, k_full), k_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, k_empty);
       const uint32_t v_full_a = ctl_a + (uint32_t)offsetof(Ctrl, v_full), v_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, v_empty);
-      const uint32_t b_full_a = ctl_a + (uint32_t)offsetof(Ctrl, b_full);
       const uint32_t sK_a = tc::smem_u32(sK), sV_a = tc::smem_u32(sV);
       const uint64_t kmap0 = reinterpret_cast<uint64_t>(&maps.k[0]), vmap0 = reinterpret_cast<uint64_t>(&maps.v[0]);
       const int n0 = (int)p.n[0], n1 = (int)p.n[1], n2 = (int)p.n[2], n3 = (int)p.n[3];
       const float qb0 = ctl->qbias2[0], qb1 = ctl->qbias2[1], qb2 = ctl->qbias2[2], qb3 = ctl->qbias2[3];
-      int ki = 0, vi = 0;              // next item of the K pass / V pass; item i is issued by warp i % 3
+      // The items of a tile are consecutive table entries (at most 32: blocks are at least 4 tokens wide).  Lane l of
+      // producer warp w takes entry first + 3*l + w, so address arithmetic, bias and copy issue of all the blocks of a
+      // tile run side by side instead of one block after the other.
+      int ki = 0, vi = 0;              // first item of the next K tile / V tile
       bool ok = true;
       // step s gathers K tile s and then V tile s-1: K runs one tile ahead of V
       for (int step = 0; ok && step <= n_tiles; ++step) {
@@ -255,30 +261,54 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           PROF_ADD(0);
           const uint32_t tile_a = sK_a + stage * C::TILE_BYTES, bar_a = k_full_a + stage * 8;
           float* bias_row = sBias + slot * 128;
-          uint32_t bytes = 0;
-          for (; ki < n_items; ++ki) {
-            const uint32_t x = sItems[ki];
-            const int tok = (int)(x >> 16) << 2;
-            if ((tok >> 7) != t) break;
-            if (ki % kProducerWarps != warp) continue;
-            const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = tok & 127, row0 = blk * P;
-            if (lane == 0) {
+          const int probe = ki + lane;
+          const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sItems[probe < n_items ? probe : 0] >> 21) == t));
+          const bool active = 3 * lane + warp < in_tile;
+          const uint32_t x = active ? sItems[ki + 3 * lane + warp] : 0u;
+          const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = ((int)(x >> 16) << 2) & 127, row0 = blk * P;
+          // logit bias of the block's columns
+          const int nl = li == 0 ? n0 : (li == 1 ? n1 : (li == 2 ? n2 : n3));
+          const float qb = li == 0 ? qb0 : (li == 1 ? qb1 : (li == 2 ? qb2 : qb3));
+          const float bias2 = (x & kItemPad) ? -INFINITY : ((x & kItemQuirk) ? qb : (float)li);
+          const int nvalid = nl - row0;
+          uint32_t my_bytes = 0;
+          if (active) {
+            if (IMG) {
+              const unsigned char* src = p.kimg + p.img.off[li] + (((int64_t)bh * p.img.groups[li] + (row0 >> 3)) * C::SLABS << 10);
+              tc::bulk_load_a(tile_a + (col >> 3) * (C::SLABS * 1024), src, (uint32_t)(P * D * 2), bar_a);
+            } else {
 #pragma unroll
               for (int sl = 0; sl < C::SLABS; ++sl)
                 tc::tma_load_3d_a(tile_a + sl * kSlabBytes + col * 128, kmap0 + (uint64_t)li * sizeof(CUtensorMap), bar_a, sl * 64, row0, bh);
             }
-            bytes += (uint32_t)C::SLABS * P * 128u;
-            // logit bias of the block's columns (every producer warp writes the bias of the blocks it issues)
-            const int nl = li == 0 ? n0 : (li == 1 ? n1 : (li == 2 ? n2 : n3));
-            const float qb = li == 0 ? qb0 : (li == 1 ? qb1 : (li == 2 ? qb2 : qb3));
-            const float bias2 = (x & kItemPad) ? -INFINITY : ((x & kItemQuirk) ? qb : (float)li);
-            const int nvalid = nl - row0;
-            for (int c = lane; c < P; c += 32) bias_row[col + c] = c < nvalid ? bias2 : -INFINITY;
+            my_bytes = (uint32_t)C::SLABS * P * 128u;
+            if (P <= 16) {   // narrow block: its lane writes the few bias words itself
+              float4* dst = reinterpret_cast<float4*>(bias_row + col);
+              for (int c = 0; c < P; c += 4)
+                dst[c >> 2] = make_float4(c < nvalid ? bias2 : -INFINITY, c + 1 < nvalid ? bias2 : -INFINITY,
+                                          c + 2 < nvalid ? bias2 : -INFINITY, c + 3 < nvalid ? bias2 : -INFINITY);
+            }
           }
-          if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
+          // wide blocks (at most 4 per tile): the whole warp writes the bias, 4 columns per lane
+          unsigned wide = __ballot_sync(0xffffffffu, active && P > 16);
+          while (wide) {
+            const int src_lane = __ffs(wide) - 1;
+            wide &= wide - 1;
+            const int w_col = __shfl_sync(0xffffffffu, col, src_lane), w_P = __shfl_sync(0xffffffffu, P, src_lane);
+            const int w_nv = __shfl_sync(0xffffffffu, nvalid, src_lane);
+            const float w_b = __shfl_sync(0xffffffffu, bias2, src_lane);
+            const int c = lane * 4;
+            if (c < w_P)
+              *reinterpret_cast<float4*>(bias_row + w_col + c) =
+                  make_float4(c < w_nv ? w_b : -INFINITY, c + 1 < w_nv ? w_b : -INFINITY, c + 2 < w_nv ? w_b : -INFINITY,
+                              c + 3 < w_nv ? w_b : -INFINITY);
+          }
+          ki += in_tile;
+          // the bias of this tile must be complete before the tile is announced: the softmax warps read it once the
+          // scores are ready, and "scores ready" follows "K tile full" through the MMA issuer
           if (t == n_tiles - 1 && warp == 0) for (int c = last_cols + lane; c < 128; c += 32) bias_row[c] = -INFINITY;
-          __syncwarp();
-          if (lane == 0) tc::mbar_arrive_a(b_full_a + slot * 8);
+          const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
+          if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
           PROF_ADD(1);
         }
         if (step > 0) {
@@ -288,20 +318,25 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           if (!ok) break;
           PROF_ADD(2);
           const uint32_t tile_a = sV_a + stage * C::TILE_BYTES, bar_a = v_full_a + stage * 8;
-          uint32_t bytes = 0;
-          for (; vi < n_items; ++vi) {
-            const uint32_t x = sItems[vi];
-            const int tok = (int)(x >> 16) << 2;
-            if ((tok >> 7) != t) break;
-            if (vi % kProducerWarps != warp) continue;
-            const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = tok & 127;
-            if (lane == 0) {
+          const int probe = vi + lane;
+          const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sItems[probe < n_items ? probe : 0] >> 21) == t));
+          const int mine = vi + 3 * lane + warp;
+          uint32_t my_bytes = 0;
+          if (3 * lane + warp < in_tile) {
+            const uint32_t x = sItems[mine];
+            const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = ((int)(x >> 16) << 2) & 127;
+            if (IMG) {
+              const unsigned char* src = p.vimg + p.img.off[li] + (((int64_t)bh * p.img.groups[li] + ((blk * P) >> 3)) * C::SLABS << 10);
+              tc::bulk_load_a(tile_a + (col >> 3) * (C::SLABS * 1024), src, (uint32_t)(P * D * 2), bar_a);
+            } else {
 #pragma unroll
               for (int sl = 0; sl < C::SLABS; ++sl)
                 tc::tma_load_3d_a(tile_a + sl * kSlabBytes + col * 128, vmap0 + (uint64_t)li * sizeof(CUtensorMap), bar_a, sl * 64, blk * P, bh);
             }
-            bytes += (uint32_t)C::SLABS * P * 128u;
+            my_bytes = (uint32_t)C::SLABS * P * 128u;
           }
+          vi += in_tile;
+          const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
           if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
           PROF_ADD(3);
         }
@@ -317,12 +352,15 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         const uint32_t idesc_pv = tc::make_idesc(FMT, 128, D, 0, 1);
         const uint32_t idesc_qk_full = tc::make_idesc(FMT, 128, 128, 0, 0);
         const uint64_t qdesc = tc::make_smem_desc(tc::smem_u32(sQ), 16, 1024);
-        const uint64_t kdesc0 = tc::make_smem_desc(tc::smem_u32(sK), 16, 1024);
-        const uint64_t vdesc0 = tc::make_smem_desc(tc::smem_u32(sV), kSlabBytes, 1024);
+        // image layout: 8-row groups are SLABS KiB apart and the slabs of a group follow each other
+        constexpr uint32_t kGroupStride = IMG ? C::SLABS * 1024 : 1024;
+        constexpr uint32_t kSlabStride = IMG ? 1024 : kSlabBytes;
+        const uint64_t kdesc0 = tc::make_smem_desc(tc::smem_u32(sK), 16, kGroupStride);
+        const uint64_t vdesc0 = tc::make_smem_desc(tc::smem_u32(sV), kSlabStride, kGroupStride);
         const uint32_t ctl_a = tc::smem_u32(ctl);
         const uint32_t k_full_a = ctl_a + (uint32_t)offsetof(Ctrl, k_full), k_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, k_empty);
         const uint32_t v_full_a = ctl_a + (uint32_t)offsetof(Ctrl, v_full), v_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, v_empty);
-        const uint32_t s_full_a = ctl_a + (uint32_t)offsetof(Ctrl, s_full), s_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, s_empty);
+        const uint32_t s_full_a = ctl_a + (uint32_t)offsetof(Ctrl, s_full);
         const uint32_t p_full_a = ctl_a + (uint32_t)offsetof(Ctrl, p_full), pv_done_a = ctl_a + (uint32_t)offsetof(Ctrl, pv_done);
         int qk_next = 0, pv_next = 0;
         uint32_t idle = 0;
@@ -342,10 +380,10 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
               if (t < n_tiles - 1 || last_cols == 128) {
                 tc::umma_ts(tO, tP, vdesc, idesc_pv, t > 0 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 1; ks < 8; ++ks) tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * (2048 >> 4)), idesc_pv, 1u);
+                for (int ks = 1; ks < 8; ++ks) tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, 1u);
               } else {
                 for (int ks = 0; ks < last_cols / 16; ++ks)
-                  tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+                  tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
               }
               tc::umma_commit_a(v_empty_a + stage * 8);   // V tile may be refilled
               tc::umma_commit_a(pv_done_a + b * 8);       // O is consistent again, P buffer b may be rewritten
@@ -354,9 +392,12 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
               PROF_ADD(0);
             }
           }
-          if (qk_next < n_tiles) {
+          // S = Q K^T of tile t is only issued once P V of tile t-2 has been: the tensor pipe runs in issue order, so
+          // "S_t ready" then also means that the softmax warps are done with score buffer t&1 (they filled P_{t-2})
+          // and that P V of tile t-2 has finished reading P buffer t&1
+          if (qk_next < n_tiles && qk_next <= pv_next + 1) {
             const int t = qk_next, b = t & 1, stage = t % C::NK;
-            if (tc::mbar_try_wait_a(k_full_a + stage * 8, (t / C::NK) & 1) && tc::mbar_try_wait_a(s_empty_a + b * 8, ((t >> 1) & 1) ^ 1)) {
+            if (tc::mbar_try_wait_a(k_full_a + stage * 8, (t / C::NK) & 1)) {
               tc::tc_fence_after();
               const uint64_t kdesc = kdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
               const uint32_t idesc_qk = t == n_tiles - 1 ? tc::make_idesc(FMT, 128, last_cols, 0, 0) : idesc_qk_full;
@@ -364,8 +405,9 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
 #pragma unroll
               for (int ks = 0; ks < D / 16; ++ks) {
                 constexpr int dummy = 0; (void)dummy;
-                const uint32_t off = (uint32_t)(((ks >> 2) * kSlabBytes + (ks & 3) * 32) >> 4);
-                tc::umma_ss(tSb, qdesc + off, kdesc + off, idesc_qk, ks > 0 ? 1u : 0u);
+                const uint32_t qoff = (uint32_t)(((ks >> 2) * kSlabBytes + (ks & 3) * 32) >> 4);
+                const uint32_t koff = (uint32_t)(((ks >> 2) * kSlabStride + (ks & 3) * 32) >> 4);
+                tc::umma_ss(tSb, qdesc + qoff, kdesc + koff, idesc_qk, ks > 0 ? 1u : 0u);
               }
               tc::umma_commit_a(k_empty_a + stage * 8);   // K tile may be refilled
               tc::umma_commit_a(s_full_a + b * 8);
@@ -403,17 +445,25 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
       float m_run = -INFINITY, l_run = 0.f;
       bool ok = true;
+#ifdef PSA_FWD_PROFILE
+      long long sprof[6] = {0, 0, 0, 0, 0, 0};
+      long long sprof_t = clock64();
+#define SPROF(i) do { long long t1_ = clock64(); sprof[i] += t1_ - sprof_t; sprof_t = t1_; } while (0)
+#else
+#define SPROF(i)
+#endif
       for (int j = 0; j < n_tiles; ++j) {
         const int slot = j % kBiasSlots, b = j & 1;
-        ok = tc::mbar_wait(&ctl->b_full[slot], (j / kBiasSlots) & 1, abort_flag);   // bias[] of this tile is visible
-        ok = ok && tc::mbar_wait(&ctl->s_full[b], (j >> 1) & 1, abort_flag);
+        ok = tc::mbar_wait(&ctl->s_full[b], (j >> 1) & 1, abort_flag);   // scores ready (and the tile's bias[] visible)
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        SPROF(0);
         tc::tc_fence_after();
         uint32_t v0[32], v1[32];
         tc::tmem_ld32(tmem + b * 128 + lane_base + half * 64, v0);
         tc::tmem_ld32(tmem + b * 128 + lane_base + half * 64 + 32, v1);
         tc::tmem_wait_ld();
+        SPROF(1);
         if (j == n_tiles - 1 && last_cols < 128) {  // columns the MMA did not write hold stale bits
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -438,13 +488,11 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           x = fmaf(__uint_as_float(v1[4 * g + 3]), p.scale_log2, bb.w); v1[4 * g + 3] = __float_as_uint(x); mx3 = fmaxf(mx3, x);
         }
         float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        // score buffer and bias slot are consumed: tile j+2 may overwrite the scores
-        tc::tc_fence_before();
-        tc::mbar_arrive(&ctl->s_empty[b]);
         // the two threads of a row exchange their partial maxima
         float* xch = sXch + (j & 1) * 256;
         xch[half * 128 + r] = mx;
         tc::named_bar_sync(1 + quarter, 64);
+        SPROF(2);
         mx = fmaxf(mx, xch[(half ^ 1) * 128 + r]);
         // raise the running maximum only when it is far off (or still unset); both threads of a row agree
         float alpha = 1.f;
@@ -454,10 +502,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           m_run = mx;
           l_run *= alpha;
         }
-        // P buffer b was last read by the P V of tile j-2
-        ok = tc::mbar_wait(&ctl->pv_done[b], ((j >> 1) & 1) ^ 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
         if (j > 0 && __any_sync(0xffffffffu, raise)) {
           // O may only be touched between two P V products: wait for the one of tile j-1
           ok = tc::mbar_wait(&ctl->pv_done[b ^ 1], ((j - 1) >> 1) & 1, abort_flag);
@@ -476,6 +520,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           tc::tmem_wait_st();
         }
         // probabilities (rounded to the element type) -> TMEM, running sum
+        SPROF(4);
         const float m_use = m_run == -INFINITY ? 0.f : m_run;
         float ls0 = 0.f, ls1 = 0.f;
         uint32_t pk[32];
@@ -493,7 +538,11 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         tc::tmem_wait_st();
         tc::tc_fence_before();
         tc::mbar_arrive(&ctl->p_full[b]);
+        SPROF(5);
       }
+#ifdef PSA_FWD_PROFILE
+      if (threadIdx.x == 128 && blockIdx.x == 3 && blockIdx.y == 0) for (int i = 0; i < 6; ++i) g_prof[32 + i] = sprof[i];
+#endif
       // epilogue
       if (ok) {
         const int t = n_tiles - 1;
@@ -602,14 +651,14 @@ bool fwd_tc_supported(const FwdArgs& a) {
   return true;
 }
 
-template <int D, int FMT>
+template <int D, int FMT, bool IMG>
 static int launch_tc(const FwdArgs& a, cudaStream_t st) {
   using C = Cfg<D>;
   TmapPack maps;
   const int is_bf16 = FMT == 1;
   int rc = encode_tmap_3d(&maps.q, a.q, 2, is_bf16, D, a.seq_q, a.bh, 128);
   if (rc != PSA_OK) return rc;
-  for (int li = 0; li < 4; ++li) {
+  for (int li = 0; li < 4 && !IMG; ++li) {
     const int P = a.bn >> li;
     rc = encode_tmap_3d(&maps.k[li], a.k[li], 2, is_bf16, D, a.n[li], a.bh, P);
     if (rc != PSA_OK) return rc;
@@ -621,19 +670,28 @@ static int launch_tc(const FwdArgs& a, cudaStream_t st) {
   for (int i = 0; i < 4; ++i) p.n[i] = a.n[i];
   p.mq = (int)cdiv64(a.seq_q, 128); p.bn = a.bn; p.tn = a.tn; p.width = a.width; p.quirk = a.quirk;
   p.scale_log2 = a.scale * 1.4426950408889634f;
-  cudaError_t e = cudaFuncSetAttribute(psa_fwd_tc_kernel<D, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  p.kimg = (const unsigned char*)a.kimg; p.vimg = (const unsigned char*)a.vimg;
+  p.img = make_img_levels(a.bh, a.seq_k, D, IMG ? a.bn : 64);
+  cudaError_t e = cudaFuncSetAttribute(psa_fwd_tc_kernel<D, FMT, IMG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   PSA_REQUIRE(e == cudaSuccess, PSA_ERR_CUDA, "psa_fwd: shared-memory opt-in (%d B) failed: %s", C::SMEM_BYTES,
               cudaGetErrorString(e));
   dim3 grid(p.mq, (unsigned)a.bh);
-  psa_fwd_tc_kernel<D, FMT><<<grid, kThreads, C::SMEM_BYTES, st>>>(maps, p);
+  psa_fwd_tc_kernel<D, FMT, IMG><<<grid, kThreads, C::SMEM_BYTES, st>>>(maps, p);
   PSA_CHECK_LAUNCH("psa_fwd(tcgen05)");
   return PSA_OK;
 }
 
 int fwd_tc_launch(const FwdArgs& a, cudaStream_t st) {
   const int fmt = a.dtype == PSA_BF16 ? 1 : 0;
-  if (a.D == 64) return fmt ? launch_tc<64, 1>(a, st) : launch_tc<64, 0>(a, st);
-  return fmt ? launch_tc<128, 1>(a, st) : launch_tc<128, 0>(a, st);
+  const bool img = a.kimg != nullptr && a.vimg != nullptr;
+  if (img) {
+    PSA_REQUIRE(a.bn >= 64, PSA_ERR_UNSUPPORTED, "tile images need block_n >= 64 (blocks of at least 8 pooled rows)");
+    PSA_REQUIRE((((uintptr_t)a.kimg | (uintptr_t)a.vimg) & 15) == 0, PSA_ERR_ARG, "tile images must be 16-byte aligned");
+    if (a.D == 64) return fmt ? launch_tc<64, 1, true>(a, st) : launch_tc<64, 0, true>(a, st);
+    return fmt ? launch_tc<128, 1, true>(a, st) : launch_tc<128, 0, true>(a, st);
+  }
+  if (a.D == 64) return fmt ? launch_tc<64, 1, false>(a, st) : launch_tc<64, 0, false>(a, st);
+  return fmt ? launch_tc<128, 1, false>(a, st) : launch_tc<128, 0, false>(a, st);
 }
 
 }  // namespace psa

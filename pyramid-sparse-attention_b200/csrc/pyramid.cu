@@ -9,6 +9,7 @@
 // size-2 dimension does, and stores 7 x 16 B.  Consecutive threads take consecutive 16-byte chunks of
 // the same token group, so every warp access covers whole 128-byte lines.
 #include "psa_common.cuh"
+#include "fwd.h"
 
 namespace psa {
 
@@ -99,5 +100,98 @@ extern "C" int psa_pyramid_kv(const void* k, const void* v, void* k2, void* k4, 
     PSA_REQUIRE(((uintptr_t)ptrs[i] & 15) == 0, PSA_ERR_ARG, "psa_pyramid_kv: pointer %d is not 16-byte aligned", i);
   cudaStream_t st = (cudaStream_t)stream;
   PSA_DISPATCH_DTYPE(dtype, T, return launch_pyramid<T>(k, v, k2, k4, k8, v2, v4, v8, bh, seq, head_dim, block_n, st));
+  return PSA_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Tile-image variant for the tensor-core forward (16-bit element types).
+//
+// The forward gathers blocks of P = block_n/level pooled rows into 128-byte-swizzled shared-memory tiles.  Fetching a
+// block from a row-major tensor needs one tensor-map TMA operation per 64-channel slab, and the TMA issue rate (about
+// one operation per 100 cycles per SM) bounds tiles made of narrow blocks.  Here every level - level 1 included - is
+// written in HBM exactly as its shared-memory image: groups of 8 rows, each group = [slab][8 rows][128 B] with the
+// 16-byte chunks of a row XOR-ed by (row & 7).  A block then is one contiguous range of P*D*2 bytes and one linear
+// bulk copy.  Algorithmic bytes: read K,V once (2 N e), write levels 1,2,4,8 (3.75 N e).
+namespace psa {
+
+template <typename T>
+__device__ __forceinline__ void img_store(unsigned char* base, int64_t bh, int64_t groups, int slabs, int64_t row, int c, const uint4& val) {
+  const int64_t g = row >> 3;
+  const int r = (int)(row & 7);
+  unsigned char* p = base + ((bh * groups + g) * slabs + (c >> 3)) * 1024 + r * 128 + (((c & 7) ^ r) << 4);
+  *reinterpret_cast<uint4*>(p) = val;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) pyramid_img_kernel(const T* __restrict__ k, const T* __restrict__ v, unsigned char* __restrict__ kimg,
+                                                          unsigned char* __restrict__ vimg, ImgLevels L, int64_t bh, int64_t S, int64_t n8,
+                                                          int cpr) {
+  const T* x = blockIdx.y ? v : k;
+  unsigned char* img = blockIdx.y ? vimg : kimg;
+  const int slabs = cpr / 8;
+  const int64_t total = bh * n8 * cpr;
+  for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(w % cpr);
+    const int64_t g = w / cpr;
+    const int64_t head = g / n8;
+    const int64_t j = g % n8;
+    const uint4* src = reinterpret_cast<const uint4*>(x) + head * S * cpr + c;
+    uint4 r[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      int64_t tok = j * 8 + t;
+      tok = tok < S ? tok : S - 1;
+      r[t] = __ldg(src + tok * cpr);
+    }
+    uint4 a[4], b[2], d;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) pair_mean<T>(r[2 * t], r[2 * t + 1], a[t]);
+    pair_mean<T>(a[0], a[1], b[0]);
+    pair_mean<T>(a[2], a[3], b[1]);
+    pair_mean<T>(b[0], b[1], d);
+#pragma unroll
+    for (int t = 0; t < 8; ++t) img_store<T>(img + L.off[0], head, L.groups[0], slabs, j * 8 + t, c, r[t]);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) img_store<T>(img + L.off[1], head, L.groups[1], slabs, j * 4 + t, c, a[t]);
+    img_store<T>(img + L.off[2], head, L.groups[2], slabs, j * 2, c, b[0]);
+    img_store<T>(img + L.off[2], head, L.groups[2], slabs, j * 2 + 1, c, b[1]);
+    img_store<T>(img + L.off[3], head, L.groups[3], slabs, j, c, d);
+  }
+}
+
+}  // namespace psa
+
+extern "C" size_t psa_kv_image_bytes(int64_t bh, int64_t seq, int head_dim, int block_n) {
+  if (bh <= 0 || seq <= 0 || (head_dim != 64 && head_dim != 128) || block_n < 64 || block_n % 64) return 0;
+  psa::ImgLevels L = psa::make_img_levels(bh, seq, head_dim, block_n);
+  return (size_t)(L.off[3] + bh * L.groups[3] * (head_dim / 64) * 1024);
+}
+
+extern "C" int psa_pyramid_kv_images(const void* k, const void* v, void* kimg, void* vimg, int64_t bh, int64_t seq, int head_dim,
+                                     int block_n, int dtype, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(k && v && kimg && vimg, PSA_ERR_ARG, "psa_pyramid_kv_images: null pointer");
+  PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "psa_pyramid_kv_images: 16-bit element types only");
+  PSA_REQUIRE(psa_kv_image_bytes(bh, seq, head_dim, block_n) > 0, PSA_ERR_ARG,
+              "psa_pyramid_kv_images: needs head_dim 64/128 and block_n a multiple of 64 (got %d, %d)", head_dim, block_n);
+  // the swizzle phase of an image row depends only on its offset inside the image, so 16 bytes (bulk-copy source
+  // alignment) is all the base needs
+  PSA_REQUIRE((((uintptr_t)k | (uintptr_t)v | (uintptr_t)kimg | (uintptr_t)vimg) & 15) == 0, PSA_ERR_ARG,
+              "psa_pyramid_kv_images: k, v and the images must be 16-byte aligned");
+  const ImgLevels L = make_img_levels(bh, seq, head_dim, block_n);
+  const int64_t s_pad = cdiv64(seq, block_n) * block_n;
+  const int64_t n8 = s_pad / 8;
+  const int cpr = head_dim * 2 / 16;
+  int64_t blocks = cdiv64(bh * n8 * cpr, 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  dim3 grid((unsigned)blocks, 2);
+  if (dtype == PSA_F16)
+    pyramid_img_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>((const __half*)k, (const __half*)v, (unsigned char*)kimg,
+                                                                       (unsigned char*)vimg, L, bh, seq, n8, cpr);
+  else
+    pyramid_img_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+                                                                              (unsigned char*)kimg, (unsigned char*)vimg, L, bh, seq, n8,
+                                                                              cpr);
+  PSA_CHECK_LAUNCH("psa_pyramid_kv_images");
   return PSA_OK;
 }

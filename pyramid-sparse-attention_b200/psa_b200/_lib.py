@@ -29,6 +29,9 @@ SIGNATURES = {
     "psa_last_error_string": (C.c_char_p, []),
     "psa_build_info": (C.c_char_p, []),
     "psa_pyramid_kv": (_i, [_p] * 8 + [_i64, _i64, _i, _i, _i, _p]),
+    "psa_kv_image_bytes": (_sz, [_i64, _i64, _i, _i]),
+    "psa_pyramid_kv_images": (_i, [_p] * 4 + [_i64, _i64, _i, _i, _i, _p]),
+    "psa_fwd_images": (_i, [_p] * 5 + [_i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]),
     "psa_block_scores_scratch_bytes": (_sz, [_i64, _i64, _i64, _i, _i, _i]),
     "psa_block_scores": (_i, [_p] * 6 + [_sz, _i64, _i64, _i64, _i, _i, _i, _i, _i, _p]),
     "psa_block_scores_static_capacity": (_sz, []),

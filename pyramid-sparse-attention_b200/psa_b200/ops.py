@@ -57,6 +57,35 @@ def pyramid_kv(k: torch.Tensor, v: torch.Tensor, block_n: int):
     return (k2, k4, k8), (v2, v4, v8)
 
 
+class KVImages:
+    """K/V of all four levels in the tile-image layout the tcgen05 forward copies from (see psa_pyramid_kv_images)."""
+
+    def __init__(self, kimg: torch.Tensor, vimg: torch.Tensor, block_n: int):
+        self.kimg, self.vimg, self.block_n = kimg, vimg, block_n
+
+
+def images_supported(k: torch.Tensor, block_m: int, block_n: int, tile_n: int) -> bool:
+    return (k.dtype in (torch.float16, torch.bfloat16) and block_m == 128 and tile_n == 32 and block_n in (64, 128)
+            and k.shape[-1] in (64, 128))
+
+
+def pyramid_kv_images(k: torch.Tensor, v: torch.Tensor, block_n: int) -> KVImages:
+    """One pass over K and V -> tile images of levels 1/2/4/8 (f16/bf16, block_n 64/128)."""
+    _need_cuda(k, v)
+    assert k.shape == v.shape and k.dtype == v.dtype
+    k, v = _flat_bh(k), _flat_bh(v)
+    B, H, S, D = k.shape
+    nbytes = lib.psa_kv_image_bytes(B * H, S, D, block_n)
+    if nbytes == 0:
+        raise ValueError(f"tile images need head_dim 64/128 and block_n 64/128 (got {D}, {block_n})")
+    with torch.cuda.device(k.device):
+        kimg = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
+        vimg = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
+        rc = lib.psa_pyramid_kv_images(_ptr(k), _ptr(v), _ptr(kimg), _ptr(vimg), B * H, S, D, block_n, _dt(k), _stream(k))
+    check(rc, "psa_pyramid_kv_images")
+    return KVImages(kimg, vimg, block_n)
+
+
 def draw_sample_indices(B: int, H: int, block: int, keep: int, device) -> torch.Tensor:
     """topk(rand(B,H,1,block), keep).indices: the same two torch calls, in the same order on the same
     generator, as _random_sample_tokens (src/psa_triton/attention.py:132-133)."""
@@ -211,6 +240,20 @@ def psa_forward(q, k, v, mask, block_m: int, block_n: int, tile_n: int, sm_scale
     Sk = k.shape[2]
     if sm_scale is None:
         sm_scale = D ** -0.5
+    use_images = isinstance(pyramid, KVImages) or (pyramid is None and impl == IMPL_AUTO and mask.shape[-1] <= 4064
+                                                   and images_supported(k, block_m, block_n, tile_n) and sm_scale > 0)
+    if use_images:
+        if pyramid is None:
+            pyramid = pyramid_kv_images(k, v, block_n)
+        with torch.cuda.device(q.device):
+            o = out if out is not None else torch.empty_like(q)
+            status = torch.zeros(1, dtype=torch.int32, device=q.device)
+            rc = lib.psa_fwd_images(_ptr(q), _ptr(pyramid.kimg), _ptr(pyramid.vimg), _ptr(mask), _ptr(o), B * H, Sq, Sk, D,
+                                    block_m, block_n, tile_n, mask.shape[-1], float(sm_scale), int(compat_quirk), _dt(q),
+                                    _ptr(status), _stream(q))
+        check(rc, "psa_fwd_images")
+        o._psa_status = status
+        return o
     if pyramid is None:
         pyramid = pyramid_kv(k, v, block_n)
     (k2, k4, k8), (v2, v4, v8) = pyramid

@@ -338,3 +338,54 @@ def test_old_mask_module_with_similarity_cap(P):
     assert sim is not None and int(mask.max()) <= 8 and int((mask > sim.unsqueeze(-2)).sum()) == 0
     ref, _ = O.legacy_forward(q.cpu(), k.cpu(), v.cpu(), mask.cpu(), False)
     assert cosine(out.float().cpu(), ref.float()) > 0.999
+
+
+# ------------------------------------------------------------------ tile images ---------------------------
+def _unswizzle_image(img, bh, rows, D):
+    """[BH][group][slab][8 rows][8 chunks of 16 B] with chunk index XOR (row & 7) -> plain [BH, rows, D] (16-bit words)."""
+    slabs = D // 64
+    groups = (rows + 7) // 8
+    x = img.view(torch.int16).view(bh, groups, slabs, 8, 8, 8).cpu()          # [..., row, stored chunk, 8 elements]
+    r = torch.arange(8).view(8, 1)
+    c = torch.arange(8).view(1, 8)
+    src = (c ^ r)                                                               # logical chunk c of row r sits at c ^ r
+    y = torch.gather(x, 4, src.view(1, 1, 1, 8, 8, 1).expand(bh, groups, slabs, 8, 8, 8))
+    y = y.permute(0, 1, 3, 2, 4, 5).reshape(bh, groups * 8, D)                  # [BH, rows_pad, slab*64 + chunk*8 + e]
+    return y[:, :rows]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+@pytest.mark.parametrize("S,D,bn", [(333, 64, 64), (1000, 128, 64), (257, 128, 128), (64, 64, 64)])
+def test_tile_images_hold_the_pyramid_values(P, dt, S, D, bn):
+    B, H = 1, 3
+    k = C.randn(21, (B, H, S, D), C.DT[dt]).to(DEV)
+    v = C.randn(22, (B, H, S, D), C.DT[dt]).to(DEV)
+    imgs = P.ops.pyramid_kv_images(k, v, bn)
+    (k2, k4, k8), (v2, v4, v8) = P.ops.pyramid_kv(k, v, bn)
+    s_pad = -(-S // bn) * bn
+    for img, plain in ((imgs.kimg, (k, k2, k4, k8)), (imgs.vimg, (v, v2, v4, v8))):
+        off = 0
+        for li, ref in enumerate(plain):
+            rows = s_pad >> li
+            nbytes = B * H * ((rows + 7) // 8) * (D // 64) * 1024
+            got = _unswizzle_image(img[off:off + nbytes], B * H, rows, D)
+            ref16 = ref.reshape(B * H, -1, D).view(torch.int16).cpu()
+            n = ref16.shape[1]                       # level 1: S rows (the tail of the image replicates the last token)
+            assert torch.equal(got[:, :n], ref16), (li,)
+            off += nbytes
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+@pytest.mark.parametrize("case", [c for c in C.FWD_CASES if c[5] >= 64], ids=lambda c: c[0])
+def test_forward_tile_image_path_vs_oracle(P, golden, case, dt):
+    name, S, D, H, bm, bn, tn, mode, rn = case
+    q, k, v = C.qkv(200, 1, H, S, D, C.DT[dt])
+    mask = t(golden[f"{name}_mask"])
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    imgs = P.ops.pyramid_kv_images(kd, vd, bn)
+    out = P.ops.psa_forward(qd, kd, vd, mask.to(DEV), bm, bn, tn, pyramid=imgs)
+    assert int(out._psa_status.item()) == 0
+    plain = P.ops.psa_forward(qd, kd, vd, mask.to(DEV), bm, bn, tn, impl=P.ops.IMPL_TENSOR)
+    assert torch.equal(out, plain)               # same arithmetic, only the K/V fetch differs
+    ref = O.psa_forward_newmask(q, k, v, mask, bm, bn, tn).float()
+    assert float((out.float().cpu() - ref).abs().max()) <= ATOL_OUT and cosine(out.float().cpu(), ref) >= COS_OUT
