@@ -30,38 +30,10 @@ __device__ __forceinline__ float key_value(uint32_t hi) {
   return __uint_as_float(u);
 }
 
+// Everything after the sort: keys[] holds the row in rank order (score key << 32 | block index); s_cnt is zeroed.
 template <typename T>
-__global__ void __launch_bounds__(256) assign_levels_kernel(const T* __restrict__ po, int32_t* __restrict__ mask,
-                                                           AssignParams p) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem_raw);
-  float* ratio = reinterpret_cast<float*>(keys + p.npow2);  // threshold mode only
-  __shared__ int s_start[PSA_MAX_LEVELS], s_end[PSA_MAX_LEVELS];
-  __shared__ int s_cnt[PSA_MAX_LEVELS];
-
-  const int64_t row = blockIdx.x;
-  const T* src = po + row * p.nk;
-  const int tid = threadIdx.x, nt = blockDim.x;
-
-  for (int i = tid; i < p.npow2; i += nt)
-    keys[i] = i < p.nk ? (((unsigned long long)desc_key(Elem<T>::to_f(src[i])) << 32) | (unsigned)i) : ~0ull;
-  if (tid < PSA_MAX_LEVELS) s_cnt[tid] = 0;
-  __syncthreads();
-
-  for (int k = 2; k <= p.npow2; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int i = tid; i < p.npow2; i += nt) {
-        int ixj = i ^ j;
-        if (ixj > i) {
-          unsigned long long a = keys[i], b = keys[ixj];
-          bool asc = (i & k) == 0;
-          if ((a > b) == asc) { keys[i] = b; keys[ixj] = a; }
-        }
-      }
-      __syncthreads();
-    }
-  }
-
+__device__ __forceinline__ void emit_mask_row(const unsigned long long* keys, float* ratio, int* s_start, int* s_end, int* s_cnt,
+                                              int32_t* __restrict__ mask, const AssignParams& p, int64_t row, int tid, int nt) {
   if (p.threshold_mode) {
     if (tid == 0) {
       if (sizeof(T) == 4) {
@@ -143,6 +115,125 @@ __global__ void __launch_bounds__(256) assign_levels_kernel(const T* __restrict_
   }
 }
 
+// General kernel (any score type, any row length up to 8192): bitonic network over 64-bit keys in shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256) assign_levels_kernel(const T* __restrict__ po, int32_t* __restrict__ mask,
+                                                           AssignParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem_raw);
+  float* ratio = reinterpret_cast<float*>(keys + p.npow2);  // threshold mode only
+  __shared__ int s_start[PSA_MAX_LEVELS], s_end[PSA_MAX_LEVELS];
+  __shared__ int s_cnt[PSA_MAX_LEVELS];
+
+  const int64_t row = blockIdx.x;
+  const T* src = po + row * p.nk;
+  const int tid = threadIdx.x, nt = blockDim.x;
+
+  for (int i = tid; i < p.npow2; i += nt)
+    keys[i] = i < p.nk ? (((unsigned long long)desc_key(Elem<T>::to_f(src[i])) << 32) | (unsigned)i) : ~0ull;
+  if (tid < PSA_MAX_LEVELS) s_cnt[tid] = 0;
+  __syncthreads();
+
+  for (int k = 2; k <= p.npow2; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = tid; i < p.npow2; i += nt) {
+        int ixj = i ^ j;
+        if (ixj > i) {
+          unsigned long long a = keys[i], b = keys[ixj];
+          bool asc = (i & k) == 0;
+          if ((a > b) == asc) { keys[i] = b; keys[ixj] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  emit_mask_row<T>(keys, ratio, s_start, s_end, s_cnt, mask, p, row, tid, nt);
+}
+
+// Fast kernel for 16-bit scores and rows of at most 4096 blocks: the key fits 32 bits (16 score bits, 16 index bits),
+// every thread keeps E consecutive keys in registers, and the network's exchanges run in registers (distance < E),
+// through warp shuffles (distance < 32 E) or through shared memory (only the last few stages).
+template <typename T, int E>
+__global__ void __launch_bounds__(256) assign_levels_reg_kernel(const T* __restrict__ po, int32_t* __restrict__ mask,
+                                                               AssignParams p) {
+  constexpr int N = E * 256;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned long long* keys = reinterpret_cast<unsigned long long*>(smem_raw);
+  float* ratio = reinterpret_cast<float*>(keys + N);          // threshold mode; doubles as exchange buffer during the sort
+  uint32_t* xch = reinterpret_cast<uint32_t*>(ratio);
+  __shared__ int s_start[PSA_MAX_LEVELS], s_end[PSA_MAX_LEVELS];
+  __shared__ int s_cnt[PSA_MAX_LEVELS];
+
+  const int64_t row = blockIdx.x;
+  const unsigned short* src = reinterpret_cast<const unsigned short*>(po + row * p.nk);
+  const int tid = threadIdx.x;
+  if (tid < PSA_MAX_LEVELS) s_cnt[tid] = 0;
+
+  uint32_t a[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const int i = tid * E + e;
+    uint32_t key = 0xffffffffu;
+    if (i < p.nk) {
+      uint32_t b = src[i];
+      if (b == 0x8000u) b = 0;                                             // -0 -> +0
+      const uint32_t ord = (b & 0x8000u) ? (~b & 0xffffu) : (b | 0x8000u);   // ascending order of the values
+      key = ((~ord & 0xffffu) << 16) | (uint32_t)i;                        // descending value, then ascending index
+    }
+    a[e] = key;
+  }
+#pragma unroll
+  for (int k = 2; k <= N; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      if (j >= 32 * E) {
+        // partner lives in another warp: same lane, same e
+#pragma unroll
+        for (int e = 0; e < E; ++e) xch[e * 256 + tid] = a[e];
+        __syncthreads();
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const int i = tid * E + e;
+          const uint32_t pv = xch[e * 256 + (tid ^ (j / E))];
+          const bool take_min = ((i & j) == 0) == ((i & k) == 0);
+          a[e] = take_min ? min(a[e], pv) : max(a[e], pv);
+        }
+        __syncthreads();
+      } else if (j >= E) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const int i = tid * E + e;
+          const uint32_t pv = __shfl_xor_sync(0xffffffffu, a[e], j / E);
+          const bool take_min = ((i & j) == 0) == ((i & k) == 0);
+          a[e] = take_min ? min(a[e], pv) : max(a[e], pv);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          if ((e & j) == 0) {
+            const int i = tid * E + e;
+            const uint32_t lo = min(a[e], a[e | j]), hi = max(a[e], a[e | j]);
+            const bool asc = (i & k) == 0;
+            a[e] = asc ? lo : hi;
+            a[e | j] = asc ? hi : lo;
+          }
+        }
+      }
+    }
+  }
+  // back to the common key format, in rank order
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const uint32_t ord = ~(a[e] >> 16) & 0xffffu;
+    const uint32_t b = (ord & 0x8000u) ? (ord & 0x7fffu) : (~ord & 0xffffu);
+    const unsigned short raw = (unsigned short)b;
+    const float v = Elem<T>::to_f(*reinterpret_cast<const T*>(&raw));
+    keys[tid * E + e] = a[e] == 0xffffffffu ? ~0ull : (((unsigned long long)desc_key(v) << 32) | (a[e] & 0xffffu));
+  }
+  __syncthreads();
+  emit_mask_row<T>(keys, ratio, s_start, s_end, s_cnt, mask, p, row, tid, 256);
+}
+
 // ------------------------------------------------------------------------------ density -------------
 // One CTA per (batch, head); a warp walks one mask row at a time.  Deterministic summation order.
 __global__ void __launch_bounds__(256) density_kernel(const int32_t* __restrict__ mask, float* __restrict__ per_bh,
@@ -214,9 +305,34 @@ extern "C" int psa_assign_levels(const void* po, int32_t* mask, int64_t rows, in
       PSA_REQUIRE(p.start[i] >= 0 && p.start[i] <= p.end[i] && p.end[i] <= nk, PSA_ERR_ARG,
                   "psa_assign_levels: interval %d = [%d,%d) outside [0,%d]", i, p.start[i], p.end[i], nk);
   }
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((dtype == PSA_F16 || dtype == PSA_BF16) && nk <= 4096) {
+    // register-resident sort: E keys per thread, 256 threads
+    const int E = np2 <= 512 ? 2 : np2 / 256;
+    p.npow2 = E * 256;
+    const size_t smem_reg = (size_t)E * 256 * 12;
+#define PSA_ASSIGN_REG(TT, EE)                                                                                              \
+  do {                                                                                                                     \
+    if (smem_reg > 40 * 1024) {                                                                                            \
+      cudaError_t e = cudaFuncSetAttribute(assign_levels_reg_kernel<TT, EE>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           (int)smem_reg);                                                                 \
+      PSA_REQUIRE(e == cudaSuccess, PSA_ERR_CUDA, "psa_assign_levels: smem opt-in failed: %s", cudaGetErrorString(e));     \
+    }                                                                                                                      \
+    assign_levels_reg_kernel<TT, EE><<<(unsigned)rows, 256, smem_reg, st>>>((const TT*)po, mask, p);                       \
+  } while (0)
+#define PSA_ASSIGN_REG_E(TT)                                                                  \
+  do {                                                                                       \
+    if (E == 2) PSA_ASSIGN_REG(TT, 2); else if (E == 4) PSA_ASSIGN_REG(TT, 4);               \
+    else if (E == 8) PSA_ASSIGN_REG(TT, 8); else PSA_ASSIGN_REG(TT, 16);                     \
+  } while (0)
+    if (dtype == PSA_F16) PSA_ASSIGN_REG_E(__half); else PSA_ASSIGN_REG_E(__nv_bfloat16);
+#undef PSA_ASSIGN_REG_E
+#undef PSA_ASSIGN_REG
+    PSA_CHECK_LAUNCH("psa_assign_levels");
+    return PSA_OK;
+  }
   size_t smem = (size_t)np2 * 8 + (threshold_mode ? (size_t)nk * 4 : 0);
   int threads = np2 / 2 < 256 ? (np2 / 2 < 32 ? 32 : np2 / 2) : 256;
-  cudaStream_t st = (cudaStream_t)stream;
   PSA_DISPATCH_DTYPE(dtype, T, {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(assign_levels_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

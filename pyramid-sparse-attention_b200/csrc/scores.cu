@@ -102,7 +102,11 @@ __global__ void __launch_bounds__(256) scores_cellmax_simt(const T* __restrict__
 
 // ---------------------------------------------------------------- stage B -------------------------
 // CTA per (query block r, bh).  Dynamic smem: n_d floats.
-template <typename T>
+template <typename T, int VEC>
+struct alignas(VEC * sizeof(T)) CellPack { T e[VEC]; };
+
+// VEC neighbouring cells per thread and load; the launcher picks the widest VEC (<= 8 bytes) that divides n_d.
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) scores_pool_normalise(const T* __restrict__ R, const float* __restrict__ rowmax,
                                                             T* __restrict__ po, ScoreDims d) {
   extern __shared__ float sm_po[];
@@ -112,16 +116,39 @@ __global__ void __launch_bounds__(256) scores_pool_normalise(const T* __restrict
   const int64_t rbase = (int64_t)bh * d.nq_s + (int64_t)r * d.kq;
   if (threadIdx.x < d.kq) s_rowmax[threadIdx.x] = rowmax[rbase + threadIdx.x];
   __syncthreads();
+  // exp2 is monotone, so the pooled maximum of exp2(x - m_t) is exp2 of the maximum of (x - m_t): one exp2 per cell.
+  // A thread owns VEC neighbouring cells and walks the block's sampled rows.
+  using Pack = CellPack<T, VEC>;
   float part = 0.f;
-  for (int c = threadIdx.x; c < d.n_d; c += blockDim.x) {
-    float best = 0.f;
-    for (int t = 0; t < d.kq; ++t) {
-      float x = Elem<T>::to_f(R[(rbase + t) * d.n_d + c]);
-      best = fmaxf(best, exp2f(x - s_rowmax[t]));
+  for (int c = threadIdx.x * VEC; c < d.n_d; c += blockDim.x * VEC) {
+    float best[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) best[v] = -INFINITY;
+    const T* col = R + rbase * d.n_d + c;
+    int t = 0;
+    for (; t + 8 <= d.kq; t += 8) {
+      Pack raw[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) raw[u] = *reinterpret_cast<const Pack*>(col + (int64_t)(t + u) * d.n_d);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float m = s_rowmax[t + u];
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) best[v] = fmaxf(best[v], Elem<T>::to_f(raw[u].e[v]) - m);
+      }
     }
-    best = Elem<T>::round(best);
-    sm_po[c] = best;
-    part += best;
+    for (; t < d.kq; ++t) {
+      const Pack raw = *reinterpret_cast<const Pack*>(col + (int64_t)t * d.n_d);
+      const float m = s_rowmax[t];
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) best[v] = fmaxf(best[v], Elem<T>::to_f(raw.e[v]) - m);
+    }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const float b = Elem<T>::round(exp2f(best[v]));
+      sm_po[c + v] = b;
+      part += b;
+    }
   }
   for (int off = 16; off; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = part;
@@ -152,7 +179,11 @@ static int launch_scores(const void* q, const void* k, const int32_t* idx_q, con
     PSA_CHECK_LAUNCH("psa_block_scores(stage A)");
   }
   dim3 gridb((unsigned)d.Mq, (unsigned)bh);
-  scores_pool_normalise<T><<<gridb, 256, d.n_d * sizeof(float), st>>>(R, rowmax, (T*)po, d);
+  // n_d is a multiple of 64 / (block_n / 4), i.e. of 2 at least; R itself is 256-byte aligned
+  constexpr int kWide = 8 / (int)sizeof(T);
+  if (d.n_d % kWide == 0) scores_pool_normalise<T, kWide><<<gridb, 256, d.n_d * sizeof(float), st>>>(R, rowmax, (T*)po, d);
+  else if (d.n_d % 2 == 0) scores_pool_normalise<T, 2><<<gridb, 256, d.n_d * sizeof(float), st>>>(R, rowmax, (T*)po, d);
+  else scores_pool_normalise<T, 1><<<gridb, 256, d.n_d * sizeof(float), st>>>(R, rowmax, (T*)po, d);
   PSA_CHECK_LAUNCH("psa_block_scores(stage B)");
   return PSA_OK;
 }

@@ -97,7 +97,7 @@ def test_assign_levels_golden(P, golden, case):
         assert np.allclose(d[0].numpy(), golden[key][1:], atol=1e-6)
 
 
-@pytest.mark.parametrize("dt", ["fp32", "bf16"])
+@pytest.mark.parametrize("dt", ["fp32", "bf16", "fp16"])
 @pytest.mark.parametrize("mode", ["topk_newtype", "thresholdbound_newtype", "topk", "thresholdbound"])
 @pytest.mark.parametrize("Nk,bn", [(512, 64), (1182, 64), (2363, 32), (1, 64), (5, 128)])
 def test_assign_levels_oracle_large(P, dt, mode, Nk, bn):
