@@ -1,24 +1,29 @@
 // Multi-level block-sparse flash-attention forward on tcgen05 tensor cores (f16/bf16, block_m = 128).
 //
 // One CTA per (128-row query block, batch*head), 12 warps:
-//   warps 0-2   producers: walk the block's index list and gather the selected K/V blocks of every pyramid level into
-//               128-token tiles, PACKING blocks of different levels into the same tile.  A block is P = block_n/level
-//               contiguous pooled rows, fetched with one TMA box {64 ch, P rows} per 64-channel slab (128-byte
-//               swizzle, never multicast).  A TMA operation costs its issuing thread ~150 cycles whatever its size,
-//               so the blocks of a tile are dealt round-robin to the three warps, which issue concurrently.
-//               K tiles and V tiles live in separate rings (K is released after S = Q K^T, V after O += P V)
-//               and K runs one tile ahead of V.  Warp 0 also writes the per-column logit bias (log2 of the level,
-//               -inf for columns that do not exist) and loads the Q tile.
-//   warp 3      MMA issuer: S = Q K^T (operands in shared memory) into one of two TMEM score buffers, and
-//               O += P V with P read from TMEM and V read MN-major from its swizzled tile.  It polls both kinds of
-//               work and issues whichever is ready, so a K/V tile that is still in flight never delays a product
-//               whose operands are there.
-//   warps 4-11  softmax: two threads per query row, 64 columns each.  One TMEM read of the row half into registers,
-//               row maximum exchanged through shared memory, exp2, running sum in fp32, probabilities rounded to the
-//               element type and stored to one of two TMEM P buffers.  The running maximum is only raised when the
-//               new maximum exceeds it by more than 2^8 ("lazy" rescale); raising it rescales the O accumulator in
-//               TMEM.  Epilogue: O / sum -> global.
-// TMEM (512 columns): S0 [0,128), S1 [128,256), O [256,256+D), P0 [384,448), P1 [448,512).
+//   warps 0-2   producers: decode the block's index list into a flat item table, then gather the selected K/V blocks of
+//               every pyramid level into 128-token tiles, PACKING blocks of different levels into the same tile.  A
+//               block is P = block_n/level contiguous pooled rows.  From tile images it is ONE linear bulk copy per
+//               operand; from row-major tensors one TMA box {64 ch, P rows} per 64-channel slab (128-byte swizzle).
+//               Never multicast.  A copy costs its issuing thread 150-200 cycles whatever its size, so the blocks of a
+//               tile are spread over the lanes of all three warps (lane l of warp w takes block 3l+w), which decode and
+//               issue side by side.  K tiles and V tiles live in separate rings (K is released after S = Q K^T, V after
+//               O += P V) and K runs one tile ahead of V.  The producers also write the logit bias of the tile's
+//               columns (log2 of the level, -inf for columns that do not exist), per column and per group of 4 columns.
+//   warp 3      MMA issuer (one thread): S = Q K^T (operands in shared memory) into one of two TMEM score buffers, and
+//               O += P V with P read from TMEM and V read MN-major from its swizzled tile.  Descriptors are built once;
+//               per MMA only an immediate is added.  It polls (non-blocking) for whichever product is ready and issues in
+//               the fixed order QK0 QK1 PV0 QK2 PV1 ...; the tensor pipe runs in issue order, so "S of tile t ready" also
+//               says that P V of tile t-2 is done with the buffer.
+//   warps 4-11  softmax: two groups of four warps, ONE thread per query row.  Group g owns tiles g, g+2, g+4, ... with
+//               its own running maximum, running sum and output accumulator (a split-KV inside the CTA), so no thread
+//               needs another thread's partial result and the two warps on a scheduler work on different tiles.  Two
+//               passes over the score tile in TMEM, 32 columns at a time with the next chunk's load in flight: maximum,
+//               then exp2 / sum / round to the element type, written back IN PLACE over the scores.  The running
+//               maximum is only raised when the new one exceeds it by more than 2^8 ("lazy" rescale of the accumulator).
+//               Epilogue: the groups exchange (max, sum), hand each other half of their partial output through shared
+//               memory and write O / sum.
+// TMEM (512 columns): S0/P0 [0,128), S1/P1 [128,256), O of even tiles [256,256+D), O of odd tiles [384,384+D).
 //
 // Every mbarrier wait is bounded; on expiry the CTA records PSA_ERR_TIMEOUT in the status word, lets copies in
 // flight land, frees its TMEM and returns.
@@ -70,7 +75,8 @@ template <int D> struct Cfg {
   static constexpr int OFF_K = OFF_Q + TILE_BYTES;
   static constexpr int OFF_V = OFF_K + NK * TILE_BYTES;
   static constexpr int OFF_BIAS = OFF_V + NV * TILE_BYTES;
-  static constexpr int OFF_XCH = OFF_BIAS + kBiasSlots * 128 * 4;
+  static constexpr int OFF_BIASG = OFF_BIAS + kBiasSlots * 128 * 4;   // one bias word per 4 columns + per-warp tile flags
+  static constexpr int OFF_XCH = OFF_BIASG + kBiasSlots * (32 + 4) * 4;
   static constexpr int OFF_ROW = OFF_XCH + 2 * 2 * 128 * 4;
   static constexpr int OFF_CTRL = OFF_ROW + kMaxItems * 4;
   static constexpr int SMEM_BYTES = OFF_CTRL + 1024 + 1024;   // control block + alignment slack
@@ -112,12 +118,15 @@ constexpr uint32_t kItemQuirk = 1u << 14, kItemPad = 1u << 15;
 #ifdef PSA_FWD_PROFILE
 }  // namespace
 __device__ long long g_prof[64];
+__device__ long long g_trace[16 * 64];
 namespace {
+#define TRACE(row, t) do { if (blockIdx.x == 3 && blockIdx.y == 0 && (t) < 64) g_trace[(row) * 64 + (t)] = clock64(); } while (0)
 #define PROF_T0() long long prof_t0 = clock64()
 #define PROF_ADD(slot) do { long long t1 = clock64(); prof_acc[slot] += t1 - prof_t0; prof_t0 = t1; } while (0)
 #else
 #define PROF_T0()
 #define PROF_ADD(slot)
+#define TRACE(row, t)
 #endif
 
 // IMG = true: K/V tiles use the image layout [8-row group][slab][8 rows][128 B] and are filled by linear bulk copies from
@@ -131,7 +140,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   unsigned char* sK = smem + C::OFF_K;
   unsigned char* sV = smem + C::OFF_V;
   float* sBias = reinterpret_cast<float*>(smem + C::OFF_BIAS);
-  float* sXch = reinterpret_cast<float*>(smem + C::OFF_XCH);      // [tile parity][half][row]
+  float* sBiasG = reinterpret_cast<float*>(smem + C::OFF_BIASG);   // [slot][32 group words | 3 producer flags | pad]
+  float* sXch = reinterpret_cast<float*>(smem + C::OFF_XCH);      // [group][max | sum][row]
   uint32_t* sItems = reinterpret_cast<uint32_t*>(smem + C::OFF_ROW);
   Ctrl* ctl = reinterpret_cast<Ctrl*>(smem + C::OFF_CTRL);
   volatile int* abort_flag = &ctl->abort_flag;
@@ -149,7 +159,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     }
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&ctl->s_full[i], 1);
-      tc::mbar_init(&ctl->p_full[i], kSoftmaxThreads);
+      tc::mbar_init(&ctl->p_full[i], 4);   // one arrival per softmax warp of the group
       tc::mbar_init(&ctl->pv_done[i], 1);
     }
     tc::mbar_init(&ctl->q_full, 1);
@@ -223,7 +233,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   const int n_tiles = ctl->n_tiles;
   const int last_cols = ctl->last_cols;
   const uint32_t tmem = ctl->tmem_base;
-  const uint32_t tO = tmem + 256;
 
   if (n_tiles > 0) {
     if (warp < kProducerWarps) {
@@ -261,6 +270,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           PROF_ADD(0);
           const uint32_t tile_a = sK_a + stage * C::TILE_BYTES, bar_a = k_full_a + stage * 8;
           float* bias_row = sBias + slot * 128;
+          float* biasg_row = sBiasG + slot * 36;
           const int probe = ki + lane;
           const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sItems[probe < n_items ? probe : 0] >> 21) == t));
           const bool active = 3 * lane + warp < in_tile;
@@ -284,11 +294,17 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             my_bytes = (uint32_t)C::SLABS * P * 128u;
             if (P <= 16) {   // narrow block: its lane writes the few bias words itself
               float4* dst = reinterpret_cast<float4*>(bias_row + col);
-              for (int c = 0; c < P; c += 4)
+              for (int c = 0; c < P; c += 4) {
                 dst[c >> 2] = make_float4(c < nvalid ? bias2 : -INFINITY, c + 1 < nvalid ? bias2 : -INFINITY,
                                           c + 2 < nvalid ? bias2 : -INFINITY, c + 3 < nvalid ? bias2 : -INFINITY);
+                biasg_row[(col + c) >> 2] = c < nvalid ? bias2 : -INFINITY;
+              }
             }
           }
+          // a block that ends inside a group of 4 columns makes the tile take the per-column path of the softmax
+          const bool odd_edge = active && nvalid > 0 && nvalid < P && (nvalid & 3) != 0;
+          const bool any_odd = __any_sync(0xffffffffu, odd_edge);
+          if (lane == 0) reinterpret_cast<int*>(biasg_row)[32 + warp] = any_odd ? 1 : 0;
           // wide blocks (at most 4 per tile): the whole warp writes the bias, 4 columns per lane
           unsigned wide = __ballot_sync(0xffffffffu, active && P > 16);
           while (wide) {
@@ -298,17 +314,21 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             const int w_nv = __shfl_sync(0xffffffffu, nvalid, src_lane);
             const float w_b = __shfl_sync(0xffffffffu, bias2, src_lane);
             const int c = lane * 4;
-            if (c < w_P)
+            if (c < w_P) {
               *reinterpret_cast<float4*>(bias_row + w_col + c) =
                   make_float4(c < w_nv ? w_b : -INFINITY, c + 1 < w_nv ? w_b : -INFINITY, c + 2 < w_nv ? w_b : -INFINITY,
                               c + 3 < w_nv ? w_b : -INFINITY);
+              biasg_row[(w_col + c) >> 2] = c < w_nv ? w_b : -INFINITY;
+            }
           }
           ki += in_tile;
           // the bias of this tile must be complete before the tile is announced: the softmax warps read it once the
           // scores are ready, and "scores ready" follows "K tile full" through the MMA issuer
-          if (t == n_tiles - 1 && warp == 0) for (int c = last_cols + lane; c < 128; c += 32) bias_row[c] = -INFINITY;
+          if (t == n_tiles - 1 && warp == 0)
+            for (int c = last_cols + lane; c < 128; c += 32) { bias_row[c] = -INFINITY; biasg_row[c >> 2] = -INFINITY; }
           const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
           if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
+          if (warp == 0 && lane == 0) TRACE(6, t);
           PROF_ADD(1);
         }
         if (step > 0) {
@@ -338,6 +358,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           vi += in_tile;
           const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
           if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
+          if (warp == 0 && lane == 0) TRACE(7, t);
           PROF_ADD(3);
         }
       }
@@ -373,32 +394,36 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           bool progressed = false;
           if (pv_next < qk_next) {
             const int t = pv_next, b = t & 1, stage = t % C::NV;
-            if (tc::mbar_try_wait_a(p_full_a + b * 8, (t >> 1) & 1) && tc::mbar_try_wait_a(v_full_a + stage * 8, (t / C::NV) & 1)) {
+            if (tc::mbar_test_wait_a(p_full_a + b * 8, (t >> 1) & 1) && tc::mbar_test_wait_a(v_full_a + stage * 8, (t / C::NV) & 1)) {
               tc::tc_fence_after();
+              TRACE(0, t);
               const uint64_t vdesc = vdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
-              const uint32_t tP = tmem + 384 + b * 64;
+              const uint32_t tP = tmem + b * 128;            // probabilities overwrite the scores they came from
+              const uint32_t tO = tmem + 256 + b * 128;      // even and odd tiles accumulate separately
               if (t < n_tiles - 1 || last_cols == 128) {
-                tc::umma_ts(tO, tP, vdesc, idesc_pv, t > 0 ? 1u : 0u);
+                tc::umma_ts(tO, tP, vdesc, idesc_pv, t > 1 ? 1u : 0u);
 #pragma unroll
                 for (int ks = 1; ks < 8; ++ks) tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, 1u);
               } else {
                 for (int ks = 0; ks < last_cols / 16; ++ks)
-                  tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+                  tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, (t > 1 || ks > 0) ? 1u : 0u);
               }
               tc::umma_commit_a(v_empty_a + stage * 8);   // V tile may be refilled
-              tc::umma_commit_a(pv_done_a + b * 8);       // O is consistent again, P buffer b may be rewritten
+              tc::umma_commit_a(pv_done_a + b * 8);       // accumulator b is consistent again
+              TRACE(1, t);
               ++pv_next;
               progressed = true;
               PROF_ADD(0);
             }
           }
           // S = Q K^T of tile t is only issued once P V of tile t-2 has been: the tensor pipe runs in issue order, so
-          // "S_t ready" then also means that the softmax warps are done with score buffer t&1 (they filled P_{t-2})
-          // and that P V of tile t-2 has finished reading P buffer t&1
+          // "S_t ready" then also means that P V of tile t-2 has finished reading the probabilities that were written over
+          // the scores of buffer t&1
           if (qk_next < n_tiles && qk_next <= pv_next + 1) {
             const int t = qk_next, b = t & 1, stage = t % C::NK;
-            if (tc::mbar_try_wait_a(k_full_a + stage * 8, (t / C::NK) & 1)) {
+            if (tc::mbar_test_wait_a(k_full_a + stage * 8, (t / C::NK) & 1)) {
               tc::tc_fence_after();
+              TRACE(2, t);
               const uint64_t kdesc = kdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
               const uint32_t idesc_qk = t == n_tiles - 1 ? tc::make_idesc(FMT, 128, last_cols, 0, 0) : idesc_qk_full;
               const uint32_t tSb = tmem + b * 128;
@@ -411,6 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
               }
               tc::umma_commit_a(k_empty_a + stage * 8);   // K tile may be refilled
               tc::umma_commit_a(s_full_a + b * 8);
+              TRACE(3, t);
               ++qk_next;
               progressed = true;
               PROF_ADD(1);
@@ -438,11 +464,17 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
 #endif
       }
     } else {
-      // ============================================================ softmax / epilogue (8 warps, 2 threads per row)
+      // ============================================================ softmax / epilogue
+      // Two groups of four warps, one thread per query row each.  Group g owns the tiles t = g, g+2, g+4, ... with its
+      // own running maximum, running sum and output accumulator, so the two warps that share a scheduler are in
+      // different phases of different tiles (one on the ex2 pipe while the other scales and searches the maximum) and
+      // no thread ever needs its neighbour's partial result.  The two partial outputs are merged once, at the end.
       const int quarter = warp & 3;                 // TMEM lanes this warp may touch
-      const int half = (warp - 4) >> 2;             // which 64 score columns / which half of the O channels
+      const int g = (warp - 4) >> 2;                // softmax group = tile parity = score buffer = accumulator
       const int r = quarter * 32 + lane;            // row inside the query block
       const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+      const uint32_t tS = tmem + g * 128 + lane_base;         // scores of my tiles; probabilities go back in place
+      const uint32_t tO = tmem + 256 + g * 128 + lane_base;   // my accumulator
       float m_run = -INFINITY, l_run = 0.f;
       bool ok = true;
 #ifdef PSA_FWD_PROFILE
@@ -452,49 +484,70 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
 #else
 #define SPROF(i)
 #endif
-      for (int j = 0; j < n_tiles; ++j) {
-        const int slot = j % kBiasSlots, b = j & 1;
-        ok = tc::mbar_wait(&ctl->s_full[b], (j >> 1) & 1, abort_flag);   // scores ready (and the tile's bias[] visible)
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+      for (int j = g; j < n_tiles; j += 2) {
+        const int slot = j % kBiasSlots, it = j >> 1;
+        ok = tc::mbar_wait(&ctl->s_full[g], it & 1, abort_flag);   // scores ready (and the tile's bias words visible)
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         SPROF(0);
+        if (r == 0) TRACE(4, j);
+        if (lane == 0) TRACE(12 + quarter, j);
         tc::tc_fence_after();
-        uint32_t v0[32], v1[32];
-        tc::tmem_ld32(tmem + b * 128 + lane_base + half * 64, v0);
-        tc::tmem_ld32(tmem + b * 128 + lane_base + half * 64 + 32, v1);
-        tc::tmem_wait_ld();
-        SPROF(1);
-        if (j == n_tiles - 1 && last_cols < 128) {  // columns the MMA did not write hold stale bits
+        const bool ragged = j == n_tiles - 1 && last_cols < 128;   // columns the MMA did not write hold stale bits
+        const float4* bias4 = reinterpret_cast<const float4*>(sBias + slot * 128);
+        const float4* bg4 = reinterpret_cast<const float4*>(sBiasG + slot * 36);     // one bias word per 4 columns
+        const int* flagw = reinterpret_cast<const int*>(sBiasG + slot * 36) + 32;
+        // Fast path: the bias is uniform inside every aligned group of 4 columns (blocks are at least 4 wide), so the
+        // maximum is taken on raw scores per group and the bias enters once per group.  A tile with a block that ends
+        // inside a group, or with unwritten columns, takes the per-column path.
+        const bool slow = ragged || (flagw[0] | flagw[1] | flagw[2]) != 0;
+        uint32_t va[32], vb[32];      // two chunks of 32 score columns in flight
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        if (!slow) {
+          // pass 1: running maximum; the load of the next chunk is issued before the current one is used
+#define PSA_MAX_CHUNK(v, c)                                                                                                  \
+  do {                                                                                                                       \
+    const float4 ga = bg4[2 * (c)], gb = bg4[2 * (c) + 1];                                                                   \
+    const float* f = reinterpret_cast<const float*>(v);                                                                      \
+    mx0 = fmaxf(mx0, fmaf(fmaxf(fmaxf(f[0], f[1]), fmaxf(f[2], f[3])), p.scale_log2, ga.x));                                 \
+    mx1 = fmaxf(mx1, fmaf(fmaxf(fmaxf(f[4], f[5]), fmaxf(f[6], f[7])), p.scale_log2, ga.y));                                 \
+    mx2 = fmaxf(mx2, fmaf(fmaxf(fmaxf(f[8], f[9]), fmaxf(f[10], f[11])), p.scale_log2, ga.z));                               \
+    mx3 = fmaxf(mx3, fmaf(fmaxf(fmaxf(f[12], f[13]), fmaxf(f[14], f[15])), p.scale_log2, ga.w));                             \
+    mx0 = fmaxf(mx0, fmaf(fmaxf(fmaxf(f[16], f[17]), fmaxf(f[18], f[19])), p.scale_log2, gb.x));                             \
+    mx1 = fmaxf(mx1, fmaf(fmaxf(fmaxf(f[20], f[21]), fmaxf(f[22], f[23])), p.scale_log2, gb.y));                             \
+    mx2 = fmaxf(mx2, fmaf(fmaxf(fmaxf(f[24], f[25]), fmaxf(f[26], f[27])), p.scale_log2, gb.z));                             \
+    mx3 = fmaxf(mx3, fmaf(fmaxf(fmaxf(f[28], f[29]), fmaxf(f[30], f[31])), p.scale_log2, gb.w));                             \
+  } while (0)
+          tc::tmem_ld32(tS, va);
+          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 32, vb); PSA_MAX_CHUNK(va, 0);
+          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 64, va); PSA_MAX_CHUNK(vb, 1);
+          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 96, vb); PSA_MAX_CHUNK(va, 2);
+          tc::tmem_wait_ld(); tc::tmem_ld32(tS, va);      PSA_MAX_CHUNK(vb, 3);   // chunk 0 again, for pass 2
+#undef PSA_MAX_CHUNK
+        } else {
+#pragma unroll 1
+          for (int h = 0; h < 4; ++h) {
+            tc::tmem_ld32(tS + h * 32, va);
+            tc::tmem_wait_ld();
+            if (ragged) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (half * 64 + i >= last_cols) v0[i] = 0u;
-            if (half * 64 + 32 + i >= last_cols) v1[i] = 0u;
+              for (int i = 0; i < 32; ++i)
+                if (h * 32 + i >= last_cols) va[i] = 0u;
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) {
+              const float4 ba = bias4[h * 8 + q4];
+              mx0 = fmaxf(mx0, fmaf(__uint_as_float(va[4 * q4 + 0]), p.scale_log2, ba.x));
+              mx1 = fmaxf(mx1, fmaf(__uint_as_float(va[4 * q4 + 1]), p.scale_log2, ba.y));
+              mx2 = fmaxf(mx2, fmaf(__uint_as_float(va[4 * q4 + 2]), p.scale_log2, ba.z));
+              mx3 = fmaxf(mx3, fmaf(__uint_as_float(va[4 * q4 + 3]), p.scale_log2, ba.w));
+            }
           }
         }
-        // biased, scaled logits (log2 domain) in place, and their maximum
-        const float4* bias4 = reinterpret_cast<const float4*>(sBias + slot * 128 + half * 64);
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;   // four chains, not one of 64
-#pragma unroll
-        for (int g = 0; g < 8; ++g) {
-          const float4 ba = bias4[g], bb = bias4[8 + g];
-          float x;
-          x = fmaf(__uint_as_float(v0[4 * g + 0]), p.scale_log2, ba.x); v0[4 * g + 0] = __float_as_uint(x); mx0 = fmaxf(mx0, x);
-          x = fmaf(__uint_as_float(v0[4 * g + 1]), p.scale_log2, ba.y); v0[4 * g + 1] = __float_as_uint(x); mx1 = fmaxf(mx1, x);
-          x = fmaf(__uint_as_float(v0[4 * g + 2]), p.scale_log2, ba.z); v0[4 * g + 2] = __float_as_uint(x); mx2 = fmaxf(mx2, x);
-          x = fmaf(__uint_as_float(v0[4 * g + 3]), p.scale_log2, ba.w); v0[4 * g + 3] = __float_as_uint(x); mx3 = fmaxf(mx3, x);
-          x = fmaf(__uint_as_float(v1[4 * g + 0]), p.scale_log2, bb.x); v1[4 * g + 0] = __float_as_uint(x); mx0 = fmaxf(mx0, x);
-          x = fmaf(__uint_as_float(v1[4 * g + 1]), p.scale_log2, bb.y); v1[4 * g + 1] = __float_as_uint(x); mx1 = fmaxf(mx1, x);
-          x = fmaf(__uint_as_float(v1[4 * g + 2]), p.scale_log2, bb.z); v1[4 * g + 2] = __float_as_uint(x); mx2 = fmaxf(mx2, x);
-          x = fmaf(__uint_as_float(v1[4 * g + 3]), p.scale_log2, bb.w); v1[4 * g + 3] = __float_as_uint(x); mx3 = fmaxf(mx3, x);
-        }
-        float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        // the two threads of a row exchange their partial maxima
-        float* xch = sXch + (j & 1) * 256;
-        xch[half * 128 + r] = mx;
-        tc::named_bar_sync(1 + quarter, 64);
-        SPROF(2);
-        mx = fmaxf(mx, xch[(half ^ 1) * 128 + r]);
-        // raise the running maximum only when it is far off (or still unset); both threads of a row agree
+        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        SPROF(1);
+        // raise the running maximum only when it is far off (or still unset)
         float alpha = 1.f;
         const bool raise = mx > m_run + 8.f;
         if (raise) {
@@ -502,75 +555,152 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           m_run = mx;
           l_run *= alpha;
         }
-        if (j > 0 && __any_sync(0xffffffffu, raise)) {
-          // O may only be touched between two P V products: wait for the one of tile j-1
-          ok = tc::mbar_wait(&ctl->pv_done[b ^ 1], ((j - 1) >> 1) & 1, abort_flag);
+        if (it > 0 && __any_sync(0xffffffffu, raise)) {
+          // the accumulator may only be touched between two of its P V products: wait for the one of tile j-2
+          ok = tc::mbar_wait(&ctl->pv_done[g], (it - 1) & 1, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc::tc_fence_after();
 #pragma unroll 1
-          for (int c0 = 0; c0 < D / 2; c0 += 32) {
-            uint32_t o[32];
-            tc::tmem_ld32(tO + lane_base + half * (D / 2) + c0, o);
+          for (int c0 = 0; c0 < D; c0 += 32) {
+            tc::tmem_ld32(tO + c0, vb);
             tc::tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tc::tmem_st32(tO + lane_base + half * (D / 2) + c0, o);
+            for (int i = 0; i < 32; ++i) vb[i] = __float_as_uint(__uint_as_float(vb[i]) * alpha);
+            tc::tmem_st32(tO + c0, vb);
           }
           tc::tmem_wait_st();
         }
-        // probabilities (rounded to the element type) -> TMEM, running sum
-        SPROF(4);
+        SPROF(2);
+        // pass 2: probabilities (rounded to the element type) written over the scores, running sum.  Chunk c reads score
+        // columns [32c, 32c+32) and writes packed columns [16c, 16c+16): always columns that were read before.
         const float m_use = m_run == -INFINITY ? 0.f : m_run;
-        float ls0 = 0.f, ls1 = 0.f;
-        uint32_t pk[32];
+        float2 ls_a = make_float2(0.f, 0.f), ls_b = make_float2(0.f, 0.f);
+        if (!slow) {
+#define PSA_EXP_GROUP(f, cg, k, acc)                                                                                          \
+  do {                                                                                                                       \
+    const float2 cc = make_float2(cg, cg);                                                                                   \
+    const float2 x01 = __ffma2_rn(make_float2(f[4 * (k)], f[4 * (k) + 1]), scale2, cc);                                      \
+    const float2 x23 = __ffma2_rn(make_float2(f[4 * (k) + 2], f[4 * (k) + 3]), scale2, cc);                                  \
+    const float2 e01 = make_float2(ex2(x01.x), ex2(x01.y)), e23 = make_float2(ex2(x23.x), ex2(x23.y));                       \
+    acc = __fadd2_rn(acc, __fadd2_rn(e01, e23));                                                                             \
+    pk[2 * (k)] = pack2<FMT>(e01.x, e01.y);                                                                                  \
+    pk[2 * (k) + 1] = pack2<FMT>(e23.x, e23.y);                                                                              \
+  } while (0)
+#define PSA_EXP_CHUNK(v, c)                                                                                                  \
+  do {                                                                                                                       \
+    const float4 ga = bg4[2 * (c)], gb = bg4[2 * (c) + 1];                                                                   \
+    const float* f = reinterpret_cast<const float*>(v);                                                                      \
+    uint32_t pk[16];                                                                                                         \
+    PSA_EXP_GROUP(f, ga.x - m_use, 0, ls_a); PSA_EXP_GROUP(f, ga.y - m_use, 1, ls_b);                                        \
+    PSA_EXP_GROUP(f, ga.z - m_use, 2, ls_a); PSA_EXP_GROUP(f, ga.w - m_use, 3, ls_b);                                        \
+    PSA_EXP_GROUP(f, gb.x - m_use, 4, ls_a); PSA_EXP_GROUP(f, gb.y - m_use, 5, ls_b);                                        \
+    PSA_EXP_GROUP(f, gb.z - m_use, 6, ls_a); PSA_EXP_GROUP(f, gb.w - m_use, 7, ls_b);                                        \
+    tc::tmem_st16(tS + 16 * (c), pk);                                                                                        \
+  } while (0)
+          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 32, vb); PSA_EXP_CHUNK(va, 0);
+          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 64, va); PSA_EXP_CHUNK(vb, 1);
+          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 96, vb); PSA_EXP_CHUNK(va, 2);
+          tc::tmem_wait_ld();                             PSA_EXP_CHUNK(vb, 3);
+#undef PSA_EXP_CHUNK
+#undef PSA_EXP_GROUP
+        } else {
+#pragma unroll 1
+          for (int h = 0; h < 4; ++h) {
+            tc::tmem_ld32(tS + h * 32, va);
+            tc::tmem_wait_ld();
+            if (ragged) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2(__uint_as_float(v0[i]) - m_use), p1 = ex2(__uint_as_float(v0[i + 1]) - m_use);
-          const float p2 = ex2(__uint_as_float(v1[i]) - m_use), p3 = ex2(__uint_as_float(v1[i + 1]) - m_use);
-          ls0 += p0 + p1;
-          ls1 += p2 + p3;
-          pk[i >> 1] = pack2<FMT>(p0, p1);
-          pk[16 + (i >> 1)] = pack2<FMT>(p2, p3);
+              for (int i = 0; i < 32; ++i)
+                if (h * 32 + i >= last_cols) va[i] = 0u;
+            }
+            uint32_t pk[16];
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) {
+              const float4 ba = bias4[h * 8 + q4];
+              const float a0 = ex2(fmaf(__uint_as_float(va[4 * q4 + 0]), p.scale_log2, ba.x) - m_use);
+              const float a1 = ex2(fmaf(__uint_as_float(va[4 * q4 + 1]), p.scale_log2, ba.y) - m_use);
+              const float a2 = ex2(fmaf(__uint_as_float(va[4 * q4 + 2]), p.scale_log2, ba.z) - m_use);
+              const float a3 = ex2(fmaf(__uint_as_float(va[4 * q4 + 3]), p.scale_log2, ba.w) - m_use);
+              ls_a.x += a0 + a1;
+              ls_b.x += a2 + a3;
+              pk[2 * q4] = pack2<FMT>(a0, a1);
+              pk[2 * q4 + 1] = pack2<FMT>(a2, a3);
+            }
+            tc::tmem_st16(tS + h * 16, pk);
+          }
         }
-        l_run += ls0 + ls1;
-        tc::tmem_st32(tmem + 384 + b * 64 + lane_base + half * 32, pk);
+        l_run += (ls_a.x + ls_a.y) + (ls_b.x + ls_b.y);
         tc::tmem_wait_st();
         tc::tc_fence_before();
-        tc::mbar_arrive(&ctl->p_full[b]);
-        SPROF(5);
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&ctl->p_full[g]);   // one arrival per warp
+        if (r == 0) TRACE(5, j);
+        if (lane == 0) TRACE(8 + quarter, j);
+        SPROF(3);
       }
 #ifdef PSA_FWD_PROFILE
       if (threadIdx.x == 128 && blockIdx.x == 3 && blockIdx.y == 0) for (int i = 0; i < 6; ++i) g_prof[32 + i] = sprof[i];
 #endif
-      // epilogue
-      if (ok) {
-        const int t = n_tiles - 1;
-        ok = tc::mbar_wait(&ctl->pv_done[t & 1], (t >> 1) & 1, abort_flag);
+      // ---- epilogue: merge the two groups' partial results
+      const int my_tiles = (n_tiles - g + 1) >> 1;
+      if (ok && my_tiles > 0) {
+        ok = tc::mbar_wait(&ctl->pv_done[g], (my_tiles - 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
       }
-      if (ok) {
-        tc::tc_fence_after();
-        float* xch = sXch + (n_tiles & 1) * 256;
-        xch[half * 128 + r] = l_run;
-        tc::named_bar_sync(1 + quarter, 64);
-        const float l_tot = l_run + xch[(half ^ 1) * 128 + r];
-        const int64_t qrow = (int64_t)m * 128 + r;
-        const float inv = 1.0f / l_tot;     // empty row: 0/0 like the reference
-        uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + half * (D / 2);
+      // group g publishes (maximum, sum); both groups then agree on the weights.  An aborting group still joins the
+      // barriers so that the other one is not left waiting.
+      sXch[g * 256 + r] = m_run;
+      sXch[g * 256 + 128 + r] = l_run;
+      tc::named_bar_sync(1, kSoftmaxThreads);
+      const float m_o = sXch[(g ^ 1) * 256 + r], l_o = sXch[(g ^ 1) * 256 + 128 + r];
+      const float m_all = fmaxf(m_run, m_o);
+      const float w_me = m_run == -INFINITY ? 0.f : ex2(m_run - m_all);
+      const float w_ot = m_o == -INFINITY ? 0.f : ex2(m_o - m_all);
+      const float inv = 1.0f / (l_run * w_me + l_o * w_ot);     // empty row: 0/0 like the reference
+      const float w = w_me * inv;
+      // each group finishes half of the channels: it hands the other half of its partial output over through shared
+      // memory (the K ring is idle by now), transposed so that a warp's 32 rows are 32 consecutive words
+      constexpr int HALF = D / 2;
+      float* stage = reinterpret_cast<float*>(sK);
+      tc::tc_fence_after();
+      if (ok && my_tiles > 0) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < D / 2; c0 += 32) {
+        for (int c0 = 0; c0 < HALF; c0 += 32) {
           uint32_t v[32];
-          tc::tmem_ld32(tO + lane_base + half * (D / 2) + c0, v);
+          tc::tmem_ld32(tO + (g ^ 1) * HALF + c0, v);
           tc::tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) stage[(g * HALF + c0 + i) * 128 + r] = __uint_as_float(v[i]) * w;
+        }
+      }
+      tc::named_bar_sync(2, kSoftmaxThreads);
+      if (ok) {
+        const bool other_has = n_tiles - my_tiles > 0;
+        const int64_t qrow = (int64_t)m * 128 + r;
+        uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + g * HALF;
+#pragma unroll 1
+        for (int c0 = 0; c0 < HALF; c0 += 32) {
+          uint32_t v[32];
+          if (my_tiles > 0) {
+            tc::tmem_ld32(tO + g * HALF + c0, v);
+            tc::tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          float f[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            f[i] = __uint_as_float(v[i]) * w + (other_has ? stage[((g ^ 1) * HALF + c0 + i) * 128 + r] : 0.f);
           if (qrow < p.seq_q) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
               uint4 o;
-              o.x = pack2<FMT>(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-              o.y = pack2<FMT>(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
-              o.z = pack2<FMT>(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
-              o.w = pack2<FMT>(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+              o.x = pack2<FMT>(f[i], f[i + 1]);
+              o.y = pack2<FMT>(f[i + 2], f[i + 3]);
+              o.z = pack2<FMT>(f[i + 4], f[i + 5]);
+              o.w = pack2<FMT>(f[i + 6], f[i + 7]);
               *reinterpret_cast<uint4*>(orow + c0 + i) = o;
             }
           }
@@ -699,5 +829,8 @@ int fwd_tc_launch(const FwdArgs& a, cudaStream_t st) {
 #ifdef PSA_FWD_PROFILE
 extern "C" int psa_debug_read_prof(long long* host64) {
   return (int)cudaMemcpyFromSymbol(host64, psa::g_prof, sizeof(long long) * 64);
+}
+extern "C" int psa_debug_read_trace(long long* host512) {
+  return (int)cudaMemcpyFromSymbol(host512, psa::g_trace, sizeof(long long) * 1024);
 }
 #endif
