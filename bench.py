@@ -121,7 +121,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="wan2.1-14b-attn-layer")
     ap.add_argument("--sparsity", default="90", choices=["90", "85"])
-    ap.add_argument("--chunks", type=int, default=5, help="head chunks per rank for all-to-all/compute overlap (N>1)")
+    ap.add_argument("--chunks", type=int, default=5, help="head chunks per rank for exchange/compute overlap (N>1)")
+    ap.add_argument("--pull-blocks", type=int, default=32, help="grid cap of the prefetching peer pulls (p2p exchange)")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="N>1: peer-memory pull + scatter by our kernels (p2p) or NCCL all-to-all (nccl)")
     ap.add_argument("--heads", type=int, default=0, help="override the head count (smaller captures for profilers)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -189,14 +192,20 @@ def main():
         ik = ops.draw_sample_indices(1, H, BLOCK_N, BLOCK_N // 4, dev)[:, h0:h0 + hp]
         return iq.contiguous(), ik.contiguous()
 
-    from psa_b200.parallel import HeadShard
+    from psa_b200.parallel import HeadShard, PeerExchange
     shard = HeadShard(world, rank, H, S, D)
     to_head_sharded, to_seq_sharded = shard.to_head_sharded, shard.to_seq_sharded
+    peer = None
+    if world > 1 and args.exchange == "p2p":
+        peer = PeerExchange(H, S, D, dtype, dev)
+        peer.q.copy_(seq_shard[0]); peer.k.copy_(seq_shard[1]); peer.v.copy_(seq_shard[2])
+        torch.cuda.synchronize()
+        dist.barrier()
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     stage_names = ["a2a_in", "sample", "pyramid", "scores", "assign", "forward", "a2a_out"]
 
-    comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    comm_stream = torch.cuda.Stream(device=dev, priority=-1) if world > 1 else None
     chunk_list = shard.chunks(args.chunks) if world > 1 else [(0, hp)]
 
     def timed(name, fn, rec, stream=None):
@@ -222,6 +231,8 @@ def main():
     def layer_step(rec=None):
         """One PSA layer.  N = 1: inputs are already [1, H, S, D].  N > 1: the rank's heads are processed in chunks; the
         all-to-all of chunk c+1 (and the return of chunk c-1) runs on a second stream under the kernels of chunk c."""
+        if peer is not None:
+            return layer_step_p2p(rec, torch.cuda.current_stream(dev))
         iq, ik = timed("sample", draw_indices, rec)
         if world == 1:
             out, mask = layer_on(q, k, v, iq, ik, rec)
@@ -254,6 +265,35 @@ def main():
                 o.record_stream(comm_stream)
         cur.wait_stream(comm_stream)
         return out_final, mask, out
+
+    pull_buf = None
+
+    def layer_step_p2p(rec, cur):
+        """N > 1 without a collective.  The rows of this rank's heads are pulled out of the peers' q/k/v buffers by a copy
+        kernel: q and k first, at full width; v follows on the second stream with a small grid while the scores and the
+        level assignment (which need only q and k) run.  The forward stores its output rows into the owners' buffers.
+        The only cross-rank synchronisation is the barrier that says "every rank's q/k/v are in place"."""
+        nonlocal pull_buf
+        dist.barrier()                                         # inputs of all ranks are in their exchange buffers
+        if pull_buf is None:
+            pull_buf = torch.empty((3, hp, S, D), dtype=dtype, device=dev)
+        comm_stream.wait_stream(cur)
+        with torch.cuda.stream(comm_stream):
+            timed("a2a_in", lambda: peer.pull(out=pull_buf, names=("q", "k")), rec, comm_stream)
+            e_qk = ev(); e_qk.record(comm_stream)
+            timed("a2a_in", lambda: peer.pull(out=pull_buf, names=("v",), max_blocks=args.pull_blocks), rec, comm_stream)
+            e_v = ev(); e_v.record(comm_stream)
+        iq, ik = timed("sample", draw_indices, rec)            # independent of the data: runs under the pull
+        cur.wait_event(e_qk)
+        qq, kk, vv = pull_buf[0].unsqueeze(0), pull_buf[1].unsqueeze(0), pull_buf[2].unsqueeze(0)
+        po = timed("scores", lambda: ops.block_scores(qq, kk, iq, ik, BLOCK_M, BLOCK_N), rec)
+        mask = timed("assign", lambda: ops.assign_levels(po, ratios, "topk_newtype", BLOCK_N, TILE_N), rec)
+        cur.wait_event(e_v)
+        pyr = timed("pyramid", lambda: ops.pyramid_kv_images(kk, vv, BLOCK_N), rec)
+        status = timed("forward", lambda: peer.forward_scatter(qq, pyr, mask, BLOCK_M, BLOCK_N, TILE_N), rec)
+        holder = torch.empty(0, device=dev)
+        holder._psa_status = status
+        return peer.o, mask, holder
 
     def barrier():
         if world > 1:
@@ -301,6 +341,14 @@ def main():
 
         def e2e_step():
             nonlocal h_out
+            if peer is not None:
+                peer.q.copy_(hx[0], non_blocking=True); peer.k.copy_(hx[1], non_blocking=True); peer.v.copy_(hx[2], non_blocking=True)
+                layer_step()                      # barrier, pull from peers, compute, scatter into the owners' o buffers
+                dist.barrier()                    # every rank's forward has finished: this rank's o is complete
+                if h_out is None:
+                    h_out = torch.empty(peer.o.shape, dtype=peer.o.dtype).pin_memory()
+                h_out.copy_(peer.o, non_blocking=True)
+                return
             if world == 1:
                 dq, dk, dv = (x.to(dev, non_blocking=True) for x in (hq, hk, hv))
             else:
@@ -332,6 +380,9 @@ def main():
         e2e = {"value": f_dense / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": per_rank_in * world, "d2h_bytes_per_step": per_rank_out * world}
 
+    if peer is not None:
+        barrier()
+        peer.close()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -349,12 +400,16 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg_json,
         "ms_per_layer": ms_step, "stage_ms": stage_ms, "density": dens, "sparsity": 1.0 - dens,
         "surviving_tflops_forward": fwd_tflops, "kernel_status": status,
-        "gpu_launches": 5 * args.steps,
+        # own kernels per chunk: pyramid images, 2 sample gathers, score GEMM, pool+normalise, level assignment, forward
+        # (+ 3 peer pulls per chunk when the exchange is ours)
+        "gpu_launches": args.steps * (10 if peer is not None else 7 * len(chunk_list)),
+        "exchange": (args.exchange if world > 1 else None),
         "roofline": {"bound": "tensor", "kernel": "psa_fwd_tc_kernel", "achieved": fwd_tflops, "peak": peak_tf,
                      "unit": "TFLOP/s", "frac": fwd_tflops / peak_tf, "traffic": None,
                      "peak_source": f"{peaks['source']} (sustained bf16: kernel timed inside a long step)",
-                     "pyramid_gbs": 3.75 * n_elem * 2 / (stage_ms["pyramid"] * 1e-3) / 1e9,
-                     "pyramid_frac_of_hbm": 3.75 * n_elem * 2 / (stage_ms["pyramid"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+                     # tile-image pyramid: read K,V once (2 N e), write levels 1,2,4,8 of both (3.75 N e)
+                     "pyramid_gbs": 5.75 * n_elem * 2 / (stage_ms["pyramid"] * 1e-3) / 1e9,
+                     "pyramid_frac_of_hbm": 5.75 * n_elem * 2 / (stage_ms["pyramid"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
         "clocks": clocks, "e2e": e2e,
     }
     if not args.no_cpu_baseline and world == 1:

@@ -150,6 +150,37 @@ int psa_legacy_bwd(const void* q, const void* k, const void* v, const void* k2, 
                    const float* lse, const void* dout, void* dq, void* dk, void* dv, float* delta, int64_t bh,
                    int64_t seq, int head_dim, int mask_cols, float sm_scale, int causal, int dtype, void* stream);
 
+/* ---------------------------------------------------------------------------------------------------------------
+ * Head sharding over the GPUs of one node, by peer memory instead of an all-to-all collective.  No counterpart in the
+ * reference (it runs on one GPU); these calls sit where a sequence-parallel host model would otherwise call
+ * all_to_all before and after the attention layer.
+ *
+ * psa_peer_alloc: cudaMalloc + IPC handle (64 bytes) for an exchange buffer; psa_peer_open maps a peer's handle into
+ * this process (peer access is enabled on demand); psa_peer_close / psa_peer_free undo them.  Set-up calls, not for
+ * the hot path.
+ *
+ * psa_pull_heads: dst [heads_local][n_peers*tokens_per_rank][head_dim] <- rows of heads [head0, head0+heads_local)
+ * read straight from the peers' buffers peer_src[r] = [tokens_per_rank][heads_total][head_dim] (token t lives on
+ * rank t / tokens_per_rank).  peer_src is a HOST array of n_peers device-accessible pointers (own buffer included).
+ * The caller orders it after the peers have written their buffers (a barrier between steps); the kernel itself never
+ * waits on a peer.  max_blocks caps the grid (0 = whole GPU): a copy that runs under compute kernels should stay
+ * small, since each of its resident CTAs keeps a compute CTA off that SM.  self_rank (0..n_peers-1) only rotates the
+ * order in which the peers are visited, so that the ranks of a node do not all read from the same GPU at once.
+ *
+ * psa_fwd_images_scatter: psa_fwd_images whose output rows go to the rank that owns the token:
+ * peer_out[t / tokens_per_rank] laid out [tokens_per_rank][heads_total][head_dim], this rank writing heads
+ * [head0, head0+bh).  peer_out is a HOST array of n_peers device-accessible pointers. */
+int psa_peer_alloc(size_t bytes, void** ptr, void* handle64);
+int psa_peer_open(const void* handle64, void** ptr);
+int psa_peer_close(void* ptr);
+int psa_peer_free(void* ptr);
+int psa_pull_heads(const void* const* peer_src, int n_peers, void* dst, int64_t tokens_per_rank, int heads_total, int head0,
+                   int heads_local, int head_dim, int elem_bytes, int max_blocks, int self_rank, void* stream);
+int psa_fwd_images_scatter(const void* q, const void* kimg, const void* vimg, const int32_t* mask, void* const* peer_out,
+                           int n_peers, int64_t tokens_per_rank, int heads_total, int head0, int64_t bh, int64_t seq_q,
+                           int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width, float sm_scale,
+                           int compat_quirk, int dtype, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -93,3 +93,36 @@ extern "C" int psa_fwd_images(const void* q, const void* kimg, const void* vimg,
               "psa_fwd_images: needs f16/bf16, block_m=128, tile_n=32, head_dim 64/128, mask width <= 4064");
   return fwd_tc_launch(a, (cudaStream_t)stream);
 }
+
+extern "C" int psa_fwd_images_scatter(const void* q, const void* kimg, const void* vimg, const int32_t* mask, void* const* peer_out,
+                                      int n_peers, int64_t tokens_per_rank, int heads_total, int head0, int64_t bh, int64_t seq_q,
+                                      int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width,
+                                      float sm_scale, int compat_quirk, int dtype, int32_t* status, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(q && kimg && vimg && mask && peer_out, PSA_ERR_ARG, "psa_fwd_images_scatter: null pointer");
+  PSA_REQUIRE(n_peers >= 1 && n_peers <= kMaxPeers, PSA_ERR_ARG, "psa_fwd_images_scatter: n_peers=%d (1..%d)", n_peers, kMaxPeers);
+  PSA_REQUIRE(bh > 0 && bh < 65536 && seq_q > 0 && seq_k > 0, PSA_ERR_ARG, "psa_fwd_images_scatter: bad shape");
+  PSA_REQUIRE(tokens_per_rank > 0 && tokens_per_rank * n_peers >= seq_q, PSA_ERR_ARG,
+              "psa_fwd_images_scatter: %d peers x %lld tokens do not cover %lld query rows", n_peers, (long long)tokens_per_rank,
+              (long long)seq_q);
+  PSA_REQUIRE(head0 >= 0 && head0 + bh <= heads_total, PSA_ERR_ARG, "psa_fwd_images_scatter: heads [%d, %lld) of %d", head0,
+              (long long)(head0 + bh), heads_total);
+  PSA_REQUIRE(block_n == 64 || block_n == 128, PSA_ERR_UNSUPPORTED, "psa_fwd_images_scatter: block_n=%d (64/128)", block_n);
+  PSA_REQUIRE(mask_width >= 1, PSA_ERR_ARG, "psa_fwd_images_scatter: mask_width=%d", mask_width);
+  const int64_t s_pad = cdiv64(seq_k, block_n) * block_n;
+  FwdArgs a;
+  a.q = q; a.mask = mask; a.out = const_cast<void*>(q); a.status = status; a.kimg = kimg; a.vimg = vimg;   // out unused
+  const int64_t nl[4] = {seq_k, s_pad / 2, s_pad / 4, s_pad / 8};
+  for (int i = 0; i < 4; ++i) { a.k[i] = q; a.v[i] = q; a.n[i] = nl[i]; }
+  a.bh = bh; a.seq_q = seq_q; a.seq_k = seq_k; a.D = head_dim; a.bm = block_m; a.bn = block_n; a.tn = tile_n;
+  a.width = mask_width; a.scale = sm_scale; a.quirk = compat_quirk; a.dtype = dtype;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    a.scatter.peer_out[i] = i < n_peers ? peer_out[i] : nullptr;
+    if (i < n_peers) PSA_REQUIRE(peer_out[i] && ((uintptr_t)peer_out[i] & 15) == 0, PSA_ERR_ARG, "psa_fwd_images_scatter: peer %d", i);
+  }
+  a.scatter.n_peers = n_peers; a.scatter.heads_total = heads_total; a.scatter.head0 = head0;
+  a.scatter.tokens_per_rank = tokens_per_rank;
+  PSA_REQUIRE(fwd_tc_supported(a), PSA_ERR_UNSUPPORTED,
+              "psa_fwd_images_scatter: needs f16/bf16, block_m=128, tile_n=32, head_dim 64/128, mask width <= 4064");
+  return fwd_tc_launch(a, (cudaStream_t)stream);
+}

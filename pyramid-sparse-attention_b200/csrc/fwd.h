@@ -25,6 +25,17 @@ inline ImgLevels make_img_levels(int64_t bh, int64_t seq, int D, int block_n) {
   return L;
 }
 
+// Output scatter for head-sharded runs: the rank computes heads [head0, head0+bh) of all tokens, and token s belongs to
+// rank s / tokens_per_rank, whose output buffer is laid out [tokens_per_rank][heads_total][D].  n_peers == 0: plain
+// local output [bh][seq_q][D].
+constexpr int kMaxPeers = 8;
+struct OutScatter {
+  void* peer_out[kMaxPeers];
+  int n_peers;
+  int heads_total, head0;
+  int64_t tokens_per_rank;
+};
+
 struct FwdArgs {
   const void* q;
   const void* k[4];  // levels 1, 2, 4, 8
@@ -38,6 +49,7 @@ struct FwdArgs {
   int64_t bh, seq_q, seq_k;
   int D, bm, bn, tn, width, quirk, dtype;
   float scale;
+  OutScatter scatter = {};   // n_peers == 0 unless the output goes to peer buffers
 };
 
 int fwd_simt_dispatch(const void* q, const void* const* kl, const void* const* vl, const int64_t* nl, const int32_t* mask,

@@ -64,6 +64,7 @@ struct TcParams {
   const unsigned char* kimg;
   const unsigned char* vimg;
   ImgLevels img;
+  OutScatter scatter;   // n_peers > 0: rows go to the peer that owns the token (plain stores over NVLink)
 };
 
 template <int D> struct Cfg {
@@ -678,7 +679,14 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       if (ok) {
         const bool other_has = n_tiles - my_tiles > 0;
         const int64_t qrow = (int64_t)m * 128 + r;
-        uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + g * HALF;
+        uint16_t* orow;
+        if (p.scatter.n_peers > 0 && qrow < p.seq_q) {
+          const int64_t owner = qrow / p.scatter.tokens_per_rank, local = qrow - owner * p.scatter.tokens_per_rank;
+          orow = reinterpret_cast<uint16_t*>(p.scatter.peer_out[owner]) +
+                 (local * p.scatter.heads_total + p.scatter.head0 + bh) * D + g * HALF;
+        } else {
+          orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + g * HALF;
+        }
 #pragma unroll 1
         for (int c0 = 0; c0 < HALF; c0 += 32) {
           uint32_t v[32];
@@ -713,6 +721,11 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     const int64_t qrow = (int64_t)m * 128 + (warp & 3) * 32 + lane;
     if (qrow < p.seq_q) {
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + half * (D / 2);
+      if (p.scatter.n_peers > 0) {
+        const int64_t owner = qrow / p.scatter.tokens_per_rank, local = qrow - owner * p.scatter.tokens_per_rank;
+        orow = reinterpret_cast<uint16_t*>(p.scatter.peer_out[owner]) +
+               (local * p.scatter.heads_total + p.scatter.head0 + bh) * D + half * (D / 2);
+      }
       const uint32_t nan2 = pack2<FMT>(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
       for (int c = 0; c < D / 2; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(nan2, nan2, nan2, nan2);
     }
@@ -802,6 +815,7 @@ static int launch_tc(const FwdArgs& a, cudaStream_t st) {
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.kimg = (const unsigned char*)a.kimg; p.vimg = (const unsigned char*)a.vimg;
   p.img = make_img_levels(a.bh, a.seq_k, D, IMG ? a.bn : 64);
+  p.scatter = a.scatter;
   cudaError_t e = cudaFuncSetAttribute(psa_fwd_tc_kernel<D, FMT, IMG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   PSA_REQUIRE(e == cudaSuccess, PSA_ERR_CUDA, "psa_fwd: shared-memory opt-in (%d B) failed: %s", C::SMEM_BYTES,
               cudaGetErrorString(e));

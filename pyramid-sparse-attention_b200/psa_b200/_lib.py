@@ -32,6 +32,12 @@ SIGNATURES = {
     "psa_kv_image_bytes": (_sz, [_i64, _i64, _i, _i]),
     "psa_pyramid_kv_images": (_i, [_p] * 4 + [_i64, _i64, _i, _i, _i, _p]),
     "psa_fwd_images": (_i, [_p] * 5 + [_i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]),
+    "psa_fwd_images_scatter": (_i, [_p] * 5 + [_i, _i64, _i, _i, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]),
+    "psa_peer_alloc": (_i, [_sz, _p, _p]),
+    "psa_peer_open": (_i, [_p, _p]),
+    "psa_peer_close": (_i, [_p]),
+    "psa_peer_free": (_i, [_p]),
+    "psa_pull_heads": (_i, [_p, _i, _p, _i64, _i, _i, _i, _i, _i, _i, _i, _p]),
     "psa_block_scores_scratch_bytes": (_sz, [_i64, _i64, _i64, _i, _i, _i]),
     "psa_block_scores": (_i, [_p] * 6 + [_sz, _i64, _i64, _i64, _i, _i, _i, _i, _i, _p]),
     "psa_block_scores_static_capacity": (_sz, []),

@@ -2,10 +2,17 @@
 
 Every stage of the layer is independent per (batch, head), so ranks own disjoint heads and no collective runs inside
 the layer.  When the surrounding model keeps activations sequence-sharded ([S/P, H, D] per rank), one all-to-all turns
-them into head shards ([H/P, S, D]) before the layer and one turns the output back (Ulysses-style).  The collective is
-NCCL's (torch.distributed.all_to_all_single) on GPUs and gloo's in the CPU tests; kernels only ever read local memory.
+them into head shards ([H/P, S, D]) before the layer and one turns the output back (Ulysses-style).
+
+Two implementations of that exchange:
+  * HeadShard: the collective (torch.distributed.all_to_all_single: NCCL on GPUs, gloo in the CPU tests).
+  * PeerExchange: no collective.  Every rank maps its peers' q/k/v/o buffers (CUDA IPC), pulls the rows of its heads
+    with a copy kernel that reads peer memory directly, and the attention forward stores its output rows straight into
+    the owning peer's buffer.  The host orders the steps with barriers; no kernel waits on another GPU.
 """
 from __future__ import annotations
+
+import ctypes as C
 
 import torch
 import torch.distributed as dist
@@ -77,3 +84,117 @@ class HeadShard:
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv, send)
         out.view(P, hp, sl, D)[:, first:first + count] = recv
+
+
+class _DeviceBuffer:
+    """A raw device allocation exposed to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, shape, dtype: torch.dtype):
+        typestr = {torch.bfloat16: "<u2", torch.float16: "<f2", torch.float32: "<f4"}[dtype]
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def _as_tensor(ptr: int, shape, dtype: torch.dtype, device) -> torch.Tensor:
+    t = torch.as_tensor(_DeviceBuffer(ptr, shape, dtype), device=device)
+    return t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+
+
+class PeerExchange:
+    """Exchange buffers of one attention layer, mapped into every rank of the node.
+
+    Each rank owns q, k, v and o buffers of shape [S/P, H, D] (its tokens, all heads), allocated by the library so that
+    an IPC handle exists for them.  After construction:
+      * `q`, `k`, `v`, `o` are torch views of this rank's own buffers (the surrounding model writes q/k/v, reads o);
+      * `pull()` returns this rank's heads of all tokens, [3, H/P, S, D], read from the peers' buffers;
+      * `forward_scatter(...)` runs the tile-image forward and stores every output row into the owner's `o`.
+    The caller places a barrier between "all ranks wrote q/k/v" and pull(), and between forward_scatter() and reading o.
+    """
+
+    def __init__(self, heads: int, seq: int, head_dim: int, dtype: torch.dtype, device, group=None):
+        from ._lib import lib, check
+        self.lib, self.check = lib, check
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("PeerExchange covers the GPUs of one node (at most 8 ranks)")
+        if heads % self.world or seq % self.world:
+            raise ValueError(f"{heads} heads / {seq} tokens do not divide over {self.world} ranks")
+        self.heads, self.seq, self.head_dim, self.dtype, self.device = heads, seq, head_dim, dtype, torch.device(device)
+        self.heads_per_rank, self.tokens_per_rank = heads // self.world, seq // self.world
+        self.head0 = self.rank * self.heads_per_rank
+        esz = torch.empty(0, dtype=dtype).element_size()
+        self.elem_bytes = esz
+        nbytes = self.tokens_per_rank * heads * head_dim * esz
+        self._own, self._opened = {}, []
+        handles = {}
+        with torch.cuda.device(self.device):
+            for name in ("q", "k", "v", "o"):
+                ptr, h = C.c_void_p(), (C.c_ubyte * 64)()
+                check(lib.psa_peer_alloc(nbytes, C.byref(ptr), h), "psa_peer_alloc")
+                self._own[name] = ptr.value
+                handles[name] = bytes(h)
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, handles, group=group)
+        self._peer = {name: [0] * self.world for name in ("q", "k", "v", "o")}
+        with torch.cuda.device(self.device):
+            for r, hs in enumerate(gathered):
+                for name in ("q", "k", "v", "o"):
+                    if r == self.rank:
+                        self._peer[name][r] = self._own[name]
+                    else:
+                        ptr = C.c_void_p()
+                        buf = (C.c_ubyte * 64).from_buffer_copy(hs[name])
+                        check(lib.psa_peer_open(buf, C.byref(ptr)), "psa_peer_open")
+                        self._peer[name][r] = ptr.value
+                        self._opened.append(ptr.value)
+        shape = (self.tokens_per_rank, heads, head_dim)
+        self.q, self.k, self.v, self.o = (_as_tensor(self._own[n], shape, dtype, self.device) for n in ("q", "k", "v", "o"))
+        self._ptr_arrays = {n: (C.c_void_p * self.world)(*self._peer[n]) for n in ("q", "k", "v", "o")}
+
+    def pull(self, first: int = 0, count: int = None, out: torch.Tensor = None, max_blocks: int = 0,
+             names=("q", "k", "v")) -> torch.Tensor:
+        """This rank's local heads [first, first+count) of all tokens: [3, count, S, D] (rows q, k, v), read from the
+        peers.  `names` restricts the copy to some of the three (the other rows of `out` are left alone), so that e.g.
+        v can follow on a second stream while the scores are computed from q and k.  max_blocks > 0 caps the copy
+        kernel's grid (use a few dozen when it runs under compute kernels)."""
+        count = self.heads_per_rank - first if count is None else count
+        if out is None:
+            out = torch.empty((3, count, self.seq, self.head_dim), dtype=self.dtype, device=self.device)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            for i, name in enumerate(("q", "k", "v")):
+                if name not in names:
+                    continue
+                rc = self.lib.psa_pull_heads(self._ptr_arrays[name], self.world, out[i].data_ptr(), self.tokens_per_rank, self.heads,
+                                             self.head0 + first, count, self.head_dim, self.elem_bytes, int(max_blocks),
+                                             self.rank, stream)
+                self.check(rc, "psa_pull_heads")
+        return out
+
+    def forward_scatter(self, q: torch.Tensor, images, mask: torch.Tensor, block_m: int, block_n: int, tile_n: int,
+                        first: int = 0, sm_scale: float = None, compat_quirk: bool = True) -> torch.Tensor:
+        """Tile-image forward on local heads [first, first+q.shape[-3]); output rows land in the owners' `o` buffers.
+        Returns the device status word of the launch."""
+        from .ops import _dt
+        hc, S, D = q.shape[-3], q.shape[-2], q.shape[-1]
+        sm_scale = D ** -0.5 if sm_scale is None else sm_scale
+        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            rc = self.lib.psa_fwd_images_scatter(q.data_ptr(), images.kimg.data_ptr(), images.vimg.data_ptr(), mask.data_ptr(),
+                                                 self._ptr_arrays["o"], self.world, self.tokens_per_rank, self.heads,
+                                                 self.head0 + first, hc, S, S, D, block_m, block_n, tile_n, mask.shape[-1],
+                                                 float(sm_scale), int(compat_quirk), _dt(q), status.data_ptr(), stream)
+        self.check(rc, "psa_fwd_images_scatter")
+        return status
+
+    def close(self):
+        """Unmap the peers' buffers and free the own ones (all ranks must be past their last use: barrier first)."""
+        with torch.cuda.device(self.device):
+            for p in self._opened:
+                self.lib.psa_peer_close(p)
+            self._opened = []
+            self.q = self.k = self.v = self.o = None
+            for p in self._own.values():
+                self.lib.psa_peer_free(p)
+            self._own = {}
