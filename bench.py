@@ -123,8 +123,9 @@ def main():
     ap.add_argument("--sparsity", default="90", choices=["90", "85"])
     ap.add_argument("--chunks", type=int, default=5, help="head chunks per rank for exchange/compute overlap (N>1)")
     ap.add_argument("--pull-blocks", type=int, default=32, help="grid cap of the prefetching peer pulls (p2p exchange)")
-    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
-                    help="N>1: peer-memory pull + scatter by our kernels (p2p) or NCCL all-to-all (nccl)")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-pull", "nccl"],
+                    help="N>1: our kernels over peer memory - rows pushed to the head owners (p2p) or pulled by them (p2p-pull), "
+                         "output rows stored into the token owners' buffers - or NCCL all-to-all (nccl)")
     ap.add_argument("--heads", type=int, default=0, help="override the head count (smaller captures for profilers)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -196,7 +197,7 @@ def main():
     shard = HeadShard(world, rank, H, S, D)
     to_head_sharded, to_seq_sharded = shard.to_head_sharded, shard.to_seq_sharded
     peer = None
-    if world > 1 and args.exchange == "p2p":
+    if world > 1 and args.exchange != "nccl":
         peer = PeerExchange(H, S, D, dtype, dev)
         peer.q.copy_(seq_shard[0]); peer.k.copy_(seq_shard[1]); peer.v.copy_(seq_shard[2])
         torch.cuda.synchronize()
@@ -267,28 +268,28 @@ def main():
         return out_final, mask, out
 
     pull_buf = None
+    step_no = 0
 
     def layer_step_p2p(rec, cur):
-        """N > 1 without a collective.  The rows of this rank's heads are pulled out of the peers' q/k/v buffers by a copy
-        kernel: q and k first, at full width; v follows on the second stream with a small grid while the scores and the
-        level assignment (which need only q and k) run.  The forward stores its output rows into the owners' buffers.
-        The only cross-rank synchronisation is the barrier that says "every rank's q/k/v are in place"."""
-        nonlocal pull_buf
-        dist.barrier()                                         # inputs of all ranks are in their exchange buffers
-        if pull_buf is None:
-            pull_buf = torch.empty((3, hp, S, D), dtype=dtype, device=dev)
-        comm_stream.wait_stream(cur)
-        with torch.cuda.stream(comm_stream):
-            timed("a2a_in", lambda: peer.pull(out=pull_buf, names=("q", "k")), rec, comm_stream)
-            e_qk = ev(); e_qk.record(comm_stream)
-            timed("a2a_in", lambda: peer.pull(out=pull_buf, names=("v",), max_blocks=args.pull_blocks), rec, comm_stream)
-            e_v = ev(); e_v.record(comm_stream)
-        iq, ik = timed("sample", draw_indices, rec)            # independent of the data: runs under the pull
-        cur.wait_event(e_qk)
-        qq, kk, vv = pull_buf[0].unsqueeze(0), pull_buf[1].unsqueeze(0), pull_buf[2].unsqueeze(0)
+        """N > 1 without a collective: q/k/v rows travel by our own copy kernel over peer memory (pushed by the token owners,
+        or pulled by the head owners), the forward stores its output rows into the token owners' buffers, and the only
+        cross-rank synchronisation is one barrier per step."""
+        nonlocal pull_buf, step_no
+        step_no += 1
+        iq, ik = timed("sample", draw_indices, rec)            # data-independent: before the exchange
+        if args.exchange == "p2p":
+            # sender-driven: every rank stores its rows into the owners' receive buffers (alternating between steps), and one
+            # barrier after the pushes tells every rank that its buffer is complete
+            x = timed("a2a_in", lambda: peer.push(step_no & 1), rec)
+            dist.barrier()
+        else:
+            dist.barrier()                                     # inputs of all ranks are in their exchange buffers
+            if pull_buf is None:
+                pull_buf = torch.empty((3, hp, S, D), dtype=dtype, device=dev)
+            x = timed("a2a_in", lambda: peer.pull(out=pull_buf), rec)
+        qq, kk, vv = x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0)
         po = timed("scores", lambda: ops.block_scores(qq, kk, iq, ik, BLOCK_M, BLOCK_N), rec)
         mask = timed("assign", lambda: ops.assign_levels(po, ratios, "topk_newtype", BLOCK_N, TILE_N), rec)
-        cur.wait_event(e_v)
         pyr = timed("pyramid", lambda: ops.pyramid_kv_images(kk, vv, BLOCK_N), rec)
         status = timed("forward", lambda: peer.forward_scatter(qq, pyr, mask, BLOCK_M, BLOCK_N, TILE_N), rec)
         holder = torch.empty(0, device=dev)

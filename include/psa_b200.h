@@ -169,13 +169,31 @@ int psa_legacy_bwd(const void* q, const void* k, const void* v, const void* k2, 
  *
  * psa_fwd_images_scatter: psa_fwd_images whose output rows go to the rank that owns the token:
  * peer_out[t / tokens_per_rank] laid out [tokens_per_rank][heads_total][head_dim], this rank writing heads
- * [head0, head0+bh).  peer_out is a HOST array of n_peers device-accessible pointers. */
+ * [head0, head0+bh).  peer_out is a HOST array of n_peers device-accessible pointers.
+ *
+ * psa_block_scores_peers / psa_pyramid_kv_images_peers: psa_block_scores (tcgen05 path) and psa_pyramid_kv_images whose
+ * row-major inputs are read straight from the peers' buffers (same layout and pointer arrays as psa_pull_heads), so
+ * k and v never need a local row-major copy: the score kernels touch only the sampled quarter of the q/k rows, and the
+ * image builder reads every k/v element exactly once, over NVLink.  seq = n_peers * tokens_per_rank. */
+int psa_block_scores_peers(const void* const* peer_q, const void* const* peer_k, int n_peers, int64_t tokens_per_rank,
+                           int heads_total, int head0, const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch,
+                           size_t scratch_bytes, int64_t heads_local, int head_dim, int block_m, int block_n, int dtype,
+                           void* stream);
+int psa_pyramid_kv_images_peers(const void* const* peer_k, const void* const* peer_v, int n_peers, int64_t tokens_per_rank,
+                                int heads_total, int head0, void* kimg, void* vimg, int64_t heads_local, int head_dim,
+                                int block_n, int dtype, int max_blocks, void* stream);
 int psa_peer_alloc(size_t bytes, void** ptr, void* handle64);
 int psa_peer_open(const void* handle64, void** ptr);
 int psa_peer_close(void* ptr);
 int psa_peer_free(void* ptr);
 int psa_pull_heads(const void* const* peer_src, int n_peers, void* dst, int64_t tokens_per_rank, int heads_total, int head0,
                    int heads_local, int head_dim, int elem_bytes, int max_blocks, int self_rank, void* stream);
+/* The same exchange in the other direction: this rank's rows src [tokens_per_rank][heads_total][head_dim] are stored into
+ * the peers' head-sharded buffers peer_dst[r] = [heads_total/n_peers][n_peers*tokens_per_rank][head_dim] (rank r owns
+ * heads [r*hp, (r+1)*hp)).  One sequential pass over local memory, posted stores over NVLink.  The receivers may read
+ * their buffers after a barrier that follows this call on every rank. */
+int psa_push_heads(const void* src, void* const* peer_dst, int n_peers, int64_t tokens_per_rank, int heads_total, int head_dim,
+                   int elem_bytes, int self_rank, int max_blocks, void* stream);
 int psa_fwd_images_scatter(const void* q, const void* kimg, const void* vimg, const int32_t* mask, void* const* peer_out,
                            int n_peers, int64_t tokens_per_rank, int heads_total, int head0, int64_t bh, int64_t seq_q,
                            int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width, float sm_scale,

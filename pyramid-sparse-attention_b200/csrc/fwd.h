@@ -36,6 +36,32 @@ struct OutScatter {
   int64_t tokens_per_rank;
 };
 
+// Where a row-major operand [bh][seq][D] lives.  n_peers == 0: one local tensor.  n_peers > 0 (head-sharded run, one
+// batch): token t of local head h is row (t % tokens_per_rank) of peer t / tokens_per_rank, whose buffer is laid out
+// [tokens_per_rank][heads_total][D]; kernels read it with plain loads.
+struct RowSource {
+  const void* base;
+  const void* peer[kMaxPeers];
+  int n_peers;
+  int heads_total, head0;
+  int64_t tokens_per_rank;
+};
+
+inline RowSource local_rows(const void* base) {
+  RowSource r = {};
+  r.base = base;
+  return r;
+}
+
+#ifdef __CUDACC__
+// 16-byte word `c` of the row of token `tok` of local head `bh` (row16 words per row)
+__device__ __forceinline__ const uint4* row_word(const RowSource& s, int64_t bh, int64_t seq, int64_t tok, int row16, int c) {
+  if (s.n_peers == 0) return reinterpret_cast<const uint4*>(s.base) + (bh * seq + tok) * row16 + c;
+  const int64_t owner = tok / s.tokens_per_rank, local = tok - owner * s.tokens_per_rank;
+  return reinterpret_cast<const uint4*>(s.peer[owner]) + (local * s.heads_total + s.head0 + bh) * row16 + c;
+}
+#endif
+
 struct FwdArgs {
   const void* q;
   const void* k[4];  // levels 1, 2, 4, 8

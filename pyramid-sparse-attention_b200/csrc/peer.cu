@@ -65,7 +65,74 @@ __global__ void __launch_bounds__(512) pull_heads_kernel(const PullArgs a) {
   }
 }
 
+// The opposite direction: every rank sends the rows of its own tokens to the ranks that own the heads.  Reads are one
+// sequential pass over the local buffer; the remote side sees posted 16-byte stores that fill whole 256-byte rows.
+struct PushArgs {
+  const uint4* src;          // [tokens_per_rank][heads_total][row16]
+  uint4* dst[kMaxPeers];     // peer r: [heads_per_rank][tokens][row16], holding heads [r*heads_per_rank, ...)
+  int n_peers, heads_total, heads_per_rank, row16, self_rank;
+  int64_t tokens_per_rank, tokens;
+};
+
+__global__ void __launch_bounds__(512) push_heads_kernel(const PushArgs a) {
+  const int64_t per_token = (int64_t)a.heads_total * a.row16;
+  const int64_t total = a.tokens_per_rank * per_token;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int64_t t0 = (int64_t)a.self_rank * a.tokens_per_rank;
+  int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; w + (kPullUnroll - 1) * stride < total; w += kPullUnroll * stride) {
+    uint4 v[kPullUnroll];
+#pragma unroll
+    for (int u = 0; u < kPullUnroll; ++u) v[u] = a.src[w + u * stride];
+#pragma unroll
+    for (int u = 0; u < kPullUnroll; ++u) {
+      const int64_t i = w + u * stride;
+      const int64_t t = i / per_token;
+      const int rem = (int)(i - t * per_token);
+      const int h = rem / a.row16, c = rem - h * a.row16;
+      const int owner = h / a.heads_per_rank, hl = h - owner * a.heads_per_rank;
+      a.dst[owner][((int64_t)hl * a.tokens + t0 + t) * a.row16 + c] = v[u];
+    }
+  }
+  for (; w < total; w += stride) {
+    const int64_t t = w / per_token;
+    const int rem = (int)(w - t * per_token);
+    const int h = rem / a.row16, c = rem - h * a.row16;
+    const int owner = h / a.heads_per_rank, hl = h - owner * a.heads_per_rank;
+    a.dst[owner][((int64_t)hl * a.tokens + t0 + t) * a.row16 + c] = a.src[w];
+  }
+}
+
 }  // namespace psa
+
+extern "C" int psa_push_heads(const void* src, void* const* peer_dst, int n_peers, int64_t tokens_per_rank, int heads_total,
+                              int head_dim, int elem_bytes, int self_rank, int max_blocks, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(src && peer_dst, PSA_ERR_ARG, "psa_push_heads: null pointer");
+  PSA_REQUIRE(n_peers >= 1 && n_peers <= kMaxPeers && self_rank >= 0 && self_rank < n_peers, PSA_ERR_ARG,
+              "psa_push_heads: rank %d of %d (at most %d)", self_rank, n_peers, kMaxPeers);
+  PSA_REQUIRE(tokens_per_rank > 0 && heads_total > 0 && heads_total % n_peers == 0, PSA_ERR_ARG,
+              "psa_push_heads: %d heads do not divide over %d ranks", heads_total, n_peers);
+  PSA_REQUIRE(head_dim > 0 && (elem_bytes == 2 || elem_bytes == 4) && (head_dim * elem_bytes) % 16 == 0 && max_blocks >= 0, PSA_ERR_ARG,
+              "psa_push_heads: rows must be a multiple of 16 bytes");
+  PSA_REQUIRE(((uintptr_t)src & 15) == 0, PSA_ERR_ARG, "psa_push_heads: src must be 16-byte aligned");
+  PushArgs a;
+  a.src = (const uint4*)src;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    a.dst[i] = i < n_peers ? (uint4*)peer_dst[i] : nullptr;
+    if (i < n_peers) PSA_REQUIRE(peer_dst[i] && ((uintptr_t)peer_dst[i] & 15) == 0, PSA_ERR_ARG, "psa_push_heads: peer %d pointer", i);
+  }
+  a.n_peers = n_peers; a.heads_total = heads_total; a.heads_per_rank = heads_total / n_peers;
+  a.row16 = head_dim * elem_bytes / 16; a.self_rank = self_rank;
+  a.tokens_per_rank = tokens_per_rank; a.tokens = tokens_per_rank * n_peers;
+  const int64_t total = tokens_per_rank * heads_total * a.row16;
+  int64_t blocks = cdiv64(total, 512 * kPullUnroll);
+  const int64_t cap = max_blocks > 0 ? max_blocks : 148 * 2;
+  if (blocks > cap) blocks = cap;
+  push_heads_kernel<<<(unsigned)blocks, 512, 0, (cudaStream_t)stream>>>(a);
+  PSA_CHECK_LAUNCH("psa_push_heads");
+  return PSA_OK;
+}
 
 extern "C" int psa_peer_alloc(size_t bytes, void** ptr, void* handle64) {
   using namespace psa;

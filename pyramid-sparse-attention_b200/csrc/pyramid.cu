@@ -123,10 +123,10 @@ __device__ __forceinline__ void img_store(unsigned char* base, int64_t bh, int64
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) pyramid_img_kernel(const T* __restrict__ k, const T* __restrict__ v, unsigned char* __restrict__ kimg,
+__global__ void __launch_bounds__(256) pyramid_img_kernel(const RowSource k, const RowSource v, unsigned char* __restrict__ kimg,
                                                           unsigned char* __restrict__ vimg, ImgLevels L, int64_t bh, int64_t S, int64_t n8,
                                                           int cpr) {
-  const T* x = blockIdx.y ? v : k;
+  const RowSource& x = blockIdx.y ? v : k;
   unsigned char* img = blockIdx.y ? vimg : kimg;
   const int slabs = cpr / 8;
   const int64_t total = bh * n8 * cpr;
@@ -135,13 +135,12 @@ __global__ void __launch_bounds__(256) pyramid_img_kernel(const T* __restrict__ 
     const int64_t g = w / cpr;
     const int64_t head = g / n8;
     const int64_t j = g % n8;
-    const uint4* src = reinterpret_cast<const uint4*>(x) + head * S * cpr + c;
     uint4 r[8];
 #pragma unroll
     for (int t = 0; t < 8; ++t) {
       int64_t tok = j * 8 + t;
       tok = tok < S ? tok : S - 1;
-      r[t] = __ldg(src + tok * cpr);
+      r[t] = *row_word(x, head, S, tok, cpr, c);
     }
     uint4 a[4], b[2], d;
 #pragma unroll
@@ -167,6 +166,26 @@ extern "C" size_t psa_kv_image_bytes(int64_t bh, int64_t seq, int head_dim, int 
   return (size_t)(L.off[3] + bh * L.groups[3] * (head_dim / 64) * 1024);
 }
 
+namespace psa {
+static int launch_pyramid_images(const RowSource& k, const RowSource& v, void* kimg, void* vimg, int64_t bh, int64_t seq, int head_dim,
+                                 int block_n, int dtype, int max_blocks, cudaStream_t st) {
+  const ImgLevels L = make_img_levels(bh, seq, head_dim, block_n);
+  const int64_t s_pad = cdiv64(seq, block_n) * block_n;
+  const int64_t n8 = s_pad / 8;
+  const int cpr = head_dim * 2 / 16;
+  int64_t blocks = cdiv64(bh * n8 * cpr, 256);
+  const int64_t cap = max_blocks > 0 ? max_blocks : 148 * 16;
+  if (blocks > cap) blocks = cap;
+  dim3 grid((unsigned)blocks, 2);
+  if (dtype == PSA_F16)
+    pyramid_img_kernel<__half><<<grid, 256, 0, st>>>(k, v, (unsigned char*)kimg, (unsigned char*)vimg, L, bh, seq, n8, cpr);
+  else
+    pyramid_img_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(k, v, (unsigned char*)kimg, (unsigned char*)vimg, L, bh, seq, n8, cpr);
+  PSA_CHECK_LAUNCH("psa_pyramid_kv_images");
+  return PSA_OK;
+}
+}  // namespace psa
+
 extern "C" int psa_pyramid_kv_images(const void* k, const void* v, void* kimg, void* vimg, int64_t bh, int64_t seq, int head_dim,
                                      int block_n, int dtype, void* stream) {
   using namespace psa;
@@ -178,20 +197,32 @@ extern "C" int psa_pyramid_kv_images(const void* k, const void* v, void* kimg, v
   // alignment) is all the base needs
   PSA_REQUIRE((((uintptr_t)k | (uintptr_t)v | (uintptr_t)kimg | (uintptr_t)vimg) & 15) == 0, PSA_ERR_ARG,
               "psa_pyramid_kv_images: k, v and the images must be 16-byte aligned");
-  const ImgLevels L = make_img_levels(bh, seq, head_dim, block_n);
-  const int64_t s_pad = cdiv64(seq, block_n) * block_n;
-  const int64_t n8 = s_pad / 8;
-  const int cpr = head_dim * 2 / 16;
-  int64_t blocks = cdiv64(bh * n8 * cpr, 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  dim3 grid((unsigned)blocks, 2);
-  if (dtype == PSA_F16)
-    pyramid_img_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>((const __half*)k, (const __half*)v, (unsigned char*)kimg,
-                                                                       (unsigned char*)vimg, L, bh, seq, n8, cpr);
-  else
-    pyramid_img_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
-                                                                              (unsigned char*)kimg, (unsigned char*)vimg, L, bh, seq, n8,
-                                                                              cpr);
-  PSA_CHECK_LAUNCH("psa_pyramid_kv_images");
-  return PSA_OK;
+  return launch_pyramid_images(local_rows(k), local_rows(v), kimg, vimg, bh, seq, head_dim, block_n, dtype, 0, (cudaStream_t)stream);
+}
+
+extern "C" int psa_pyramid_kv_images_peers(const void* const* peer_k, const void* const* peer_v, int n_peers, int64_t tokens_per_rank,
+                                           int heads_total, int head0, void* kimg, void* vimg, int64_t heads_local, int head_dim,
+                                           int block_n, int dtype, int max_blocks, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(peer_k && peer_v && kimg && vimg, PSA_ERR_ARG, "psa_pyramid_kv_images_peers: null pointer");
+  PSA_REQUIRE(n_peers >= 1 && n_peers <= kMaxPeers, PSA_ERR_ARG, "psa_pyramid_kv_images_peers: n_peers=%d (1..%d)", n_peers, kMaxPeers);
+  PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "psa_pyramid_kv_images_peers: 16-bit element types only");
+  PSA_REQUIRE(heads_local > 0 && head0 >= 0 && head0 + heads_local <= heads_total && tokens_per_rank > 0 && max_blocks >= 0,
+              PSA_ERR_ARG, "psa_pyramid_kv_images_peers: bad head range, shard size or grid cap");
+  const int64_t seq = tokens_per_rank * n_peers;
+  PSA_REQUIRE(psa_kv_image_bytes(heads_local, seq, head_dim, block_n) > 0, PSA_ERR_ARG,
+              "psa_pyramid_kv_images_peers: needs head_dim 64/128 and block_n a multiple of 64 (got %d, %d)", head_dim, block_n);
+  PSA_REQUIRE((((uintptr_t)kimg | (uintptr_t)vimg) & 15) == 0, PSA_ERR_ARG, "psa_pyramid_kv_images_peers: images must be 16-byte aligned");
+  RowSource k = {}, v = {};
+  for (int i = 0; i < n_peers; ++i) {
+    PSA_REQUIRE(peer_k[i] && peer_v[i] && (((uintptr_t)peer_k[i] | (uintptr_t)peer_v[i]) & 15) == 0, PSA_ERR_ARG,
+                "psa_pyramid_kv_images_peers: peer %d pointer", i);
+    k.peer[i] = peer_k[i];
+    v.peer[i] = peer_v[i];
+  }
+  k.n_peers = v.n_peers = n_peers;
+  k.heads_total = v.heads_total = heads_total;
+  k.head0 = v.head0 = head0;
+  k.tokens_per_rank = v.tokens_per_rank = tokens_per_rank;
+  return launch_pyramid_images(k, v, kimg, vimg, heads_local, seq, head_dim, block_n, dtype, max_blocks, (cudaStream_t)stream);
 }

@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(256) scores_pool_normalise(const T* __restrict
 }
 
 template <typename T>
-static int launch_scores(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* po,
+static int launch_scores(const RowSource& q, const RowSource& k, const int32_t* idx_q, const int32_t* idx_k, void* po,
                          void* scratch, const ScoreDims& d, int64_t bh, int impl, cudaStream_t st) {
   T* R = (T*)scratch;
   const size_t r_bytes = ((size_t)bh * d.nq_s * d.n_d * sizeof(T) + 255) & ~(size_t)255;
@@ -174,8 +174,9 @@ static int launch_scores(const void* q, const void* k, const int32_t* idx_q, con
                                       (std::is_same<T, __half>::value ? PSA_F16 : PSA_BF16), st);
     if (rc != PSA_OK) return rc;
   } else {
+    PSA_REQUIRE(q.n_peers == 0 && k.n_peers == 0, PSA_ERR_UNSUPPORTED, "the scalar score kernel reads local tensors only");
     dim3 grid((unsigned)cdiv64(d.nq_s, 64), (unsigned)bh);
-    scores_cellmax_simt<T><<<grid, 256, 0, st>>>((const T*)q, (const T*)k, idx_q, idx_k, R, rowmax, d);
+    scores_cellmax_simt<T><<<grid, 256, 0, st>>>((const T*)q.base, (const T*)k.base, idx_q, idx_k, R, rowmax, d);
     PSA_CHECK_LAUNCH("psa_block_scores(stage A)");
   }
   dim3 gridb((unsigned)d.Mq, (unsigned)bh);
@@ -232,7 +233,7 @@ extern "C" int psa_block_scores(const void* q, const void* k, const int32_t* idx
               "psa_block_scores: scratch too small (%zu bytes)", scratch_bytes);
   PSA_REQUIRE(impl >= 0 && impl <= 2, PSA_ERR_ARG, "psa_block_scores: impl=%d", impl);
   cudaStream_t st = (cudaStream_t)stream;
-  PSA_DISPATCH_DTYPE(dtype, T, return launch_scores<T>(q, k, idx_q, idx_k, po, scratch, d, bh, impl, st));
+  PSA_DISPATCH_DTYPE(dtype, T, return launch_scores<T>(local_rows(q), local_rows(k), idx_q, idx_k, po, scratch, d, bh, impl, st));
   return PSA_OK;
 }
 
@@ -292,6 +293,40 @@ extern "C" int psa_block_scores_static(const void* q, const void* k, const int32
   rc = static_scratch_ptr(&scratch);
   if (rc != PSA_OK) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  PSA_DISPATCH_DTYPE(dtype, T, return launch_scores<T>(q, k, idx_q, idx_k, po, scratch, d, bh, impl, st));
+  PSA_DISPATCH_DTYPE(dtype, T, return launch_scores<T>(local_rows(q), local_rows(k), idx_q, idx_k, po, scratch, d, bh, impl, st));
   return PSA_OK;
+}
+
+extern "C" int psa_block_scores_peers(const void* const* peer_q, const void* const* peer_k, int n_peers, int64_t tokens_per_rank,
+                                      int heads_total, int head0, const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch,
+                                      size_t scratch_bytes, int64_t heads_local, int head_dim, int block_m, int block_n, int dtype,
+                                      void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(peer_q && peer_k && idx_q && idx_k && po && scratch, PSA_ERR_ARG, "psa_block_scores_peers: null pointer");
+  PSA_REQUIRE(n_peers >= 1 && n_peers <= kMaxPeers, PSA_ERR_ARG, "psa_block_scores_peers: n_peers=%d (1..%d)", n_peers, kMaxPeers);
+  PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "psa_block_scores_peers: f16/bf16 only");
+  PSA_REQUIRE(heads_local > 0 && head0 >= 0 && head0 + heads_local <= heads_total && tokens_per_rank > 0, PSA_ERR_ARG,
+              "psa_block_scores_peers: bad head range or shard size");
+  PSA_REQUIRE(((uintptr_t)scratch & 255) == 0, PSA_ERR_ARG, "psa_block_scores_peers: scratch must be 256-byte aligned");
+  const int64_t seq = tokens_per_rank * n_peers;
+  ScoreDims d;
+  int rc = make_score_dims(d, seq, seq, head_dim, block_m, block_n);
+  if (rc != PSA_OK) return rc;
+  PSA_REQUIRE(scores_tc_supported(d), PSA_ERR_UNSUPPORTED, "psa_block_scores_peers: block sizes not covered by the tcgen05 path");
+  PSA_REQUIRE(scratch_bytes >= psa_block_scores_scratch_bytes(heads_local, seq, seq, block_m, block_n, dtype), PSA_ERR_ARG,
+              "psa_block_scores_peers: scratch too small (%zu bytes)", scratch_bytes);
+  RowSource q = {}, k = {};
+  for (int i = 0; i < n_peers; ++i) {
+    PSA_REQUIRE(peer_q[i] && peer_k[i] && (((uintptr_t)peer_q[i] | (uintptr_t)peer_k[i]) & 15) == 0, PSA_ERR_ARG,
+                "psa_block_scores_peers: peer %d pointer", i);
+    q.peer[i] = peer_q[i];
+    k.peer[i] = peer_k[i];
+  }
+  q.n_peers = k.n_peers = n_peers;
+  q.heads_total = k.heads_total = heads_total;
+  q.head0 = k.head0 = head0;
+  q.tokens_per_rank = k.tokens_per_rank = tokens_per_rank;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == PSA_F16) return launch_scores<__half>(q, k, idx_q, idx_k, po, scratch, d, heads_local, 2, st);
+  return launch_scores<__nv_bfloat16>(q, k, idx_q, idx_k, po, scratch, d, heads_local, 2, st);
 }

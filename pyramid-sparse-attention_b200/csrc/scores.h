@@ -4,6 +4,8 @@
 #include <stdint.h>
 #include <type_traits>
 
+#include "fwd.h"
+
 namespace psa {
 
 struct ScoreDims {
@@ -23,7 +25,7 @@ int make_score_dims(ScoreDims& d, int64_t seq_q, int64_t seq_k, int D, int bm, i
 bool scores_tc_supported(const ScoreDims& d);
 // bytes of scratch the tcgen05 path needs beyond R and rowmax (compacted sample matrices)
 size_t scores_tc_extra_scratch(const ScoreDims& d, int64_t bh);
-int launch_scores_cellmax_tc(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* R,
+int launch_scores_cellmax_tc(const RowSource& q, const RowSource& k, const int32_t* idx_q, const int32_t* idx_k, void* R,
                              float* rowmax, void* extra, const ScoreDims& d, int64_t bh, int dtype, cudaStream_t st);
 
 }  // namespace psa

@@ -22,12 +22,11 @@ constexpr int kThreads = 192;
 constexpr int kStages = 2;
 
 template <typename T>
-__global__ void __launch_bounds__(256) gather_samples_kernel(const T* __restrict__ x, const int32_t* __restrict__ idx,
+__global__ void __launch_bounds__(256) gather_samples_kernel(const RowSource x, const int32_t* __restrict__ idx,
                                                              T* __restrict__ out, int64_t seq, int D, int block, int keep,
                                                              int n_valid, int n_out) {
   const int cpr = D * (int)sizeof(T) / 16;
   const int64_t bh = blockIdx.y;
-  const uint4* src = reinterpret_cast<const uint4*>(x + bh * seq * D);
   uint4* dst = reinterpret_cast<uint4*>(out + bh * (int64_t)n_out * D);
   const int64_t total = (int64_t)n_out * cpr;
   for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
@@ -36,7 +35,7 @@ __global__ void __launch_bounds__(256) gather_samples_kernel(const T* __restrict
     const int ic = i < n_valid ? i : n_valid - 1;
     int64_t tok = (int64_t)(ic / keep) * block + idx[bh * keep + (ic % keep)];
     tok = tok < seq ? tok : seq - 1;
-    dst[(int64_t)i * cpr + c] = __ldg(src + tok * cpr + c);
+    dst[(int64_t)i * cpr + c] = *row_word(x, bh, seq, tok, cpr, c);
   }
 }
 
@@ -249,8 +248,8 @@ size_t scores_tc_extra_scratch(const ScoreDims& d, int64_t bh) {
   return qb + kb;
 }
 
-int launch_scores_cellmax_tc(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* R, float* rowmax,
-                             void* extra, const ScoreDims& d, int64_t bh, int dtype, cudaStream_t st) {
+int launch_scores_cellmax_tc(const RowSource& q, const RowSource& k, const int32_t* idx_q, const int32_t* idx_k, void* R,
+                             float* rowmax, void* extra, const ScoreDims& d, int64_t bh, int dtype, cudaStream_t st) {
   PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "the tcgen05 score kernel needs f16/bf16 inputs");
   PSA_REQUIRE(scores_tc_supported(d), PSA_ERR_UNSUPPORTED, "the tcgen05 score kernel does not cover this block size");
   const size_t qb = ((size_t)bh * d.nq_s * d.D * 2 + 255) & ~(size_t)255;
@@ -260,9 +259,9 @@ int launch_scores_cellmax_tc(const void* q, const void* k, const int32_t* idx_q,
     const int cpr = d.D * 2 / 16;
     dim3 gq((unsigned)std::min<int64_t>(cdiv64((int64_t)d.nq_s * cpr, 256), 148 * 8), (unsigned)bh);
     dim3 gk((unsigned)std::min<int64_t>(cdiv64((int64_t)d.nk_cols * cpr, 256), 148 * 8), (unsigned)bh);
-    gather_samples_kernel<uint16_t><<<gq, 256, 0, st>>>((const uint16_t*)q, idx_q, (uint16_t*)qs, d.seq_q, d.D, d.bm, d.kq,
+    gather_samples_kernel<uint16_t><<<gq, 256, 0, st>>>(q, idx_q, (uint16_t*)qs, d.seq_q, d.D, d.bm, d.kq,
                                                          d.nq_s, d.nq_s);
-    gather_samples_kernel<uint16_t><<<gk, 256, 0, st>>>((const uint16_t*)k, idx_k, (uint16_t*)ks, d.seq_k, d.D, d.bn, d.kk,
+    gather_samples_kernel<uint16_t><<<gk, 256, 0, st>>>(k, idx_k, (uint16_t*)ks, d.seq_k, d.D, d.bn, d.kk,
                                                          d.nk_s, d.nk_cols);
     PSA_CHECK_LAUNCH("psa_block_scores(gather)");
   }

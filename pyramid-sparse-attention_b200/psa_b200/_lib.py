@@ -33,6 +33,9 @@ SIGNATURES = {
     "psa_pyramid_kv_images": (_i, [_p] * 4 + [_i64, _i64, _i, _i, _i, _p]),
     "psa_fwd_images": (_i, [_p] * 5 + [_i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]),
     "psa_fwd_images_scatter": (_i, [_p] * 5 + [_i, _i64, _i, _i, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]),
+    "psa_block_scores_peers": (_i, [_p, _p, _i, _i64, _i, _i, _p, _p, _p, _p, _sz, _i64, _i, _i, _i, _i, _p]),
+    "psa_pyramid_kv_images_peers": (_i, [_p, _p, _i, _i64, _i, _i, _p, _p, _i64, _i, _i, _i, _i, _p]),
+    "psa_push_heads": (_i, [_p, _p, _i, _i64, _i, _i, _i, _i, _i, _p]),
     "psa_peer_alloc": (_i, [_sz, _p, _p]),
     "psa_peer_open": (_i, [_p, _p]),
     "psa_peer_close": (_i, [_p]),

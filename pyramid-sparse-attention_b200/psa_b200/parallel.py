@@ -106,11 +106,12 @@ class PeerExchange:
     an IPC handle exists for them.  After construction:
       * `q`, `k`, `v`, `o` are torch views of this rank's own buffers (the surrounding model writes q/k/v, reads o);
       * `pull()` returns this rank's heads of all tokens, [3, H/P, S, D], read from the peers' buffers;
+      * `push(parity)` is the same exchange driven by the senders (posted stores into the peers' receive buffers);
       * `forward_scatter(...)` runs the tile-image forward and stores every output row into the owner's `o`.
     The caller places a barrier between "all ranks wrote q/k/v" and pull(), and between forward_scatter() and reading o.
     """
 
-    def __init__(self, heads: int, seq: int, head_dim: int, dtype: torch.dtype, device, group=None):
+    def __init__(self, heads: int, seq: int, head_dim: int, dtype: torch.dtype, device, group=None, push_buffers: bool = True):
         from ._lib import lib, check
         self.lib, self.check = lib, check
         self.group = group
@@ -125,20 +126,26 @@ class PeerExchange:
         esz = torch.empty(0, dtype=dtype).element_size()
         self.elem_bytes = esz
         nbytes = self.tokens_per_rank * heads * head_dim * esz
+        # q/k/v/o: this rank's tokens, all heads.  r0/r1: two head-sharded receive buffers [3, H/P, S, D] for push()
+        # (alternating between steps, so a fast rank never overwrites what a slow one still reads).
+        sizes = {"q": nbytes, "k": nbytes, "v": nbytes, "o": nbytes}
+        if push_buffers:
+            sizes["r0"] = sizes["r1"] = 3 * self.heads_per_rank * seq * head_dim * esz
+        names = tuple(sizes)
         self._own, self._opened = {}, []
         handles = {}
         with torch.cuda.device(self.device):
-            for name in ("q", "k", "v", "o"):
+            for name in names:
                 ptr, h = C.c_void_p(), (C.c_ubyte * 64)()
-                check(lib.psa_peer_alloc(nbytes, C.byref(ptr), h), "psa_peer_alloc")
+                check(lib.psa_peer_alloc(sizes[name], C.byref(ptr), h), "psa_peer_alloc")
                 self._own[name] = ptr.value
                 handles[name] = bytes(h)
         gathered = [None] * self.world
         dist.all_gather_object(gathered, handles, group=group)
-        self._peer = {name: [0] * self.world for name in ("q", "k", "v", "o")}
+        self._peer = {name: [0] * self.world for name in names}
         with torch.cuda.device(self.device):
             for r, hs in enumerate(gathered):
-                for name in ("q", "k", "v", "o"):
+                for name in names:
                     if r == self.rank:
                         self._peer[name][r] = self._own[name]
                     else:
@@ -150,6 +157,26 @@ class PeerExchange:
         shape = (self.tokens_per_rank, heads, head_dim)
         self.q, self.k, self.v, self.o = (_as_tensor(self._own[n], shape, dtype, self.device) for n in ("q", "k", "v", "o"))
         self._ptr_arrays = {n: (C.c_void_p * self.world)(*self._peer[n]) for n in ("q", "k", "v", "o")}
+        self._recv, self._push_arrays = [], []
+        if push_buffers:
+            one = self.heads_per_rank * seq * head_dim * esz
+            for par in ("r0", "r1"):
+                self._recv.append(_as_tensor(self._own[par], (3, self.heads_per_rank, seq, head_dim), dtype, self.device))
+                self._push_arrays.append([(C.c_void_p * self.world)(*[p + i * one for p in self._peer[par]]) for i in range(3)])
+
+    def push(self, parity: int, names=("q", "k", "v"), max_blocks: int = 0) -> torch.Tensor:
+        """Send this rank's rows of q/k/v to the ranks that own the heads (receive buffer `parity` of every peer) and return
+        this rank's receive buffer [3, H/P, S, D].  It holds all ranks' rows once a barrier that every rank enqueues after
+        its push has completed."""
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            for i, name in enumerate(("q", "k", "v")):
+                if name not in names:
+                    continue
+                rc = self.lib.psa_push_heads(self._own[name], self._push_arrays[parity][i], self.world, self.tokens_per_rank,
+                                             self.heads, self.head_dim, self.elem_bytes, self.rank, int(max_blocks), stream)
+                self.check(rc, "psa_push_heads")
+        return self._recv[parity]
 
     def pull(self, first: int = 0, count: int = None, out: torch.Tensor = None, max_blocks: int = 0,
              names=("q", "k", "v")) -> torch.Tensor:
@@ -170,6 +197,43 @@ class PeerExchange:
                                              self.rank, stream)
                 self.check(rc, "psa_pull_heads")
         return out
+
+    def block_scores(self, idx_q: torch.Tensor, idx_k: torch.Tensor, block_m: int, block_n: int) -> torch.Tensor:
+        """Block scores [1, H/P, Mq, Nk] of this rank's heads; the sampled q/k rows are read from the peers' buffers."""
+        from .ops import _dt
+        hp = self.heads_per_rank
+        assert idx_q.shape == (1, hp, block_m // 4) and idx_k.shape == (1, hp, block_n // 4)
+        iq, ik = idx_q.to(torch.int32).contiguous(), idx_k.to(torch.int32).contiguous()
+        Mq, Nk = -(-self.seq // block_m), -(-self.seq // block_n)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            po = torch.empty((1, hp, Mq, Nk), dtype=self.dtype, device=self.device)
+            nbytes = self.lib.psa_block_scores_scratch_bytes(hp, self.seq, self.seq, block_m, block_n, _dt(po))
+            if nbytes == 0:
+                raise ValueError(f"unsupported block sizes m={block_m} n={block_n}")
+            scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            rc = self.lib.psa_block_scores_peers(self._ptr_arrays["q"], self._ptr_arrays["k"], self.world, self.tokens_per_rank,
+                                                 self.heads, self.head0, iq.data_ptr(), ik.data_ptr(), po.data_ptr(),
+                                                 scratch.data_ptr(), nbytes, hp, self.head_dim, block_m, block_n, _dt(po), stream)
+        self.check(rc, "psa_block_scores_peers")
+        return po
+
+    def pyramid_images(self, block_n: int, max_blocks: int = 0):
+        """Tile images of this rank's heads of K and V, every element read once from the peer that owns the token."""
+        from .ops import KVImages, _dt
+        hp = self.heads_per_rank
+        nbytes = self.lib.psa_kv_image_bytes(hp, self.seq, self.head_dim, block_n)
+        if nbytes == 0:
+            raise ValueError(f"tile images need head_dim 64/128 and block_n 64/128 (got {self.head_dim}, {block_n})")
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            kimg = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            vimg = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            rc = self.lib.psa_pyramid_kv_images_peers(self._ptr_arrays["k"], self._ptr_arrays["v"], self.world, self.tokens_per_rank,
+                                                      self.heads, self.head0, kimg.data_ptr(), vimg.data_ptr(), hp, self.head_dim,
+                                                      block_n, _dt(self.k), int(max_blocks), stream)
+        self.check(rc, "psa_pyramid_kv_images_peers")
+        return KVImages(kimg, vimg, block_n)
 
     def forward_scatter(self, q: torch.Tensor, images, mask: torch.Tensor, block_m: int, block_n: int, tile_n: int,
                         first: int = 0, sm_scale: float = None, compat_quirk: bool = True) -> torch.Tensor:
@@ -195,6 +259,7 @@ class PeerExchange:
                 self.lib.psa_peer_close(p)
             self._opened = []
             self.q = self.k = self.v = self.o = None
+            self._recv = []
             for p in self._own.values():
                 self.lib.psa_peer_free(p)
             self._own = {}

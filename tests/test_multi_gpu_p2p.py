@@ -53,6 +53,11 @@ def _worker(rank: int, world: int, port: int, H: int, S: int, D: int, q):
         assert torch.equal(got, want), "pull differs from the source data"
         part = ex.pull(first=1, count=hp - 1)
         assert torch.equal(part, ref[:, 1:])
+        for parity in (0, 1):
+            recv = ex.push(parity)
+            dist.barrier()                              # enqueued after the push on every rank
+            torch.cuda.synchronize()
+            assert torch.equal(recv, ref), "push differs from the all-to-all"
 
         # scattering forward == local forward + return all-to-all
         bm, bn, tn = 128, 64, 32
@@ -63,6 +68,10 @@ def _worker(rank: int, world: int, port: int, H: int, S: int, D: int, q):
         po = ops.block_scores(qq, kk, iq, ik, bm, bn)
         mask = ops.assign_levels(po, C.DEFAULT_RATIOS, "topk_newtype", bn, tn)
         imgs = ops.pyramid_kv_images(kk, vv, bn)
+        # the peer-reading variants of the score and image kernels see the same rows
+        assert torch.equal(ex.block_scores(iq, ik, bm, bn), po), "scores from peer rows differ"
+        peer_imgs = ex.pyramid_images(bn, max_blocks=24)
+        assert torch.equal(peer_imgs.kimg, imgs.kimg) and torch.equal(peer_imgs.vimg, imgs.vimg), "images from peer rows differ"
         local = ops.psa_forward(qq, kk, vv, mask, bm, bn, tn, pyramid=imgs)
         back = shard.to_seq_sharded(local[0])                              # [H, S/P, D]
         ex.o.zero_()
