@@ -54,6 +54,13 @@ class ClockSampler:
 
     def __init__(self, gpu_index: int):
         self.gpu_index, self.proc, self.lines = gpu_index, None, []
+        self.t_begin = self.t_end = None
+
+    def mark_begin(self):
+        self.t_begin = time.monotonic()
+
+    def mark_end(self):
+        self.t_end = time.monotonic()
 
     def start(self):
         try:
@@ -66,7 +73,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.monotonic(), line.strip()))
 
     def stop(self):
         if self.proc is None:
@@ -76,8 +83,14 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
+        # the sampler is started before the warm-up steps (nvidia-smi takes a while to come up); only the samples taken
+        # inside the marked (timed) window count, widened by one sampling period when the window was very short
+        lo = (self.t_begin or 0.0) - 0.06
+        hi = (self.t_end or float("inf")) + 0.06
         sm, mx, reasons = [], [], set()
-        for ln in self.lines:
+        for ts, ln in self.lines:
+            if not (lo <= ts <= hi):
+                continue
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -301,17 +314,18 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         out_final, mask, out = layer_step()
     barrier()
     status = int(out._psa_status.item())
     dens = float(ops.density(mask, True).mean().item())
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     records = []
     barrier()
+    sampler.mark_begin()
     e0, e1 = ev(), ev()
     torch.cuda.profiler.start()          # lets `ncu --profile-from-start off` see the timed region only
     e0.record()
@@ -320,6 +334,7 @@ def main():
     e1.record()
     barrier()
     torch.cuda.profiler.stop()
+    sampler.mark_end()
     clocks = sampler.stop() if rank == 0 else None
     ms_total = e0.elapsed_time(e1)
     t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
