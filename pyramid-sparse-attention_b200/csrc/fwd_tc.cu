@@ -150,6 +150,9 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m = blockIdx.x;
   const int bh = blockIdx.y;
+#ifdef PSA_FWD_PROFILE
+  if (threadIdx.x == 0 && blockIdx.x == 3 && blockIdx.y == 0) g_prof[48] = clock64();
+#endif
   const int32_t* mrow = p.mask + ((int64_t)bh * p.mq + m) * p.width;
 
   // ---------------------------------------------------------------- setup
@@ -167,6 +170,10 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     ctl->abort_flag = 0;
     ctl->n_sep = 0;
     tc::fence_mbar_init();
+    // the query tile does not depend on the index list: fetch it while the list is decoded
+    tc::tma_prefetch_desc(&maps.q);
+    for (int s = 0; s < C::SLABS; ++s) tc::tma_load_3d(sQ + s * kSlabBytes, &maps.q, &ctl->q_full, s * 64, m * 128, bh);
+    tc::mbar_arrive_expect_tx(&ctl->q_full, C::TILE_BYTES);
   }
   // the raw index list is staged in the (still unused) K ring; the item table built from it stays resident
   int32_t* sTmp = reinterpret_cast<int32_t*>(sK);
@@ -231,6 +238,9 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   tc::tc_fence_before();
   __syncthreads();
   tc::tc_fence_after();
+#ifdef PSA_FWD_PROFILE
+  if (threadIdx.x == 0 && blockIdx.x == 3 && blockIdx.y == 0) g_prof[49] = clock64();   // item table ready
+#endif
   const int n_tiles = ctl->n_tiles;
   const int last_cols = ctl->last_cols;
   const uint32_t tmem = ctl->tmem_base;
@@ -238,11 +248,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   if (n_tiles > 0) {
     if (warp < kProducerWarps) {
       // ============================================================ producers
-      if (warp == 0 && lane == 0) {
-        tc::tma_prefetch_desc(&maps.q);
-        for (int s = 0; s < C::SLABS; ++s) tc::tma_load_3d(sQ + s * kSlabBytes, &maps.q, &ctl->q_full, s * 64, m * 128, bh);
-        tc::mbar_arrive_expect_tx(&ctl->q_full, C::TILE_BYTES);
-      }
       const int n_items = ctl->n_items;
 #ifdef PSA_FWD_PROFILE
       long long prof_acc[4] = {0, 0, 0, 0};
@@ -649,6 +654,9 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         ok = tc::mbar_wait(&ctl->pv_done[g], (my_tiles - 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
       }
+#ifdef PSA_FWD_PROFILE
+      if (threadIdx.x == 128 && blockIdx.x == 3 && blockIdx.y == 0) g_prof[50] = clock64();   // group 0 through its last P V
+#endif
       // group g publishes (maximum, sum); both groups then agree on the weights.  An aborting group still joins the
       // barriers so that the other one is not left waiting.
       sXch[g * 256 + r] = m_run;
@@ -732,8 +740,12 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   }
 
   // ---------------------------------------------------------------- teardown
+  if (n_tiles == 0 && threadIdx.x == 0) tc::mbar_wait(&ctl->q_full, 0, abort_flag);   // the early query fetch must land first
   tc::tc_fence_before();
   __syncthreads();
+#ifdef PSA_FWD_PROFILE
+  if (threadIdx.x == 0 && blockIdx.x == 3 && blockIdx.y == 0) g_prof[51] = clock64();
+#endif
   if (ctl->abort_flag) {
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, PSA_ERR_TIMEOUT);
     for (int i = 0; i < 64; ++i) __nanosleep(1000);   // let copies in flight land before the CTA retires

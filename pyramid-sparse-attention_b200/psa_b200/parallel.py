@@ -86,6 +86,18 @@ class HeadShard:
         out.view(P, hp, sl, D)[:, first:first + count] = recv
 
 
+# Address contract of the peer exchange (what psa_push_heads / psa_pull_heads / psa_fwd_images_scatter compute per row).
+def push_destination(rank: int, t_local: int, head: int, tokens_per_rank: int, heads_per_rank: int):
+    """Row (t_local, head) of rank `rank`'s [S/P, H, D] buffer goes to -> (owner rank, local head, global token)."""
+    return head // heads_per_rank, head % heads_per_rank, rank * tokens_per_rank + t_local
+
+
+def pull_source(token: int, local_head: int, head0: int, tokens_per_rank: int):
+    """Row (local_head, token) of a head owner's [H/P, S, D] buffer comes from -> (owner rank, local token, global head);
+    the scattering forward stores output row (local_head, token) to the same place of the owner's o buffer."""
+    return token // tokens_per_rank, token % tokens_per_rank, head0 + local_head
+
+
 class _DeviceBuffer:
     """A raw device allocation exposed to torch through the CUDA array interface."""
 

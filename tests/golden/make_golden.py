@@ -73,7 +73,8 @@ def maxdiff(a, b):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("PSA_REFERENCE_DIR"), required=os.environ.get("PSA_REFERENCE_DIR") is None,
+                    help="checkout of ziplab/Pyramid-Sparse-Attention (or set PSA_REFERENCE_DIR)")
     args = ap.parse_args()
     load_reference(args.ref)
     import psa_triton.attention as RA

@@ -52,3 +52,33 @@ def test_head_shard_validation():
         HeadShard(4, 0, 12, 32761, 128)          # tokens must divide too
     hs = HeadShard(8, 3, 40, 75600, 128)
     assert hs.head_range == (15, 20) and hs.tokens_per_rank == 9450
+
+
+def test_peer_exchange_address_contract_matches_the_reshuffle():
+    """The per-row address formulas of the peer-memory exchange (push, pull, scattered output) applied to emulated rank
+    buffers give exactly the head-sharded / sequence-sharded layouts of the all-to-all reshuffle."""
+    sys.path.insert(0, os.path.join(ROOT, "pyramid-sparse-attention_b200"))
+    from psa_b200.parallel import push_destination, pull_source
+    world, H, S, D = 4, 8, 24, 2
+    hp, sl = H // world, S // world
+    g = torch.Generator().manual_seed(3)
+    full = torch.randn(S, H, D, generator=g)
+    seq_shards = [full[r * sl:(r + 1) * sl] for r in range(world)]                     # [S/P, H, D] per rank
+    want_head_shards = [full[:, r * hp:(r + 1) * hp].permute(1, 0, 2) for r in range(world)]   # [H/P, S, D] per rank
+    pushed = [torch.zeros(hp, S, D) for _ in range(world)]
+    for r in range(world):
+        for t in range(sl):
+            for h in range(H):
+                owner, hl, tok = push_destination(r, t, h, sl, hp)
+                pushed[owner][hl, tok] = seq_shards[r][t, h]
+    pulled = [torch.zeros(hp, S, D) for _ in range(world)]
+    outs = [torch.zeros(sl, H, D) for _ in range(world)]
+    for r in range(world):
+        for hl in range(hp):
+            for tok in range(S):
+                owner, tl, h = pull_source(tok, hl, r * hp, sl)
+                pulled[r][hl, tok] = seq_shards[owner][tl, h]
+                outs[owner][tl, h] = want_head_shards[r][hl, tok] * 3.0              # "forward output" scattered home
+    for r in range(world):
+        assert torch.equal(pushed[r], want_head_shards[r]) and torch.equal(pulled[r], want_head_shards[r])
+        assert torch.equal(outs[r], seq_shards[r] * 3.0)
