@@ -28,6 +28,7 @@
 // Every mbarrier wait is bounded; on expiry the CTA records PSA_ERR_TIMEOUT in the status word, lets copies in
 // flight land, frees its TMEM and returns.
 #include <cstddef>
+#include <mutex>
 
 #include "psa_common.cuh"
 #include "fwd.h"
@@ -37,8 +38,8 @@ namespace psa {
 
 namespace {
 
-constexpr int kMaxWidth = 4064;        // longest index list (entries) the kernel handles
-constexpr int kMaxItems = 4096;        // item table capacity (entries + extra + padding blocks)
+constexpr int kMaxWidth = 1472;        // longest index list (entries) the kernel handles
+constexpr int kMaxItems = 1504;        // item table capacity (entries + extra + padding blocks); two tables
 constexpr int kSlabBytes = 128 * 128;  // 128 rows x 128 B (64 16-bit channels)
 constexpr int kProducerWarps = 3;
 constexpr int kProducerThreads = kProducerWarps * 32;
@@ -59,6 +60,8 @@ struct TcParams {
   int64_t seq_q;
   int64_t n[4];
   int mq, bn, tn, width, quirk;
+  int total_rows;     // query blocks of all heads: mq * bh
+  int* row_counter;   // device word, zero at launch: rows beyond the first one of every CTA are claimed from it
   float scale_log2;   // sm_scale * log2(e)
   // tile-image mode: K/V of all levels pre-laid-out as shared-memory images (one linear bulk copy per block)
   const unsigned char* kimg;
@@ -78,21 +81,24 @@ template <int D> struct Cfg {
   static constexpr int OFF_BIAS = OFF_V + NV * TILE_BYTES;
   static constexpr int OFF_BIASG = OFF_BIAS + kBiasSlots * 128 * 4;   // one bias word per 4 columns + per-warp tile flags
   static constexpr int OFF_XCH = OFF_BIASG + kBiasSlots * (32 + 4) * 4;
-  static constexpr int OFF_ROW = OFF_XCH + 2 * 2 * 128 * 4;
-  static constexpr int OFF_CTRL = OFF_ROW + kMaxItems * 4;
+  static constexpr int OFF_ROW = OFF_XCH + 2 * 2 * 2 * 128 * 4;   // (max, sum) of both groups, two rows in flight
+  static constexpr int OFF_RAW = OFF_ROW + 2 * kMaxItems * 4;      // raw index list of the row being decoded
+  static constexpr int OFF_CTRL = OFF_RAW + kMaxWidth * 4;
   static constexpr int SMEM_BYTES = OFF_CTRL + 1024 + 1024;   // control block + alignment slack
 };
 
 struct Ctrl {
   uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
   uint64_t s_full[2], p_full[2], pv_done[2], q_full;
+  uint64_t row_ready[4], row_done[4], q_free, o_free;   // hand-over of query rows between the roles of a persistent CTA
+  uint64_t prod_sync, xch_full;                         // bounded rendezvous of the producer warps / of the softmax warps
+  int row_tiles[4], row_last_cols[4], row_index[4];   // row_index >= total_rows: no more rows
+  int claimed[2];
   uint32_t tmem_base;
   int abort_flag;
   int n_sep;
   int sep[16];
-  int n_tiles, last_cols, n_items;
-  int seg_start[4], seg_cnt[4], item_base[4], tok_base[4];
-  float qbias2[4];
+  struct RowDec { int n_tiles, last_cols, n_items; float qbias2[4]; } dec[2];   // decoded rows (current / next)
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -111,6 +117,16 @@ template <> __device__ __forceinline__ uint32_t pack2<0>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// Rendezvous of a fixed set of warps on an mbarrier (count = number of warps): like a named barrier, but the wait is
+// bounded, so a role that gave up can never leave the others parked in a hardware barrier.  `uses` counts the calls.
+__device__ __forceinline__ bool warps_rendezvous(uint64_t* bar, int& uses, volatile int* abort_flag) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) tc::mbar_arrive(bar);
+  const bool ok = tc::mbar_wait(bar, uses & 1, abort_flag);
+  ++uses;
+  return __all_sync(0xffffffffu, ok);
+}
+
 // Item table entry (one gathered block): bits 0-11 block index, 12-13 level index, 14 extra block of a narrow level
 // (reference compatibility), 15 inert padding block, 16-31 first tile column of the block counted from the start
 // of the row's token stream, in units of 4 tokens.
@@ -121,13 +137,15 @@ constexpr uint32_t kItemQuirk = 1u << 14, kItemPad = 1u << 15;
 __device__ long long g_prof[64];
 __device__ long long g_trace[16 * 64];
 namespace {
-#define TRACE(row, t) do { if (blockIdx.x == 3 && blockIdx.y == 0 && (t) < 64) g_trace[(row) * 64 + (t)] = clock64(); } while (0)
+#define TRACE(row, t)
+#define RTRACE(row, rit) do { if (blockIdx.x == 3 && (rit) < 64) g_trace[(row) * 64 + (rit)] = clock64(); } while (0)
 #define PROF_T0() long long prof_t0 = clock64()
 #define PROF_ADD(slot) do { long long t1 = clock64(); prof_acc[slot] += t1 - prof_t0; prof_t0 = t1; } while (0)
 #else
 #define PROF_T0()
 #define PROF_ADD(slot)
 #define TRACE(row, t)
+#define RTRACE(row, rit)
 #endif
 
 // IMG = true: K/V tiles use the image layout [8-row group][slab][8 rows][128 B] and are filled by linear bulk copies from
@@ -148,370 +166,525 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   volatile int* abort_flag = &ctl->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m = blockIdx.x;
-  const int bh = blockIdx.y;
-#ifdef PSA_FWD_PROFILE
-  if (threadIdx.x == 0 && blockIdx.x == 3 && blockIdx.y == 0) g_prof[48] = clock64();
-#endif
-  const int32_t* mrow = p.mask + ((int64_t)bh * p.mq + m) * p.width;
+  int32_t* sRaw = reinterpret_cast<int32_t*>(smem + C::OFF_RAW);
 
-  // ---------------------------------------------------------------- setup
+  // ---------------------------------------------------------------- setup (once per CTA)
   if (threadIdx.x == 0) {
     for (int i = 0; i < 4; ++i) {
       tc::mbar_init(&ctl->k_full[i], kProducerWarps); tc::mbar_init(&ctl->k_empty[i], 1);
       tc::mbar_init(&ctl->v_full[i], kProducerWarps); tc::mbar_init(&ctl->v_empty[i], 1);
     }
+    ctl->abort_flag = 0;
+    tc::fence_mbar_init();
+  } else if (threadIdx.x == 32) {
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&ctl->s_full[i], 1);
       tc::mbar_init(&ctl->p_full[i], 4);   // one arrival per softmax warp of the group
       tc::mbar_init(&ctl->pv_done[i], 1);
     }
     tc::mbar_init(&ctl->q_full, 1);
-    ctl->abort_flag = 0;
-    ctl->n_sep = 0;
+    tc::mbar_init(&ctl->q_free, 1);
+    tc::mbar_init(&ctl->o_free, 8);        // one arrival per softmax warp
     tc::fence_mbar_init();
-    // the query tile does not depend on the index list: fetch it while the list is decoded
-    tc::tma_prefetch_desc(&maps.q);
-    for (int s = 0; s < C::SLABS; ++s) tc::tma_load_3d(sQ + s * kSlabBytes, &maps.q, &ctl->q_full, s * 64, m * 128, bh);
-    tc::mbar_arrive_expect_tx(&ctl->q_full, C::TILE_BYTES);
+  } else if (threadIdx.x == 64) {
+    for (int i = 0; i < 4; ++i) {
+      tc::mbar_init(&ctl->row_ready[i], 1);
+      tc::mbar_init(&ctl->row_done[i], 9);   // eight softmax warps and the MMA issuer
+    }
+    tc::mbar_init(&ctl->prod_sync, kProducerWarps);
+    tc::mbar_init(&ctl->xch_full, 8);
+    tc::fence_mbar_init();
   }
-  // the raw index list is staged in the (still unused) K ring; the item table built from it stays resident
-  int32_t* sTmp = reinterpret_cast<int32_t*>(sK);
-  for (int i = threadIdx.x; i < p.width; i += kThreads) sTmp[i] = mrow[i];
-  __syncthreads();
   if (warp == 3) {
     tc::tmem_alloc(&ctl->tmem_base, 512);
     tc::tmem_relinquish();
   }
-  // separators of the index list (their order is recovered by a tiny sort)
-  for (int i = threadIdx.x; i < p.width; i += kThreads)
-    if (sTmp[i] == -1) {
-      int slot = atomicAdd(&ctl->n_sep, 1);
-      if (slot < 16) ctl->sep[slot] = i;
-    }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int ns = ctl->n_sep < 16 ? ctl->n_sep : 16;
-    for (int a = 1; a < ns; ++a) {   // insertion sort, <= 16 entries
-      int v = ctl->sep[a], b = a - 1;
-      while (b >= 0 && ctl->sep[b] > v) { ctl->sep[b + 1] = ctl->sep[b]; --b; }
-      ctl->sep[b + 1] = v;
-    }
-    int prev = -1, tokens = 0, n_items = 0, last_P = p.bn;
-    for (int li = 0; li < 4; ++li) {
-      int end = li < ns ? ctl->sep[li] : p.width;
-      int start = prev + 1;
-      int cnt = end > start ? end - start : 0;      // a row that ended early leaves later segments empty
-      ctl->seg_start[li] = start;
-      ctl->seg_cnt[li] = cnt;
-      ctl->item_base[li] = n_items;
-      ctl->tok_base[li] = tokens;
-      const int P = p.bn >> li;
-      int items = cnt;
-      const bool quirk = p.quirk && P < p.tn && cnt >= 2;
-      if (quirk) items += p.tn / P - 2;
-      ctl->qbias2[li] = quirk ? (float)li + log2f((float)(cnt / 2)) : 0.f;
-      if (items > 0) last_P = P;
-      tokens += items * P;
-      n_items += items;
-      prev = end;
-    }
-    // inert padding blocks (block 0 of the last used level, bias -inf) up to a multiple of 16 columns
-    const int padded = (tokens + 15) & ~15;
-    const int last_li = 31 - __clz(p.bn / last_P);
-    for (int t = tokens; t < padded; t += last_P)
-      sItems[n_items++] = (uint32_t)last_li << 12 | kItemPad | ((uint32_t)(t >> 2) << 16);
-    ctl->n_items = n_items;
-    ctl->n_tiles = (padded + 127) / 128;
-    ctl->last_cols = padded - (ctl->n_tiles - 1) * 128;
-  }
-  __syncthreads();
-  for (int li = 0; li < 4; ++li) {
-    const int P = p.bn >> li, cnt = ctl->seg_cnt[li], start = ctl->seg_start[li];
-    const int ib = ctl->item_base[li], tb = ctl->tok_base[li];
-    for (int e = threadIdx.x; e < cnt; e += kThreads)
-      sItems[ib + e] = ((uint32_t)sTmp[start + e] & 0xfffu) | (uint32_t)li << 12 | ((uint32_t)((tb + e * P) >> 2) << 16);
-    if (p.quirk && P < p.tn && cnt >= 2)
-      for (int j = 2 + threadIdx.x; j < p.tn / P; j += kThreads)
-        sItems[ib + cnt + j - 2] = (uint32_t)j | (uint32_t)li << 12 | kItemQuirk | ((uint32_t)((tb + (cnt + j - 2) * P) >> 2) << 16);
-  }
   tc::tc_fence_before();
   __syncthreads();
   tc::tc_fence_after();
-#ifdef PSA_FWD_PROFILE
-  if (threadIdx.x == 0 && blockIdx.x == 3 && blockIdx.y == 0) g_prof[49] = clock64();   // item table ready
-#endif
-  const int n_tiles = ctl->n_tiles;
-  const int last_cols = ctl->last_cols;
   const uint32_t tmem = ctl->tmem_base;
+  volatile int* row_tiles = ctl->row_tiles;
+  volatile int* row_last_cols = ctl->row_last_cols;
+  volatile int* row_index = ctl->row_index;
 
-  if (n_tiles > 0) {
-    if (warp < kProducerWarps) {
-      // ============================================================ producers
-      const int n_items = ctl->n_items;
+  // A CTA is persistent: it starts with query row R = blockIdx.x (R = bh * mq + m) and claims further rows from a global
+  // counter (SMs do not all run at the same speed, so a fixed split would leave the fast ones idle at the end); its three
+  // roles run the rows as one continuous stream of tiles.  Ring stages, score buffers and barrier phases are indexed by
+  // the running tile count g0 + t, so the producers decode and prefetch the next row while the MMAs and the softmax of
+  // the current row are still in flight, and the first scores of the next row are computed under the epilogue.
+  if (warp < kProducerWarps) {
+    // ============================================================ producers
+#ifdef PSA_FWD_PROFILE
+    long long prof_acc[4] = {0, 0, 0, 0};
+#endif
+    PROF_T0();
+    const uint32_t ctl_a = tc::smem_u32(ctl);
+    const uint32_t k_full_a = ctl_a + (uint32_t)offsetof(Ctrl, k_full), k_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, k_empty);
+    const uint32_t v_full_a = ctl_a + (uint32_t)offsetof(Ctrl, v_full), v_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, v_empty);
+    const uint32_t sK_a = tc::smem_u32(sK), sV_a = tc::smem_u32(sV);
+    const uint64_t kmap0 = reinterpret_cast<uint64_t>(&maps.k[0]), vmap0 = reinterpret_cast<uint64_t>(&maps.v[0]);
+    const int n0 = (int)p.n[0], n1 = (int)p.n[1], n2 = (int)p.n[2], n3 = (int)p.n[3];
+    const int ptid = threadIdx.x;                     // 0..95
+    int g0 = 0, q_rows = 0, syncs = 0;
+    bool ok = true;
+    // The raw index list of a row is fetched (cp.async, 4 bytes per entry) long before it is decoded.
+    auto prefetch_raw = [&](int R_n) {
+      if (R_n >= p.total_rows) return;
+      const int32_t* mrow = p.mask + (int64_t)R_n * p.width;
+      const uint32_t raw_a = tc::smem_u32(sRaw);
+      for (int i = ptid; i < p.width; i += kProducerThreads)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(raw_a + 4u * (uint32_t)i), "l"(mrow + i) : "memory");
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    // Decode row number rit_n (query row R_n) into item table rit_n & 1, publish it to the other roles, and start the
+    // fetch of the row after it.  Called by all producer threads at the same point of their loops.
+    auto decode_row = [&](int rit_n) -> bool {
+      const int R_n = ctl->claimed[rit_n & 1];     // written before the rendezvous that ended the previous decode
+      if (R_n >= p.total_rows) {
+        // no more rows: tell the other roles through the same slot mechanism
+        bool good = true;
+        if (warp == 0) {
+          const int rs = rit_n & 3;
+          if (rit_n >= 4) {
+            good = tc::mbar_wait(&ctl->row_done[rs], ((rit_n >> 2) - 1) & 1, abort_flag);
+            good = __all_sync(0xffffffffu, good);
+          }
+          if (good && lane == 0) {
+            row_index[rs] = R_n;
+            __threadfence_block();
+            tc::mbar_arrive(&ctl->row_ready[rs]);
+          }
+        }
+        return good;
+      }
+      if (ptid == 0) RTRACE(0, rit_n);     // decode start
+      uint32_t* table = sItems + (rit_n & 1) * kMaxItems;
+      asm volatile("cp.async.wait_all;" ::: "memory");
+      if (!warps_rendezvous(&ctl->prod_sync, syncs, abort_flag)) return false;
+      for (int i = ptid; i < p.width; i += kProducerThreads)
+        if (sRaw[i] == -1) {
+          int slot = atomicAdd(&ctl->n_sep, 1);
+          if (slot < 16) ctl->sep[slot] = i;
+        }
+      if (!warps_rendezvous(&ctl->prod_sync, syncs, abort_flag)) return false;
+      // every thread derives the level segments from the (at most 16) separator positions by itself: the four smallest
+      const int ns = ctl->n_sep < 16 ? ctl->n_sep : 16;
+      int sp[4];
+      {
+        int below = -1;
+        for (int li = 0; li < 4; ++li) {
+          int best = p.width;
+          for (int a = 0; a < ns; ++a) {
+            const int v = ctl->sep[a];
+            if (v > below && v < best) best = v;
+          }
+          sp[li] = best;
+          below = best < p.width ? best : p.width;
+        }
+      }
+      int prev = -1, tokens = 0, n_items = 0, last_P = p.bn;
+      float qb[4];
+#pragma unroll
+      for (int li = 0; li < 4; ++li) {
+        const int end = sp[li];
+        const int start = prev + 1;
+        const int cnt = end > start ? end - start : 0;      // a row that ended early leaves later segments empty
+        const int P = p.bn >> li;
+        const bool quirk = p.quirk && P < p.tn && cnt >= 2;
+        const int ib = n_items, tb = tokens;
+        for (int e = ptid; e < cnt; e += kProducerThreads)
+          table[ib + e] = ((uint32_t)sRaw[start + e] & 0xfffu) | (uint32_t)li << 12 | ((uint32_t)((tb + e * P) >> 2) << 16);
+        if (quirk)
+          for (int j = 2 + ptid; j < p.tn / P; j += kProducerThreads)
+            table[ib + cnt + j - 2] = (uint32_t)j | (uint32_t)li << 12 | kItemQuirk | ((uint32_t)((tb + (cnt + j - 2) * P) >> 2) << 16);
+        const int items = cnt + (quirk ? p.tn / P - 2 : 0);
+        qb[li] = quirk ? (float)li + log2f((float)(cnt / 2)) : 0.f;
+        if (items > 0) last_P = P;
+        tokens += items * P;
+        n_items += items;
+        prev = end < p.width ? end : p.width;
+      }
+      // inert padding blocks (block 0 of the last used level, bias -inf) up to a multiple of 16 columns
+      const int padded = (tokens + 15) & ~15;
+      const int n_tiles = (padded + 127) / 128;
+      if (ptid == 0) {
+        const int last_li = 31 - __clz(p.bn / last_P);
+        for (int t = tokens; t < padded; t += last_P)
+          table[n_items++] = (uint32_t)last_li << 12 | kItemPad | ((uint32_t)(t >> 2) << 16);
+        Ctrl::RowDec& d = ctl->dec[rit_n & 1];
+        d.n_items = n_items;
+        d.n_tiles = n_tiles;
+        d.last_cols = padded - (n_tiles - 1) * 128;
+        for (int li = 0; li < 4; ++li) d.qbias2[li] = qb[li];
+      }
+      // thread 0 also claims the row after this one
+      if (ptid == 0) ctl->claimed[(rit_n + 1) & 1] = (int)gridDim.x + atomicAdd(p.row_counter, 1);
+      if (!warps_rendezvous(&ctl->prod_sync, syncs, abort_flag)) return false;
+      if (ptid == 0) ctl->n_sep = 0;
+      // publish the row to the other roles.  The slot was last used four rows ago: wait until that row is finished.
+      bool good = true;
+      if (warp == 0) {
+        const int rs = rit_n & 3;
+        if (rit_n >= 4) {
+          good = tc::mbar_wait(&ctl->row_done[rs], ((rit_n >> 2) - 1) & 1, abort_flag);
+          good = __all_sync(0xffffffffu, good);
+        }
+        if (good && lane == 0) {
+          row_tiles[rs] = n_tiles;
+          row_last_cols[rs] = padded - (n_tiles - 1) * 128;
+          row_index[rs] = R_n;
+          __threadfence_block();
+          tc::mbar_arrive(&ctl->row_ready[rs]);
+          RTRACE(1, rit_n);     // row published
+        }
+      }
+      prefetch_raw(ctl->claimed[(rit_n + 1) & 1]);
+      return good;
+    };
+    if (ptid == 0) ctl->n_sep = 0;
+    if (ptid == 0) ctl->claimed[0] = (int)blockIdx.x;
+    prefetch_raw(blockIdx.x);
+    ok = warps_rendezvous(&ctl->prod_sync, syncs, abort_flag) && decode_row(0);
+    for (int rit = 0; ok; ++rit) {
+      const int R = ctl->claimed[rit & 1];         // fixed since the decode of this row
+      if (R >= p.total_rows) break;
+      const int m = R % p.mq, bh = R / p.mq;
+      const uint32_t* sIt = sItems + (rit & 1) * kMaxItems;     // this row's item table
+      // the decode (by every producer thread) ended with a rendezvous, so the row's figures are visible
+      const int n_tiles = ctl->dec[rit & 1].n_tiles, last_cols = ctl->dec[rit & 1].last_cols, n_items = ctl->dec[rit & 1].n_items;
+      const float qb0 = ctl->dec[rit & 1].qbias2[0], qb1 = ctl->dec[rit & 1].qbias2[1], qb2 = ctl->dec[rit & 1].qbias2[2],
+                  qb3 = ctl->dec[rit & 1].qbias2[3];
+      const int decode_step = n_tiles < C::NK ? n_tiles : C::NK;   // where the next row is decoded: the rings are full by then
+      // The row's query tile replaces the previous one as soon as the last Q K^T of the previous non-empty row has read
+      // it; warp 0 polls for that between its copies instead of holding the K/V stream back.
+      bool q_pending = warp == 0 && n_tiles > 0;
+      const int q_prev = q_rows;
+      auto fetch_q = [&](bool block) {
+        bool ready = q_prev == 0;
+        if (!ready) {
+          if (block) {
+            ready = tc::mbar_wait(&ctl->q_free, (q_prev - 1) & 1, abort_flag);
+            ready = __all_sync(0xffffffffu, ready);
+            if (!ready) ok = false;
+          } else {
+            ready = __all_sync(0xffffffffu, tc::mbar_try_wait(&ctl->q_free, (q_prev - 1) & 1));
+          }
+        }
+        if (ready) {
+          if (lane == 0) {
+            for (int s = 0; s < C::SLABS; ++s) tc::tma_load_3d(sQ + s * kSlabBytes, &maps.q, &ctl->q_full, s * 64, m * 128, bh);
+            tc::mbar_arrive_expect_tx(&ctl->q_full, C::TILE_BYTES);
+          }
+          q_pending = false;
+        }
+      };
+      if (q_pending) fetch_q(false);
+      if (n_tiles > 0) ++q_rows;
+      int ki = 0, vi = 0;              // first item of the next K tile / V tile
+        // step s gathers K tile s and then V tile s-1: K runs one tile ahead of V
+        for (int step = 0; ok && step <= n_tiles; ++step) {
+          if (q_pending) fetch_q(step >= C::NK - 1);   // latest before the copy that needs the previous row's last tile gone
+          if (ok && step == decode_step) ok = decode_row(rit + 1);
+          if (!ok) break;
+          if (step < n_tiles) {
+            const int t = step, gt = g0 + t, stage = gt % C::NK, slot = gt % kBiasSlots;
+            ok = tc::mbar_wait_a(k_empty_a + stage * 8, ((gt / C::NK) & 1) ^ 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            PROF_ADD(0);
+            const uint32_t tile_a = sK_a + stage * C::TILE_BYTES, bar_a = k_full_a + stage * 8;
+            float* bias_row = sBias + slot * 128;
+            float* biasg_row = sBiasG + slot * 36;
+            const int probe = ki + lane;
+            const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sIt[probe < n_items ? probe : 0] >> 21) == t));
+            const bool active = 3 * lane + warp < in_tile;
+            const uint32_t x = active ? sIt[ki + 3 * lane + warp] : 0u;
+            const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = ((int)(x >> 16) << 2) & 127, row0 = blk * P;
+            // logit bias of the block's columns
+            const int nl = li == 0 ? n0 : (li == 1 ? n1 : (li == 2 ? n2 : n3));
+            const float qb = li == 0 ? qb0 : (li == 1 ? qb1 : (li == 2 ? qb2 : qb3));
+            const float bias2 = (x & kItemPad) ? -INFINITY : ((x & kItemQuirk) ? qb : (float)li);
+            const int nvalid = nl - row0;
+            uint32_t my_bytes = 0;
+            if (active) {
+              if (IMG) {
+                const unsigned char* src = p.kimg + p.img.off[li] + (((int64_t)bh * p.img.groups[li] + (row0 >> 3)) * C::SLABS << 10);
+                tc::bulk_load_a(tile_a + (col >> 3) * (C::SLABS * 1024), src, (uint32_t)(P * D * 2), bar_a);
+              } else {
+#pragma unroll
+                for (int sl = 0; sl < C::SLABS; ++sl)
+                  tc::tma_load_3d_a(tile_a + sl * kSlabBytes + col * 128, kmap0 + (uint64_t)li * sizeof(CUtensorMap), bar_a, sl * 64, row0, bh);
+              }
+              my_bytes = (uint32_t)C::SLABS * P * 128u;
+              if (P <= 16) {   // narrow block: its lane writes the few bias words itself
+                float4* dst = reinterpret_cast<float4*>(bias_row + col);
+                for (int c = 0; c < P; c += 4) {
+                  dst[c >> 2] = make_float4(c < nvalid ? bias2 : -INFINITY, c + 1 < nvalid ? bias2 : -INFINITY,
+                                            c + 2 < nvalid ? bias2 : -INFINITY, c + 3 < nvalid ? bias2 : -INFINITY);
+                  biasg_row[(col + c) >> 2] = c < nvalid ? bias2 : -INFINITY;
+                }
+              }
+            }
+            // a block that ends inside a group of 4 columns makes the tile take the per-column path of the softmax
+            const bool odd_edge = active && nvalid > 0 && nvalid < P && (nvalid & 3) != 0;
+            const bool any_odd = __any_sync(0xffffffffu, odd_edge);
+            if (lane == 0) reinterpret_cast<int*>(biasg_row)[32 + warp] = any_odd ? 1 : 0;
+            // wide blocks (at most 4 per tile): the whole warp writes the bias, 4 columns per lane
+            unsigned wide = __ballot_sync(0xffffffffu, active && P > 16);
+            while (wide) {
+              const int src_lane = __ffs(wide) - 1;
+              wide &= wide - 1;
+              const int w_col = __shfl_sync(0xffffffffu, col, src_lane), w_P = __shfl_sync(0xffffffffu, P, src_lane);
+              const int w_nv = __shfl_sync(0xffffffffu, nvalid, src_lane);
+              const float w_b = __shfl_sync(0xffffffffu, bias2, src_lane);
+              const int c = lane * 4;
+              if (c < w_P) {
+                *reinterpret_cast<float4*>(bias_row + w_col + c) =
+                    make_float4(c < w_nv ? w_b : -INFINITY, c + 1 < w_nv ? w_b : -INFINITY, c + 2 < w_nv ? w_b : -INFINITY,
+                                c + 3 < w_nv ? w_b : -INFINITY);
+                biasg_row[(w_col + c) >> 2] = c < w_nv ? w_b : -INFINITY;
+              }
+            }
+            ki += in_tile;
+            // the bias of this tile must be complete before the tile is announced: the softmax warps read it once the
+            // scores are ready, and "scores ready" follows "K tile full" through the MMA issuer
+            if (t == n_tiles - 1 && warp == 0)
+              for (int c = last_cols + lane; c < 128; c += 32) { bias_row[c] = -INFINITY; biasg_row[c >> 2] = -INFINITY; }
+            const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
+            if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
+            if (warp == 0 && lane == 0) TRACE(6, t);
+            PROF_ADD(1);
+          }
+          if (step > 0) {
+            const int t = step - 1, gt = g0 + t, stage = gt % C::NV;
+            ok = tc::mbar_wait_a(v_empty_a + stage * 8, ((gt / C::NV) & 1) ^ 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            PROF_ADD(2);
+            const uint32_t tile_a = sV_a + stage * C::TILE_BYTES, bar_a = v_full_a + stage * 8;
+            const int probe = vi + lane;
+            const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sIt[probe < n_items ? probe : 0] >> 21) == t));
+            const int mine = vi + 3 * lane + warp;
+            uint32_t my_bytes = 0;
+            if (3 * lane + warp < in_tile) {
+              const uint32_t x = sIt[mine];
+              const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = ((int)(x >> 16) << 2) & 127;
+              if (IMG) {
+                const unsigned char* src = p.vimg + p.img.off[li] + (((int64_t)bh * p.img.groups[li] + ((blk * P) >> 3)) * C::SLABS << 10);
+                tc::bulk_load_a(tile_a + (col >> 3) * (C::SLABS * 1024), src, (uint32_t)(P * D * 2), bar_a);
+              } else {
+#pragma unroll
+                for (int sl = 0; sl < C::SLABS; ++sl)
+                  tc::tma_load_3d_a(tile_a + sl * kSlabBytes + col * 128, vmap0 + (uint64_t)li * sizeof(CUtensorMap), bar_a, sl * 64, blk * P, bh);
+              }
+              my_bytes = (uint32_t)C::SLABS * P * 128u;
+            }
+            vi += in_tile;
+            const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
+            if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
+            if (warp == 0 && lane == 0) TRACE(7, t);
+            PROF_ADD(3);
+          }
+        }
+      if (ok && q_pending) fetch_q(true);
+      if (ptid == 0) RTRACE(2, rit);     // last copy of the row issued
+      g0 += n_tiles;
+      if (!ok) break;
+    }
+#ifdef PSA_FWD_PROFILE
+    if (lane == 0 && blockIdx.x == 3) for (int i = 0; i < 4; ++i) g_prof[warp * 4 + i] = prof_acc[i];
+#endif
+  } else if (warp == 3) {
+    // ============================================================ MMA issuer
+    if (lane == 0) {
+      bool ok = true;
+      // ready-made descriptors: per tile only the stage offset is added, per MMA only an immediate
+      const uint32_t idesc_pv = tc::make_idesc(FMT, 128, D, 0, 1);
+      const uint32_t idesc_qk_full = tc::make_idesc(FMT, 128, 128, 0, 0);
+      const uint64_t qdesc = tc::make_smem_desc(tc::smem_u32(sQ), 16, 1024);
+      // image layout: 8-row groups are SLABS KiB apart and the slabs of a group follow each other
+      constexpr uint32_t kGroupStride = IMG ? C::SLABS * 1024 : 1024;
+      constexpr uint32_t kSlabStride = IMG ? 1024 : kSlabBytes;
+      const uint64_t kdesc0 = tc::make_smem_desc(tc::smem_u32(sK), 16, kGroupStride);
+      const uint64_t vdesc0 = tc::make_smem_desc(tc::smem_u32(sV), kSlabStride, kGroupStride);
+      const uint32_t ctl_a = tc::smem_u32(ctl);
+      const uint32_t k_full_a = ctl_a + (uint32_t)offsetof(Ctrl, k_full), k_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, k_empty);
+      const uint32_t v_full_a = ctl_a + (uint32_t)offsetof(Ctrl, v_full), v_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, v_empty);
+      const uint32_t s_full_a = ctl_a + (uint32_t)offsetof(Ctrl, s_full);
+      const uint32_t p_full_a = ctl_a + (uint32_t)offsetof(Ctrl, p_full), pv_done_a = ctl_a + (uint32_t)offsetof(Ctrl, pv_done);
+      const uint32_t q_free_a = ctl_a + (uint32_t)offsetof(Ctrl, q_free), o_free_a = ctl_a + (uint32_t)offsetof(Ctrl, o_free);
+      uint32_t idle = 0;
 #ifdef PSA_FWD_PROFILE
       long long prof_acc[4] = {0, 0, 0, 0};
 #endif
       PROF_T0();
-      // everything the per-block issue needs, as plain 32-bit shared addresses / 64-bit map addresses
-      const uint32_t ctl_a = tc::smem_u32(ctl);
-      const uint32_t k_full_a = ctl_a + (uint32_t)offsetof(Ctrl, k_full), k_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, k_empty);
-      const uint32_t v_full_a = ctl_a + (uint32_t)offsetof(Ctrl, v_full), v_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, v_empty);
-      const uint32_t sK_a = tc::smem_u32(sK), sV_a = tc::smem_u32(sV);
-      const uint64_t kmap0 = reinterpret_cast<uint64_t>(&maps.k[0]), vmap0 = reinterpret_cast<uint64_t>(&maps.v[0]);
-      const int n0 = (int)p.n[0], n1 = (int)p.n[1], n2 = (int)p.n[2], n3 = (int)p.n[3];
-      const float qb0 = ctl->qbias2[0], qb1 = ctl->qbias2[1], qb2 = ctl->qbias2[2], qb3 = ctl->qbias2[3];
-      // The items of a tile are consecutive table entries (at most 32: blocks are at least 4 tokens wide).  Lane l of
-      // producer warp w takes entry first + 3*l + w, so address arithmetic, bias and copy issue of all the blocks of a
-      // tile run side by side instead of one block after the other.
-      int ki = 0, vi = 0;              // first item of the next K tile / V tile
-      bool ok = true;
-      // step s gathers K tile s and then V tile s-1: K runs one tile ahead of V
-      for (int step = 0; ok && step <= n_tiles; ++step) {
-        if (step < n_tiles) {
-          const int t = step, stage = t % C::NK, slot = t % kBiasSlots;
-          ok = tc::mbar_wait_a(k_empty_a + stage * 8, ((t / C::NK) & 1) ^ 1, abort_flag);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          PROF_ADD(0);
-          const uint32_t tile_a = sK_a + stage * C::TILE_BYTES, bar_a = k_full_a + stage * 8;
-          float* bias_row = sBias + slot * 128;
-          float* biasg_row = sBiasG + slot * 36;
-          const int probe = ki + lane;
-          const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sItems[probe < n_items ? probe : 0] >> 21) == t));
-          const bool active = 3 * lane + warp < in_tile;
-          const uint32_t x = active ? sItems[ki + 3 * lane + warp] : 0u;
-          const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = ((int)(x >> 16) << 2) & 127, row0 = blk * P;
-          // logit bias of the block's columns
-          const int nl = li == 0 ? n0 : (li == 1 ? n1 : (li == 2 ? n2 : n3));
-          const float qb = li == 0 ? qb0 : (li == 1 ? qb1 : (li == 2 ? qb2 : qb3));
-          const float bias2 = (x & kItemPad) ? -INFINITY : ((x & kItemQuirk) ? qb : (float)li);
-          const int nvalid = nl - row0;
-          uint32_t my_bytes = 0;
-          if (active) {
-            if (IMG) {
-              const unsigned char* src = p.kimg + p.img.off[li] + (((int64_t)bh * p.img.groups[li] + (row0 >> 3)) * C::SLABS << 10);
-              tc::bulk_load_a(tile_a + (col >> 3) * (C::SLABS * 1024), src, (uint32_t)(P * D * 2), bar_a);
-            } else {
-#pragma unroll
-              for (int sl = 0; sl < C::SLABS; ++sl)
-                tc::tma_load_3d_a(tile_a + sl * kSlabBytes + col * 128, kmap0 + (uint64_t)li * sizeof(CUtensorMap), bar_a, sl * 64, row0, bh);
-            }
-            my_bytes = (uint32_t)C::SLABS * P * 128u;
-            if (P <= 16) {   // narrow block: its lane writes the few bias words itself
-              float4* dst = reinterpret_cast<float4*>(bias_row + col);
-              for (int c = 0; c < P; c += 4) {
-                dst[c >> 2] = make_float4(c < nvalid ? bias2 : -INFINITY, c + 1 < nvalid ? bias2 : -INFINITY,
-                                          c + 2 < nvalid ? bias2 : -INFINITY, c + 3 < nvalid ? bias2 : -INFINITY);
-                biasg_row[(col + c) >> 2] = c < nvalid ? bias2 : -INFINITY;
-              }
-            }
-          }
-          // a block that ends inside a group of 4 columns makes the tile take the per-column path of the softmax
-          const bool odd_edge = active && nvalid > 0 && nvalid < P && (nvalid & 3) != 0;
-          const bool any_odd = __any_sync(0xffffffffu, odd_edge);
-          if (lane == 0) reinterpret_cast<int*>(biasg_row)[32 + warp] = any_odd ? 1 : 0;
-          // wide blocks (at most 4 per tile): the whole warp writes the bias, 4 columns per lane
-          unsigned wide = __ballot_sync(0xffffffffu, active && P > 16);
-          while (wide) {
-            const int src_lane = __ffs(wide) - 1;
-            wide &= wide - 1;
-            const int w_col = __shfl_sync(0xffffffffu, col, src_lane), w_P = __shfl_sync(0xffffffffu, P, src_lane);
-            const int w_nv = __shfl_sync(0xffffffffu, nvalid, src_lane);
-            const float w_b = __shfl_sync(0xffffffffu, bias2, src_lane);
-            const int c = lane * 4;
-            if (c < w_P) {
-              *reinterpret_cast<float4*>(bias_row + w_col + c) =
-                  make_float4(c < w_nv ? w_b : -INFINITY, c + 1 < w_nv ? w_b : -INFINITY, c + 2 < w_nv ? w_b : -INFINITY,
-                              c + 3 < w_nv ? w_b : -INFINITY);
-              biasg_row[(w_col + c) >> 2] = c < w_nv ? w_b : -INFINITY;
-            }
-          }
-          ki += in_tile;
-          // the bias of this tile must be complete before the tile is announced: the softmax warps read it once the
-          // scores are ready, and "scores ready" follows "K tile full" through the MMA issuer
-          if (t == n_tiles - 1 && warp == 0)
-            for (int c = last_cols + lane; c < 128; c += 32) { bias_row[c] = -INFINITY; biasg_row[c >> 2] = -INFINITY; }
-          const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
-          if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
-          if (warp == 0 && lane == 0) TRACE(6, t);
-          PROF_ADD(1);
+      int g0 = 0, q_rows = 0;
+      for (int rit = 0; ok; ++rit) {
+        const int rslot = rit & 3;
+        ok = tc::mbar_wait(&ctl->row_ready[rslot], (rit >> 2) & 1, abort_flag);
+        if (!ok || row_index[rslot] >= p.total_rows) break;
+        const int n_tiles = row_tiles[rslot], last_cols = row_last_cols[rslot];
+        if (n_tiles == 0) {
+          tc::mbar_arrive(&ctl->row_done[rslot]);
+          continue;
         }
-        if (step > 0) {
-          const int t = step - 1, stage = t % C::NV;
-          ok = tc::mbar_wait_a(v_empty_a + stage * 8, ((t / C::NV) & 1) ^ 1, abort_flag);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          PROF_ADD(2);
-          const uint32_t tile_a = sV_a + stage * C::TILE_BYTES, bar_a = v_full_a + stage * 8;
-          const int probe = vi + lane;
-          const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sItems[probe < n_items ? probe : 0] >> 21) == t));
-          const int mine = vi + 3 * lane + warp;
-          uint32_t my_bytes = 0;
-          if (3 * lane + warp < in_tile) {
-            const uint32_t x = sItems[mine];
-            const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = ((int)(x >> 16) << 2) & 127;
-            if (IMG) {
-              const unsigned char* src = p.vimg + p.img.off[li] + (((int64_t)bh * p.img.groups[li] + ((blk * P) >> 3)) * C::SLABS << 10);
-              tc::bulk_load_a(tile_a + (col >> 3) * (C::SLABS * 1024), src, (uint32_t)(P * D * 2), bar_a);
-            } else {
-#pragma unroll
-              for (int sl = 0; sl < C::SLABS; ++sl)
-                tc::tma_load_3d_a(tile_a + sl * kSlabBytes + col * 128, vmap0 + (uint64_t)li * sizeof(CUtensorMap), bar_a, sl * 64, blk * P, bh);
-            }
-            my_bytes = (uint32_t)C::SLABS * P * 128u;
-          }
-          vi += in_tile;
-          const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
-          if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
-          if (warp == 0 && lane == 0) TRACE(7, t);
-          PROF_ADD(3);
-        }
-      }
-#ifdef PSA_FWD_PROFILE
-      if (lane == 0 && blockIdx.x == 3 && blockIdx.y == 0) for (int i = 0; i < 4; ++i) g_prof[warp * 4 + i] = prof_acc[i];
-#endif
-    } else if (warp == 3) {
-      // ============================================================ MMA issuer
-      if (lane == 0) {
-        bool ok = tc::mbar_wait(&ctl->q_full, 0, abort_flag);
-        // ready-made descriptors: per tile only the stage offset is added, per MMA only an immediate
-        const uint32_t idesc_pv = tc::make_idesc(FMT, 128, D, 0, 1);
-        const uint32_t idesc_qk_full = tc::make_idesc(FMT, 128, 128, 0, 0);
-        const uint64_t qdesc = tc::make_smem_desc(tc::smem_u32(sQ), 16, 1024);
-        // image layout: 8-row groups are SLABS KiB apart and the slabs of a group follow each other
-        constexpr uint32_t kGroupStride = IMG ? C::SLABS * 1024 : 1024;
-        constexpr uint32_t kSlabStride = IMG ? 1024 : kSlabBytes;
-        const uint64_t kdesc0 = tc::make_smem_desc(tc::smem_u32(sK), 16, kGroupStride);
-        const uint64_t vdesc0 = tc::make_smem_desc(tc::smem_u32(sV), kSlabStride, kGroupStride);
-        const uint32_t ctl_a = tc::smem_u32(ctl);
-        const uint32_t k_full_a = ctl_a + (uint32_t)offsetof(Ctrl, k_full), k_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, k_empty);
-        const uint32_t v_full_a = ctl_a + (uint32_t)offsetof(Ctrl, v_full), v_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, v_empty);
-        const uint32_t s_full_a = ctl_a + (uint32_t)offsetof(Ctrl, s_full);
-        const uint32_t p_full_a = ctl_a + (uint32_t)offsetof(Ctrl, p_full), pv_done_a = ctl_a + (uint32_t)offsetof(Ctrl, pv_done);
+        RTRACE(3, rit);                  // issuer: row known
+        ok = tc::mbar_wait(&ctl->q_full, q_rows & 1, abort_flag);
+        if (!ok) break;
+        RTRACE(4, rit);                  // issuer: query tile there
+        // both accumulators are overwritten by this row's first P V products: the previous row's epilogue must have read
+        // them by then (the first Q K^T products of the row do not wait for that)
+        bool o_ok = q_rows == 0;
+        tc::tc_fence_after();
         int qk_next = 0, pv_next = 0;
-        uint32_t idle = 0;
-#ifdef PSA_FWD_PROFILE
-        long long prof_acc[4] = {0, 0, 0, 0};
-        long long n_idle = 0;
-#endif
-        PROF_T0();
-        while (ok && pv_next < n_tiles) {
-          bool progressed = false;
-          if (pv_next < qk_next) {
-            const int t = pv_next, b = t & 1, stage = t % C::NV;
-            if (tc::mbar_test_wait_a(p_full_a + b * 8, (t >> 1) & 1) && tc::mbar_test_wait_a(v_full_a + stage * 8, (t / C::NV) & 1)) {
-              tc::tc_fence_after();
-              TRACE(0, t);
-              const uint64_t vdesc = vdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
-              const uint32_t tP = tmem + b * 128;            // probabilities overwrite the scores they came from
-              const uint32_t tO = tmem + 256 + b * 128;      // even and odd tiles accumulate separately
-              if (t < n_tiles - 1 || last_cols == 128) {
-                tc::umma_ts(tO, tP, vdesc, idesc_pv, t > 1 ? 1u : 0u);
+          while (ok && pv_next < n_tiles) {
+            bool progressed = false;
+            if (pv_next < qk_next) {
+              const int t = pv_next, gt = g0 + t, b = gt & 1, stage = gt % C::NV;
+              if (!o_ok) o_ok = tc::mbar_test_wait_a(o_free_a, (q_rows - 1) & 1);
+            if (o_ok && tc::mbar_test_wait_a(p_full_a + b * 8, (gt >> 1) & 1) && tc::mbar_test_wait_a(v_full_a + stage * 8, (gt / C::NV) & 1)) {
+                tc::tc_fence_after();
+                TRACE(0, t);
+                const uint64_t vdesc = vdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
+                const uint32_t tP = tmem + b * 128;            // probabilities overwrite the scores they came from
+                const uint32_t tO = tmem + 256 + b * 128;      // even and odd tiles accumulate separately
+                if (t < n_tiles - 1 || last_cols == 128) {
+                  tc::umma_ts(tO, tP, vdesc, idesc_pv, t > 1 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 1; ks < 8; ++ks) tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, 1u);
-              } else {
-                for (int ks = 0; ks < last_cols / 16; ++ks)
-                  tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, (t > 1 || ks > 0) ? 1u : 0u);
+                  for (int ks = 1; ks < 8; ++ks) tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, 1u);
+                } else {
+                  for (int ks = 0; ks < last_cols / 16; ++ks)
+                    tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, (t > 1 || ks > 0) ? 1u : 0u);
+                }
+                tc::umma_commit_a(v_empty_a + stage * 8);   // V tile may be refilled
+                tc::umma_commit_a(pv_done_a + b * 8);       // accumulator b is consistent again
+                TRACE(1, t);
+                ++pv_next;
+                progressed = true;
+                PROF_ADD(0);
               }
-              tc::umma_commit_a(v_empty_a + stage * 8);   // V tile may be refilled
-              tc::umma_commit_a(pv_done_a + b * 8);       // accumulator b is consistent again
-              TRACE(1, t);
-              ++pv_next;
-              progressed = true;
-              PROF_ADD(0);
+            }
+            // S = Q K^T of tile t is only issued once P V of tile t-2 has been: the tensor pipe runs in issue order, so
+            // "S_t ready" then also means that P V of tile t-2 has finished reading the probabilities that were written over
+            // the scores of buffer t&1
+            if (qk_next < n_tiles && qk_next <= pv_next + 1) {
+              const int t = qk_next, gt = g0 + t, b = gt & 1, stage = gt % C::NK;
+              if (tc::mbar_test_wait_a(k_full_a + stage * 8, (gt / C::NK) & 1)) {
+                tc::tc_fence_after();
+                TRACE(2, t);
+                const uint64_t kdesc = kdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
+                const uint32_t idesc_qk = t == n_tiles - 1 ? tc::make_idesc(FMT, 128, last_cols, 0, 0) : idesc_qk_full;
+                const uint32_t tSb = tmem + b * 128;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                  constexpr int dummy = 0; (void)dummy;
+                  const uint32_t qoff = (uint32_t)(((ks >> 2) * kSlabBytes + (ks & 3) * 32) >> 4);
+                  const uint32_t koff = (uint32_t)(((ks >> 2) * kSlabStride + (ks & 3) * 32) >> 4);
+                  tc::umma_ss(tSb, qdesc + qoff, kdesc + koff, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+                tc::umma_commit_a(k_empty_a + stage * 8);   // K tile may be refilled
+                tc::umma_commit_a(s_full_a + b * 8);
+              if (t == n_tiles - 1) tc::umma_commit_a(q_free_a);   // the query tile may be replaced
+                TRACE(3, t);
+                ++qk_next;
+                progressed = true;
+                PROF_ADD(1);
+              }
+            }
+            if (progressed) {
+              idle = 0;
+            } else if (++idle > (1u << 24) || ((idle & 255) == 255 && *abort_flag)) {
+              *abort_flag = 1;
+              ok = false;
             }
           }
-          // S = Q K^T of tile t is only issued once P V of tile t-2 has been: the tensor pipe runs in issue order, so
-          // "S_t ready" then also means that P V of tile t-2 has finished reading the probabilities that were written over
-          // the scores of buffer t&1
-          if (qk_next < n_tiles && qk_next <= pv_next + 1) {
-            const int t = qk_next, b = t & 1, stage = t % C::NK;
-            if (tc::mbar_test_wait_a(k_full_a + stage * 8, (t / C::NK) & 1)) {
-              tc::tc_fence_after();
-              TRACE(2, t);
-              const uint64_t kdesc = kdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
-              const uint32_t idesc_qk = t == n_tiles - 1 ? tc::make_idesc(FMT, 128, last_cols, 0, 0) : idesc_qk_full;
-              const uint32_t tSb = tmem + b * 128;
-#pragma unroll
-              for (int ks = 0; ks < D / 16; ++ks) {
-                constexpr int dummy = 0; (void)dummy;
-                const uint32_t qoff = (uint32_t)(((ks >> 2) * kSlabBytes + (ks & 3) * 32) >> 4);
-                const uint32_t koff = (uint32_t)(((ks >> 2) * kSlabStride + (ks & 3) * 32) >> 4);
-                tc::umma_ss(tSb, qdesc + qoff, kdesc + koff, idesc_qk, ks > 0 ? 1u : 0u);
-              }
-              tc::umma_commit_a(k_empty_a + stage * 8);   // K tile may be refilled
-              tc::umma_commit_a(s_full_a + b * 8);
-              TRACE(3, t);
-              ++qk_next;
-              progressed = true;
-              PROF_ADD(1);
-            }
-          }
-          if (progressed) {
-            idle = 0;
-          } else if (++idle > (1u << 24) || ((idle & 255) == 255 && *abort_flag)) {
-            *abort_flag = 1;
-            ok = false;
-          }
-#ifdef PSA_FWD_PROFILE
-          if (!progressed) {
-            const bool pv_possible = pv_next < qk_next;
-            int slot = 2;
-            if (pv_possible && !tc::mbar_try_wait(&ctl->p_full[pv_next & 1], (pv_next >> 1) & 1)) slot = 2;
-            else if (pv_possible && !tc::mbar_try_wait(&ctl->v_full[pv_next % C::NV], (pv_next / C::NV) & 1)) slot = 3;
-            if (qk_next < n_tiles && !tc::mbar_try_wait(&ctl->k_full[qk_next % C::NK], (qk_next / C::NK) & 1)) ++n_idle;
-            PROF_ADD(slot);
-          }
-#endif
-        }
-#ifdef PSA_FWD_PROFILE
-        if (blockIdx.x == 3 && blockIdx.y == 0) { for (int i = 0; i < 4; ++i) g_prof[16 + i] = prof_acc[i]; g_prof[20] = n_idle; g_prof[21] = n_tiles; g_prof[22] = ctl->n_items; }
-#endif
+        RTRACE(5, rit);                  // issuer: last product of the row issued
+        if (ok) tc::mbar_arrive(&ctl->row_done[rslot]);
+        ++q_rows;
+        g0 += n_tiles;
       }
-    } else {
-      // ============================================================ softmax / epilogue
-      // Two groups of four warps, one thread per query row each.  Group g owns the tiles t = g, g+2, g+4, ... with its
-      // own running maximum, running sum and output accumulator, so the two warps that share a scheduler are in
-      // different phases of different tiles (one on the ex2 pipe while the other scales and searches the maximum) and
-      // no thread ever needs its neighbour's partial result.  The two partial outputs are merged once, at the end.
-      const int quarter = warp & 3;                 // TMEM lanes this warp may touch
-      const int g = (warp - 4) >> 2;                // softmax group = tile parity = score buffer = accumulator
-      const int r = quarter * 32 + lane;            // row inside the query block
-      const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-      const uint32_t tS = tmem + g * 128 + lane_base;         // scores of my tiles; probabilities go back in place
-      const uint32_t tO = tmem + 256 + g * 128 + lane_base;   // my accumulator
-      float m_run = -INFINITY, l_run = 0.f;
-      bool ok = true;
 #ifdef PSA_FWD_PROFILE
-      long long sprof[6] = {0, 0, 0, 0, 0, 0};
-      long long sprof_t = clock64();
+      if (blockIdx.x == 3) { for (int i = 0; i < 4; ++i) g_prof[16 + i] = prof_acc[i]; g_prof[21] = g0; }
+#endif
+    }
+  } else {
+    // ============================================================ softmax / epilogue
+    // Two groups of four warps, one thread per query row.  Group g owns the tiles whose running index is g (mod 2),
+    // with its own running maximum, running sum and output accumulator, so the two warps that share a scheduler are in
+    // different phases of different tiles and no thread ever needs its neighbour's partial result.  At the end of a row
+    // every thread reads BOTH accumulators of its row from TMEM (a warp may read any column of its own lanes) and writes
+    // half of the channels.
+    const int quarter = warp & 3;                 // TMEM lanes this warp may touch
+    const int g = (warp - 4) >> 2;                // softmax group = tile parity = score buffer = accumulator
+    const int r = quarter * 32 + lane;            // row inside the query block
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tS = tmem + g * 128 + lane_base;         // scores of my tiles; probabilities go back in place
+    const uint32_t tO = tmem + 256 + g * 128 + lane_base;   // my accumulator
+    const uint32_t tO_other = tmem + 256 + (g ^ 1) * 128 + lane_base;
+    const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+    bool ok = true;
+#ifdef PSA_FWD_PROFILE
+    long long sprof[6] = {0, 0, 0, 0, 0, 0};
+    long long sprof_t = clock64();
 #define SPROF(i) do { long long t1_ = clock64(); sprof[i] += t1_ - sprof_t; sprof_t = t1_; } while (0)
 #else
 #define SPROF(i)
 #endif
-      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
-      for (int j = g; j < n_tiles; j += 2) {
-        const int slot = j % kBiasSlots, it = j >> 1;
-        ok = tc::mbar_wait(&ctl->s_full[g], it & 1, abort_flag);   // scores ready (and the tile's bias words visible)
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        SPROF(0);
-        if (r == 0) TRACE(4, j);
-        if (lane == 0) TRACE(12 + quarter, j);
-        tc::tc_fence_after();
-        const bool ragged = j == n_tiles - 1 && last_cols < 128;   // columns the MMA did not write hold stale bits
-        const float4* bias4 = reinterpret_cast<const float4*>(sBias + slot * 128);
-        const float4* bg4 = reinterpret_cast<const float4*>(sBiasG + slot * 36);     // one bias word per 4 columns
-        const int* flagw = reinterpret_cast<const int*>(sBiasG + slot * 36) + 32;
-        // Fast path: the bias is uniform inside every aligned group of 4 columns (blocks are at least 4 wide), so the
-        // maximum is taken on raw scores per group and the bias enters once per group.  A tile with a block that ends
-        // inside a group, or with unwritten columns, takes the per-column path.
-        const bool slow = ragged || (flagw[0] | flagw[1] | flagw[2]) != 0;
-        uint32_t va[32], vb[32];      // two chunks of 32 score columns in flight
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-        if (!slow) {
-          // pass 1: running maximum; the load of the next chunk is issued before the current one is used
+    int g0 = 0, q_rows = 0;
+    for (int rit = 0; ok; ++rit) {
+      const int rslot = rit & 3;
+      ok = tc::mbar_wait(&ctl->row_ready[rslot], (rit >> 2) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int R = row_index[rslot];
+      if (R >= p.total_rows) break;
+      const int m = R % p.mq, bh = R / p.mq;
+      const int n_tiles = row_tiles[rslot], last_cols = row_last_cols[rslot];
+      constexpr int HALF = D / 2;
+      const int64_t qrow = (int64_t)m * 128 + r;
+      uint16_t* orow;
+      if (p.scatter.n_peers > 0 && qrow < p.seq_q) {
+        const int64_t owner = qrow / p.scatter.tokens_per_rank, local = qrow - owner * p.scatter.tokens_per_rank;
+        orow = reinterpret_cast<uint16_t*>(p.scatter.peer_out[owner]) +
+               (local * p.scatter.heads_total + p.scatter.head0 + bh) * D + g * HALF;
+      } else {
+        orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + g * HALF;
+      }
+      if (n_tiles == 0) {
+        // no block selected at all: the reference divides 0 by 0
+        if (qrow < p.seq_q) {
+          const uint32_t nan2 = pack2<FMT>(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
+          for (int c = 0; c < HALF; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(nan2, nan2, nan2, nan2);
+        }
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&ctl->row_done[rslot]);
+        continue;
+      }
+      float m_run = -INFINITY, l_run = 0.f;
+      const int first = ((g0 & 1) == g) ? 0 : 1;    // my first tile of this row
+      if (lane == 0 && quarter == 0) RTRACE(6 + g * 5, rit);     // softmax group: row start
+        for (int j = first; j < n_tiles; j += 2) {
+          const int gj = g0 + j, slot = gj % kBiasSlots, it = gj >> 1;
+          ok = tc::mbar_wait(&ctl->s_full[g], it & 1, abort_flag);   // scores ready (and the tile's bias words visible)
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          SPROF(0);
+          if (r == 0) TRACE(4, j);
+          if (lane == 0) TRACE(12 + quarter, j);
+          if (lane == 0 && quarter == 0 && j == first) RTRACE(7 + g * 5, rit);   // first scores seen
+          tc::tc_fence_after();
+          const bool ragged = j == n_tiles - 1 && last_cols < 128;   // columns the MMA did not write hold stale bits
+          const float4* bias4 = reinterpret_cast<const float4*>(sBias + slot * 128);
+          const float4* bg4 = reinterpret_cast<const float4*>(sBiasG + slot * 36);     // one bias word per 4 columns
+          const int* flagw = reinterpret_cast<const int*>(sBiasG + slot * 36) + 32;
+          // Fast path: the bias is uniform inside every aligned group of 4 columns (blocks are at least 4 wide), so the
+          // maximum is taken on raw scores per group and the bias enters once per group.  A tile with a block that ends
+          // inside a group, or with unwritten columns, takes the per-column path.
+          const bool slow = ragged || (flagw[0] | flagw[1] | flagw[2]) != 0;
+          uint32_t va[32], vb[32];      // two chunks of 32 score columns in flight
+          float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+          if (!slow) {
+            // pass 1: running maximum; the load of the next chunk is issued before the current one is used
 #define PSA_MAX_CHUNK(v, c)                                                                                                  \
   do {                                                                                                                       \
     const float4 ga = bg4[2 * (c)], gb = bg4[2 * (c) + 1];                                                                   \
@@ -525,64 +698,64 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     mx2 = fmaxf(mx2, fmaf(fmaxf(fmaxf(f[24], f[25]), fmaxf(f[26], f[27])), p.scale_log2, gb.z));                             \
     mx3 = fmaxf(mx3, fmaf(fmaxf(fmaxf(f[28], f[29]), fmaxf(f[30], f[31])), p.scale_log2, gb.w));                             \
   } while (0)
-          tc::tmem_ld32(tS, va);
-          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 32, vb); PSA_MAX_CHUNK(va, 0);
-          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 64, va); PSA_MAX_CHUNK(vb, 1);
-          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 96, vb); PSA_MAX_CHUNK(va, 2);
-          tc::tmem_wait_ld(); tc::tmem_ld32(tS, va);      PSA_MAX_CHUNK(vb, 3);   // chunk 0 again, for pass 2
+            tc::tmem_ld32(tS, va);
+            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 32, vb); PSA_MAX_CHUNK(va, 0);
+            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 64, va); PSA_MAX_CHUNK(vb, 1);
+            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 96, vb); PSA_MAX_CHUNK(va, 2);
+            tc::tmem_wait_ld(); tc::tmem_ld32(tS, va);      PSA_MAX_CHUNK(vb, 3);   // chunk 0 again, for pass 2
 #undef PSA_MAX_CHUNK
-        } else {
+          } else {
 #pragma unroll 1
-          for (int h = 0; h < 4; ++h) {
-            tc::tmem_ld32(tS + h * 32, va);
-            tc::tmem_wait_ld();
-            if (ragged) {
+            for (int h = 0; h < 4; ++h) {
+              tc::tmem_ld32(tS + h * 32, va);
+              tc::tmem_wait_ld();
+              if (ragged) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (h * 32 + i >= last_cols) va[i] = 0u;
-            }
+                for (int i = 0; i < 32; ++i)
+                  if (h * 32 + i >= last_cols) va[i] = 0u;
+              }
 #pragma unroll
-            for (int q4 = 0; q4 < 8; ++q4) {
-              const float4 ba = bias4[h * 8 + q4];
-              mx0 = fmaxf(mx0, fmaf(__uint_as_float(va[4 * q4 + 0]), p.scale_log2, ba.x));
-              mx1 = fmaxf(mx1, fmaf(__uint_as_float(va[4 * q4 + 1]), p.scale_log2, ba.y));
-              mx2 = fmaxf(mx2, fmaf(__uint_as_float(va[4 * q4 + 2]), p.scale_log2, ba.z));
-              mx3 = fmaxf(mx3, fmaf(__uint_as_float(va[4 * q4 + 3]), p.scale_log2, ba.w));
+              for (int q4 = 0; q4 < 8; ++q4) {
+                const float4 ba = bias4[h * 8 + q4];
+                mx0 = fmaxf(mx0, fmaf(__uint_as_float(va[4 * q4 + 0]), p.scale_log2, ba.x));
+                mx1 = fmaxf(mx1, fmaf(__uint_as_float(va[4 * q4 + 1]), p.scale_log2, ba.y));
+                mx2 = fmaxf(mx2, fmaf(__uint_as_float(va[4 * q4 + 2]), p.scale_log2, ba.z));
+                mx3 = fmaxf(mx3, fmaf(__uint_as_float(va[4 * q4 + 3]), p.scale_log2, ba.w));
+              }
             }
           }
-        }
-        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        SPROF(1);
-        // raise the running maximum only when it is far off (or still unset)
-        float alpha = 1.f;
-        const bool raise = mx > m_run + 8.f;
-        if (raise) {
-          alpha = m_run == -INFINITY ? 0.f : ex2(m_run - mx);
-          m_run = mx;
-          l_run *= alpha;
-        }
-        if (it > 0 && __any_sync(0xffffffffu, raise)) {
-          // the accumulator may only be touched between two of its P V products: wait for the one of tile j-2
-          ok = tc::mbar_wait(&ctl->pv_done[g], (it - 1) & 1, abort_flag);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc::tc_fence_after();
-#pragma unroll 1
-          for (int c0 = 0; c0 < D; c0 += 32) {
-            tc::tmem_ld32(tO + c0, vb);
-            tc::tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) vb[i] = __float_as_uint(__uint_as_float(vb[i]) * alpha);
-            tc::tmem_st32(tO + c0, vb);
+          const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+          SPROF(1);
+          // raise the running maximum only when it is far off (or still unset)
+          float alpha = 1.f;
+          const bool raise = mx > m_run + 8.f;
+          if (raise) {
+            alpha = m_run == -INFINITY ? 0.f : ex2(m_run - mx);
+            m_run = mx;
+            l_run *= alpha;
           }
-          tc::tmem_wait_st();
-        }
-        SPROF(2);
-        // pass 2: probabilities (rounded to the element type) written over the scores, running sum.  Chunk c reads score
-        // columns [32c, 32c+32) and writes packed columns [16c, 16c+16): always columns that were read before.
-        const float m_use = m_run == -INFINITY ? 0.f : m_run;
-        float2 ls_a = make_float2(0.f, 0.f), ls_b = make_float2(0.f, 0.f);
-        if (!slow) {
+          if (j >= 2 && __any_sync(0xffffffffu, raise)) {
+            // the accumulator may only be touched between two of its P V products: wait for the one of tile j-2
+            ok = tc::mbar_wait(&ctl->pv_done[g], (it - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc::tc_fence_after();
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+              tc::tmem_ld32(tO + c0, vb);
+              tc::tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) vb[i] = __float_as_uint(__uint_as_float(vb[i]) * alpha);
+              tc::tmem_st32(tO + c0, vb);
+            }
+            tc::tmem_wait_st();
+          }
+          SPROF(2);
+          // pass 2: probabilities (rounded to the element type) written over the scores, running sum.  Chunk c reads score
+          // columns [32c, 32c+32) and writes packed columns [16c, 16c+16): always columns that were read before.
+          const float m_use = m_run == -INFINITY ? 0.f : m_run;
+          float2 ls_a = make_float2(0.f, 0.f), ls_b = make_float2(0.f, 0.f);
+          if (!slow) {
 #define PSA_EXP_GROUP(f, cg, k, acc)                                                                                          \
   do {                                                                                                                       \
     const float2 cc = make_float2(cg, cg);                                                                                   \
@@ -604,148 +777,140 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     PSA_EXP_GROUP(f, gb.z - m_use, 6, ls_a); PSA_EXP_GROUP(f, gb.w - m_use, 7, ls_b);                                        \
     tc::tmem_st16(tS + 16 * (c), pk);                                                                                        \
   } while (0)
-          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 32, vb); PSA_EXP_CHUNK(va, 0);
-          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 64, va); PSA_EXP_CHUNK(vb, 1);
-          tc::tmem_wait_ld(); tc::tmem_ld32(tS + 96, vb); PSA_EXP_CHUNK(va, 2);
-          tc::tmem_wait_ld();                             PSA_EXP_CHUNK(vb, 3);
+            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 32, vb); PSA_EXP_CHUNK(va, 0);
+            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 64, va); PSA_EXP_CHUNK(vb, 1);
+            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 96, vb); PSA_EXP_CHUNK(va, 2);
+            tc::tmem_wait_ld();                             PSA_EXP_CHUNK(vb, 3);
 #undef PSA_EXP_CHUNK
 #undef PSA_EXP_GROUP
-        } else {
+          } else {
 #pragma unroll 1
-          for (int h = 0; h < 4; ++h) {
-            tc::tmem_ld32(tS + h * 32, va);
-            tc::tmem_wait_ld();
-            if (ragged) {
+            for (int h = 0; h < 4; ++h) {
+              tc::tmem_ld32(tS + h * 32, va);
+              tc::tmem_wait_ld();
+              if (ragged) {
 #pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (h * 32 + i >= last_cols) va[i] = 0u;
-            }
-            uint32_t pk[16];
+                for (int i = 0; i < 32; ++i)
+                  if (h * 32 + i >= last_cols) va[i] = 0u;
+              }
+              uint32_t pk[16];
 #pragma unroll
-            for (int q4 = 0; q4 < 8; ++q4) {
-              const float4 ba = bias4[h * 8 + q4];
-              const float a0 = ex2(fmaf(__uint_as_float(va[4 * q4 + 0]), p.scale_log2, ba.x) - m_use);
-              const float a1 = ex2(fmaf(__uint_as_float(va[4 * q4 + 1]), p.scale_log2, ba.y) - m_use);
-              const float a2 = ex2(fmaf(__uint_as_float(va[4 * q4 + 2]), p.scale_log2, ba.z) - m_use);
-              const float a3 = ex2(fmaf(__uint_as_float(va[4 * q4 + 3]), p.scale_log2, ba.w) - m_use);
-              ls_a.x += a0 + a1;
-              ls_b.x += a2 + a3;
-              pk[2 * q4] = pack2<FMT>(a0, a1);
-              pk[2 * q4 + 1] = pack2<FMT>(a2, a3);
+              for (int q4 = 0; q4 < 8; ++q4) {
+                const float4 ba = bias4[h * 8 + q4];
+                const float a0 = ex2(fmaf(__uint_as_float(va[4 * q4 + 0]), p.scale_log2, ba.x) - m_use);
+                const float a1 = ex2(fmaf(__uint_as_float(va[4 * q4 + 1]), p.scale_log2, ba.y) - m_use);
+                const float a2 = ex2(fmaf(__uint_as_float(va[4 * q4 + 2]), p.scale_log2, ba.z) - m_use);
+                const float a3 = ex2(fmaf(__uint_as_float(va[4 * q4 + 3]), p.scale_log2, ba.w) - m_use);
+                ls_a.x += a0 + a1;
+                ls_b.x += a2 + a3;
+                pk[2 * q4] = pack2<FMT>(a0, a1);
+                pk[2 * q4 + 1] = pack2<FMT>(a2, a3);
+              }
+              tc::tmem_st16(tS + h * 16, pk);
             }
-            tc::tmem_st16(tS + h * 16, pk);
           }
+          l_run += (ls_a.x + ls_a.y) + (ls_b.x + ls_b.y);
+          tc::tmem_wait_st();
+          tc::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&ctl->p_full[g]);   // one arrival per warp
+          if (r == 0) TRACE(5, j);
+          if (lane == 0) TRACE(8 + quarter, j);
+          SPROF(3);
         }
-        l_run += (ls_a.x + ls_a.y) + (ls_b.x + ls_b.y);
-        tc::tmem_wait_st();
-        tc::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) tc::mbar_arrive(&ctl->p_full[g]);   // one arrival per warp
-        if (r == 0) TRACE(5, j);
-        if (lane == 0) TRACE(8 + quarter, j);
-        SPROF(3);
-      }
-#ifdef PSA_FWD_PROFILE
-      if (threadIdx.x == 128 && blockIdx.x == 3 && blockIdx.y == 0) for (int i = 0; i < 6; ++i) g_prof[32 + i] = sprof[i];
-#endif
+      if (lane == 0 && quarter == 0) RTRACE(8 + g * 5, rit);       // last probabilities written
       // ---- epilogue: merge the two groups' partial results
-      const int my_tiles = (n_tiles - g + 1) >> 1;
+      const int my_tiles = n_tiles > first ? (n_tiles - first + 1) >> 1 : 0;
       if (ok && my_tiles > 0) {
-        ok = tc::mbar_wait(&ctl->pv_done[g], (my_tiles - 1) & 1, abort_flag);
+        const int last_it = (g0 + first + 2 * (my_tiles - 1)) >> 1;
+        ok = tc::mbar_wait(&ctl->pv_done[g], last_it & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
       }
-#ifdef PSA_FWD_PROFILE
-      if (threadIdx.x == 128 && blockIdx.x == 3 && blockIdx.y == 0) g_prof[50] = clock64();   // group 0 through its last P V
-#endif
-      // group g publishes (maximum, sum); both groups then agree on the weights.  An aborting group still joins the
-      // barriers so that the other one is not left waiting.
-      sXch[g * 256 + r] = m_run;
-      sXch[g * 256 + 128 + r] = l_run;
-      tc::named_bar_sync(1, kSoftmaxThreads);
-      const float m_o = sXch[(g ^ 1) * 256 + r], l_o = sXch[(g ^ 1) * 256 + 128 + r];
-      const float m_all = fmaxf(m_run, m_o);
-      const float w_me = m_run == -INFINITY ? 0.f : ex2(m_run - m_all);
-      const float w_ot = m_o == -INFINITY ? 0.f : ex2(m_o - m_all);
-      const float inv = 1.0f / (l_run * w_me + l_o * w_ot);     // empty row: 0/0 like the reference
-      const float w = w_me * inv;
-      // each group finishes half of the channels: it hands the other half of its partial output over through shared
-      // memory (the K ring is idle by now), transposed so that a warp's 32 rows are 32 consecutive words
-      constexpr int HALF = D / 2;
-      float* stage = reinterpret_cast<float*>(sK);
-      tc::tc_fence_after();
-      if (ok && my_tiles > 0) {
-#pragma unroll 1
+      // group g publishes (maximum, sum); after the barrier both groups' last products are complete.  An aborting group
+      // still joins the barrier so that the other one is not left waiting.
+      float* xch = sXch + (rit & 1) * 512;
+      xch[g * 256 + r] = m_run;
+      xch[g * 256 + 128 + r] = l_run;
+      if (ok) ok = warps_rendezvous(&ctl->xch_full, q_rows, abort_flag); else ++q_rows;
+      if (lane == 0 && quarter == 0) RTRACE(9 + g * 5, rit);       // both groups through their last product
+      if (ok) {
+        const float m_o = xch[(g ^ 1) * 256 + r], l_o = xch[(g ^ 1) * 256 + 128 + r];
+        const float m_all = fmaxf(m_run, m_o);
+        const float w_me = m_run == -INFINITY ? 0.f : ex2(m_run - m_all);
+        const float w_ot = m_o == -INFINITY ? 0.f : ex2(m_o - m_all);
+        const float inv = 1.0f / (l_run * w_me + l_o * w_ot);     // empty row: 0/0 like the reference
+        const float w = w_me * inv, wo = w_ot * inv;
+        const bool other_has = n_tiles - my_tiles > 0;
+        tc::tc_fence_after();
+        float f[HALF];
+#pragma unroll
         for (int c0 = 0; c0 < HALF; c0 += 32) {
-          uint32_t v[32];
-          tc::tmem_ld32(tO + (g ^ 1) * HALF + c0, v);
+          uint32_t va[32], vb[32];
+          if (my_tiles > 0) tc::tmem_ld32(tO + g * HALF + c0, va);
+          if (other_has) tc::tmem_ld32(tO_other + g * HALF + c0, vb);
           tc::tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) stage[(g * HALF + c0 + i) * 128 + r] = __uint_as_float(v[i]) * w;
-        }
-      }
-      tc::named_bar_sync(2, kSoftmaxThreads);
-      if (ok) {
-        const bool other_has = n_tiles - my_tiles > 0;
-        const int64_t qrow = (int64_t)m * 128 + r;
-        uint16_t* orow;
-        if (p.scatter.n_peers > 0 && qrow < p.seq_q) {
-          const int64_t owner = qrow / p.scatter.tokens_per_rank, local = qrow - owner * p.scatter.tokens_per_rank;
-          orow = reinterpret_cast<uint16_t*>(p.scatter.peer_out[owner]) +
-                 (local * p.scatter.heads_total + p.scatter.head0 + bh) * D + g * HALF;
-        } else {
-          orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + g * HALF;
-        }
-#pragma unroll 1
-        for (int c0 = 0; c0 < HALF; c0 += 32) {
-          uint32_t v[32];
-          if (my_tiles > 0) {
-            tc::tmem_ld32(tO + g * HALF + c0, v);
-            tc::tmem_wait_ld();
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0u;
-          }
-          float f[32];
-#pragma unroll
           for (int i = 0; i < 32; ++i)
-            f[i] = __uint_as_float(v[i]) * w + (other_has ? stage[((g ^ 1) * HALF + c0 + i) * 128 + r] : 0.f);
-          if (qrow < p.seq_q) {
+            f[c0 + i] = (my_tiles > 0 ? __uint_as_float(va[i]) * w : 0.f) + (other_has ? __uint_as_float(vb[i]) * wo : 0.f);
+        }
+        // the accumulators may be overwritten by the next row from here on
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&ctl->o_free);
+        // A thread holds HALF channels of its own row; stored as they are, every store instruction of a warp would touch 32
+        // different 128-byte lines.  The 16-byte pieces are transposed inside groups of 8 lanes first (three butterfly
+        // stages), so that 8 lanes write one row's contiguous 128 bytes.
+        constexpr int NCH = HALF / 8;                 // 16-byte pieces per thread: 8 (D = 128) or 4 (D = 64)
+        uint4 ch[NCH];
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 o;
-              o.x = pack2<FMT>(f[i], f[i + 1]);
-              o.y = pack2<FMT>(f[i + 2], f[i + 3]);
-              o.z = pack2<FMT>(f[i + 4], f[i + 5]);
-              o.w = pack2<FMT>(f[i + 6], f[i + 7]);
-              *reinterpret_cast<uint4*>(orow + c0 + i) = o;
+        for (int c = 0; c < NCH; ++c) {
+          ch[c].x = pack2<FMT>(f[8 * c + 0], f[8 * c + 1]);
+          ch[c].y = pack2<FMT>(f[8 * c + 2], f[8 * c + 3]);
+          ch[c].z = pack2<FMT>(f[8 * c + 4], f[8 * c + 5]);
+          ch[c].w = pack2<FMT>(f[8 * c + 6], f[8 * c + 7]);
+        }
+#pragma unroll
+        for (int sft = 1; sft < NCH; sft <<= 1) {
+          const bool upper = (lane & sft) != 0;
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+            if ((c & sft) == 0) {
+              // the lower lane keeps piece c and receives the partner's piece c; the upper lane keeps piece c|sft
+              const uint4 send = upper ? ch[c] : ch[c | sft];
+              uint4 recv;
+              recv.x = __shfl_xor_sync(0xffffffffu, send.x, sft);
+              recv.y = __shfl_xor_sync(0xffffffffu, send.y, sft);
+              recv.z = __shfl_xor_sync(0xffffffffu, send.z, sft);
+              recv.w = __shfl_xor_sync(0xffffffffu, send.w, sft);
+              if (upper) ch[c] = recv; else ch[c | sft] = recv;
             }
           }
         }
+        // now piece k of lane (base + i) is piece i of row (base + k), base = the first lane of the group of NCH lanes
+        {
+          const int sub = lane & (NCH - 1), base = lane & ~(NCH - 1);
+          const unsigned long long my_ptr = reinterpret_cast<unsigned long long>(orow);
+#pragma unroll
+          for (int k = 0; k < NCH; ++k) {
+            const unsigned long long dst = __shfl_sync(0xffffffffu, my_ptr, base + k);
+            const int64_t row_k = (int64_t)m * 128 + quarter * 32 + base + k;
+            if (row_k < p.seq_q) *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dst) + sub * 8) = ch[k];
+          }
+        }
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&ctl->row_done[rslot]);
+        if (lane == 0 && quarter == 0) RTRACE(10 + g * 5, rit);    // output written
       }
+      g0 += n_tiles;
     }
-  } else if (warp >= 4) {
-    // no block selected at all: the reference divides 0 by 0
-    const int half = (warp - 4) >> 2;
-    const int64_t qrow = (int64_t)m * 128 + (warp & 3) * 32 + lane;
-    if (qrow < p.seq_q) {
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + half * (D / 2);
-      if (p.scatter.n_peers > 0) {
-        const int64_t owner = qrow / p.scatter.tokens_per_rank, local = qrow - owner * p.scatter.tokens_per_rank;
-        orow = reinterpret_cast<uint16_t*>(p.scatter.peer_out[owner]) +
-               (local * p.scatter.heads_total + p.scatter.head0 + bh) * D + half * (D / 2);
-      }
-      const uint32_t nan2 = pack2<FMT>(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
-      for (int c = 0; c < D / 2; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(nan2, nan2, nan2, nan2);
-    }
+#ifdef PSA_FWD_PROFILE
+    if (threadIdx.x == 128 && blockIdx.x == 3) for (int i = 0; i < 6; ++i) g_prof[32 + i] = sprof[i];
+#endif
   }
 
   // ---------------------------------------------------------------- teardown
-  if (n_tiles == 0 && threadIdx.x == 0) tc::mbar_wait(&ctl->q_full, 0, abort_flag);   // the early query fetch must land first
   tc::tc_fence_before();
   __syncthreads();
-#ifdef PSA_FWD_PROFILE
-  if (threadIdx.x == 0 && blockIdx.x == 3 && blockIdx.y == 0) g_prof[51] = clock64();
-#endif
   if (ctl->abort_flag) {
     if (threadIdx.x == 0 && p.status) atomicExch(p.status, PSA_ERR_TIMEOUT);
     for (int i = 0; i < 64; ++i) __nanosleep(1000);   // let copies in flight land before the CTA retires
@@ -806,6 +971,34 @@ bool fwd_tc_supported(const FwdArgs& a) {
   return true;
 }
 
+// Row counters of the persistent forward: a ring of device words; every launch takes the next one and zeroes it on its
+// own stream right before the kernel, so launches in flight on different streams do not share a counter (unless more than
+// kCounterRing launches of one device overlap in time).
+constexpr int kCounterRing = 256;
+__device__ int g_row_counters[kCounterRing];
+
+static int next_row_counter(int** out, cudaStream_t st) {
+  constexpr int kMaxDevices = 64;
+  static int* base[kMaxDevices] = {nullptr};
+  static unsigned next[kMaxDevices] = {0};
+  static std::mutex mu;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  PSA_REQUIRE(e == cudaSuccess && dev >= 0 && dev < kMaxDevices, PSA_ERR_CUDA, "psa_fwd: cudaGetDevice failed: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_row_counters);
+    PSA_REQUIRE(e == cudaSuccess && ptr, PSA_ERR_CUDA, "psa_fwd: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    base[dev] = (int*)ptr;
+  }
+  int* c = base[dev] + (next[dev]++ % kCounterRing);
+  e = cudaMemsetAsync(c, 0, sizeof(int), st);
+  PSA_REQUIRE(e == cudaSuccess, PSA_ERR_CUDA, "psa_fwd: cudaMemsetAsync failed: %s", cudaGetErrorString(e));
+  *out = c;
+  return PSA_OK;
+}
+
 template <int D, int FMT, bool IMG>
 static int launch_tc(const FwdArgs& a, cudaStream_t st) {
   using C = Cfg<D>;
@@ -825,13 +1018,22 @@ static int launch_tc(const FwdArgs& a, cudaStream_t st) {
   for (int i = 0; i < 4; ++i) p.n[i] = a.n[i];
   p.mq = (int)cdiv64(a.seq_q, 128); p.bn = a.bn; p.tn = a.tn; p.width = a.width; p.quirk = a.quirk;
   p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.total_rows = (int)((int64_t)p.mq * a.bh);
   p.kimg = (const unsigned char*)a.kimg; p.vimg = (const unsigned char*)a.vimg;
   p.img = make_img_levels(a.bh, a.seq_k, D, IMG ? a.bn : 64);
   p.scatter = a.scatter;
   cudaError_t e = cudaFuncSetAttribute(psa_fwd_tc_kernel<D, FMT, IMG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   PSA_REQUIRE(e == cudaSuccess, PSA_ERR_CUDA, "psa_fwd: shared-memory opt-in (%d B) failed: %s", C::SMEM_BYTES,
               cudaGetErrorString(e));
-  dim3 grid(p.mq, (unsigned)a.bh);
+  // persistent: one CTA per SM (221 KB of shared memory and all 512 TMEM columns each), rows dealt round-robin so that
+  // the CTAs running at the same time work on neighbouring rows of the same head (K/V stay in L2)
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  PSA_REQUIRE(sms > 0, PSA_ERR_CUDA, "psa_fwd: cannot read the SM count");
+  const unsigned grid = (unsigned)(p.total_rows < sms ? p.total_rows : sms);
+  rc = next_row_counter(&p.row_counter, st);
+  if (rc != PSA_OK) return rc;
   psa_fwd_tc_kernel<D, FMT, IMG><<<grid, kThreads, C::SMEM_BYTES, st>>>(maps, p);
   PSA_CHECK_LAUNCH("psa_fwd(tcgen05)");
   return PSA_OK;

@@ -240,7 +240,7 @@ def psa_forward(q, k, v, mask, block_m: int, block_n: int, tile_n: int, sm_scale
     Sk = k.shape[2]
     if sm_scale is None:
         sm_scale = D ** -0.5
-    use_images = isinstance(pyramid, KVImages) or (pyramid is None and impl == IMPL_AUTO and mask.shape[-1] <= 4064
+    use_images = isinstance(pyramid, KVImages) or (pyramid is None and impl == IMPL_AUTO and mask.shape[-1] <= 2976
                                                    and images_supported(k, block_m, block_n, tile_n) and sm_scale > 0)
     if use_images:
         if pyramid is None:
