@@ -1,31 +1,39 @@
 // Multi-level block-sparse flash-attention forward on tcgen05 tensor cores (f16/bf16, block_m = 128).
 //
-// One CTA per (128-row query block, batch*head), 12 warps:
-//   warps 0-2   producers: decode the block's index list into a flat item table, then gather the selected K/V blocks of
-//               every pyramid level into 128-token tiles, PACKING blocks of different levels into the same tile.  A
-//               block is P = block_n/level contiguous pooled rows.  From tile images it is ONE linear bulk copy per
-//               operand; from row-major tensors one TMA box {64 ch, P rows} per 64-channel slab (128-byte swizzle).
-//               Never multicast.  A copy costs its issuing thread 150-200 cycles whatever its size, so the blocks of a
-//               tile are spread over the lanes of all three warps (lane l of warp w takes block 3l+w), which decode and
-//               issue side by side.  K tiles and V tiles live in separate rings (K is released after S = Q K^T, V after
-//               O += P V) and K runs one tile ahead of V.  The producers also write the logit bias of the tile's
-//               columns (log2 of the level, -inf for columns that do not exist), per column and per group of 4 columns.
+// Persistent CTAs, one per SM (221 KB of shared memory and all 512 TMEM columns each), 12 warps.  A CTA starts with query
+// row R = blockIdx.x (R = batch*head * Mq + query block) and claims further rows from a global counter; its roles run the
+// rows as ONE continuous stream of 128-token tiles: ring stages, score buffers and barrier phases are indexed by the
+// running tile count, so nothing is drained between rows.
+//   warps 0-2   producers: decode a row's index list into a flat item table (double-buffered; the next row is decoded,
+//               and the list after it prefetched with cp.async, while the rings of the current row are full), then gather
+//               the selected K/V blocks of every pyramid level into 128-token tiles, PACKING blocks of different levels
+//               into the same tile.  A block is P = block_n/level contiguous pooled rows.  From tile images it is ONE
+//               linear bulk copy per operand; from row-major tensors one TMA box {64 ch, P rows} per 64-channel slab
+//               (128-byte swizzle).  Never multicast.  A copy costs its issuing thread 150-200 cycles whatever its size,
+//               so the blocks of a tile are spread over the lanes of all three warps (lane l of warp w takes block 3l+w),
+//               which decode and issue side by side.  K tiles and V tiles live in separate rings (K is released after
+//               S = Q K^T, V after O += P V) and K runs one tile ahead of V.  The producers also write the logit bias of
+//               the tile's columns (log2 of the level, -inf for columns that do not exist), per column and per group of
+//               4 columns, publish every row (tile count) to the other roles and fetch its query tile as soon as the
+//               previous row's last Q K^T has read the old one.
 //   warp 3      MMA issuer (one thread): S = Q K^T (operands in shared memory) into one of two TMEM score buffers, and
 //               O += P V with P read from TMEM and V read MN-major from its swizzled tile.  Descriptors are built once;
 //               per MMA only an immediate is added.  It polls (non-blocking) for whichever product is ready and issues in
 //               the fixed order QK0 QK1 PV0 QK2 PV1 ...; the tensor pipe runs in issue order, so "S of tile t ready" also
-//               says that P V of tile t-2 is done with the buffer.
-//   warps 4-11  softmax: two groups of four warps, ONE thread per query row.  Group g owns tiles g, g+2, g+4, ... with
-//               its own running maximum, running sum and output accumulator (a split-KV inside the CTA), so no thread
-//               needs another thread's partial result and the two warps on a scheduler work on different tiles.  Two
-//               passes over the score tile in TMEM, 32 columns at a time with the next chunk's load in flight: maximum,
-//               then exp2 / sum / round to the element type, written back IN PLACE over the scores.  The running
-//               maximum is only raised when the new one exceeds it by more than 2^8 ("lazy" rescale of the accumulator).
-//               Epilogue: the groups exchange (max, sum), hand each other half of their partial output through shared
-//               memory and write O / sum.
+//               says that P V of tile t-2 is done with the buffer.  The first scores of the next row are computed while
+//               the softmax warps are still in the epilogue of the current one.
+//   warps 4-11  softmax: two groups of four warps, ONE thread per query row.  Group g owns the tiles whose running index
+//               is g (mod 2), with its own running maximum, running sum and output accumulator (a split-KV inside the
+//               CTA), so no thread needs another thread's partial result and the two warps on a scheduler work on
+//               different tiles.  Two passes over the score tile in TMEM, 32 columns at a time with the next chunk's load
+//               in flight: maximum, then exp2 / sum / round to the element type, written back IN PLACE over the scores.
+//               The running maximum is only raised when the new one exceeds it by more than 2^8 ("lazy" rescale of the
+//               accumulator).  Epilogue of a row: the groups exchange (max, sum), every thread reads BOTH accumulators of
+//               its row from TMEM, and after an 8x8 transpose by warp shuffles 8 lanes store one row's 128 contiguous bytes.
 // TMEM (512 columns): S0/P0 [0,128), S1/P1 [128,256), O of even tiles [256,256+D), O of odd tiles [384,384+D).
 //
-// Every mbarrier wait is bounded; on expiry the CTA records PSA_ERR_TIMEOUT in the status word, lets copies in
+// Every wait is bounded - mbarrier waits, the issuer's polling loop and the warp-group rendezvous (mbarriers, never
+// bar.sync, inside the role loops); on expiry the CTA records PSA_ERR_TIMEOUT in the status word, lets copies in
 // flight land, frees its TMEM and returns.
 #include <cstddef>
 #include <mutex>
