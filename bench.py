@@ -422,10 +422,10 @@ def main():
         "exchange": (args.exchange if world > 1 else None),
         "roofline": {"bound": "tensor", "kernel": "psa_fwd_tc_kernel", "achieved": fwd_tflops, "peak": peak_tf,
                      "unit": "TFLOP/s", "frac": fwd_tflops / peak_tf,
-                     # dram read+write of one forward launch: ncu-measured 1531 B per (head x token) on the 6-head
+                     # dram read+write of one forward launch: ncu-measured 1539 B per (head x token) on the 6-head
                      # Wan2.1-1.3B-shape capture (every byte of Q, O and the K/V images crosses HBM about once, so
                      # the figure scales with heads x tokens)
-                     "traffic": 1531.0 * hp * S, "traffic_unit": "bytes per launch",
+                     "traffic": 1539.0 * hp * S, "traffic_unit": "bytes per launch",
                      "traffic_source": "profiles/psa_fwd_tc_kernel__wan2.1-1.3b-shape_6heads.md, scaled by heads x tokens",
                      "peak_source": f"{peaks['source']} (sustained bf16: kernel timed inside a long step)",
                      # tile-image pyramid: read K,V once (2 N e), write levels 1,2,4,8 of both (3.75 N e)
