@@ -90,7 +90,7 @@ extern "C" int psa_fwd_images(const void* q, const void* kimg, const void* vimg,
   a.bh = bh; a.seq_q = seq_q; a.seq_k = seq_k; a.D = head_dim; a.bm = block_m; a.bn = block_n; a.tn = tile_n;
   a.width = mask_width; a.scale = sm_scale; a.quirk = compat_quirk; a.dtype = dtype;
   PSA_REQUIRE(fwd_tc_supported(a), PSA_ERR_UNSUPPORTED,
-              "psa_fwd_images: needs f16/bf16, block_m=128, tile_n=32, head_dim 64/128, mask width <= 2976");
+              "psa_fwd_images: needs f16/bf16, block_m=128, tile_n=32, head_dim 64/128, mask width <= 1472");
   return fwd_tc_launch(a, (cudaStream_t)stream);
 }
 
@@ -123,6 +123,6 @@ extern "C" int psa_fwd_images_scatter(const void* q, const void* kimg, const voi
   a.scatter.n_peers = n_peers; a.scatter.heads_total = heads_total; a.scatter.head0 = head0;
   a.scatter.tokens_per_rank = tokens_per_rank;
   PSA_REQUIRE(fwd_tc_supported(a), PSA_ERR_UNSUPPORTED,
-              "psa_fwd_images_scatter: needs f16/bf16, block_m=128, tile_n=32, head_dim 64/128, mask width <= 2976");
+              "psa_fwd_images_scatter: needs f16/bf16, block_m=128, tile_n=32, head_dim 64/128, mask width <= 1472");
   return fwd_tc_launch(a, (cudaStream_t)stream);
 }

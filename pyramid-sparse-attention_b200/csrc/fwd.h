@@ -76,6 +76,8 @@ struct FwdArgs {
   int D, bm, bn, tn, width, quirk, dtype;
   float scale;
   OutScatter scatter = {};   // n_peers == 0 unless the output goes to peer buffers
+  float* lse = nullptr;      // optional [bh][seq_q]: log-sum-exp of every row (natural log)
+  int legacy = 0;            // legacy semantics: a row without any visible key gives 0 (lse -inf) instead of 0/0
 };
 
 int fwd_simt_dispatch(const void* q, const void* const* kl, const void* const* vl, const int64_t* nl, const int32_t* mask,

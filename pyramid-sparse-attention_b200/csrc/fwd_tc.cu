@@ -76,6 +76,8 @@ struct TcParams {
   const unsigned char* vimg;
   ImgLevels img;
   OutScatter scatter;   // n_peers > 0: rows go to the peer that owns the token (plain stores over NVLink)
+  float* lse;           // optional log-sum-exp output
+  int legacy;           // rows without a visible key give 0 / -inf instead of 0/0
 };
 
 template <int D> struct Cfg {
@@ -661,8 +663,9 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       if (n_tiles == 0) {
         // no block selected at all: the reference divides 0 by 0
         if (qrow < p.seq_q) {
-          const uint32_t nan2 = pack2<FMT>(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
+          const uint32_t nan2 = p.legacy ? 0u : pack2<FMT>(__int_as_float(0x7fc00000), __int_as_float(0x7fc00000));
           for (int c = 0; c < HALF; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(nan2, nan2, nan2, nan2);
+          if (p.lse && g == 0) p.lse[(int64_t)bh * p.seq_q + qrow] = p.legacy ? -INFINITY : __int_as_float(0x7fc00000);
         }
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&ctl->row_done[rslot]);
@@ -846,8 +849,12 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         const float m_all = fmaxf(m_run, m_o);
         const float w_me = m_run == -INFINITY ? 0.f : ex2(m_run - m_all);
         const float w_ot = m_o == -INFINITY ? 0.f : ex2(m_o - m_all);
-        const float inv = 1.0f / (l_run * w_me + l_o * w_ot);     // empty row: 0/0 like the reference
+        const float l_all = l_run * w_me + l_o * w_ot;
+        const bool dead = p.legacy && m_all == -INFINITY;         // legacy kernel: no visible key -> 0, lse -inf
+        const float inv = dead ? 0.f : 1.0f / l_all;              // otherwise an empty row is 0/0 like the reference
         const float w = w_me * inv, wo = w_ot * inv;
+        if (p.lse && g == 0 && qrow < p.seq_q)
+          p.lse[(int64_t)bh * p.seq_q + qrow] = dead ? -INFINITY : (m_all + log2f(l_all)) * 0.6931471805599453f;
         const bool other_has = n_tiles - my_tiles > 0;
         tc::tc_fence_after();
         float f[HALF];
@@ -1030,6 +1037,7 @@ static int launch_tc(const FwdArgs& a, cudaStream_t st) {
   p.kimg = (const unsigned char*)a.kimg; p.vimg = (const unsigned char*)a.vimg;
   p.img = make_img_levels(a.bh, a.seq_k, D, IMG ? a.bn : 64);
   p.scatter = a.scatter;
+  p.lse = a.lse; p.legacy = a.legacy;
   cudaError_t e = cudaFuncSetAttribute(psa_fwd_tc_kernel<D, FMT, IMG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   PSA_REQUIRE(e == cudaSuccess, PSA_ERR_CUDA, "psa_fwd: shared-memory opt-in (%d B) failed: %s", C::SMEM_BYTES,
               cudaGetErrorString(e));

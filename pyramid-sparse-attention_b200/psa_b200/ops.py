@@ -240,7 +240,7 @@ def psa_forward(q, k, v, mask, block_m: int, block_n: int, tile_n: int, sm_scale
     Sk = k.shape[2]
     if sm_scale is None:
         sm_scale = D ** -0.5
-    use_images = isinstance(pyramid, KVImages) or (pyramid is None and impl == IMPL_AUTO and mask.shape[-1] <= 2976
+    use_images = isinstance(pyramid, KVImages) or (pyramid is None and impl == IMPL_AUTO and mask.shape[-1] <= 1472
                                                    and images_supported(k, block_m, block_n, tile_n) and sm_scale > 0)
     if use_images:
         if pyramid is None:
@@ -281,6 +281,21 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
     B, H, S, D = q.shape
     if sm_scale is None:
         sm_scale = D ** -0.5
+    n128 = -(-S // 128)
+    if (not causal and pyramid is None and not need_lse and q.dtype in (torch.float16, torch.bfloat16) and n128 + 5 <= 1472
+            and sm_scale > 0):
+        # inference path of the old-mask presets: the tcgen05 forward on tile images (the row-major pyramid the backward
+        # would need is not built)
+        imgs = pyramid_kv_images(k, v, 128)
+        with torch.cuda.device(q.device):
+            o = torch.empty_like(q)
+            scratch = torch.empty(lib.psa_legacy_index_bytes(B * H, S) // 4, dtype=torch.int32, device=q.device)
+            status = torch.zeros(1, dtype=torch.int32, device=q.device)
+            rc = lib.psa_legacy_fwd_images(_ptr(q), _ptr(imgs.kimg), _ptr(imgs.vimg), _ptr(mask), _ptr(scratch), _ptr(o), None,
+                                           B * H, S, D, mask.shape[-1], float(sm_scale), _dt(q), _ptr(status), _stream(q))
+        check(rc, "psa_legacy_fwd_images")
+        o._psa_status = status
+        return o, None, None
     if pyramid is None:
         pyramid = pyramid_kv(k, v, 128)
     (k2, k4, k8), (v2, v4, v8) = pyramid
@@ -292,6 +307,27 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
                                 _dt(q), _stream(q))
     check(rc, "psa_legacy_fwd")
     return o, lse, pyramid
+
+
+def legacy_forward_tc(q, k, v, mask, sm_scale: Optional[float] = None, need_lse: bool = True):
+    """Non-causal legacy forward on the tcgen05 kernel (psa_legacy_fwd_images); returns (o, lse or None)."""
+    _need_cuda(q, k, v, mask)
+    q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _flat_bh(mask)
+    if mask.dtype != torch.int32:
+        mask = mask.to(torch.int32)
+    B, H, S, D = q.shape
+    sm_scale = D ** -0.5 if sm_scale is None else sm_scale
+    imgs = pyramid_kv_images(k, v, 128)
+    with torch.cuda.device(q.device):
+        o = torch.empty_like(q)
+        lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if need_lse else None
+        scratch = torch.empty(lib.psa_legacy_index_bytes(B * H, S) // 4, dtype=torch.int32, device=q.device)
+        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        rc = lib.psa_legacy_fwd_images(_ptr(q), _ptr(imgs.kimg), _ptr(imgs.vimg), _ptr(mask), _ptr(scratch), _ptr(o), _ptr(lse),
+                                       B * H, S, D, mask.shape[-1], float(sm_scale), _dt(q), _ptr(status), _stream(q))
+    check(rc, "psa_legacy_fwd_images")
+    o._psa_status = status
+    return o, lse
 
 
 def legacy_backward(q, k, v, mask, o, lse, do, causal: bool, sm_scale: float, pyramid):
