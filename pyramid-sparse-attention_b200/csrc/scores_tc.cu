@@ -9,6 +9,9 @@
 //    256 TMEM columns and ~100 KB of shared memory per CTA, so two CTAs share an SM and one's epilogue overlaps
 //    the other's MMAs.
 // Tensor-bound: F_est = 2*BH*(Sq/4)*(Sk/4)*D per call.  Every mbarrier wait is bounded.
+#include <algorithm>
+#include <cmath>
+
 #include "psa_common.cuh"
 #include "scores.h"
 #include "tc_common.cuh"
@@ -49,8 +52,20 @@ struct Params {
   void* R;
   float* rowmax;
   int nq_s, n_d, kk, n_tiles;
+  int ksplit;          // CTAs per query tile, each with a contiguous share of the key tiles (grid.z)
   float qk_scale;
 };
+
+// max of floats through integer atomics; *addr must start at -inf
+__device__ __forceinline__ void atomic_max_float(float* addr, float v) {
+  v += 0.0f;   // -0 -> +0
+  if (v >= 0.f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+
+__global__ void fill_neg_inf(float* x, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) x[i] = -INFINITY;
+}
 
 template <int D, int FMT>
 __global__ void __launch_bounds__(kThreads, 2) scores_cellmax_tc_kernel(const __grid_constant__ CUtensorMap tm_q,
@@ -83,7 +98,10 @@ __global__ void __launch_bounds__(kThreads, 2) scores_cellmax_tc_kernel(const __
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
-  const int n_tiles = p.n_tiles;
+  // this CTA's share of the key tiles: [j0, j0 + n_tiles)
+  const int per = (p.n_tiles + p.ksplit - 1) / p.ksplit;
+  const int j0 = (int)blockIdx.z * per;
+  const int n_tiles = p.n_tiles - j0 < per ? (p.n_tiles - j0 > 0 ? p.n_tiles - j0 : 0) : per;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -93,7 +111,7 @@ __global__ void __launch_bounds__(kThreads, 2) scores_cellmax_tc_kernel(const __
         const int stage = j % kStages;
         if (!tc::mbar_wait(&ctl->empty[stage], ((j / kStages) & 1) ^ 1, abort_flag)) break;
         for (int s = 0; s < SLABS; ++s)
-          tc::tma_load_3d(sK + stage * TILE_BYTES + s * kSlabBytes, &tm_k, &ctl->full[stage], s * 64, j * 128, bh);
+          tc::tma_load_3d(sK + stage * TILE_BYTES + s * kSlabBytes, &tm_k, &ctl->full[stage], s * 64, (j0 + j) * 128, bh);
         tc::mbar_arrive_expect_tx(&ctl->full[stage], TILE_BYTES);
       }
     }
@@ -136,7 +154,7 @@ __global__ void __launch_bounds__(kThreads, 2) scores_cellmax_tc_kernel(const __
       if (!ok) break;
       tc::tc_fence_after();
       uint32_t packed[8];     // up to 16 cells of a tile (kk = 8), two per word
-      const int cell0 = j * cells_per_tile;
+      const int cell0 = (j0 + j) * cells_per_tile;
 #pragma unroll
       for (int c0 = 0; c0 < 128; c0 += 32) {
         uint32_t v[32];
@@ -200,7 +218,10 @@ __global__ void __launch_bounds__(kThreads, 2) scores_cellmax_tc_kernel(const __
         }
       }
     }
-    if (ok && row < p.nq_s) p.rowmax[(int64_t)bh * p.nq_s + row] = run_max;
+    if (ok && row < p.nq_s) {
+      if (p.ksplit == 1) p.rowmax[(int64_t)bh * p.nq_s + row] = run_max;
+      else atomic_max_float(&p.rowmax[(int64_t)bh * p.nq_s + row], run_max);
+    }
   }
 
   tc::tc_fence_before();
@@ -230,7 +251,26 @@ int launch_cellmax(const void* qs, const void* ks, void* R, float* rowmax, const
   const int smem = (D / 64) * kSlabBytes * (1 + kStages) + 256 + 1024;
   cudaError_t e = cudaFuncSetAttribute(scores_cellmax_tc_kernel<D, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   PSA_REQUIRE(e == cudaSuccess, PSA_ERR_CUDA, "psa_block_scores: shared-memory opt-in failed: %s", cudaGetErrorString(e));
-  dim3 grid((d.nq_s + 127) / 128, (unsigned)bh);
+  // Two CTAs share an SM.  When the query tiles do not fill whole waves (few heads per GPU), the key range of every
+  // query tile is split over 2 or 4 CTAs; their row maxima meet through atomics.
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const double slots = 2.0 * (sms > 0 ? sms : 148);
+  const int64_t ctas = (int64_t)((d.nq_s + 127) / 128) * bh;
+  int ksplit = 1;
+  double best = 0.0;
+  for (int ks = 1; ks <= 4 && ks <= p.n_tiles; ks *= 2) {
+    const double waves = (double)(ctas * ks) / slots;
+    const double eff = waves / ceil(waves) - 0.01 * (ks - 1);      // a split costs a little (query tile loaded again)
+    if (eff > best + 1e-9) { best = eff; ksplit = ks; }
+  }
+  p.ksplit = ksplit;
+  if (ksplit > 1) {
+    const int64_t n = bh * (int64_t)d.nq_s;
+    fill_neg_inf<<<(unsigned)std::min<int64_t>((n + 255) / 256, 1024), 256, 0, st>>>(rowmax, n);
+  }
+  dim3 grid((d.nq_s + 127) / 128, (unsigned)bh, (unsigned)ksplit);
   scores_cellmax_tc_kernel<D, FMT><<<grid, kThreads, smem, st>>>(tq, tk, p);
   PSA_CHECK_LAUNCH("psa_block_scores(tcgen05 stage A)");
   return PSA_OK;
