@@ -135,9 +135,10 @@ def main():
     ap.add_argument("--workload", default="wan2.1-14b-attn-layer")
     ap.add_argument("--sparsity", default="90", choices=["90", "85"])
     ap.add_argument("--chunks", type=int, default=5, help="head chunks per rank for exchange/compute overlap (N>1)")
-    ap.add_argument("--pull-blocks", type=int, default=32, help="grid cap of the prefetching peer pulls (p2p exchange)")
-    ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-pull", "nccl"],
-                    help="N>1: our kernels over peer memory - rows pushed to the head owners (p2p) or pulled by them (p2p-pull), "
+    ap.add_argument("--pull-blocks", type=int, default=148, help="grid cap of the full-row push that runs under the score kernels")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-push", "p2p-pull", "nccl"],
+                    help="N>1: our kernels over peer memory - sampled rows pushed first, full rows under the scores (p2p), all "
+                         "rows pushed before the layer (p2p-push) or pulled by the head owners (p2p-pull), "
                          "output rows stored into the token owners' buffers - or NCCL all-to-all (nccl)")
     ap.add_argument("--heads", type=int, default=0, help="override the head count (smaller captures for profilers)")
     ap.add_argument("--no-e2e", action="store_true")
@@ -200,6 +201,20 @@ def main():
         del qs, ks, vs
         q = k = v = None
 
+    fence_buf = None
+
+    def fence():
+        """Cross-rank ordering point on the current stream (a one-word all-reduce: unlike dist.barrier() it does not make
+        the host wait for the device)."""
+        nonlocal fence_buf
+        if fence_buf is None:
+            fence_buf = torch.zeros(1, device=dev)
+        dist.all_reduce(fence_buf)
+
+    def draw_indices_all():
+        torch.manual_seed(2000)                      # same draw on every rank
+        return (ops.draw_sample_indices(1, H, BLOCK_M, BLOCK_M // 4, dev), ops.draw_sample_indices(1, H, BLOCK_N, BLOCK_N // 4, dev))
+
     def draw_indices():
         torch.manual_seed(2000)                      # same draw on every rank, sliced by head
         iq = ops.draw_sample_indices(1, H, BLOCK_M, BLOCK_M // 4, dev)[:, h0:h0 + hp]
@@ -212,6 +227,8 @@ def main():
     peer = None
     if world > 1 and args.exchange != "nccl":
         peer = PeerExchange(H, S, D, dtype, dev)
+        if args.exchange == "p2p":
+            peer.enable_sample_push(BLOCK_M, BLOCK_N)
         peer.q.copy_(seq_shard[0]); peer.k.copy_(seq_shard[1]); peer.v.copy_(seq_shard[2])
         torch.cuda.synchronize()
         dist.barrier()
@@ -289,20 +306,37 @@ def main():
         cross-rank synchronisation is one barrier per step."""
         nonlocal pull_buf, step_no
         step_no += 1
-        iq, ik = timed("sample", draw_indices, rec)            # data-independent: before the exchange
+        par = step_no & 1
         if args.exchange == "p2p":
-            # sender-driven: every rank stores its rows into the owners' receive buffers (alternating between steps), and one
-            # barrier after the pushes tells every rank that its buffer is complete
-            x = timed("a2a_in", lambda: peer.push(step_no & 1), rec)
-            dist.barrier()
+            # Sender-driven and pipelined: (1) the sampled rows (a quarter of q and k) go first; (2) one barrier; (3) the
+            # block scores and the level assignment run from them while, on a second stream, every rank stores its full
+            # rows into the owners' receive buffers (alternating between steps) and a second barrier follows; (4) images
+            # and forward wait for that.
+            iq_all, ik_all = timed("sample", draw_indices_all, rec)
+            timed("a2a_in", lambda: peer.push_samples(par, iq_all, ik_all), rec)
+            fence()
+            comm_stream.wait_stream(cur)
+            with torch.cuda.stream(comm_stream):
+                x = timed("a2a_in", lambda: peer.push(par, max_blocks=args.pull_blocks), rec, comm_stream)
+                fence()
+                e_side = ev(); e_side.record(comm_stream)
+            po = timed("scores", lambda: peer.scores_from_samples(par), rec)
+            mask = timed("assign", lambda: ops.assign_levels(po, ratios, "topk_newtype", BLOCK_N, TILE_N), rec)
+            cur.wait_event(e_side)
+            qq, kk, vv = x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0)
         else:
-            dist.barrier()                                     # inputs of all ranks are in their exchange buffers
-            if pull_buf is None:
-                pull_buf = torch.empty((3, hp, S, D), dtype=dtype, device=dev)
-            x = timed("a2a_in", lambda: peer.pull(out=pull_buf), rec)
-        qq, kk, vv = x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0)
-        po = timed("scores", lambda: ops.block_scores(qq, kk, iq, ik, BLOCK_M, BLOCK_N), rec)
-        mask = timed("assign", lambda: ops.assign_levels(po, ratios, "topk_newtype", BLOCK_N, TILE_N), rec)
+            iq, ik = timed("sample", draw_indices, rec)            # data-independent: before the exchange
+            if args.exchange == "p2p-push":
+                x = timed("a2a_in", lambda: peer.push(par), rec)
+                fence()
+            else:
+                fence()                                            # inputs of all ranks are in their exchange buffers
+                if pull_buf is None:
+                    pull_buf = torch.empty((3, hp, S, D), dtype=dtype, device=dev)
+                x = timed("a2a_in", lambda: peer.pull(out=pull_buf), rec)
+            qq, kk, vv = x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0)
+            po = timed("scores", lambda: ops.block_scores(qq, kk, iq, ik, BLOCK_M, BLOCK_N), rec)
+            mask = timed("assign", lambda: ops.assign_levels(po, ratios, "topk_newtype", BLOCK_N, TILE_N), rec)
         pyr = timed("pyramid", lambda: ops.pyramid_kv_images(kk, vv, BLOCK_N), rec)
         status = timed("forward", lambda: peer.forward_scatter(qq, pyr, mask, BLOCK_M, BLOCK_N, TILE_N), rec)
         holder = torch.empty(0, device=dev)

@@ -203,6 +203,17 @@ int psa_pull_heads(const void* const* peer_src, int n_peers, void* dst, int64_t 
  * their buffers after a barrier that follows this call on every rank. */
 int psa_push_heads(const void* src, void* const* peer_dst, int n_peers, int64_t tokens_per_rank, int heads_total, int head_dim,
                    int elem_bytes, int self_rank, int max_blocks, void* stream);
+/* Sampled rows first: psa_push_samples sends only the rows the block-score stage reads (a quarter of q and of k) into
+ * the head owners' compacted sample matrices (peer_dst[r] = [heads_total/n_peers][n_out][head_dim]; idx = the sample
+ * offsets of ALL heads, [heads_total][keep]; geometry from psa_sample_rows), and psa_block_scores_samples computes the
+ * block scores from such matrices, skipping the gather of psa_block_scores.  The full rows can then travel while the
+ * scores are computed. */
+int psa_sample_rows(int64_t seq_q, int64_t seq_k, int block_m, int block_n, int64_t* nq, int64_t* nk_valid, int64_t* nk);
+int psa_push_samples(const void* src, const int32_t* idx, void* const* peer_dst, int n_peers, int64_t tokens_per_rank,
+                     int heads_total, int head_dim, int elem_bytes, int block, int keep, int64_t n_valid, int64_t n_out,
+                     int self_rank, void* stream);
+int psa_block_scores_samples(const void* qs, const void* ks, void* po, void* scratch, size_t scratch_bytes, int64_t bh,
+                             int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int dtype, void* stream);
 int psa_fwd_images_scatter(const void* q, const void* kimg, const void* vimg, const int32_t* mask, void* const* peer_out,
                            int n_peers, int64_t tokens_per_rank, int heads_total, int head0, int64_t bh, int64_t seq_q,
                            int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width, float sm_scale,

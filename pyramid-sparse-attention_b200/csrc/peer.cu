@@ -103,7 +103,65 @@ __global__ void __launch_bounds__(512) push_heads_kernel(const PushArgs a) {
   }
 }
 
+// Sampled rows only (what the block-score stage reads): row i of head h's compacted sample matrix is token
+// min((ic / keep) * block + idx[h][ic % keep], seq - 1), ic = min(i, n_valid - 1); the rank that owns that token stores
+// it into the head owner's sample matrix [heads_per_rank][n_out][row16].
+struct PushSampleArgs {
+  const uint4* src;          // [tokens_per_rank][heads_total][row16]
+  const int32_t* idx;        // [heads_total][keep]
+  uint4* dst[kMaxPeers];
+  int n_peers, heads_total, heads_per_rank, row16, self_rank, block, keep, n_valid, n_out;
+  int64_t tokens_per_rank, seq;
+};
+
+__global__ void __launch_bounds__(256) push_samples_kernel(const PushSampleArgs a) {
+  const int64_t total = (int64_t)a.heads_total * a.n_out * a.row16;
+  for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(w % a.row16);
+    const int64_t hi = w / a.row16;
+    const int i = (int)(hi % a.n_out), h = (int)(hi / a.n_out);
+    const int ic = i < a.n_valid ? i : a.n_valid - 1;
+    int64_t tok = (int64_t)(ic / a.keep) * a.block + a.idx[h * a.keep + (ic % a.keep)];
+    tok = tok < a.seq ? tok : a.seq - 1;
+    const int64_t local = tok - (int64_t)a.self_rank * a.tokens_per_rank;
+    if (local < 0 || local >= a.tokens_per_rank) continue;
+    const int owner = h / a.heads_per_rank, hl = h - owner * a.heads_per_rank;
+    a.dst[owner][((int64_t)hl * a.n_out + i) * a.row16 + c] = a.src[(local * a.heads_total + h) * a.row16 + c];
+  }
+}
+
 }  // namespace psa
+
+extern "C" int psa_push_samples(const void* src, const int32_t* idx, void* const* peer_dst, int n_peers, int64_t tokens_per_rank,
+                                int heads_total, int head_dim, int elem_bytes, int block, int keep, int64_t n_valid, int64_t n_out,
+                                int self_rank, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(src && idx && peer_dst, PSA_ERR_ARG, "psa_push_samples: null pointer");
+  PSA_REQUIRE(n_peers >= 1 && n_peers <= kMaxPeers && self_rank >= 0 && self_rank < n_peers, PSA_ERR_ARG,
+              "psa_push_samples: rank %d of %d (at most %d)", self_rank, n_peers, kMaxPeers);
+  PSA_REQUIRE(tokens_per_rank > 0 && heads_total > 0 && heads_total % n_peers == 0, PSA_ERR_ARG,
+              "psa_push_samples: %d heads do not divide over %d ranks", heads_total, n_peers);
+  PSA_REQUIRE(block > 0 && keep > 0 && n_valid > 0 && n_out >= n_valid && n_out < (1ll << 31), PSA_ERR_ARG,
+              "psa_push_samples: bad sample geometry");
+  PSA_REQUIRE(head_dim > 0 && (elem_bytes == 2 || elem_bytes == 4) && (head_dim * elem_bytes) % 16 == 0, PSA_ERR_ARG,
+              "psa_push_samples: rows must be a multiple of 16 bytes");
+  PushSampleArgs a;
+  a.src = (const uint4*)src; a.idx = idx;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    a.dst[i] = i < n_peers ? (uint4*)peer_dst[i] : nullptr;
+    if (i < n_peers) PSA_REQUIRE(peer_dst[i] && ((uintptr_t)peer_dst[i] & 15) == 0, PSA_ERR_ARG, "psa_push_samples: peer %d pointer", i);
+  }
+  a.n_peers = n_peers; a.heads_total = heads_total; a.heads_per_rank = heads_total / n_peers;
+  a.row16 = head_dim * elem_bytes / 16; a.self_rank = self_rank; a.block = block; a.keep = keep;
+  a.n_valid = (int)n_valid; a.n_out = (int)n_out;
+  a.tokens_per_rank = tokens_per_rank; a.seq = tokens_per_rank * n_peers;
+  const int64_t total = (int64_t)heads_total * n_out * a.row16;
+  int64_t blocks = cdiv64(total, 256 * 4);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  push_samples_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a);
+  PSA_CHECK_LAUNCH("psa_push_samples");
+  return PSA_OK;
+}
 
 extern "C" int psa_push_heads(const void* src, void* const* peer_dst, int n_peers, int64_t tokens_per_rank, int heads_total,
                               int head_dim, int elem_bytes, int self_rank, int max_blocks, void* stream) {

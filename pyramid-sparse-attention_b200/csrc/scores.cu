@@ -330,3 +330,51 @@ extern "C" int psa_block_scores_peers(const void* const* peer_q, const void* con
   if (dtype == PSA_F16) return launch_scores<__half>(q, k, idx_q, idx_k, po, scratch, d, heads_local, 2, st);
   return launch_scores<__nv_bfloat16>(q, k, idx_q, idx_k, po, scratch, d, heads_local, 2, st);
 }
+
+// Rows of the compacted sample matrices of one block-score call: queries nq (= ceil(seq/block_m) * block_m/4), keys nk
+// (the same for block_n, padded up to a multiple of 64 rows; rows past the last valid sample repeat it).
+extern "C" int psa_sample_rows(int64_t seq_q, int64_t seq_k, int block_m, int block_n, int64_t* nq, int64_t* nk_valid, int64_t* nk) {
+  using namespace psa;
+  ScoreDims d;
+  int rc = make_score_dims(d, seq_q, seq_k, 128, block_m, block_n);
+  if (rc != PSA_OK) return rc;
+  if (nq) *nq = d.nq_s;
+  if (nk_valid) *nk_valid = d.nk_s;
+  if (nk) *nk = d.nk_cols;
+  return PSA_OK;
+}
+
+extern "C" int psa_block_scores_samples(const void* qs, const void* ks, void* po, void* scratch, size_t scratch_bytes, int64_t bh,
+                                        int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int dtype,
+                                        void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(qs && ks && po && scratch, PSA_ERR_ARG, "psa_block_scores_samples: null pointer");
+  PSA_REQUIRE(bh > 0 && bh < 65536, PSA_ERR_ARG, "psa_block_scores_samples: bh=%lld out of range", (long long)bh);
+  PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "psa_block_scores_samples: f16/bf16 only");
+  PSA_REQUIRE(((uintptr_t)scratch & 255) == 0 && (((uintptr_t)qs | (uintptr_t)ks) & 15) == 0, PSA_ERR_ARG,
+              "psa_block_scores_samples: scratch must be 256-byte aligned, samples 16-byte aligned");
+  ScoreDims d;
+  int rc = make_score_dims(d, seq_q, seq_k, head_dim, block_m, block_n);
+  if (rc != PSA_OK) return rc;
+  PSA_REQUIRE(scratch_bytes >= psa_block_scores_scratch_bytes(bh, seq_q, seq_k, block_m, block_n, dtype), PSA_ERR_ARG,
+              "psa_block_scores_samples: scratch too small (%zu bytes)", scratch_bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t es = 2;
+  void* R = scratch;
+  const size_t r_bytes = ((size_t)bh * d.nq_s * d.n_d * es + 255) & ~(size_t)255;
+  float* rowmax = (float*)((char*)scratch + r_bytes);
+  rc = launch_scores_cellmax_tc_samples(qs, ks, R, rowmax, d, bh, dtype, st);
+  if (rc != PSA_OK) return rc;
+  dim3 gridb((unsigned)d.Mq, (unsigned)bh);
+  if (dtype == PSA_F16) {
+    if (d.n_d % 4 == 0) scores_pool_normalise<__half, 4><<<gridb, 256, d.n_d * sizeof(float), st>>>((const __half*)R, rowmax, (__half*)po, d);
+    else scores_pool_normalise<__half, 2><<<gridb, 256, d.n_d * sizeof(float), st>>>((const __half*)R, rowmax, (__half*)po, d);
+  } else {
+    if (d.n_d % 4 == 0)
+      scores_pool_normalise<__nv_bfloat16, 4><<<gridb, 256, d.n_d * sizeof(float), st>>>((const __nv_bfloat16*)R, rowmax, (__nv_bfloat16*)po, d);
+    else
+      scores_pool_normalise<__nv_bfloat16, 2><<<gridb, 256, d.n_d * sizeof(float), st>>>((const __nv_bfloat16*)R, rowmax, (__nv_bfloat16*)po, d);
+  }
+  PSA_CHECK_LAUNCH("psa_block_scores_samples(stage B)");
+  return PSA_OK;
+}

@@ -310,4 +310,13 @@ int launch_scores_cellmax_tc(const RowSource& q, const RowSource& k, const int32
   return fmt ? launch_cellmax<128, 1>(qs, ks, R, rowmax, d, bh, st) : launch_cellmax<128, 0>(qs, ks, R, rowmax, d, bh, st);
 }
 
+int launch_scores_cellmax_tc_samples(const void* qs, const void* ks, void* R, float* rowmax, const ScoreDims& d, int64_t bh,
+                                     int dtype, cudaStream_t st) {
+  PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "the tcgen05 score kernel needs f16/bf16 inputs");
+  PSA_REQUIRE(scores_tc_supported(d), PSA_ERR_UNSUPPORTED, "the tcgen05 score kernel does not cover this block size");
+  const int fmt = dtype == PSA_BF16;
+  if (d.D == 64) return fmt ? launch_cellmax<64, 1>(qs, ks, R, rowmax, d, bh, st) : launch_cellmax<64, 0>(qs, ks, R, rowmax, d, bh, st);
+  return fmt ? launch_cellmax<128, 1>(qs, ks, R, rowmax, d, bh, st) : launch_cellmax<128, 0>(qs, ks, R, rowmax, d, bh, st);
+}
+
 }  // namespace psa

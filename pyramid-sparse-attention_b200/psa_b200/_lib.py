@@ -37,6 +37,9 @@ SIGNATURES = {
     "psa_fwd_images_scatter": (_i, [_p] * 5 + [_i, _i64, _i, _i, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]),
     "psa_block_scores_peers": (_i, [_p, _p, _i, _i64, _i, _i, _p, _p, _p, _p, _sz, _i64, _i, _i, _i, _i, _p]),
     "psa_pyramid_kv_images_peers": (_i, [_p, _p, _i, _i64, _i, _i, _p, _p, _i64, _i, _i, _i, _i, _p]),
+    "psa_sample_rows": (_i, [_i64, _i64, _i, _i, _p, _p, _p]),
+    "psa_push_samples": (_i, [_p, _p, _p, _i, _i64, _i, _i, _i, _i, _i, _i64, _i64, _i, _p]),
+    "psa_block_scores_samples": (_i, [_p, _p, _p, _p, _sz, _i64, _i64, _i64, _i, _i, _i, _i, _p]),
     "psa_push_heads": (_i, [_p, _p, _i, _i64, _i, _i, _i, _i, _i, _p]),
     "psa_peer_alloc": (_i, [_sz, _p, _p]),
     "psa_peer_open": (_i, [_p, _p]),

@@ -210,6 +210,77 @@ class PeerExchange:
                 self.check(rc, "psa_pull_heads")
         return out
 
+    # ------------------------------------------------------------------ sampled rows first
+    def enable_sample_push(self, block_m: int, block_n: int):
+        """Allocate and map the compacted sample matrices (two sets, alternating between steps) that push_samples() fills
+        on the head owners.  Collective: every rank calls it once, with the same block sizes."""
+        nq, nkv, nk = C.c_int64(), C.c_int64(), C.c_int64()
+        self.check(self.lib.psa_sample_rows(self.seq, self.seq, block_m, block_n, C.byref(nq), C.byref(nkv), C.byref(nk)),
+                   "psa_sample_rows")
+        self._samp = dict(block_m=block_m, block_n=block_n, nq=nq.value, nk_valid=nkv.value, nk=nk.value)
+        hp, D, esz = self.heads_per_rank, self.head_dim, self.elem_bytes
+        q_bytes, k_bytes = hp * nq.value * D * esz, hp * nk.value * D * esz
+        q_bytes = (q_bytes + 255) // 256 * 256
+        handles, own = {}, {}
+        with torch.cuda.device(self.device):
+            for name in ("s0", "s1"):
+                ptr, h = C.c_void_p(), (C.c_ubyte * 64)()
+                self.check(self.lib.psa_peer_alloc(q_bytes + k_bytes, C.byref(ptr), h), "psa_peer_alloc")
+                own[name], handles[name] = ptr.value, bytes(h)
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, handles, group=self.group)
+        self._samp_ptrs, self._samp_views = [], []
+        with torch.cuda.device(self.device):
+            for name in ("s0", "s1"):
+                peers = []
+                for r, hs in enumerate(gathered):
+                    if r == self.rank:
+                        peers.append(own[name])
+                    else:
+                        ptr = C.c_void_p()
+                        buf = (C.c_ubyte * 64).from_buffer_copy(hs[name])
+                        self.check(self.lib.psa_peer_open(buf, C.byref(ptr)), "psa_peer_open")
+                        peers.append(ptr.value)
+                        self._opened.append(ptr.value)
+                self._own[name] = own[name]
+                self._samp_ptrs.append(((C.c_void_p * self.world)(*peers), (C.c_void_p * self.world)(*[p + q_bytes for p in peers])))
+                self._samp_views.append((own[name], own[name] + q_bytes))
+
+    def push_samples(self, parity: int, idx_q_all: torch.Tensor, idx_k_all: torch.Tensor):
+        """Send the sampled rows of this rank's tokens (offsets of ALL heads: [1, H, block/4]) to the head owners' sample
+        matrices number `parity`.  Complete on every rank after a barrier enqueued behind it."""
+        sp = self._samp
+        iq = idx_q_all.to(torch.int32).contiguous()
+        ik = idx_k_all.to(torch.int32).contiguous()
+        assert iq.shape == (1, self.heads, sp["block_m"] // 4) and ik.shape == (1, self.heads, sp["block_n"] // 4)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            rc = self.lib.psa_push_samples(self._own["q"], iq.data_ptr(), self._samp_ptrs[parity][0], self.world, self.tokens_per_rank,
+                                           self.heads, self.head_dim, self.elem_bytes, sp["block_m"], sp["block_m"] // 4, sp["nq"],
+                                           sp["nq"], self.rank, stream)
+            self.check(rc, "psa_push_samples")
+            rc = self.lib.psa_push_samples(self._own["k"], ik.data_ptr(), self._samp_ptrs[parity][1], self.world, self.tokens_per_rank,
+                                           self.heads, self.head_dim, self.elem_bytes, sp["block_n"], sp["block_n"] // 4,
+                                           sp["nk_valid"], sp["nk"], self.rank, stream)
+            self.check(rc, "psa_push_samples")
+        self._keep = (iq, ik)      # the kernels read the offsets asynchronously
+
+    def scores_from_samples(self, parity: int) -> torch.Tensor:
+        """Block scores [1, H/P, Mq, Nk] of this rank's heads from the sample matrices number `parity`."""
+        from .ops import _dt
+        sp, hp = self._samp, self.heads_per_rank
+        Mq, Nk = -(-self.seq // sp["block_m"]), -(-self.seq // sp["block_n"])
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            po = torch.empty((1, hp, Mq, Nk), dtype=self.dtype, device=self.device)
+            nbytes = self.lib.psa_block_scores_scratch_bytes(hp, self.seq, self.seq, sp["block_m"], sp["block_n"], _dt(po))
+            scratch = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+            qs, ks = self._samp_views[parity]
+            rc = self.lib.psa_block_scores_samples(qs, ks, po.data_ptr(), scratch.data_ptr(), nbytes, hp, self.seq, self.seq,
+                                                   self.head_dim, sp["block_m"], sp["block_n"], _dt(po), stream)
+        self.check(rc, "psa_block_scores_samples")
+        return po
+
     def block_scores(self, idx_q: torch.Tensor, idx_k: torch.Tensor, block_m: int, block_n: int) -> torch.Tensor:
         """Block scores [1, H/P, Mq, Nk] of this rank's heads; the sampled q/k rows are read from the peers' buffers."""
         from .ops import _dt

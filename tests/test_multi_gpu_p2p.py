@@ -68,6 +68,19 @@ def _worker(rank: int, world: int, port: int, H: int, S: int, D: int, q):
         po = ops.block_scores(qq, kk, iq, ik, bm, bn)
         mask = ops.assign_levels(po, C.DEFAULT_RATIOS, "topk_newtype", bn, tn)
         imgs = ops.pyramid_kv_images(kk, vv, bn)
+        # sampled rows pushed ahead of the full rows give the same scores
+        torch.manual_seed(7)
+        iq_all = ops.draw_sample_indices(1, H, bm, bm // 4, dev)
+        ik_all = ops.draw_sample_indices(1, H, bn, bn // 4, dev)
+        ex.enable_sample_push(bm, bn)
+        for parity in (0, 1):
+            ex.push_samples(parity, iq_all, ik_all)
+            dist.barrier()
+            torch.cuda.synchronize()
+            po_s = ex.scores_from_samples(parity)
+            po_l = ops.block_scores(qq, kk, iq_all[:, rank * hp:(rank + 1) * hp].contiguous(),
+                                    ik_all[:, rank * hp:(rank + 1) * hp].contiguous(), bm, bn)
+            assert torch.equal(po_s, po_l), "scores from pushed samples differ"
         # the peer-reading variants of the score and image kernels see the same rows
         assert torch.equal(ex.block_scores(iq, ik, bm, bn), po), "scores from peer rows differ"
         peer_imgs = ex.pyramid_images(bn, max_blocks=24)
