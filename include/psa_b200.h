@@ -141,14 +141,14 @@ int psa_legacy_fwd(const void* q, const void* k, const void* v, const void* k2, 
                    int64_t bh, int64_t seq, int head_dim, int mask_cols, float sm_scale, int causal, int dtype,
                    void* stream);
 
-/* The same legacy forward, NON-CAUSAL case, on the tcgen05 kernel: the dense level row is regrouped into an index row
+/* The same legacy forward on the tcgen05 kernel: the dense level row is regrouped into an index row
  * (index_scratch: psa_legacy_index_bytes(bh, seq) bytes of device memory) and the tile-image forward runs with block 128
  * and no compatibility extras; lse (may be NULL) and the "no visible key -> 0, lse = -inf" rule follow the legacy kernel
  * (psa_kernel_legacy.py:931).  kimg/vimg: psa_pyramid_kv_images(..., block_n = 128).  f16/bf16 only. */
 size_t psa_legacy_index_bytes(int64_t bh, int64_t seq);
 int psa_legacy_fwd_images(const void* q, const void* kimg, const void* vimg, const int32_t* mask, int32_t* index_scratch,
                           void* out, float* lse, int64_t bh, int64_t seq, int head_dim, int mask_cols, float sm_scale,
-                          int dtype, int32_t* status, void* stream);
+                          int causal, int dtype, int32_t* status, void* stream);
 
 /* Legacy backward.  Replaces _sparse_attention.backward and its kernels/helpers,
  * src/psa_triton/kernels/psa_kernel_legacy.py:947-1320.  dq/dk/dv: [BH, seq, D] in dtype; delta: float32

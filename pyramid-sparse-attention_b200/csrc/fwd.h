@@ -78,6 +78,7 @@ struct FwdArgs {
   OutScatter scatter = {};   // n_peers == 0 unless the output goes to peer buffers
   float* lse = nullptr;      // optional [bh][seq_q]: log-sum-exp of every row (natural log)
   int legacy = 0;            // legacy semantics: a row without any visible key gives 0 (lse -inf) instead of 0/0
+  int causal = 0;            // legacy causal rule: pooled token j of level l is visible iff (j+1)*l - 1 <= query position
 };
 
 int fwd_simt_dispatch(const void* q, const void* const* kl, const void* const* vl, const int64_t* nl, const int32_t* mask,

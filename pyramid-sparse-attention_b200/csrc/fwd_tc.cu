@@ -78,6 +78,7 @@ struct TcParams {
   OutScatter scatter;   // n_peers > 0: rows go to the peer that owns the token (plain stores over NVLink)
   float* lse;           // optional log-sum-exp output
   int legacy;           // rows without a visible key give 0 / -inf instead of 0/0
+  int causal;           // legacy causal rule on the diagonal block (index rows hold no block beyond the diagonal)
 };
 
 template <int D> struct Cfg {
@@ -90,7 +91,8 @@ template <int D> struct Cfg {
   static constexpr int OFF_V = OFF_K + NK * TILE_BYTES;
   static constexpr int OFF_BIAS = OFF_V + NV * TILE_BYTES;
   static constexpr int OFF_BIASG = OFF_BIAS + kBiasSlots * 128 * 4;   // one bias word per 4 columns + per-warp tile flags
-  static constexpr int OFF_XCH = OFF_BIASG + kBiasSlots * (32 + 4) * 4;
+  static constexpr int OFF_MINROW = OFF_BIASG + kBiasSlots * (32 + 4) * 4;   // causal: first query row that sees a column
+  static constexpr int OFF_XCH = OFF_MINROW + kBiasSlots * 128;
   static constexpr int OFF_ROW = OFF_XCH + 2 * 2 * 2 * 128 * 4;   // (max, sum) of both groups, two rows in flight
   static constexpr int OFF_RAW = OFF_ROW + 2 * kMaxItems * 4;      // raw index list of the row being decoded
   static constexpr int OFF_CTRL = OFF_RAW + kMaxWidth * 4;
@@ -160,7 +162,7 @@ namespace {
 
 // IMG = true: K/V tiles use the image layout [8-row group][slab][8 rows][128 B] and are filled by linear bulk copies from
 // the tile-image buffers; IMG = false: [slab][128 rows][128 B] filled by tensor-map TMA boxes from row-major tensors.
-template <int D, int FMT, bool IMG>
+template <int D, int FMT, bool IMG, bool CAUSAL>
 __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_constant__ TmapPack maps, const TcParams p) {
   using C = Cfg<D>;
   extern __shared__ unsigned char smem_dyn[];
@@ -170,6 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   unsigned char* sV = smem + C::OFF_V;
   float* sBias = reinterpret_cast<float*>(smem + C::OFF_BIAS);
   float* sBiasG = reinterpret_cast<float*>(smem + C::OFF_BIASG);   // [slot][32 group words | 3 producer flags | pad]
+  unsigned char* sMinRow = smem + C::OFF_MINROW;                   // [slot][128]
   float* sXch = reinterpret_cast<float*>(smem + C::OFF_XCH);      // [group][max | sum][row]
   uint32_t* sItems = reinterpret_cast<uint32_t*>(smem + C::OFF_ROW);
   Ctrl* ctl = reinterpret_cast<Ctrl*>(smem + C::OFF_CTRL);
@@ -415,6 +418,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             const float qb = li == 0 ? qb0 : (li == 1 ? qb1 : (li == 2 ? qb2 : qb3));
             const float bias2 = (x & kItemPad) ? -INFINITY : ((x & kItemQuirk) ? qb : (float)li);
             const int nvalid = nl - row0;
+            const bool diag = CAUSAL && active && blk == m && !(x & (kItemPad | kItemQuirk));
+            unsigned char* minrow_row = sMinRow + slot * 128;
             uint32_t my_bytes = 0;
             if (active) {
               if (IMG) {
@@ -432,11 +437,17 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
                   dst[c >> 2] = make_float4(c < nvalid ? bias2 : -INFINITY, c + 1 < nvalid ? bias2 : -INFINITY,
                                             c + 2 < nvalid ? bias2 : -INFINITY, c + 3 < nvalid ? bias2 : -INFINITY);
                   biasg_row[(col + c) >> 2] = c < nvalid ? bias2 : -INFINITY;
+                  if (CAUSAL) {
+                    const int l = 1 << li;
+                    *reinterpret_cast<uchar4*>(minrow_row + col + c) =
+                        diag ? make_uchar4((c + 1) * l - 1, (c + 2) * l - 1, (c + 3) * l - 1, (c + 4) * l - 1) : make_uchar4(0, 0, 0, 0);
+                  }
                 }
               }
             }
-            // a block that ends inside a group of 4 columns makes the tile take the per-column path of the softmax
-            const bool odd_edge = active && nvalid > 0 && nvalid < P && (nvalid & 3) != 0;
+            // a block that ends inside a group of 4 columns, or the diagonal block of a causal row, makes the tile take the
+            // per-column path of the softmax
+            const bool odd_edge = active && ((nvalid > 0 && nvalid < P && (nvalid & 3) != 0) || diag);
             const bool any_odd = __any_sync(0xffffffffu, odd_edge);
             if (lane == 0) reinterpret_cast<int*>(biasg_row)[32 + warp] = any_odd ? 1 : 0;
             // wide blocks (at most 4 per tile): the whole warp writes the bias, 4 columns per lane
@@ -447,12 +458,18 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
               const int w_col = __shfl_sync(0xffffffffu, col, src_lane), w_P = __shfl_sync(0xffffffffu, P, src_lane);
               const int w_nv = __shfl_sync(0xffffffffu, nvalid, src_lane);
               const float w_b = __shfl_sync(0xffffffffu, bias2, src_lane);
+              const int w_diag = __shfl_sync(0xffffffffu, (int)diag, src_lane), w_li = __shfl_sync(0xffffffffu, li, src_lane);
               const int c = lane * 4;
               if (c < w_P) {
                 *reinterpret_cast<float4*>(bias_row + w_col + c) =
                     make_float4(c < w_nv ? w_b : -INFINITY, c + 1 < w_nv ? w_b : -INFINITY, c + 2 < w_nv ? w_b : -INFINITY,
                                 c + 3 < w_nv ? w_b : -INFINITY);
                 biasg_row[(w_col + c) >> 2] = c < w_nv ? w_b : -INFINITY;
+                if (CAUSAL) {
+                  const int l = 1 << w_li;
+                  *reinterpret_cast<uchar4*>(minrow_row + w_col + c) =
+                      w_diag ? make_uchar4((c + 1) * l - 1, (c + 2) * l - 1, (c + 3) * l - 1, (c + 4) * l - 1) : make_uchar4(0, 0, 0, 0);
+                }
               }
             }
             ki += in_tile;
@@ -688,6 +705,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           const float4* bias4 = reinterpret_cast<const float4*>(sBias + slot * 128);
           const float4* bg4 = reinterpret_cast<const float4*>(sBiasG + slot * 36);     // one bias word per 4 columns
           const int* flagw = reinterpret_cast<const int*>(sBiasG + slot * 36) + 32;
+          const uchar4* minrow4 = reinterpret_cast<const uchar4*>(sMinRow + slot * 128);
           // Fast path: the bias is uniform inside every aligned group of 4 columns (blocks are at least 4 wide), so the
           // maximum is taken on raw scores per group and the bias enters once per group.  A tile with a block that ends
           // inside a group, or with unwritten columns, takes the per-column path.
@@ -727,7 +745,14 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
               }
 #pragma unroll
               for (int q4 = 0; q4 < 8; ++q4) {
-                const float4 ba = bias4[h * 8 + q4];
+                float4 ba = bias4[h * 8 + q4];
+                if (CAUSAL) {
+                  const uchar4 mr = minrow4[h * 8 + q4];
+                  if (r < mr.x) ba.x = -INFINITY;
+                  if (r < mr.y) ba.y = -INFINITY;
+                  if (r < mr.z) ba.z = -INFINITY;
+                  if (r < mr.w) ba.w = -INFINITY;
+                }
                 mx0 = fmaxf(mx0, fmaf(__uint_as_float(va[4 * q4 + 0]), p.scale_log2, ba.x));
                 mx1 = fmaxf(mx1, fmaf(__uint_as_float(va[4 * q4 + 1]), p.scale_log2, ba.y));
                 mx2 = fmaxf(mx2, fmaf(__uint_as_float(va[4 * q4 + 2]), p.scale_log2, ba.z));
@@ -807,7 +832,14 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
               uint32_t pk[16];
 #pragma unroll
               for (int q4 = 0; q4 < 8; ++q4) {
-                const float4 ba = bias4[h * 8 + q4];
+                float4 ba = bias4[h * 8 + q4];
+                if (CAUSAL) {
+                  const uchar4 mr = minrow4[h * 8 + q4];
+                  if (r < mr.x) ba.x = -INFINITY;
+                  if (r < mr.y) ba.y = -INFINITY;
+                  if (r < mr.z) ba.z = -INFINITY;
+                  if (r < mr.w) ba.w = -INFINITY;
+                }
                 const float a0 = ex2(fmaf(__uint_as_float(va[4 * q4 + 0]), p.scale_log2, ba.x) - m_use);
                 const float a1 = ex2(fmaf(__uint_as_float(va[4 * q4 + 1]), p.scale_log2, ba.y) - m_use);
                 const float a2 = ex2(fmaf(__uint_as_float(va[4 * q4 + 2]), p.scale_log2, ba.z) - m_use);
@@ -1014,7 +1046,7 @@ static int next_row_counter(int** out, cudaStream_t st) {
   return PSA_OK;
 }
 
-template <int D, int FMT, bool IMG>
+template <int D, int FMT, bool IMG, bool CAUSAL = false>
 static int launch_tc(const FwdArgs& a, cudaStream_t st) {
   using C = Cfg<D>;
   TmapPack maps;
@@ -1037,8 +1069,8 @@ static int launch_tc(const FwdArgs& a, cudaStream_t st) {
   p.kimg = (const unsigned char*)a.kimg; p.vimg = (const unsigned char*)a.vimg;
   p.img = make_img_levels(a.bh, a.seq_k, D, IMG ? a.bn : 64);
   p.scatter = a.scatter;
-  p.lse = a.lse; p.legacy = a.legacy;
-  cudaError_t e = cudaFuncSetAttribute(psa_fwd_tc_kernel<D, FMT, IMG>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  p.lse = a.lse; p.legacy = a.legacy; p.causal = a.causal;
+  cudaError_t e = cudaFuncSetAttribute(psa_fwd_tc_kernel<D, FMT, IMG, CAUSAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   PSA_REQUIRE(e == cudaSuccess, PSA_ERR_CUDA, "psa_fwd: shared-memory opt-in (%d B) failed: %s", C::SMEM_BYTES,
               cudaGetErrorString(e));
   // persistent: one CTA per SM (221 KB of shared memory and all 512 TMEM columns each), rows dealt round-robin so that
@@ -1050,7 +1082,7 @@ static int launch_tc(const FwdArgs& a, cudaStream_t st) {
   const unsigned grid = (unsigned)(p.total_rows < sms ? p.total_rows : sms);
   rc = next_row_counter(&p.row_counter, st);
   if (rc != PSA_OK) return rc;
-  psa_fwd_tc_kernel<D, FMT, IMG><<<grid, kThreads, C::SMEM_BYTES, st>>>(maps, p);
+  psa_fwd_tc_kernel<D, FMT, IMG, CAUSAL><<<grid, kThreads, C::SMEM_BYTES, st>>>(maps, p);
   PSA_CHECK_LAUNCH("psa_fwd(tcgen05)");
   return PSA_OK;
 }
@@ -1061,9 +1093,14 @@ int fwd_tc_launch(const FwdArgs& a, cudaStream_t st) {
   if (img) {
     PSA_REQUIRE(a.bn >= 64, PSA_ERR_UNSUPPORTED, "tile images need block_n >= 64 (blocks of at least 8 pooled rows)");
     PSA_REQUIRE((((uintptr_t)a.kimg | (uintptr_t)a.vimg) & 15) == 0, PSA_ERR_ARG, "tile images must be 16-byte aligned");
+    if (a.causal) {   // only the legacy forward asks for it; a variant of its own keeps the common kernel lean
+      if (a.D == 64) return fmt ? launch_tc<64, 1, true, true>(a, st) : launch_tc<64, 0, true, true>(a, st);
+      return fmt ? launch_tc<128, 1, true, true>(a, st) : launch_tc<128, 0, true, true>(a, st);
+    }
     if (a.D == 64) return fmt ? launch_tc<64, 1, true>(a, st) : launch_tc<64, 0, true>(a, st);
     return fmt ? launch_tc<128, 1, true>(a, st) : launch_tc<128, 0, true>(a, st);
   }
+  PSA_REQUIRE(!a.causal, PSA_ERR_UNSUPPORTED, "the causal rule needs the tile-image path");
   if (a.D == 64) return fmt ? launch_tc<64, 1, false>(a, st) : launch_tc<64, 0, false>(a, st);
   return fmt ? launch_tc<128, 1, false>(a, st) : launch_tc<128, 0, false>(a, st);
 }

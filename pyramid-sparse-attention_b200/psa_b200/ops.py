@@ -282,7 +282,7 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
     if sm_scale is None:
         sm_scale = D ** -0.5
     n128 = -(-S // 128)
-    if (not causal and pyramid is None and not need_lse and q.dtype in (torch.float16, torch.bfloat16) and n128 + 5 <= 1472
+    if (pyramid is None and not need_lse and q.dtype in (torch.float16, torch.bfloat16) and n128 + 5 <= 1472
             and sm_scale > 0):
         # inference path of the old-mask presets: the tcgen05 forward on tile images (the row-major pyramid the backward
         # would need is not built)
@@ -292,7 +292,7 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
             scratch = torch.empty(lib.psa_legacy_index_bytes(B * H, S) // 4, dtype=torch.int32, device=q.device)
             status = torch.zeros(1, dtype=torch.int32, device=q.device)
             rc = lib.psa_legacy_fwd_images(_ptr(q), _ptr(imgs.kimg), _ptr(imgs.vimg), _ptr(mask), _ptr(scratch), _ptr(o), None,
-                                           B * H, S, D, mask.shape[-1], float(sm_scale), _dt(q), _ptr(status), _stream(q))
+                                           B * H, S, D, mask.shape[-1], float(sm_scale), int(causal), _dt(q), _ptr(status), _stream(q))
         check(rc, "psa_legacy_fwd_images")
         o._psa_status = status
         return o, None, None
@@ -309,8 +309,8 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
     return o, lse, pyramid
 
 
-def legacy_forward_tc(q, k, v, mask, sm_scale: Optional[float] = None, need_lse: bool = True):
-    """Non-causal legacy forward on the tcgen05 kernel (psa_legacy_fwd_images); returns (o, lse or None)."""
+def legacy_forward_tc(q, k, v, mask, sm_scale: Optional[float] = None, need_lse: bool = True, causal: bool = False):
+    """Legacy forward on the tcgen05 kernel (psa_legacy_fwd_images); returns (o, lse or None)."""
     _need_cuda(q, k, v, mask)
     q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _flat_bh(mask)
     if mask.dtype != torch.int32:
@@ -324,7 +324,7 @@ def legacy_forward_tc(q, k, v, mask, sm_scale: Optional[float] = None, need_lse:
         scratch = torch.empty(lib.psa_legacy_index_bytes(B * H, S) // 4, dtype=torch.int32, device=q.device)
         status = torch.zeros(1, dtype=torch.int32, device=q.device)
         rc = lib.psa_legacy_fwd_images(_ptr(q), _ptr(imgs.kimg), _ptr(imgs.vimg), _ptr(mask), _ptr(scratch), _ptr(o), _ptr(lse),
-                                       B * H, S, D, mask.shape[-1], float(sm_scale), _dt(q), _ptr(status), _stream(q))
+                                       B * H, S, D, mask.shape[-1], float(sm_scale), int(causal), _dt(q), _ptr(status), _stream(q))
     check(rc, "psa_legacy_fwd_images")
     o._psa_status = status
     return o, lse

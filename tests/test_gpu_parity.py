@@ -158,16 +158,17 @@ def test_legacy_forward_golden(P, golden, case):
 
 
 @pytest.mark.parametrize("dt", ["bf16", "fp16"])
+@pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("S,D,H", [(512, 64, 2), (600, 64, 1), (1100, 128, 2)])
-def test_legacy_forward_tensor_core_vs_oracle(P, S, D, H, dt):
-    """Non-causal legacy forward through the tcgen05 kernel (old mask regrouped into index rows): output, log-sum-exp and
-    the "row without any visible key" rule against the oracle on the same 16-bit inputs."""
+def test_legacy_forward_tensor_core_vs_oracle(P, S, D, H, causal, dt):
+    """Legacy forward through the tcgen05 kernel (old mask regrouped into index rows): output, log-sum-exp, the causal
+    rule on the diagonal block and the "row without any visible key" rule against the oracle on the same 16-bit inputs."""
     q, k, v = C.qkv(410, 1, H, S, D, C.DT[dt])
-    mask = C.legacy_mask(415, 1, H, S, False, False)
+    mask = C.legacy_mask(415, 1, H, S, causal, False)            # mixed levels on the diagonal too
     mask[0, 0, 1, :] = 0                                         # one query block attends nothing
-    o, lse = P.ops.legacy_forward_tc(q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV))
+    o, lse = P.ops.legacy_forward_tc(q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), causal=causal)
     assert int(o._psa_status.item()) == 0
-    o_ref, lse_ref = O.legacy_forward(q, k, v, mask, False)
+    o_ref, lse_ref = O.legacy_forward(q, k, v, mask, causal)
     o, lse = o.float().cpu(), lse.cpu()
     assert float((o - o_ref.float()).abs().max()) <= 2e-2 and cosine(o, o_ref.float()) >= 0.999
     dead = torch.isinf(lse_ref)
@@ -175,7 +176,7 @@ def test_legacy_forward_tensor_core_vs_oracle(P, S, D, H, dt):
     assert float(o[0, 0, 128:256].abs().max()) == 0.0
     assert float((lse[~dead] - lse_ref[~dead]).abs().max()) <= 2e-2
     # the inference path of the old-mask presets picks this kernel by itself
-    o2, lse2, pyr = P.ops.legacy_forward(q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), False)
+    o2, lse2, pyr = P.ops.legacy_forward(q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), causal)
     assert lse2 is None and pyr is None and torch.equal(o2.float().cpu(), o)
 
 
