@@ -180,6 +180,28 @@ def test_legacy_forward_tensor_core_vs_oracle(P, S, D, H, causal, dt):
     assert lse2 is None and pyr is None and torch.equal(o2.float().cpu(), o)
 
 
+def test_causal_legacy_full_size_properties(P):
+    """The causal forward + backward case at its full size (B=2, 16 heads, D=128, S=32768, bf16), where the CPU oracle is
+    out of reach: the tcgen05 forward and the scalar forward (itself checked against the oracle at small sizes) must
+    agree, the log-sum-exp too, and the backward must be finite and linear in the upstream gradient."""
+    B, H, D, S = 2, 16, 128, 32768
+    g = torch.Generator(device=DEV).manual_seed(11)
+    q, k, v = (torch.randn(B, H, S, D, device=DEV, dtype=torch.bfloat16, generator=g) for _ in range(3))
+    mask = C.legacy_mask(77, B, H, S, True, False).to(DEV)
+    o_tc, lse_tc = P.ops.legacy_forward_tc(q, k, v, mask, causal=True)
+    o_sc, lse_sc, pyr = P.ops.legacy_forward(q, k, v, mask, True, need_lse=True)
+    assert int(o_tc._psa_status.item()) == 0
+    assert float((o_tc.float() - o_sc.float()).abs().max()) <= 2e-2 and cosine(o_tc.float(), o_sc.float()) >= 0.999
+    fin = torch.isfinite(lse_sc)
+    assert torch.equal(torch.isfinite(lse_tc), fin) and float((lse_tc[fin] - lse_sc[fin]).abs().max()) <= 1e-3
+    do = torch.randn(B, H, S, D, device=DEV, dtype=torch.bfloat16, generator=g)
+    grads = P.ops.legacy_backward(q, k, v, mask, o_sc, lse_sc, do, True, D ** -0.5, pyr)
+    grads2 = P.ops.legacy_backward(q, k, v, mask, o_sc, lse_sc, 2 * do, True, D ** -0.5, pyr)
+    for a, a2 in zip(grads, grads2):
+        assert bool(torch.isfinite(a).all())
+        assert float((a2.float() - 2 * a.float()).abs().max()) <= 1e-2 * float(a.float().abs().max())
+
+
 # ------------------------------------------------------------------ K similarity ---------------------
 @pytest.mark.parametrize("case", C.KSIM_CASES, ids=lambda c: c[0])
 def test_ksim_golden(P, golden, case):
