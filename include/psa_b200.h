@@ -132,6 +132,31 @@ int psa_fwd_images(const void* q, const void* kimg, const void* vimg, const int3
                    int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width,
                    float sm_scale, int compat_quirk, int dtype, int32_t* status, void* stream);
 
+/* Token reordering folded into the kernels.  Replaces GilbertRearranger.rearrange / rearrange_single / reversed_rearrange,
+ * src/psa_triton/utils/rearranger.py:69-132 (three index_select copies of q, k, v before the attention and one of the
+ * output after it; the text tokens move from the front of the sequence to its end and back).
+ * perm: int32 [seq], a permutation of 0..seq-1 shared by all heads: token t of the sequence the attention works on is
+ * row perm[t] of the tensor as stored.  k, v and the sampled quarter of q are read through perm by the kernels that
+ * read them anyway; the forward stores output row t at row out_perm[t], so with out_perm == perm the output is back
+ * in the stored order; only q needs a reordered copy (psa_gather_rows), because the forward fetches query tiles with
+ * bulk tensor copies.  Results are bit-identical to reordering q, k, v first, running psa_pyramid_kv_images /
+ * psa_block_scores / psa_fwd_images, and reordering the output back.
+ *   psa_gather_rows:            dst[bh][t][:] = src[bh][perm[t]][:]   (rows a multiple of 16 bytes; not in place)
+ *   psa_pyramid_kv_images_perm: psa_pyramid_kv_images of the reordered k, v
+ *   psa_block_scores_perm:      psa_block_scores (tcgen05 path, f16/bf16) of the reordered q, k
+ *   psa_fwd_images_perm:        psa_fwd_images with q already reordered and the output rows stored through out_perm */
+int psa_gather_rows(const void* src, const int32_t* perm, void* dst, int64_t bh, int64_t seq, int head_dim, int elem_bytes,
+                    void* stream);
+int psa_pyramid_kv_images_perm(const void* k, const void* v, const int32_t* perm, void* kimg, void* vimg, int64_t bh,
+                               int64_t seq, int head_dim, int block_n, int dtype, void* stream);
+int psa_block_scores_perm(const void* q, const void* k, const int32_t* perm_q, const int32_t* perm_k, const int32_t* idx_q,
+                          const int32_t* idx_k, void* po, void* scratch, size_t scratch_bytes, int64_t bh, int64_t seq_q,
+                          int64_t seq_k, int head_dim, int block_m, int block_n, int dtype, void* stream);
+int psa_fwd_images_perm(const void* q, const void* kimg, const void* vimg, const int32_t* mask, void* out,
+                        const int32_t* out_perm, int64_t bh, int64_t seq_q, int64_t seq_k, int head_dim, int block_m,
+                        int block_n, int tile_n, int mask_width, float sm_scale, int compat_quirk, int dtype, int32_t* status,
+                        void* stream);
+
 /* Legacy forward on the dense old-format mask, optional causal.  Replaces _fwd_kernel / _forward,
  * src/psa_triton/kernels/psa_kernel_legacy.py:415-799, 837-938 (block sizes fixed 128/32/128, :1333-1351).
  * mask: int32 [BH, ceil(seq/128), mask_cols] in {0,1,2,4,8}; lse: float32 [BH, seq] = M + ln(max(L,1e-8))

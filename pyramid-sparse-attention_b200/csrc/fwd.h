@@ -27,24 +27,28 @@ inline ImgLevels make_img_levels(int64_t bh, int64_t seq, int D, int block_n) {
 
 // Output scatter for head-sharded runs: the rank computes heads [head0, head0+bh) of all tokens, and token s belongs to
 // rank s / tokens_per_rank, whose output buffer is laid out [tokens_per_rank][heads_total][D].  n_peers == 0: plain
-// local output [bh][seq_q][D].
+// local output [bh][seq_q][D].  row_perm (local output only): query row s is stored at row row_perm[s] of its head, which
+// undoes a token reordering applied on the way in (int32 [seq_q], a permutation).
 constexpr int kMaxPeers = 8;
 struct OutScatter {
   void* peer_out[kMaxPeers];
   int n_peers;
   int heads_total, head0;
   int64_t tokens_per_rank;
+  const int32_t* row_perm;
 };
 
 // Where a row-major operand [bh][seq][D] lives.  n_peers == 0: one local tensor.  n_peers > 0 (head-sharded run, one
 // batch): token t of local head h is row (t % tokens_per_rank) of peer t / tokens_per_rank, whose buffer is laid out
-// [tokens_per_rank][heads_total][D]; kernels read it with plain loads.
+// [tokens_per_rank][heads_total][D]; kernels read it with plain loads.  perm != null: the operand is read in a reordered
+// token sequence, token t of the sequence being row perm[t] of the stored tensor (int32 [seq]).
 struct RowSource {
   const void* base;
   const void* peer[kMaxPeers];
   int n_peers;
   int heads_total, head0;
   int64_t tokens_per_rank;
+  const int32_t* perm;
 };
 
 inline RowSource local_rows(const void* base) {
@@ -56,6 +60,7 @@ inline RowSource local_rows(const void* base) {
 #ifdef __CUDACC__
 // 16-byte word `c` of the row of token `tok` of local head `bh` (row16 words per row)
 __device__ __forceinline__ const uint4* row_word(const RowSource& s, int64_t bh, int64_t seq, int64_t tok, int row16, int c) {
+  if (s.perm) tok = s.perm[tok];
   if (s.n_peers == 0) return reinterpret_cast<const uint4*>(s.base) + (bh * seq + tok) * row16 + c;
   const int64_t owner = tok / s.tokens_per_rank, local = tok - owner * s.tokens_per_rank;
   return reinterpret_cast<const uint4*>(s.peer[owner]) + (local * s.heads_total + s.head0 + bh) * row16 + c;

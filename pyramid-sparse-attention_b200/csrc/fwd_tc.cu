@@ -675,7 +675,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         orow = reinterpret_cast<uint16_t*>(p.scatter.peer_out[owner]) +
                (local * p.scatter.heads_total + p.scatter.head0 + bh) * D + g * HALF;
       } else {
-        orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + qrow) * D + g * HALF;
+        const int64_t drow = (p.scatter.row_perm && qrow < p.seq_q) ? (int64_t)p.scatter.row_perm[qrow] : qrow;
+        orow = reinterpret_cast<uint16_t*>(p.out) + ((int64_t)bh * p.seq_q + drow) * D + g * HALF;
       }
       if (n_tiles == 0) {
         // no block selected at all: the reference divides 0 by 0

@@ -200,6 +200,22 @@ extern "C" int psa_pyramid_kv_images(const void* k, const void* v, void* kimg, v
   return launch_pyramid_images(local_rows(k), local_rows(v), kimg, vimg, bh, seq, head_dim, block_n, dtype, 0, (cudaStream_t)stream);
 }
 
+extern "C" int psa_pyramid_kv_images_perm(const void* k, const void* v, const int32_t* perm, void* kimg, void* vimg, int64_t bh,
+                                          int64_t seq, int head_dim, int block_n, int dtype, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(k && v && perm && kimg && vimg, PSA_ERR_ARG, "psa_pyramid_kv_images_perm: null pointer");
+  PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "psa_pyramid_kv_images_perm: 16-bit element types only");
+  PSA_REQUIRE(seq < ((int64_t)1 << 31), PSA_ERR_ARG, "psa_pyramid_kv_images_perm: seq=%lld does not fit the int32 order table",
+              (long long)seq);
+  PSA_REQUIRE(psa_kv_image_bytes(bh, seq, head_dim, block_n) > 0, PSA_ERR_ARG,
+              "psa_pyramid_kv_images_perm: needs head_dim 64/128 and block_n a multiple of 64 (got %d, %d)", head_dim, block_n);
+  PSA_REQUIRE((((uintptr_t)k | (uintptr_t)v | (uintptr_t)kimg | (uintptr_t)vimg) & 15) == 0, PSA_ERR_ARG,
+              "psa_pyramid_kv_images_perm: k, v and the images must be 16-byte aligned");
+  RowSource ks = local_rows(k), vs = local_rows(v);
+  ks.perm = vs.perm = perm;
+  return launch_pyramid_images(ks, vs, kimg, vimg, bh, seq, head_dim, block_n, dtype, 0, (cudaStream_t)stream);
+}
+
 extern "C" int psa_pyramid_kv_images_peers(const void* const* peer_k, const void* const* peer_v, int n_peers, int64_t tokens_per_rank,
                                            int heads_total, int head0, void* kimg, void* vimg, int64_t heads_local, int head_dim,
                                            int block_n, int dtype, int max_blocks, void* stream) {

@@ -32,6 +32,10 @@ SIGNATURES = {
     "psa_kv_image_bytes": (_sz, [_i64, _i64, _i, _i]),
     "psa_pyramid_kv_images": (_i, [_p] * 4 + [_i64, _i64, _i, _i, _i, _p]),
     "psa_fwd_images": (_i, [_p] * 5 + [_i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]),
+    "psa_gather_rows": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _p]),
+    "psa_pyramid_kv_images_perm": (_i, [_p] * 5 + [_i64, _i64, _i, _i, _i, _p]),
+    "psa_block_scores_perm": (_i, [_p] * 8 + [_sz, _i64, _i64, _i64, _i, _i, _i, _i, _p]),
+    "psa_fwd_images_perm": (_i, [_p] * 6 + [_i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]),
     "psa_legacy_index_bytes": (_sz, [_i64, _i64]),
     "psa_legacy_fwd_images": (_i, [_p] * 7 + [_i64, _i64, _i, _i, _f, _i, _i, _p, _p]),
     "psa_fwd_images_scatter": (_i, [_p] * 5 + [_i, _i64, _i, _i, _i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _i, _p, _p]),

@@ -49,13 +49,16 @@ class PSAConfig:
                     f"Got block_n={self.block_n}.")
 
 
-def compute_block_mask(q, k, config, text_length: int = 0, idx_q=None, idx_k=None):
+def compute_block_mask(q, k, config, text_length: int = 0, idx_q=None, idx_k=None, perm=None):
     """Scores -> level mask (-> similarity cap), the no-grad half of PSAAttention.forward
     (src/psa_triton/attention.py:178-223, 276-299).  Returns (mask, scores, sim_mask).
     The sample offsets are drawn from torch's generator of q's device, Q first and K second, exactly as
-    the reference does; tests may pass them in instead."""
+    the reference does; tests may pass them in instead.  perm (int32 [S], no similarity cap): the mask of
+    q[..., perm, :], k[..., perm, :] with the rows read in place."""
     B, H = q.shape[0], q.shape[1]
     sim = None
+    if perm is not None and config.use_sim_mask:
+        raise ValueError("the similarity cap reads k row-major: reorder k first instead of passing perm")
     if config.use_sim_mask:
         sim = ops.k_similarity(k, config.block_n, float(config.sim_2x_threshold), float(config.sim_4x_threshold),
                                float(config.sim_8x_threshold))
@@ -63,7 +66,7 @@ def compute_block_mask(q, k, config, text_length: int = 0, idx_q=None, idx_k=Non
         idx_q = ops.draw_sample_indices(B, H, config.block_m, config.block_m // 4, q.device)
     if idx_k is None:
         idx_k = ops.draw_sample_indices(B, H, config.block_n, config.block_n // 4, q.device)
-    po = ops.block_scores(q, k, idx_q, idx_k, config.block_m, config.block_n)
+    po = ops.block_scores(q, k, idx_q, idx_k, config.block_m, config.block_n, perm_q=perm, perm_k=perm)
     if config.attn_impl == "old_mask_type":
         mode = config.mask_mode
     else:

@@ -69,8 +69,29 @@ def images_supported(k: torch.Tensor, block_m: int, block_n: int, tile_n: int) -
             and k.shape[-1] in (64, 128))
 
 
-def pyramid_kv_images(k: torch.Tensor, v: torch.Tensor, block_n: int) -> KVImages:
-    """One pass over K and V -> tile images of levels 1/2/4/8 (f16/bf16, block_n 64/128)."""
+def _perm32(perm: torch.Tensor, seq: int) -> torch.Tensor:
+    if perm.device.type != "cuda" or perm.dtype != torch.int32 or perm.dim() != 1 or perm.numel() != seq:
+        raise ValueError(f"perm must be a CUDA int32 tensor of {seq} row numbers")
+    return perm.contiguous()
+
+
+def gather_rows(x: torch.Tensor, perm: torch.Tensor) -> torch.Tensor:
+    """x[..., perm, :] for [B,H,S,D] tensors (the q copy of a reordered layer; GilbertRearranger.rearrange_single,
+    src/psa_triton/utils/rearranger.py:97-115, with the text move folded into perm)."""
+    _need_cuda(x, perm)
+    x = _flat_bh(x)
+    B, H, S, D = x.shape
+    perm = _perm32(perm, S)
+    with torch.cuda.device(x.device):
+        out = torch.empty_like(x)
+        rc = lib.psa_gather_rows(_ptr(x), _ptr(perm), _ptr(out), B * H, S, D, x.element_size(), _stream(x))
+    check(rc, "psa_gather_rows")
+    return out
+
+
+def pyramid_kv_images(k: torch.Tensor, v: torch.Tensor, block_n: int, perm: Optional[torch.Tensor] = None) -> KVImages:
+    """One pass over K and V -> tile images of levels 1/2/4/8 (f16/bf16, block_n 64/128).  perm: build the images of
+    k[..., perm, :], v[..., perm, :] without materialising them."""
     _need_cuda(k, v)
     assert k.shape == v.shape and k.dtype == v.dtype
     k, v = _flat_bh(k), _flat_bh(v)
@@ -81,7 +102,12 @@ def pyramid_kv_images(k: torch.Tensor, v: torch.Tensor, block_n: int) -> KVImage
     with torch.cuda.device(k.device):
         kimg = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
         vimg = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
-        rc = lib.psa_pyramid_kv_images(_ptr(k), _ptr(v), _ptr(kimg), _ptr(vimg), B * H, S, D, block_n, _dt(k), _stream(k))
+        if perm is None:
+            rc = lib.psa_pyramid_kv_images(_ptr(k), _ptr(v), _ptr(kimg), _ptr(vimg), B * H, S, D, block_n, _dt(k), _stream(k))
+        else:
+            perm = _perm32(perm, S)
+            rc = lib.psa_pyramid_kv_images_perm(_ptr(k), _ptr(v), _ptr(perm), _ptr(kimg), _ptr(vimg), B * H, S, D, block_n,
+                                                _dt(k), _stream(k))
     check(rc, "psa_pyramid_kv_images")
     return KVImages(kimg, vimg, block_n)
 
@@ -94,8 +120,9 @@ def draw_sample_indices(B: int, H: int, block: int, keep: int, device) -> torch.
     return idx.view(B, H, keep)
 
 
-def block_scores(q, k, idx_q, idx_k, block_m: int, block_n: int, impl: int = IMPL_AUTO) -> torch.Tensor:
-    """Block-importance scores Po [B,H,Mq,Nk] (q.dtype).  idx_q [B,H,block_m/4], idx_k [B,H,block_n/4]."""
+def block_scores(q, k, idx_q, idx_k, block_m: int, block_n: int, impl: int = IMPL_AUTO, perm_q=None, perm_k=None) -> torch.Tensor:
+    """Block-importance scores Po [B,H,Mq,Nk] (q.dtype).  idx_q [B,H,block_m/4], idx_k [B,H,block_n/4].
+    perm_q / perm_k (both or neither): the scores of q[..., perm_q, :], k[..., perm_k, :], read in place (f16/bf16)."""
     _need_cuda(q, k, idx_q, idx_k)
     q, k = _flat_bh(q), _flat_bh(k)
     B, H, Sq, D = q.shape
@@ -110,8 +137,13 @@ def block_scores(q, k, idx_q, idx_k, block_m: int, block_n: int, impl: int = IMP
         if nbytes == 0:
             raise ValueError(f"psa_block_scores: unsupported block sizes m={block_m} n={block_n}")
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
-        rc = lib.psa_block_scores(_ptr(q), _ptr(k), _ptr(iq), _ptr(ik), _ptr(po), _ptr(scratch), nbytes, B * H, Sq, Sk,
-                                  D, block_m, block_n, _dt(q), impl, _stream(q))
+        if perm_q is None and perm_k is None:
+            rc = lib.psa_block_scores(_ptr(q), _ptr(k), _ptr(iq), _ptr(ik), _ptr(po), _ptr(scratch), nbytes, B * H, Sq, Sk,
+                                      D, block_m, block_n, _dt(q), impl, _stream(q))
+        else:
+            perm_q, perm_k = _perm32(perm_q, Sq), _perm32(perm_k, Sk)
+            rc = lib.psa_block_scores_perm(_ptr(q), _ptr(k), _ptr(perm_q), _ptr(perm_k), _ptr(iq), _ptr(ik), _ptr(po),
+                                           _ptr(scratch), nbytes, B * H, Sq, Sk, D, block_m, block_n, _dt(q), _stream(q))
     check(rc, "psa_block_scores")
     return po
 
@@ -226,9 +258,10 @@ def k_similarity(k: torch.Tensor, block_n: int, t2: float, t4: float, t8: float)
 
 # ------------------------------------------------------------------------------------------------
 def psa_forward(q, k, v, mask, block_m: int, block_n: int, tile_n: int, sm_scale: Optional[float] = None,
-                compat_quirk: bool = True, impl: int = IMPL_AUTO, pyramid=None, out=None) -> torch.Tensor:
+                compat_quirk: bool = True, impl: int = IMPL_AUTO, pyramid=None, out=None, out_perm=None) -> torch.Tensor:
     """Multi-level block-sparse forward on the separator-format mask
-    (_forward, src/psa_triton/kernels/psa_kernel.py:351-432)."""
+    (_forward, src/psa_triton/kernels/psa_kernel.py:351-432).  out_perm (tile-image path only): output row t is stored
+    at row out_perm[t]."""
     _need_cuda(q, k, v, mask)
     assert q.shape[-1] == k.shape[-1] == v.shape[-1]
     assert k.shape[2] == v.shape[2]
@@ -248,12 +281,20 @@ def psa_forward(q, k, v, mask, block_m: int, block_n: int, tile_n: int, sm_scale
         with torch.cuda.device(q.device):
             o = out if out is not None else torch.empty_like(q)
             status = torch.zeros(1, dtype=torch.int32, device=q.device)
-            rc = lib.psa_fwd_images(_ptr(q), _ptr(pyramid.kimg), _ptr(pyramid.vimg), _ptr(mask), _ptr(o), B * H, Sq, Sk, D,
-                                    block_m, block_n, tile_n, mask.shape[-1], float(sm_scale), int(compat_quirk), _dt(q),
-                                    _ptr(status), _stream(q))
+            if out_perm is None:
+                rc = lib.psa_fwd_images(_ptr(q), _ptr(pyramid.kimg), _ptr(pyramid.vimg), _ptr(mask), _ptr(o), B * H, Sq, Sk, D,
+                                        block_m, block_n, tile_n, mask.shape[-1], float(sm_scale), int(compat_quirk), _dt(q),
+                                        _ptr(status), _stream(q))
+            else:
+                out_perm = _perm32(out_perm, Sq)
+                rc = lib.psa_fwd_images_perm(_ptr(q), _ptr(pyramid.kimg), _ptr(pyramid.vimg), _ptr(mask), _ptr(o),
+                                             _ptr(out_perm), B * H, Sq, Sk, D, block_m, block_n, tile_n, mask.shape[-1],
+                                             float(sm_scale), int(compat_quirk), _dt(q), _ptr(status), _stream(q))
         check(rc, "psa_fwd_images")
         o._psa_status = status
         return o
+    if out_perm is not None:
+        raise ValueError("out_perm needs the tile-image forward (f16/bf16, block_m 128, tile_n 32, block_n 64/128)")
     if pyramid is None:
         pyramid = pyramid_kv(k, v, block_n)
     (k2, k4, k8), (v2, v4, v8) = pyramid

@@ -118,14 +118,41 @@ class PyramidSparseAttention(nn.Module):
             return (self.sparsity_counter // self.layer_num) % self.inference_num
         return (self.sparsity_counter // (2 * self.layer_num)) % self.inference_num
 
+    def _rows_in_place(self, q, k) -> bool:
+        """Whether the Gilbert order can be folded into the kernels (k, v, the output and the sampled q rows are never
+        copied): 16-bit tensors on the tcgen05 kernels, separator-format mask, no similarity cap."""
+        c = self.config
+        return (self.use_rearrange and c.attn_impl == "new_mask_type" and not c.use_sim_mask and q.is_cuda
+                and q.shape[2] == k.shape[2] == self.gilbert_rearranger.total_elements + self.gilbert_rearranger.text_length
+                and ops.images_supported(k, c.block_m, c.block_n, c.tile_n)
+                and -(-k.shape[2] // c.block_n) + 5 <= 1472)
+
+    def _forward_rows_in_place(self, q, k, v, compute_stats):
+        c = self.config
+        perm = self.gilbert_rearranger.source_rows(q.device)
+        with torch.no_grad():
+            mask, _, _ = compute_block_mask(q, k, c, text_length=c.text_length, perm=perm)
+        images = ops.pyramid_kv_images(k.contiguous(), v.contiguous(), c.block_n, perm=perm)
+        q_r = ops.gather_rows(q.contiguous(), perm)
+        out = ops.psa_forward(q_r, k, v, mask, c.block_m, c.block_n, c.tile_n, None, pyramid=images, out_perm=perm)
+        dens = ops.density(mask, True) if compute_stats else None
+        return out.view(q.shape), dens
+
     def forward(self, q, k, v, layer_idx):
+        is_warmup = self.get_current_time() < self.config.warmup_steps
+        compute_stats = self.config.verbose or self.logger is not None
+        dens = None
+        if not is_warmup and self._rows_in_place(q, k):
+            out, dens = self._forward_rows_in_place(q, k, v, compute_stats)
+            self.sparsity_counter += 1
+            if self.logger is not None:
+                self.logger.log_sparsity(layer_idx=layer_idx, density=dens, sequence_length=q.shape[2],
+                                         batch_size=q.shape[0], num_heads=q.shape[1], is_warmup=False)
+            return out
         if self.use_rearrange:
             q_r, k_r, v_r = self.gilbert_rearranger.rearrange(q, k, v)
         else:
             q_r, k_r, v_r = q, k, v
-        is_warmup = self.get_current_time() < self.config.warmup_steps
-        compute_stats = self.config.verbose or self.logger is not None
-        dens = None
         if is_warmup:
             # dense warm-up steps, exactly what the reference runs (:353-357)
             out_r = torch.nn.functional.scaled_dot_product_attention(q_r, k_r, v_r)

@@ -102,6 +102,17 @@ class GilbertRearranger:
             self._device_cache[key] = src.to(device, non_blocking=True)
         return self._device_cache[key]
 
+    def source_rows(self, device) -> torch.Tensor:
+        """int32 [video + text]: row t of the rearranged sequence is row source_rows[t] of the tensor as the model
+        holds it (text first).  rearrange_single(x) == x[..., source_rows, :], and writing row t of the attention's
+        output to row source_rows[t] is reversed_rearrange - what the kernels that take a row table use."""
+        key = (str(device), "rows")
+        if key not in self._device_cache:
+            video = self.original_order2gilbert_order_cpu.to(torch.int32) + self.text_length
+            text = torch.arange(self.text_length, dtype=torch.int32)
+            self._device_cache[key] = torch.cat((video, text)).to(device)
+        return self._device_cache[key]
+
     def rearrange_single(self, x: torch.Tensor) -> torch.Tensor:
         idx = self._indices(x.device, True)
         if self.text_length == 0:

@@ -1,0 +1,113 @@
+"""GPU: the token reordering folded into the kernels (row tables read in place) against reordering with copies.
+
+Every comparison is bit for bit: the kernels do the same arithmetic on the same values, only the addresses differ.  The
+copy-based path they are compared with is itself checked against the CPU oracle in test_gpu_parity.py; the module test
+here also compares with the oracle composed with the reordering."""
+import pytest
+import torch
+
+import cases as C
+from oracle import psa_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def P():
+    import psa_b200
+    assert torch.cuda.is_available()
+    return psa_b200
+
+
+def _perm(seed, n):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randperm(n, generator=g).to(torch.int32)
+
+
+@pytest.mark.parametrize("dt,D,S", [(torch.bfloat16, 128, 1000), (torch.float16, 64, 333), (torch.float32, 64, 130),
+                                    (torch.bfloat16, 64, 1)])
+def test_gather_rows(P, dt, D, S):
+    x = C.randn(5, (2, 3, S, D), dt).to(DEV)
+    perm = _perm(1, S).to(DEV)
+    assert torch.equal(P.ops.gather_rows(x, perm), x.index_select(2, perm.long()))
+
+
+def test_gather_rows_rejects_bad_tables(P):
+    x = C.randn(5, (1, 1, 64, 64), torch.bfloat16).to(DEV)
+    with pytest.raises(ValueError):
+        P.ops.gather_rows(x, _perm(1, 63).to(DEV))
+    with pytest.raises(ValueError):
+        P.ops.gather_rows(x, _perm(1, 64).long().to(DEV))
+
+
+@pytest.mark.parametrize("dt,D,S,bn", [(torch.bfloat16, 128, 1000, 64), (torch.float16, 64, 777, 128), (torch.bfloat16, 64, 64, 64)])
+def test_tile_images_through_row_table(P, dt, D, S, bn):
+    k = C.randn(11, (1, 3, S, D), dt).to(DEV)
+    v = C.randn(12, (1, 3, S, D), dt).to(DEV)
+    perm = _perm(2, S).to(DEV)
+    a = P.ops.pyramid_kv_images(k, v, bn, perm=perm)
+    b = P.ops.pyramid_kv_images(k.index_select(2, perm.long()), v.index_select(2, perm.long()), bn)
+    assert torch.equal(a.kimg, b.kimg) and torch.equal(a.vimg, b.vimg)
+
+
+@pytest.mark.parametrize("dt,D,S,bn", [(torch.bfloat16, 128, 1000, 64), (torch.float16, 64, 777, 128)])
+def test_block_scores_through_row_table(P, dt, D, S, bn):
+    H = 3
+    q, k, _ = C.qkv(100, 1, H, S, D, dt)
+    q, k = q.to(DEV), k.to(DEV)
+    iq, ik = C.sample_idx(7, 1, H, 128, 32).to(DEV), C.sample_idx(8, 1, H, bn, bn // 4).to(DEV)
+    perm = _perm(3, S).to(DEV)
+    a = P.ops.block_scores(q, k, iq, ik, 128, bn, perm_q=perm, perm_k=perm)
+    b = P.ops.block_scores(q.index_select(2, perm.long()), k.index_select(2, perm.long()), iq, ik, 128, bn,
+                           impl=P.ops.IMPL_TENSOR)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dt,D,S,bn", [(torch.bfloat16, 128, 1000, 64), (torch.float16, 64, 777, 128)])
+def test_forward_stores_rows_through_table(P, dt, D, S, bn):
+    from psa_b200.attention import PSAConfig, compute_block_mask
+    H = 2
+    q, k, v = (x.to(DEV) for x in C.qkv(200, 1, H, S, D, dt))
+    cfg = PSAConfig(block_m=128, block_n=bn, tile_n=32, mask_ratios=C.DEFAULT_RATIOS, mask_mode="topk")
+    torch.manual_seed(5)
+    mask, _, _ = compute_block_mask(q, k, cfg)
+    perm = _perm(4, S).to(DEV)
+    plain = P.ops.psa_forward(q, k, v, mask, 128, bn, 32)
+    moved = P.ops.psa_forward(q, k, v, mask, 128, bn, 32, out_perm=perm)
+    assert int(moved._psa_status.item()) == 0
+    assert torch.equal(moved.index_select(2, perm.long()), plain)
+
+
+@pytest.mark.parametrize("text", [0, 37])
+def test_module_reorders_in_place(P, text):
+    """PyramidSparseAttention with the Gilbert order on 16-bit inputs takes the in-place route; its output equals the
+    route with four reordering copies bit for bit (same sample offsets), and the oracle composed the same way."""
+    from psa_b200.attention import compute_block_mask
+    from psa_b200.pyramid_sparse_attention import AttentionConfig, PyramidSparseAttention
+    W, Hh, T, H, D = 12, 8, 9, 2, 128                      # 864 video tokens (+ text)
+    cfg = AttentionConfig(width=W, height=Hh, depth=T, text_length=text, use_rearrange=True, rearrange_method="Gilbert",
+                          block_m=128, block_n=64, tile_n=32, use_sim_mask=False, mask_ratios=C.DEFAULT_RATIOS, mask_mode="topk",
+                          warmup_steps=0, attn_impl="new_mask_type")
+    mod = PyramidSparseAttention(cfg, inference_num=10, layer_num=1, model_type="cogvideo")
+    S = W * Hh * T + text
+    q, k, v = C.qkv(991, 1, H, S, D, torch.bfloat16)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    assert mod._rows_in_place(qd, kd)
+    torch.manual_seed(321)
+    fused = mod(qd, kd, vd, 0)
+    # the same layer with explicit copies
+    torch.manual_seed(321)
+    qr, kr, vr = mod.gilbert_rearranger.rearrange(qd, kd, vd)
+    mask, _, _ = compute_block_mask(qr, kr, cfg, text_length=text)
+    o = P.ops.psa_forward(qr.contiguous(), kr.contiguous(), vr.contiguous(), mask, 128, 64, 32)
+    copied = mod.gilbert_rearranger.reversed_rearrange(o)
+    assert torch.equal(fused, copied)
+    # the oracle's forward on the reordered 16-bit inputs and the same level mask, reordered back
+    qc, kc, vc = mod.gilbert_rearranger.rearrange(q, k, v)
+    oo = O.psa_forward_newmask(qc, kc, vc, mask.cpu(), 128, 64, 32).float()
+    ref = mod.gilbert_rearranger.reversed_rearrange(oo)
+    assert float((fused.float().cpu() - ref).abs().max()) <= 2e-2
+    a, b = fused.float().cpu().double().flatten(), ref.double().flatten()
+    assert float((a @ b) / (a.norm() * b.norm())) >= 0.999
+    assert mod.logger.records[0]["density"].shape == (1, H)

@@ -27,6 +27,12 @@ def test_gilbert_rearranger_round_trip_with_text():
     assert torch.equal(q[..., -5:, :], x[..., :5, :])                 # text moved to the end
     assert torch.equal(r.reversed_rearrange(q), x)
     assert torch.equal(r.reversed_rearrange(v), x + 2)
+    # the row table the kernels read: gathering through it is rearrange_single, scattering through it is the inverse
+    rows = r.source_rows("cpu").long()
+    assert torch.equal(x.index_select(-2, rows), q)
+    back = torch.empty_like(q)
+    back[..., rows, :] = q
+    assert torch.equal(back, x)
     r0 = GilbertRearranger(6, 4, 3, text_length=0)
     y = x[..., :72, :]
     assert torch.equal(r0.reversed_rearrange(r0.rearrange_single(y)), y)
