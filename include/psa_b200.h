@@ -157,6 +157,29 @@ int psa_fwd_images_perm(const void* q, const void* kimg, const void* vimg, const
                         int block_n, int tile_n, int mask_width, float sm_scale, int compat_quirk, int dtype, int32_t* status,
                         void* stream);
 
+/* Token-major tensors.  Replaces the three transpose(1, 2) of q, k, v in front of the attention call and the
+ * transpose(1, 2).flatten(2, 3) behind it in the diffusers processors, modify_diffusers.py:302-307 and :357-371 (each
+ * becomes a full copy when the reference makes the tensors contiguous, src/psa_triton/attention.py:302-306), optionally
+ * together with the token reordering above.
+ * q, k, v, out: one batch element, [seq][heads][head_dim] as the projection layers produce / consume them.  perm
+ * (may be NULL): int32 [seq], token t of the attention's sequence is stored token perm[t].  The score and tile-image
+ * kernels read the rows where they lie, the forward stores output row t into out[perm[t]][head]; q alone is regrouped
+ * by head (psa_gather_heads), because the forward fetches query tiles with bulk tensor copies.  Bit-identical to the
+ * head-major calls on transposed (and reordered) copies.
+ *   psa_gather_heads:          dst[h][t][:] = src[perm ? perm[t] : t][h][:]
+ *   psa_pyramid_kv_images_tm:  psa_pyramid_kv_images      psa_block_scores_tm: psa_block_scores (tcgen05 path, f16/bf16)
+ *   psa_fwd_images_tm:         psa_fwd_images, q head-major [heads][seq][head_dim], out token-major */
+int psa_gather_heads(const void* src, const int32_t* perm, void* dst, int heads, int64_t seq, int head_dim, int elem_bytes,
+                     void* stream);
+int psa_pyramid_kv_images_tm(const void* k, const void* v, const int32_t* perm, void* kimg, void* vimg, int heads, int64_t seq,
+                             int head_dim, int block_n, int dtype, void* stream);
+int psa_block_scores_tm(const void* q, const void* k, const int32_t* perm, const int32_t* idx_q, const int32_t* idx_k, void* po,
+                        void* scratch, size_t scratch_bytes, int heads, int64_t seq, int head_dim, int block_m, int block_n,
+                        int dtype, void* stream);
+int psa_fwd_images_tm(const void* q, const void* kimg, const void* vimg, const int32_t* mask, void* out, const int32_t* out_perm,
+                      int heads, int64_t seq, int head_dim, int block_m, int block_n, int tile_n, int mask_width, float sm_scale,
+                      int compat_quirk, int dtype, int32_t* status, void* stream);
+
 /* Legacy forward on the dense old-format mask, optional causal.  Replaces _fwd_kernel / _forward,
  * src/psa_triton/kernels/psa_kernel_legacy.py:415-799, 837-938 (block sizes fixed 128/32/128, :1333-1351).
  * mask: int32 [BH, ceil(seq/128), mask_cols] in {0,1,2,4,8}; lse: float32 [BH, seq] = M + ln(max(L,1e-8))

@@ -117,6 +117,30 @@ extern "C" int psa_fwd_images_perm(const void* q, const void* kimg, const void* 
   return fwd_tc_launch(a, (cudaStream_t)stream);
 }
 
+extern "C" int psa_fwd_images_tm(const void* q, const void* kimg, const void* vimg, const int32_t* mask, void* out,
+                                const int32_t* out_perm, int heads, int64_t seq, int head_dim, int block_m, int block_n, int tile_n,
+                                int mask_width, float sm_scale, int compat_quirk, int dtype, int32_t* status, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(q && kimg && vimg && mask && out, PSA_ERR_ARG, "psa_fwd_images_tm: null pointer");
+  PSA_REQUIRE(heads > 0 && heads < 65536 && seq > 0 && seq < ((int64_t)1 << 31), PSA_ERR_ARG, "psa_fwd_images_tm: bad shape");
+  PSA_REQUIRE(block_n == 64 || block_n == 128, PSA_ERR_UNSUPPORTED, "psa_fwd_images_tm: block_n=%d (64/128)", block_n);
+  PSA_REQUIRE(mask_width >= 1, PSA_ERR_ARG, "psa_fwd_images_tm: mask_width=%d", mask_width);
+  PSA_REQUIRE(((uintptr_t)out & 15) == 0, PSA_ERR_ARG, "psa_fwd_images_tm: out must be 16-byte aligned");
+  const int64_t s_pad = cdiv64(seq, block_n) * block_n;
+  FwdArgs a;
+  a.q = q; a.mask = mask; a.out = nullptr; a.status = status; a.kimg = kimg; a.vimg = vimg;
+  const int64_t nl[4] = {seq, s_pad / 2, s_pad / 4, s_pad / 8};
+  for (int i = 0; i < 4; ++i) { a.k[i] = q; a.v[i] = q; a.n[i] = nl[i]; }   // row-major levels are not read in image mode
+  a.bh = heads; a.seq_q = seq; a.seq_k = seq; a.D = head_dim; a.bm = block_m; a.bn = block_n; a.tn = tile_n;
+  a.width = mask_width; a.scale = sm_scale; a.quirk = compat_quirk; a.dtype = dtype;
+  a.scatter.peer_out[0] = out;
+  a.scatter.n_peers = 1; a.scatter.heads_total = heads; a.scatter.head0 = 0; a.scatter.tokens_per_rank = seq;
+  a.scatter.row_perm = out_perm;
+  PSA_REQUIRE(fwd_tc_supported(a), PSA_ERR_UNSUPPORTED,
+              "psa_fwd_images_tm: needs f16/bf16, block_m=128, tile_n=32, head_dim 64/128, mask width <= 1472");
+  return fwd_tc_launch(a, (cudaStream_t)stream);
+}
+
 extern "C" int psa_fwd_images_scatter(const void* q, const void* kimg, const void* vimg, const int32_t* mask, void* const* peer_out,
                                       int n_peers, int64_t tokens_per_rank, int heads_total, int head0, int64_t bh, int64_t seq_q,
                                       int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width,

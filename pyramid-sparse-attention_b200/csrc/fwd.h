@@ -27,8 +27,8 @@ inline ImgLevels make_img_levels(int64_t bh, int64_t seq, int D, int block_n) {
 
 // Output scatter for head-sharded runs: the rank computes heads [head0, head0+bh) of all tokens, and token s belongs to
 // rank s / tokens_per_rank, whose output buffer is laid out [tokens_per_rank][heads_total][D].  n_peers == 0: plain
-// local output [bh][seq_q][D].  row_perm (local output only): query row s is stored at row row_perm[s] of its head, which
-// undoes a token reordering applied on the way in (int32 [seq_q], a permutation).
+// local output [bh][seq_q][D].  row_perm != null: query row s is stored as token row_perm[s] (of its head, or of the
+// token-major buffers), which undoes a token reordering applied on the way in (int32 [seq_q], a permutation).
 constexpr int kMaxPeers = 8;
 struct OutScatter {
   void* peer_out[kMaxPeers];

@@ -671,7 +671,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       const int64_t qrow = (int64_t)m * 128 + r;
       uint16_t* orow;
       if (p.scatter.n_peers > 0 && qrow < p.seq_q) {
-        const int64_t owner = qrow / p.scatter.tokens_per_rank, local = qrow - owner * p.scatter.tokens_per_rank;
+        const int64_t drow = p.scatter.row_perm ? (int64_t)p.scatter.row_perm[qrow] : qrow;
+        const int64_t owner = drow / p.scatter.tokens_per_rank, local = drow - owner * p.scatter.tokens_per_rank;
         orow = reinterpret_cast<uint16_t*>(p.scatter.peer_out[owner]) +
                (local * p.scatter.heads_total + p.scatter.head0 + bh) * D + g * HALF;
       } else {

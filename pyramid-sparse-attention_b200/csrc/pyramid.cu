@@ -216,6 +216,25 @@ extern "C" int psa_pyramid_kv_images_perm(const void* k, const void* v, const in
   return launch_pyramid_images(ks, vs, kimg, vimg, bh, seq, head_dim, block_n, dtype, 0, (cudaStream_t)stream);
 }
 
+extern "C" int psa_pyramid_kv_images_tm(const void* k, const void* v, const int32_t* perm, void* kimg, void* vimg, int heads,
+                                        int64_t seq, int head_dim, int block_n, int dtype, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(k && v && kimg && vimg, PSA_ERR_ARG, "psa_pyramid_kv_images_tm: null pointer");
+  PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "psa_pyramid_kv_images_tm: 16-bit element types only");
+  PSA_REQUIRE(heads > 0 && seq > 0 && seq < ((int64_t)1 << 31), PSA_ERR_ARG, "psa_pyramid_kv_images_tm: bad shape");
+  PSA_REQUIRE(psa_kv_image_bytes(heads, seq, head_dim, block_n) > 0, PSA_ERR_ARG,
+              "psa_pyramid_kv_images_tm: needs head_dim 64/128 and block_n a multiple of 64 (got %d, %d)", head_dim, block_n);
+  PSA_REQUIRE((((uintptr_t)k | (uintptr_t)v | (uintptr_t)kimg | (uintptr_t)vimg) & 15) == 0, PSA_ERR_ARG,
+              "psa_pyramid_kv_images_tm: k, v and the images must be 16-byte aligned");
+  RowSource ks = {}, vs = {};
+  ks.peer[0] = k; vs.peer[0] = v;
+  ks.n_peers = vs.n_peers = 1;
+  ks.heads_total = vs.heads_total = heads;
+  ks.tokens_per_rank = vs.tokens_per_rank = seq;
+  ks.perm = vs.perm = perm;
+  return launch_pyramid_images(ks, vs, kimg, vimg, heads, seq, head_dim, block_n, dtype, 0, (cudaStream_t)stream);
+}
+
 extern "C" int psa_pyramid_kv_images_peers(const void* const* peer_k, const void* const* peer_v, int n_peers, int64_t tokens_per_rank,
                                            int heads_total, int head0, void* kimg, void* vimg, int64_t heads_local, int head_dim,
                                            int block_n, int dtype, int max_blocks, void* stream) {

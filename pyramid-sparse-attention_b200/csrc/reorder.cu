@@ -25,6 +25,20 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restric
   }
 }
 
+// dst[h][t][:] = src[perm ? perm[t] : t][h][:]: token-major rows regrouped by head (and reordered) in one pass.
+__global__ void __launch_bounds__(256) gather_heads_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ perm,
+                                                           uint4* __restrict__ dst, int64_t seq, int heads, int cpr) {
+  const int64_t h = blockIdx.y;
+  uint4* d = dst + h * seq * cpr;
+  const int64_t total = seq * cpr;
+  for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = w / cpr;
+    const int c = (int)(w - t * cpr);
+    const int64_t row = perm ? (int64_t)perm[t] : t;
+    d[w] = src[(row * heads + h) * cpr + c];
+  }
+}
+
 }  // namespace
 }  // namespace psa
 
@@ -46,5 +60,25 @@ extern "C" int psa_gather_rows(const void* src, const int32_t* perm, void* dst, 
   dim3 grid((unsigned)blocks, (unsigned)bh);
   gather_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, perm, (uint4*)dst, seq, cpr);
   PSA_CHECK_LAUNCH("psa_gather_rows");
+  return PSA_OK;
+}
+
+extern "C" int psa_gather_heads(const void* src, const int32_t* perm, void* dst, int heads, int64_t seq, int head_dim,
+                                int elem_bytes, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(src && dst, PSA_ERR_ARG, "psa_gather_heads: null pointer");
+  PSA_REQUIRE(src != dst, PSA_ERR_ARG, "psa_gather_heads: cannot regroup in place");
+  PSA_REQUIRE(heads > 0 && heads < 65536 && seq > 0 && seq < ((int64_t)1 << 31), PSA_ERR_ARG, "psa_gather_heads: bad shape");
+  PSA_REQUIRE(elem_bytes == 2 || elem_bytes == 4, PSA_ERR_ARG, "psa_gather_heads: elem_bytes=%d (2 or 4)", elem_bytes);
+  PSA_REQUIRE(head_dim > 0 && (head_dim * elem_bytes) % 16 == 0, PSA_ERR_ARG,
+              "psa_gather_heads: rows of %d bytes are not a multiple of 16", head_dim * elem_bytes);
+  PSA_REQUIRE((((uintptr_t)src | (uintptr_t)dst) & 15) == 0, PSA_ERR_ARG, "psa_gather_heads: src and dst must be 16-byte aligned");
+  const int cpr = head_dim * elem_bytes / 16;
+  int64_t blocks = cdiv64(seq * cpr, 256);
+  const int64_t cap = cdiv64(148 * 16, heads);
+  if (blocks > cap) blocks = cap;
+  dim3 grid((unsigned)blocks, (unsigned)heads);
+  gather_heads_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)src, perm, (uint4*)dst, seq, heads, cpr);
+  PSA_CHECK_LAUNCH("psa_gather_heads");
   return PSA_OK;
 }

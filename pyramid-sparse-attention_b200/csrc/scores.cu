@@ -321,6 +321,32 @@ extern "C" int psa_block_scores_perm(const void* q, const void* k, const int32_t
   return launch_scores<__nv_bfloat16>(qs, ks, idx_q, idx_k, po, scratch, d, bh, 2, st);
 }
 
+extern "C" int psa_block_scores_tm(const void* q, const void* k, const int32_t* perm, const int32_t* idx_q, const int32_t* idx_k,
+                                   void* po, void* scratch, size_t scratch_bytes, int heads, int64_t seq, int head_dim, int block_m,
+                                   int block_n, int dtype, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(q && k && idx_q && idx_k && po && scratch, PSA_ERR_ARG, "psa_block_scores_tm: null pointer");
+  PSA_REQUIRE(heads > 0 && heads < 65536 && seq > 0 && seq < ((int64_t)1 << 31), PSA_ERR_ARG, "psa_block_scores_tm: bad shape");
+  PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "psa_block_scores_tm: f16/bf16 only");
+  PSA_REQUIRE(((uintptr_t)scratch & 255) == 0 && (((uintptr_t)q | (uintptr_t)k) & 15) == 0, PSA_ERR_ARG,
+              "psa_block_scores_tm: scratch must be 256-byte aligned, q and k 16-byte aligned");
+  ScoreDims d;
+  int rc = make_score_dims(d, seq, seq, head_dim, block_m, block_n);
+  if (rc != PSA_OK) return rc;
+  PSA_REQUIRE(scores_tc_supported(d), PSA_ERR_UNSUPPORTED, "psa_block_scores_tm: block sizes not covered by the tcgen05 path");
+  PSA_REQUIRE(scratch_bytes >= psa_block_scores_scratch_bytes(heads, seq, seq, block_m, block_n, dtype), PSA_ERR_ARG,
+              "psa_block_scores_tm: scratch too small (%zu bytes)", scratch_bytes);
+  RowSource qs = {}, ks = {};
+  qs.peer[0] = q; ks.peer[0] = k;
+  qs.n_peers = ks.n_peers = 1;
+  qs.heads_total = ks.heads_total = heads;
+  qs.tokens_per_rank = ks.tokens_per_rank = seq;
+  qs.perm = ks.perm = perm;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == PSA_F16) return launch_scores<__half>(qs, ks, idx_q, idx_k, po, scratch, d, heads, 2, st);
+  return launch_scores<__nv_bfloat16>(qs, ks, idx_q, idx_k, po, scratch, d, heads, 2, st);
+}
+
 extern "C" int psa_block_scores_peers(const void* const* peer_q, const void* const* peer_k, int n_peers, int64_t tokens_per_rank,
                                       int heads_total, int head0, const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch,
                                       size_t scratch_bytes, int64_t heads_local, int head_dim, int block_m, int block_n, int dtype,

@@ -77,6 +77,42 @@ def compute_block_mask(q, k, config, text_length: int = 0, idx_q=None, idx_k=Non
     return mask, po, sim
 
 
+def token_major_view(x: torch.Tensor):
+    """If x ([B, H, S, D]) is the transpose(1, 2) view of a contiguous [B, S, H, D] tensor - what the diffusers
+    processors pass (modify_diffusers.py:302-304, :357-359) - return that tensor, else None."""
+    if x.dim() != 4 or x.shape[1] == 1 or x.shape[2] == 1:
+        return None
+    t = x.transpose(1, 2)
+    return t if t.is_contiguous() else None
+
+
+def psa_attention_token_major(q, k, v, config, perm=None, text_length: int = 0, idx_q=None, idx_k=None):
+    """The PSA layer on token-major tensors: q, k, v [B, S, H, D] contiguous (16-bit, separator-format mask, no
+    similarity cap), perm an optional int32 [S] row table (attention token t = stored token perm[t]).  Returns
+    (out [B, S, H, D], mask).  No transposed or reordered copy of k, v or the output is made; the result equals
+    PSAAttention on q.transpose(1, 2)[:, :, perm] ... put back, bit for bit (same sample offsets)."""
+    B, S, H, D = q.shape
+    if config.use_sim_mask or config.attn_impl != "new_mask_type":
+        raise ValueError("the token-major route covers new_mask_type without the similarity cap")
+    if not ops.images_supported(q, config.block_m, config.block_n, config.tile_n):
+        raise ValueError("the token-major route needs f16/bf16, block_m 128, tile_n 32, block_n 64/128, head_dim 64/128")
+    if idx_q is None:
+        idx_q = ops.draw_sample_indices(B, H, config.block_m, config.block_m // 4, q.device)
+    if idx_k is None:
+        idx_k = ops.draw_sample_indices(B, H, config.block_n, config.block_n // 4, q.device)
+    with torch.no_grad():
+        po = torch.cat([ops.block_scores_tm(q[b], k[b], idx_q[b], idx_k[b], config.block_m, config.block_n, perm=perm)
+                        for b in range(B)], dim=0)
+        mask = ops.assign_levels(po, config.mask_ratios, f"{config.mask_mode}_newtype", config.block_n, config.tile_n,
+                                 text_length=text_length)
+    out = torch.empty_like(q)
+    for b in range(B):
+        images = ops.pyramid_kv_images_tm(k[b], v[b], config.block_n, perm=perm)
+        q_heads = ops.gather_heads(q[b], perm)
+        ops.psa_forward_tm(q_heads, images, mask[b], out[b], config.block_m, config.block_n, config.tile_n, out_perm=perm)
+    return out, mask
+
+
 class PSAAttention(nn.Module):
     """Drop-in attention: ``out = PSAAttention(config)(q, k, v)`` with q, k, v of shape [B, H, L, D]."""
 

@@ -112,6 +112,87 @@ def pyramid_kv_images(k: torch.Tensor, v: torch.Tensor, block_n: int, perm: Opti
     return KVImages(kimg, vimg, block_n)
 
 
+# ------------------------------------------------------------------------------------------------
+# Token-major tensors ([S, H, D], one batch element): what a transformer block's projections produce and consume.
+def _tm_check(*ts):
+    _need_cuda(*ts)
+    x = ts[0]
+    for t in ts:
+        if t.dim() != 3 or t.shape != x.shape or t.dtype != x.dtype or not t.is_contiguous():
+            raise ValueError("token-major operands must be contiguous [S, H, D] tensors of one shape and dtype")
+    return x.shape
+
+
+def gather_heads(x: torch.Tensor, perm: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[S, H, D] -> [1, H, S, D] with out[0, h, t] = x[perm[t], h] (perm None: a plain transpose copy)."""
+    S, H, D = _tm_check(x)
+    perm = None if perm is None else _perm32(perm, S)
+    with torch.cuda.device(x.device):
+        out = torch.empty((1, H, S, D), dtype=x.dtype, device=x.device)
+        rc = lib.psa_gather_heads(_ptr(x), _ptr(perm), _ptr(out), H, S, D, x.element_size(), _stream(x))
+    check(rc, "psa_gather_heads")
+    return out
+
+
+def pyramid_kv_images_tm(k: torch.Tensor, v: torch.Tensor, block_n: int, perm: Optional[torch.Tensor] = None) -> KVImages:
+    """pyramid_kv_images of k, v given token-major ([S, H, D]), optionally read through a row table."""
+    S, H, D = _tm_check(k, v)
+    perm = None if perm is None else _perm32(perm, S)
+    nbytes = lib.psa_kv_image_bytes(H, S, D, block_n)
+    if nbytes == 0:
+        raise ValueError(f"tile images need head_dim 64/128 and block_n 64/128 (got {D}, {block_n})")
+    with torch.cuda.device(k.device):
+        kimg = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
+        vimg = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
+        rc = lib.psa_pyramid_kv_images_tm(_ptr(k), _ptr(v), _ptr(perm), _ptr(kimg), _ptr(vimg), H, S, D, block_n, _dt(k),
+                                          _stream(k))
+    check(rc, "psa_pyramid_kv_images_tm")
+    return KVImages(kimg, vimg, block_n)
+
+
+def block_scores_tm(q, k, idx_q, idx_k, block_m: int, block_n: int, perm: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """block_scores of q, k given token-major ([S, H, D]); idx_q [H, block_m/4], idx_k [H, block_n/4].  -> [1, H, Mq, Nk]."""
+    S, H, D = _tm_check(q, k)
+    _need_cuda(idx_q, idx_k)
+    assert idx_q.shape == (H, block_m // 4) and idx_k.shape == (H, block_n // 4)
+    perm = None if perm is None else _perm32(perm, S)
+    iq = idx_q.to(torch.int32).contiguous()
+    ik = idx_k.to(torch.int32).contiguous()
+    Mq, Nk = -(-S // block_m), -(-S // block_n)
+    with torch.cuda.device(q.device):
+        po = torch.empty((1, H, Mq, Nk), dtype=q.dtype, device=q.device)
+        nbytes = lib.psa_block_scores_scratch_bytes(H, S, S, block_m, block_n, _dt(q))
+        if nbytes == 0:
+            raise ValueError(f"psa_block_scores_tm: unsupported block sizes m={block_m} n={block_n}")
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        rc = lib.psa_block_scores_tm(_ptr(q), _ptr(k), _ptr(perm), _ptr(iq), _ptr(ik), _ptr(po), _ptr(scratch), nbytes, H, S, D,
+                                     block_m, block_n, _dt(q), _stream(q))
+    check(rc, "psa_block_scores_tm")
+    return po
+
+
+def psa_forward_tm(q_heads, images: KVImages, mask, out_tm, block_m: int, block_n: int, tile_n: int,
+                   sm_scale: Optional[float] = None, compat_quirk: bool = True, out_perm=None) -> torch.Tensor:
+    """Tile-image forward with q head-major ([1, H, S, D], from gather_heads) whose output rows are stored token-major
+    into out_tm ([S, H, D]), row t at token out_perm[t].  Returns the status word."""
+    _need_cuda(q_heads, mask, out_tm)
+    _, H, S, D = q_heads.shape
+    assert out_tm.shape == (S, H, D) and out_tm.is_contiguous() and out_tm.dtype == q_heads.dtype
+    mask = _flat_bh(mask)
+    if mask.dtype != torch.int32:
+        mask = mask.to(torch.int32)
+    out_perm = None if out_perm is None else _perm32(out_perm, S)
+    if sm_scale is None:
+        sm_scale = D ** -0.5
+    with torch.cuda.device(q_heads.device):
+        status = torch.zeros(1, dtype=torch.int32, device=q_heads.device)
+        rc = lib.psa_fwd_images_tm(_ptr(q_heads), _ptr(images.kimg), _ptr(images.vimg), _ptr(mask), _ptr(out_tm), _ptr(out_perm),
+                                   H, S, D, block_m, block_n, tile_n, mask.shape[-1], float(sm_scale), int(compat_quirk),
+                                   _dt(q_heads), _ptr(status), _stream(q_heads))
+    check(rc, "psa_fwd_images_tm")
+    return status
+
+
 def draw_sample_indices(B: int, H: int, block: int, keep: int, device) -> torch.Tensor:
     """topk(rand(B,H,1,block), keep).indices: the same two torch calls, in the same order on the same
     generator, as _random_sample_tokens (src/psa_triton/attention.py:132-133)."""

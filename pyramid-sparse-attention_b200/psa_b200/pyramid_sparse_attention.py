@@ -14,7 +14,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
-from .attention import compute_block_mask
+from .attention import compute_block_mask, psa_attention_token_major, token_major_view
 from .kernels import legacy_sparse_attention_factory, sparse_attention_factory
 from .rearrange import GilbertRearranger
 
@@ -143,7 +143,16 @@ class PyramidSparseAttention(nn.Module):
         compute_stats = self.config.verbose or self.logger is not None
         dens = None
         if not is_warmup and self._rows_in_place(q, k):
-            out, dens = self._forward_rows_in_place(q, k, v, compute_stats)
+            tm = [token_major_view(x) for x in (q, k, v)]
+            if all(t is not None for t in tm):
+                # the processors hand over transposed views of [B, S, H, D] tensors: read those where they lie and return
+                # the same kind of view, so that the caller's transpose(1, 2).flatten(2, 3) costs nothing
+                out_tm, mask = psa_attention_token_major(*tm, self.config, perm=self.gilbert_rearranger.source_rows(q.device),
+                                                         text_length=self.config.text_length)
+                out = out_tm.transpose(1, 2)
+                dens = ops.density(mask, True) if compute_stats else None
+            else:
+                out, dens = self._forward_rows_in_place(q, k, v, compute_stats)
             self.sparsity_counter += 1
             if self.logger is not None:
                 self.logger.log_sparsity(layer_idx=layer_idx, density=dens, sequence_length=q.shape[2],

@@ -111,3 +111,62 @@ def test_module_reorders_in_place(P, text):
     a, b = fused.float().cpu().double().flatten(), ref.double().flatten()
     assert float((a @ b) / (a.norm() * b.norm())) >= 0.999
     assert mod.logger.records[0]["density"].shape == (1, H)
+
+
+# ------------------------------------------------------------------ token-major tensors ----------------
+@pytest.mark.parametrize("with_perm", [False, True])
+def test_gather_heads(P, with_perm):
+    S, H, D = 517, 3, 64
+    x = C.randn(6, (S, H, D), torch.bfloat16).to(DEV)
+    perm = _perm(8, S).to(DEV) if with_perm else None
+    ref = x.transpose(0, 1)
+    if with_perm:
+        ref = ref.index_select(1, perm.long())
+    assert torch.equal(P.ops.gather_heads(x, perm)[0], ref)
+
+
+@pytest.mark.parametrize("with_perm", [False, True])
+@pytest.mark.parametrize("dt,D,S,bn,B", [(torch.bfloat16, 128, 1000, 64, 2), (torch.float16, 64, 777, 128, 1)])
+def test_token_major_layer_equals_head_major(P, dt, D, S, bn, B, with_perm):
+    from psa_b200.attention import PSAConfig, compute_block_mask, psa_attention_token_major
+    H = 3
+    qs, ks, vs = zip(*(C.qkv(300 + b, 1, H, S, D, dt) for b in range(B)))
+    q, k, v = (torch.cat(x, 0).to(DEV) for x in (qs, ks, vs))            # [B, H, S, D]
+    q_tm, k_tm, v_tm = (x.transpose(1, 2).contiguous() for x in (q, k, v))   # [B, S, H, D]
+    cfg = PSAConfig(block_m=128, block_n=bn, tile_n=32, mask_ratios=C.DEFAULT_RATIOS, mask_mode="topk")
+    iq = torch.cat([C.sample_idx(7 + b, 1, H, 128, 32) for b in range(B)], 0).to(DEV)
+    ik = torch.cat([C.sample_idx(17 + b, 1, H, bn, bn // 4) for b in range(B)], 0).to(DEV)
+    perm = _perm(9, S).to(DEV) if with_perm else None
+    out_tm, mask_tm = psa_attention_token_major(q_tm, k_tm, v_tm, cfg, perm=perm, idx_q=iq, idx_k=ik)
+    # head-major, with copies
+    if with_perm:
+        qr, kr, vr = (x.index_select(2, perm.long()) for x in (q, k, v))
+    else:
+        qr, kr, vr = q, k, v
+    mask, _, _ = compute_block_mask(qr, kr, cfg, idx_q=iq, idx_k=ik)
+    assert torch.equal(mask_tm, mask)
+    o = P.ops.psa_forward(qr, kr, vr, mask, 128, bn, 32)
+    if with_perm:
+        back = torch.empty_like(o)
+        back[:, :, perm.long()] = o
+        o = back
+    assert torch.equal(out_tm, o.transpose(1, 2))
+
+
+def test_module_reads_transposed_views_in_place(P):
+    """Handed q.transpose(1, 2) views of [B, S, H, D] tensors (what the diffusers processors pass), the module returns a
+    view of a token-major output: the same values as for contiguous head-major inputs, no transposed copy on either side."""
+    from psa_b200.pyramid_sparse_attention import AttentionConfig, PyramidSparseAttention
+    W, Hh, T, H, D, text = 12, 8, 9, 2, 128, 20
+    cfg = AttentionConfig(width=W, height=Hh, depth=T, text_length=text, use_rearrange=True, rearrange_method="Gilbert",
+                          block_m=128, block_n=64, tile_n=32, use_sim_mask=False, mask_ratios=C.DEFAULT_RATIOS, mask_mode="topk",
+                          warmup_steps=0, attn_impl="new_mask_type")
+    mod = PyramidSparseAttention(cfg, inference_num=10, layer_num=1, model_type="cogvideo")
+    q, k, v = (x.to(DEV) for x in C.qkv(992, 1, H, W * Hh * T + text, D, torch.bfloat16))
+    torch.manual_seed(55)
+    a = mod(q, k, v, 0)                                                     # head-major, contiguous
+    q_tm, k_tm, v_tm = (x.transpose(1, 2).contiguous() for x in (q, k, v))
+    torch.manual_seed(55)
+    b = mod(q_tm.transpose(1, 2), k_tm.transpose(1, 2), v_tm.transpose(1, 2), 0)
+    assert b.shape == a.shape and b.transpose(1, 2).is_contiguous()
+    assert torch.equal(a, b)
