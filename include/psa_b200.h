@@ -180,6 +180,32 @@ int psa_fwd_images_tm(const void* q, const void* kimg, const void* vimg, const i
                       int heads, int64_t seq, int head_dim, int block_m, int block_n, int tile_n, int mask_width, float sm_scale,
                       int compat_quirk, int dtype, int32_t* status, void* stream);
 
+/* Antidiagonal block-importance estimate of the causal (vision-language) call site.  Replaces estimate_block_importance
+ * with select_mode "inverse", softmax, kdb 1 - and its Triton kernels flat_group_gemm_fuse_reshape /
+ * softmax_fuse_block_sum - qwen2.5-vl-example/src/attention/PSA_casual/utils/block_importance.py:282-562,
+ * kernels/block_importance_kernels.py:7-117, 256-325.
+ * q, k: [BH, seq, D] (f16/bf16, equal lengths, D 64/128).  Tokens are zero-padded to a multiple of chunk_size and taken
+ * in groups of `stride`; logit(i, j) = sum_s q[i*stride + stride-1-s] . k[j*stride + s] / sqrt(D) / stride; causal: group
+ * i sees groups j <= i, else all groups of the padded length; out [BH, nb, nb] (dtype), nb = ceil(seq/block_size) =
+ * softmax mass per (query block, key block).  block_size/stride must be a power of two in 2..32.
+ * scratch: psa_antidiag_scratch_bytes() bytes (the fp32 logits), 16-byte aligned. */
+size_t psa_antidiag_scratch_bytes(int64_t bh, int64_t seq, int head_dim, int block_size, int stride, int chunk_size);
+int psa_antidiag_scores(const void* q, const void* k, void* out, void* scratch, size_t scratch_bytes, int64_t bh, int64_t seq,
+                        int head_dim, int block_size, int stride, int chunk_size, int causal, int dtype, void* stream);
+
+/* Level assignment of the causal call site.  Replaces transfer_attn_to_mask,
+ * qwen2.5-vl-example/src/attention/PSA_casual/PyramidAdaptiveBlockSparseAttn.py:85-168.
+ * attn: [BH, n, n] scores (dtype); mask: int32 [BH, n, n] in {0,1,2,4,8}.  Rows are sorted descending, equal scores in
+ * ascending column order.  energy_mode 0 ("topk"): level i takes ranks [int(len*start_ratios[i]), int(len*end_ratios[i]))
+ * with len = row+1 (causal) or n, products in fp32; energy_mode 1 ("energybound"): level i takes the ranks whose
+ * cumulative share e of the row sum satisfies lower_bounds[i] < e <= upper_bounds[i] (bounds already rounded to dtype by
+ * the caller, lower = max(start, previous end)).  Later levels overwrite earlier ones.  Then: the last special_blocks
+ * columns and rows are 1, entries above the diagonal 0 (causal), the diagonal and column 0 are 1.
+ * level_values, ratios and bounds are HOST arrays of n_levels <= PSA_MAX_LEVELS entries. */
+int psa_assign_levels_causal(const void* attn, int32_t* mask, int64_t bh, int n, int dtype, int energy_mode, int causal,
+                             int n_levels, const int32_t* level_values, const float* start_ratios, const float* end_ratios,
+                             const float* lower_bounds, const float* upper_bounds, int special_blocks, void* stream);
+
 /* Legacy forward on the dense old-format mask, optional causal.  Replaces _fwd_kernel / _forward,
  * src/psa_triton/kernels/psa_kernel_legacy.py:415-799, 837-938 (block sizes fixed 128/32/128, :1333-1351).
  * mask: int32 [BH, ceil(seq/128), mask_cols] in {0,1,2,4,8}; lse: float32 [BH, seq] = M + ln(max(L,1e-8))

@@ -511,3 +511,100 @@ def psa_attention(q, k, v, *, block_m=128, block_n=64, tile_n=32, mask_ratios=No
         mask = assign_levels(Po, mask_ratios, mask_mode, block_n, tile_n, text_length=0)
         out, _ = legacy_forward(q, k, v, mask, causal=False)
     return out, mask, Po
+
+
+# =====================================================================================================
+# Causal (vision-language) call site: antidiagonal block-importance estimate and its level mask.
+# =====================================================================================================
+def antidiag_block_scores(q: torch.Tensor, k: torch.Tensor, block_size: int, stride: int, causal: bool = True,
+                          chunk_size: int = 4096, norm: float = 1.0) -> torch.Tensor:
+    """estimate_block_importance with select_mode='inverse', softmax=True, kdb=1
+    (qwen2.5-vl-example/src/attention/PSA_casual/utils/block_importance.py:282-562) as exact maths in fp64.
+
+    q, k: [B, H, L, D] with equal lengths.  Tokens are zero-padded to a multiple of chunk_size and grouped by `stride`:
+    logit[i, j] = sum_s q[i*stride + stride-1-s] . k[j*stride + s] / sqrt(D) / stride / norm.  Causal: group i sees groups
+    j <= i; otherwise every group of the padded length (zero keys included, logit 0), as both of the reference's code
+    paths do.  Groups without a valid query token give zero rows.  Result [B, H, ceil(L/block), ceil(L/block)] (fp64) =
+    the softmax mass per (query block, key block).  The reference's PyTorch fallback additionally hides all earlier
+    chunks when L is a multiple of chunk_size (its '[-0:]' slice); its Triton path, which is what runs on a GPU, does
+    not, and neither does this function."""
+    B, H, L, D = q.shape
+    assert k.shape == q.shape and block_size % stride == 0 and chunk_size % block_size == 0
+    Lp = -(-L // chunk_size) * chunk_size
+    n = Lp // stride
+    qp = F.pad(q.double(), (0, 0, 0, Lp - L)).view(B, H, n, stride, D)
+    kp = F.pad(k.double(), (0, 0, 0, Lp - L)).view(B, H, n, stride, D)
+    logits = torch.einsum("bhisd,bhjsd->bhij", qp.flip(3), kp) / math.sqrt(D) / stride / norm
+    if causal:
+        hide = torch.triu(torch.ones(n, n, dtype=torch.bool), diagonal=1)
+        logits = logits.masked_fill(hide, float("-inf"))
+    p = torch.softmax(logits, dim=-1)
+    n_valid = -(-L // stride)
+    p[:, :, n_valid:, :] = 0
+    rb = block_size // stride
+    sums = p.view(B, H, n // rb, rb, n // rb, rb).sum(dim=(3, 5))
+    nb = -(-L // block_size)
+    return sums[:, :, :nb, :nb]
+
+
+def causal_level_mask(attn: torch.Tensor, mask_ratios: Dict[int, Tuple[float, float]], text_length: int, mode: str,
+                      block_size: int, causal: bool) -> torch.Tensor:
+    """transfer_attn_to_mask of the causal call site
+    (qwen2.5-vl-example/src/attention/PSA_casual/PyramidAdaptiveBlockSparseAttn.py:85-168), row by row.
+    attn [B, H, n, n] -> int32 [B, H, n, n] in {0, 1, 2, 4, 8}.  Equal scores rank in ascending column order.
+    'energybound' arithmetic: row sum and running sum are taken sequentially in fp32 (fp64 for fp32 scores) and rounded to
+    the score type (the running sum at every element), the ratio is rounded to the score type and compared with the
+    bounds rounded to the score type."""
+    if not mask_ratios:
+        raise ValueError("mask_ratios must not be empty")
+    if mode not in {"topk", "energybound"}:
+        raise ValueError("mode must be 'topk' or 'energybound'")
+    B, H, n, _ = attn.shape
+    dt = attn.dtype
+    out = torch.zeros((B, H, n, n), dtype=torch.int32)
+    f32 = np.float32
+    nsb = min(math.ceil(text_length / block_size) if text_length > 0 else 0, n)
+    acc_t = np.float64 if dt == torch.float32 else np.float32
+
+    def rnd(x):
+        return float(torch.tensor(float(x), dtype=torch.float64).to(dt).double())
+
+    for b in range(B):
+        for h in range(H):
+            for i in range(n):
+                row = attn[b, h, i].double().numpy()
+                order = np.lexsort((np.arange(n), -row))          # descending score, ascending column
+                m = np.zeros(n, dtype=np.int32)
+                if mode == "topk":
+                    valid = f32(i + 1) if causal else f32(n)
+                    for value, (s_ratio, e_ratio) in mask_ratios.items():
+                        s = min(int(f32(valid * f32(s_ratio))), n)
+                        e = min(int(f32(valid * f32(e_ratio))), n)
+                        if e > s:
+                            m[order[s:e]] = value
+                else:
+                    total = acc_t(0)
+                    for x in row:
+                        total = acc_t(total + acc_t(x))
+                    total = max(rnd(total), rnd(1e-10))
+                    run = acc_t(0)
+                    prev_upper = 0.0
+                    ratio = np.empty(n)
+                    for r, c in enumerate(order):
+                        run = acc_t(run + acc_t(row[c]))
+                        ratio[r] = rnd(rnd(run) / total)
+                    for value, (s_ratio, e_ratio) in mask_ratios.items():
+                        lower = max(s_ratio, prev_upper)
+                        prev_upper = e_ratio
+                        sel = (ratio > rnd(lower)) & (ratio <= rnd(e_ratio))
+                        m[order[sel]] = value
+                out[b, h, i] = torch.from_numpy(m)
+    if nsb:
+        out[:, :, :, -nsb:] = 1
+        out[:, :, -nsb:, :] = 1
+    if causal:
+        out[:, :, torch.triu(torch.ones(n, n, dtype=torch.bool), diagonal=1)] = 0
+    d = torch.arange(n)
+    out[:, :, d, d] = 1
+    out[:, :, :, 0] = 1
+    return out

@@ -17,6 +17,9 @@ struct AssignParams {
   int nk, width, n_levels, threshold_mode, newtype, min_index, text_blocks, npow2;
   int level[PSA_MAX_LEVELS], start[PSA_MAX_LEVELS], end[PSA_MAX_LEVELS], align[PSA_MAX_LEVELS];
   float thr[PSA_MAX_LEVELS];
+  // causal call site (variant 1): square score matrices, quotas that follow the row's causal length
+  int variant, causal, special;
+  float rs[PSA_MAX_LEVELS], re[PSA_MAX_LEVELS], lo[PSA_MAX_LEVELS];
 };
 
 __device__ __forceinline__ uint32_t desc_key(float v) {
@@ -115,6 +118,62 @@ __device__ __forceinline__ void emit_mask_row(const unsigned long long* keys, fl
   }
 }
 
+// Mask row of the causal call site (dense format, square matrices): quotas are fractions of the row's causal length
+// i+1 (fp32 product, truncated), or bands of the cumulative mass; then the fixed rules: special (text) blocks, nothing
+// above the diagonal, diagonal and first column always at level 1.
+template <typename T>
+__device__ __forceinline__ void emit_causal_row(const unsigned long long* keys, float* ratio, const T* __restrict__ src,
+                                                int32_t* __restrict__ mask, const AssignParams& p, int64_t row, int tid, int nt) {
+  const int n = p.nk;
+  const int i = (int)(row % n);
+  int32_t* dst = mask + row * n;
+  for (int pos = tid; pos < n; pos += nt) dst[pos] = 0;
+  __syncthreads();
+  if (!p.threshold_mode) {
+    const float valid = p.causal ? (float)(i + 1) : (float)n;
+    for (int l = 0; l < p.n_levels; ++l) {
+      int s = (int)__fmul_rn(valid, p.rs[l]), e = (int)__fmul_rn(valid, p.re[l]);
+      s = s < n ? s : n; e = e < n ? e : n;
+      for (int rank = s + tid; rank < e; rank += nt) dst[(int)(keys[rank] & 0xffffffffu)] = p.level[l];
+      __syncthreads();   // later levels overwrite earlier ones, in order
+    }
+  } else {
+    __shared__ float s_total;
+    if (tid == 0) {
+      float total;
+      if (sizeof(T) == 4) {
+        double t = 0.0, acc = 0.0;
+        for (int c = 0; c < n; ++c) t += (double)Elem<T>::to_f(src[c]);
+        for (int r = 0; r < n; ++r) { acc += (double)key_value((uint32_t)(keys[r] >> 32)); ratio[r] = (float)acc; }
+        total = (float)t;
+      } else {
+        float t = 0.f, acc = 0.f;
+        for (int c = 0; c < n; ++c) t += Elem<T>::to_f(src[c]);
+        for (int r = 0; r < n; ++r) { acc += key_value((uint32_t)(keys[r] >> 32)); ratio[r] = Elem<T>::round(acc); }
+        total = Elem<T>::round(t);
+      }
+      s_total = fmaxf(total, Elem<T>::round(1e-10f));
+    }
+    __syncthreads();
+    const float total = s_total;
+    for (int r = tid; r < n; r += nt) {
+      const float e = Elem<T>::round(__fdiv_rn(ratio[r], total));
+      int32_t val = 0;
+      for (int l = 0; l < p.n_levels; ++l)
+        if (e > p.lo[l] && e <= p.thr[l]) val = p.level[l];
+      dst[(int)(keys[r] & 0xffffffffu)] = val;
+    }
+    __syncthreads();
+  }
+  for (int j = tid; j < n; j += nt) {
+    int32_t v = dst[j];
+    if (p.special > 0 && (j >= n - p.special || i >= n - p.special)) v = 1;
+    if (p.causal && j > i) v = 0;
+    if (j == i || j == 0) v = 1;
+    dst[j] = v;
+  }
+}
+
 // General kernel (any score type, any row length up to 8192): bitonic network over 64-bit keys in shared memory.
 template <typename T>
 __global__ void __launch_bounds__(256) assign_levels_kernel(const T* __restrict__ po, int32_t* __restrict__ mask,
@@ -147,7 +206,8 @@ __global__ void __launch_bounds__(256) assign_levels_kernel(const T* __restrict_
       __syncthreads();
     }
   }
-  emit_mask_row<T>(keys, ratio, s_start, s_end, s_cnt, mask, p, row, tid, nt);
+  if (p.variant == 1) emit_causal_row<T>(keys, ratio, src, mask, p, row, tid, nt);
+  else emit_mask_row<T>(keys, ratio, s_start, s_end, s_cnt, mask, p, row, tid, nt);
 }
 
 // Fast kernel for 16-bit scores and rows of at most 4096 blocks: the key fits 32 bits (16 score bits, 16 index bits),
@@ -231,7 +291,8 @@ __global__ void __launch_bounds__(256) assign_levels_reg_kernel(const T* __restr
     keys[tid * E + e] = a[e] == 0xffffffffu ? ~0ull : (((unsigned long long)desc_key(v) << 32) | (a[e] & 0xffffu));
   }
   __syncthreads();
-  emit_mask_row<T>(keys, ratio, s_start, s_end, s_cnt, mask, p, row, tid, 256);
+  if (p.variant == 1) emit_causal_row<T>(keys, ratio, po + row * p.nk, mask, p, row, tid, 256);
+  else emit_mask_row<T>(keys, ratio, s_start, s_end, s_cnt, mask, p, row, tid, 256);
 }
 
 // ------------------------------------------------------------------------------ density -------------
@@ -278,34 +339,13 @@ __global__ void __launch_bounds__(256) density_kernel(const int32_t* __restrict_
 
 }  // namespace psa
 
-extern "C" int psa_assign_levels(const void* po, int32_t* mask, int64_t rows, int nk, int dtype, int threshold_mode,
-                                 int newtype, int n_levels, const int32_t* level_values, const int32_t* starts,
-                                 const int32_t* ends, const float* thresholds, const int32_t* aligns, int min_index,
-                                 int text_blocks, void* stream) {
-  using namespace psa;
-  PSA_REQUIRE(po && mask && level_values, PSA_ERR_ARG, "psa_assign_levels: null pointer");
-  PSA_REQUIRE(rows > 0 && rows < (1ll << 31), PSA_ERR_ARG, "psa_assign_levels: rows=%lld out of range", (long long)rows);
-  PSA_REQUIRE(nk > 0 && nk <= 8192, PSA_ERR_ARG, "psa_assign_levels: nk=%d out of range (1..8192)", nk);
-  PSA_REQUIRE(n_levels > 0 && n_levels <= PSA_MAX_LEVELS, PSA_ERR_ARG, "psa_assign_levels: n_levels=%d", n_levels);
-  if (threshold_mode) PSA_REQUIRE(thresholds && aligns, PSA_ERR_ARG, "psa_assign_levels: thresholds/aligns missing");
-  else PSA_REQUIRE(starts && ends, PSA_ERR_ARG, "psa_assign_levels: starts/ends missing");
-  AssignParams p;
-  p.nk = nk; p.n_levels = n_levels; p.threshold_mode = threshold_mode; p.newtype = newtype;
-  p.width = newtype ? nk + n_levels : nk;
-  p.min_index = min_index; p.text_blocks = text_blocks;
+namespace psa {
+// Launch of the sort + emit kernels for a filled parameter block (p.npow2 is set here).
+static int launch_assign(const void* po, int32_t* mask, int64_t rows, AssignParams p, int dtype, cudaStream_t st) {
+  const int nk = p.nk;
+  const int threshold_mode = p.threshold_mode;
   int np2 = 2; while (np2 < nk) np2 <<= 1;
   p.npow2 = np2;
-  for (int i = 0; i < PSA_MAX_LEVELS; ++i) {
-    p.level[i] = i < n_levels ? level_values[i] : 0;
-    p.start[i] = (i < n_levels && !threshold_mode) ? starts[i] : 0;
-    p.end[i] = (i < n_levels && !threshold_mode) ? ends[i] : 0;
-    p.align[i] = (i < n_levels && threshold_mode) ? aligns[i] : 1;
-    p.thr[i] = (i < n_levels && threshold_mode) ? thresholds[i] : 0.f;
-    if (i < n_levels && !threshold_mode)
-      PSA_REQUIRE(p.start[i] >= 0 && p.start[i] <= p.end[i] && p.end[i] <= nk, PSA_ERR_ARG,
-                  "psa_assign_levels: interval %d = [%d,%d) outside [0,%d]", i, p.start[i], p.end[i], nk);
-  }
-  cudaStream_t st = (cudaStream_t)stream;
   if ((dtype == PSA_F16 || dtype == PSA_BF16) && nk <= 4096) {
     // register-resident sort: E keys per thread, 256 threads
     const int E = np2 <= 512 ? 2 : np2 / 256;
@@ -342,6 +382,57 @@ extern "C" int psa_assign_levels(const void* po, int32_t* mask, int64_t rows, in
   });
   PSA_CHECK_LAUNCH("psa_assign_levels");
   return PSA_OK;
+}
+}  // namespace psa
+
+extern "C" int psa_assign_levels(const void* po, int32_t* mask, int64_t rows, int nk, int dtype, int threshold_mode,
+                                 int newtype, int n_levels, const int32_t* level_values, const int32_t* starts,
+                                 const int32_t* ends, const float* thresholds, const int32_t* aligns, int min_index,
+                                 int text_blocks, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(po && mask && level_values, PSA_ERR_ARG, "psa_assign_levels: null pointer");
+  PSA_REQUIRE(rows > 0 && rows < (1ll << 31), PSA_ERR_ARG, "psa_assign_levels: rows=%lld out of range", (long long)rows);
+  PSA_REQUIRE(nk > 0 && nk <= 8192, PSA_ERR_ARG, "psa_assign_levels: nk=%d out of range (1..8192)", nk);
+  PSA_REQUIRE(n_levels > 0 && n_levels <= PSA_MAX_LEVELS, PSA_ERR_ARG, "psa_assign_levels: n_levels=%d", n_levels);
+  if (threshold_mode) PSA_REQUIRE(thresholds && aligns, PSA_ERR_ARG, "psa_assign_levels: thresholds/aligns missing");
+  else PSA_REQUIRE(starts && ends, PSA_ERR_ARG, "psa_assign_levels: starts/ends missing");
+  AssignParams p = {};
+  p.nk = nk; p.n_levels = n_levels; p.threshold_mode = threshold_mode; p.newtype = newtype;
+  p.width = newtype ? nk + n_levels : nk;
+  p.min_index = min_index; p.text_blocks = text_blocks;
+  for (int i = 0; i < PSA_MAX_LEVELS; ++i) {
+    p.level[i] = i < n_levels ? level_values[i] : 0;
+    p.start[i] = (i < n_levels && !threshold_mode) ? starts[i] : 0;
+    p.end[i] = (i < n_levels && !threshold_mode) ? ends[i] : 0;
+    p.align[i] = (i < n_levels && threshold_mode) ? aligns[i] : 1;
+    p.thr[i] = (i < n_levels && threshold_mode) ? thresholds[i] : 0.f;
+    if (i < n_levels && !threshold_mode)
+      PSA_REQUIRE(p.start[i] >= 0 && p.start[i] <= p.end[i] && p.end[i] <= nk, PSA_ERR_ARG,
+                  "psa_assign_levels: interval %d = [%d,%d) outside [0,%d]", i, p.start[i], p.end[i], nk);
+  }
+  return launch_assign(po, mask, rows, p, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int psa_assign_levels_causal(const void* attn, int32_t* mask, int64_t bh, int n, int dtype, int energy_mode, int causal,
+                                        int n_levels, const int32_t* level_values, const float* start_ratios,
+                                        const float* end_ratios, const float* lower_bounds, const float* upper_bounds,
+                                        int special_blocks, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(attn && mask && level_values, PSA_ERR_ARG, "psa_assign_levels_causal: null pointer");
+  PSA_REQUIRE(bh > 0 && n > 0 && n <= 8192 && bh * n < (1ll << 31), PSA_ERR_ARG, "psa_assign_levels_causal: bad shape");
+  PSA_REQUIRE(n_levels > 0 && n_levels <= PSA_MAX_LEVELS, PSA_ERR_ARG, "psa_assign_levels_causal: n_levels=%d", n_levels);
+  PSA_REQUIRE(special_blocks >= 0 && special_blocks <= n, PSA_ERR_ARG, "psa_assign_levels_causal: special_blocks=%d", special_blocks);
+  if (energy_mode) PSA_REQUIRE(lower_bounds && upper_bounds, PSA_ERR_ARG, "psa_assign_levels_causal: bounds missing");
+  else PSA_REQUIRE(start_ratios && end_ratios, PSA_ERR_ARG, "psa_assign_levels_causal: ratios missing");
+  AssignParams p = {};
+  p.nk = n; p.width = n; p.n_levels = n_levels; p.threshold_mode = energy_mode ? 1 : 0; p.newtype = 0;
+  p.variant = 1; p.causal = causal ? 1 : 0; p.special = special_blocks;
+  for (int i = 0; i < n_levels; ++i) {
+    p.level[i] = level_values[i];
+    if (energy_mode) { p.lo[i] = lower_bounds[i]; p.thr[i] = upper_bounds[i]; }
+    else { p.rs[i] = start_ratios[i]; p.re[i] = end_ratios[i]; }
+  }
+  return launch_assign(attn, mask, bh * n, p, dtype, (cudaStream_t)stream);
 }
 
 extern "C" int psa_density(const int32_t* mask, float* per_bh, int64_t bh, int64_t mq, int width, int newtype,

@@ -310,6 +310,65 @@ def assign_levels(po: torch.Tensor, mask_ratios: Dict[int, Tuple[float, float]],
     return mask
 
 
+def antidiag_block_scores(q, k, block_size: int, stride: int, chunk_size: int, causal: bool = True) -> torch.Tensor:
+    """Antidiagonal block-importance estimate [B, H, nb, nb] (q.dtype), nb = ceil(L/block_size): estimate_block_importance
+    with select_mode='inverse' (qwen2.5-vl-example/src/attention/PSA_casual/utils/block_importance.py:282-562)."""
+    _need_cuda(q, k)
+    q, k = _flat_bh(q), _flat_bh(k)
+    B, H, L, D = q.shape
+    assert k.shape == q.shape and k.dtype == q.dtype
+    nbytes = lib.psa_antidiag_scratch_bytes(B * H, L, D, block_size, stride, chunk_size)
+    if nbytes == 0:
+        raise ValueError(f"antidiagonal estimate: unsupported sizes (head_dim {D}, block {block_size}, stride {stride}, "
+                         f"chunk {chunk_size})")
+    nb = -(-L // block_size)
+    with torch.cuda.device(q.device):
+        out = torch.empty((B, H, nb, nb), dtype=q.dtype, device=q.device)
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        rc = lib.psa_antidiag_scores(_ptr(q), _ptr(k), _ptr(out), _ptr(scratch), nbytes, B * H, L, D, block_size, stride,
+                                     chunk_size, int(causal), _dt(q), _stream(q))
+    check(rc, "psa_antidiag_scores")
+    return out
+
+
+def assign_levels_causal(attn: torch.Tensor, mask_ratios: Dict[int, Tuple[float, float]], text_length: int, mode: str,
+                         block_size: int, causal: bool) -> torch.Tensor:
+    """Square score matrices -> dense level mask of the causal call site; same arguments and errors as its
+    transfer_attn_to_mask (qwen2.5-vl-example/src/attention/PSA_casual/PyramidAdaptiveBlockSparseAttn.py:85-168)."""
+    if not mask_ratios:
+        raise ValueError("mask_ratios must not be empty")
+    if mode not in {"topk", "energybound"}:
+        raise ValueError("mode must be 'topk' or 'energybound'")
+    _need_cuda(attn)
+    attn = _flat_bh(attn)
+    B, H, n, n2 = attn.shape
+    assert n == n2, "the causal call site scores square block matrices"
+    nl = len(mask_ratios)
+    if nl > 8:
+        raise ValueError("at most 8 levels")
+    I32, F32 = C.c_int32 * nl, C.c_float * nl
+    items = list(mask_ratios.items())              # dict order: later levels overwrite earlier ones
+    levels = I32(*[int(l) for l, _ in items])
+    rs = re = lo = hi = None
+    if mode == "topk":
+        rs = F32(*[float(r[0]) for _, r in items])
+        re = F32(*[float(r[1]) for _, r in items])
+    else:
+        lows, prev = [], 0.0
+        for _, (s_ratio, e_ratio) in items:
+            lows.append(max(s_ratio, prev))
+            prev = e_ratio
+        lo = F32(*[_round_to_dtype(x, attn.dtype) for x in lows])
+        hi = F32(*[_round_to_dtype(r[1], attn.dtype) for _, r in items])
+    special = min((text_length + block_size - 1) // block_size if text_length > 0 else 0, n)
+    with torch.cuda.device(attn.device):
+        mask = torch.empty((B, H, n, n), dtype=torch.int32, device=attn.device)
+        rc = lib.psa_assign_levels_causal(_ptr(attn), _ptr(mask), B * H, n, _dt(attn), int(mode == "energybound"), int(causal),
+                                          nl, levels, rs, re, lo, hi, special, _stream(attn))
+    check(rc, "psa_assign_levels_causal")
+    return mask
+
+
 def density(mask: torch.Tensor, newtype: bool) -> torch.Tensor:
     """Per-(batch, head) mean density [B,H] float32 on the device (no host sync).
     calc_density_newtype / calc_density, src/psa_triton/utils/transfer_attn_to_mask.py:510-622."""

@@ -141,3 +141,31 @@ def order_checksum(order) -> int:
     """Position-weighted checksum of a visiting order (detects any transposition)."""
     o = np.asarray(order, dtype=np.int64)
     return int(((np.arange(o.size, dtype=np.int64) % 1000003) * (o % 999983)).sum() % (1 << 61))
+
+
+# ---- causal (vision-language) call site: antidiagonal estimate and its level mask -------------------------------------
+RATIOS_CAUSAL = {1: (0.0, 0.05), 2: (0.05, 0.15), 4: (0.15, 0.25), 8: (0.25, 0.5), 0: (0.5, 1.0)}
+RATIOS_ENERGY = {1: (0.0, 0.6), 2: (0.6, 0.75), 4: (0.75, 0.85), 8: (0.85, 0.95), 0: (0.95, 1.0)}
+# name, L, D, H, block, stride, chunk, causal
+ANTIDIAG_CASES = [
+    ("ad_1000_d64", 1000, 64, 2, 128, 16, 4096, True),
+    ("ad_700_d128_s8", 700, 128, 2, 128, 8, 1024, True),
+    ("ad_1500_two_chunks", 1500, 64, 1, 128, 16, 1024, True),
+    ("ad_900_noncausal", 900, 64, 2, 128, 16, 1024, False),
+    ("ad_1024_exact", 1024, 128, 1, 128, 16, 1024, True),
+]
+# name, n, H, dtype, mode, causal, text_length
+CAUSAL_MASK_CASES = [(f"cm_{n}_{dt}_{mode}_{'c' if causal else 'n'}_{text}", n, 2, dt, mode, causal, text)
+                     for n in (8, 23, 64) for dt in ("fp32", "bf16", "fp16") for mode in ("topk", "energybound")
+                     for causal in (True, False) for text in (0, 300)]
+
+
+def causal_scores(seed: int, H: int, n: int, dtype, causal: bool) -> torch.Tensor:
+    """Block scores shaped like the estimator's output: positive rows that sum to about one block's worth of mass,
+    zero above the diagonal when causal."""
+    rng = np.random.default_rng(seed)
+    x = rng.gamma(0.3, 1.0, size=(1, H, n, n)).astype(np.float32) + 1e-4
+    if causal:
+        x = np.tril(x)
+    x = x / x.sum(-1, keepdims=True) * 8.0
+    return torch.from_numpy(x).to(dtype)
