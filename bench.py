@@ -405,7 +405,10 @@ def main():
                 h_out.copy_(peer.o, non_blocking=True)
                 return
             if world == 1:
-                dq, dk, dv = (x.to(dev, non_blocking=True) for x in (hq, hk, hv))
+                # the library's host-buffer call: head chunks, copies in and out overlapped with the compute
+                iq, ik = draw_indices()
+                h_out = psa_b200.psa_attention_host(hq, hk, hv, cfg, out=h_out, device=dev, idx_q=iq, idx_k=ik)
+                return
             else:
                 x = to_head_sharded(hx.to(dev, non_blocking=True))
                 dq, dk, dv = x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0)

@@ -148,3 +148,72 @@ def psa_attention(q, k, v, *, config: PSAConfig = None, mask_ratios=None, mask_m
         config.block_n = block_n
         config.tile_n = min(32, block_n)
     return PSAAttention(config)(q, k, v)
+
+
+def psa_attention_host(q, k, v, config: PSAConfig = None, out=None, device=None, heads_per_chunk: int = 0,
+                       idx_q=None, idx_k=None):
+    """The PSA layer for tensors that live in pinned HOST memory: q, k, v [B, H, L, D] -> out [B, H, L, D] (pinned host).
+
+    Heads are independent in every stage, so the layer runs chunk by chunk over the heads with the copies on two side
+    streams: while chunk c is computed, chunk c+1 is on its way to the device and the output of chunk c-1 on its way
+    back, and the call costs about the longer of (transfer, compute) instead of their sum.  The sample offsets are drawn
+    once for all heads (same generator consumption as PSAAttention), so the result equals PSAAttention on device copies
+    bit for bit.  The returned tensor is complete once the current stream has been synchronised."""
+    config = config if config is not None else PSAConfig()
+    for t in (q, k, v):
+        if t.device.type != "cpu" or not t.is_pinned() or not t.is_contiguous():
+            raise ValueError("psa_attention_host takes contiguous tensors in pinned host memory")
+    B, H, L, D = q.shape
+    dev = torch.device(device if device is not None else "cuda")
+    module = PSAAttention(config)
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    hc = heads_per_chunk if heads_per_chunk > 0 else max(1, -(-H // 8))
+    chunks = [(h0, min(H, h0 + hc)) for h0 in range(0, H, hc)]
+    with torch.cuda.device(dev):
+        main = torch.cuda.current_stream()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        if idx_q is None:
+            idx_q = ops.draw_sample_indices(B, H, config.block_m, config.block_m // 4, dev)
+        if idx_k is None:
+            idx_k = ops.draw_sample_indices(B, H, config.block_n, config.block_n // 4, dev)
+        # two sets of staging buffers, allocated on the current stream before any side stream touches them
+        stage = [[torch.empty((B, hc, L, D), dtype=q.dtype, device=dev) for _ in range(3)] for _ in range(2)]
+        outs = [torch.empty((B, hc, L, D), dtype=q.dtype, device=dev) for _ in range(2)]
+        start = torch.cuda.Event()
+        start.record(main)
+        s_in.wait_event(start)
+        s_out.wait_event(start)
+        computed = [None, None]      # per buffer set: compute of the chunk that last used the inputs has finished
+        drained = [None, None]       # per buffer set: the output copy of the chunk that last used it has finished
+        for c, (h0, h1) in enumerate(chunks):
+            b, n = c & 1, h1 - h0
+            with torch.cuda.stream(s_in):
+                if computed[b] is not None:
+                    s_in.wait_event(computed[b])
+                for dst, src in zip(stage[b], (q, k, v)):
+                    dst[:, :n].copy_(src[:, h0:h1], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(s_in)
+            main.wait_event(arrived)
+            if drained[b] is not None:
+                main.wait_event(drained[b])
+            dq, dk, dv = (t[:, :n] for t in stage[b])
+            if n != hc:
+                dq, dk, dv = dq.contiguous(), dk.contiguous(), dv.contiguous()
+            with torch.no_grad():
+                mask, _, _ = compute_block_mask(dq, dk, config, idx_q=idx_q[:, h0:h1].contiguous(),
+                                                idx_k=idx_k[:, h0:h1].contiguous())
+            o = module.sparse_attention_fn(dq, dk, dv, mask, None)
+            outs[b][:, :n].copy_(o)
+            computed[b] = torch.cuda.Event()
+            computed[b].record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(computed[b])
+                out[:, h0:h1].copy_(outs[b][:, :n], non_blocking=True)
+                drained[b] = torch.cuda.Event()
+                drained[b].record(s_out)
+        for e in drained:
+            if e is not None:
+                main.wait_event(e)
+    return out

@@ -170,3 +170,31 @@ def test_module_reads_transposed_views_in_place(P):
     b = mod(q_tm.transpose(1, 2), k_tm.transpose(1, 2), v_tm.transpose(1, 2), 0)
     assert b.shape == a.shape and b.transpose(1, 2).is_contiguous()
     assert torch.equal(a, b)
+
+
+# ------------------------------------------------------------------ host buffers, pipelined by head chunks ----------
+@pytest.mark.parametrize("H,hc", [(5, 2), (4, 0), (3, 8)])
+def test_host_buffer_layer_equals_device_layer(P, H, hc):
+    """psa_attention_host (pinned host tensors in and out, head chunks with overlapped copies) gives the bits of
+    PSAAttention on device copies: ragged last chunk, default chunking, one chunk."""
+    S, D = 900, 128
+    q, k, v = (x.pin_memory() for x in C.qkv(410, 1, H, S, D, torch.bfloat16))
+    cfg = P.PSAConfig(block_m=128, block_n=64, tile_n=32, mask_ratios=C.DEFAULT_RATIOS, mask_mode="topk")
+    torch.manual_seed(31)
+    out = P.psa_attention_host(q, k, v, cfg, device=DEV, heads_per_chunk=hc)
+    torch.cuda.synchronize()
+    torch.manual_seed(31)
+    ref = P.PSAAttention(cfg)(q.to(DEV), k.to(DEV), v.to(DEV))
+    assert out.is_pinned() and torch.equal(out, ref.cpu())
+    # a second call into the same output buffer, explicit offsets
+    iq, ik = C.sample_idx(7, 1, H, 128, 32).to(DEV), C.sample_idx(8, 1, H, 64, 16).to(DEV)
+    out2 = P.psa_attention_host(q, k, v, cfg, out=out, device=DEV, heads_per_chunk=hc, idx_q=iq, idx_k=ik)
+    torch.cuda.synchronize()
+    assert out2 is out
+    assert torch.equal(out2, P.PSAAttention(cfg)(q.to(DEV), k.to(DEV), v.to(DEV), idx_q=iq, idx_k=ik).cpu())
+
+
+def test_host_buffer_layer_rejects_pageable_memory(P):
+    q, k, v = C.qkv(410, 1, 2, 256, 64, torch.bfloat16)
+    with pytest.raises(ValueError):
+        P.psa_attention_host(q, k, v, device=DEV)
