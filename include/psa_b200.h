@@ -233,6 +233,14 @@ int psa_legacy_bwd(const void* q, const void* k, const void* v, const void* k2, 
                    const float* lse, const void* dout, void* dq, void* dk, void* dv, float* delta, int64_t bh,
                    int64_t seq, int head_dim, int mask_cols, float sm_scale, int causal, int dtype, void* stream);
 
+/* The same backward on tensor cores (warp-level mma, f16/bf16 operands, fp32 accumulation; f16/bf16 only).  Same
+ * arguments and reference code as psa_legacy_bwd; the products ds*c and p*c (c = visible copies of a pooled token) are
+ * rounded to the element type once more where c is 3, 5, 6 or 7 (causal diagonal, replicate-padded tail). */
+int psa_legacy_bwd_tc(const void* q, const void* k, const void* v, const void* k2, const void* k4, const void* k8,
+                      const void* v2, const void* v4, const void* v8, const int32_t* mask, const void* out,
+                      const float* lse, const void* dout, void* dq, void* dk, void* dv, float* delta, int64_t bh,
+                      int64_t seq, int head_dim, int mask_cols, float sm_scale, int causal, int dtype, void* stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * Head sharding over the GPUs of one node, by peer memory instead of an all-to-all collective.  No counterpart in the
  * reference (it runs on one GPU); these calls sit where a sequence-parallel host model would otherwise call

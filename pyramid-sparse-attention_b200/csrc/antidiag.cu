@@ -11,7 +11,7 @@
 // already multiplied by log2(e)/sqrt(D)/stride.  Causal launches skip the tiles above the diagonal.
 // Kernel 2 (HBM-bound: reads the logits once per pass): one CTA per query block, a warp per group row: maximum, sum
 // of exp2, then the cell sums, accumulated per warp in shared memory in a fixed order (deterministic).
-#include "psa_common.cuh"
+#include "mma_sync.cuh"
 
 namespace psa {
 namespace {
@@ -19,22 +19,6 @@ namespace {
 constexpr int kTile = 128;       // groups per CTA tile, both ways
 constexpr int kBK = 64;          // channels per K-chunk
 constexpr int kRowHalves = 72;   // shared-memory row pitch in 16-bit elements (64 + 8: conflict-free fragment loads)
-
-template <typename T> struct MmaOp;
-template <> struct MmaOp<__half> {
-  static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-  }
-};
-template <> struct MmaOp<__nv_bfloat16> {
-  static __device__ __forceinline__ void run(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-  }
-};
 
 struct AdParams {
   int64_t seq;      // valid tokens

@@ -450,7 +450,7 @@ def psa_forward(q, k, v, mask, block_m: int, block_n: int, tile_n: int, sm_scale
 
 
 def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float] = None, need_lse: bool = False,
-                   pyramid=None):
+                   pyramid=None, impl: int = IMPL_AUTO):
     """Legacy forward on the dense old-format mask (_forward, src/psa_triton/kernels/psa_kernel_legacy.py:837-938)."""
     _need_cuda(q, k, v, mask)
     assert q.shape[-1] == k.shape[-1] == v.shape[-1]
@@ -463,20 +463,21 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
     if sm_scale is None:
         sm_scale = D ** -0.5
     n128 = -(-S // 128)
-    if (pyramid is None and not need_lse and q.dtype in (torch.float16, torch.bfloat16) and n128 + 5 <= 1472
+    if (pyramid is None and impl != IMPL_SCALAR and q.dtype in (torch.float16, torch.bfloat16) and n128 + 5 <= 1472
             and sm_scale > 0):
-        # inference path of the old-mask presets: the tcgen05 forward on tile images (the row-major pyramid the backward
-        # would need is not built)
+        # 16-bit tensors: the tcgen05 forward on tile images.  A training step (need_lse) also gets the log-sum-exp rows
+        # and the row-major pyramid its backward reads (one more pass over k and v).
         imgs = pyramid_kv_images(k, v, 128)
         with torch.cuda.device(q.device):
             o = torch.empty_like(q)
+            lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if need_lse else None
             scratch = torch.empty(lib.psa_legacy_index_bytes(B * H, S) // 4, dtype=torch.int32, device=q.device)
             status = torch.zeros(1, dtype=torch.int32, device=q.device)
-            rc = lib.psa_legacy_fwd_images(_ptr(q), _ptr(imgs.kimg), _ptr(imgs.vimg), _ptr(mask), _ptr(scratch), _ptr(o), None,
+            rc = lib.psa_legacy_fwd_images(_ptr(q), _ptr(imgs.kimg), _ptr(imgs.vimg), _ptr(mask), _ptr(scratch), _ptr(o), _ptr(lse),
                                            B * H, S, D, mask.shape[-1], float(sm_scale), int(causal), _dt(q), _ptr(status), _stream(q))
         check(rc, "psa_legacy_fwd_images")
         o._psa_status = status
-        return o, None, None
+        return o, lse, (pyramid_kv(k, v, 128) if need_lse else None)
     if pyramid is None:
         pyramid = pyramid_kv(k, v, 128)
     (k2, k4, k8), (v2, v4, v8) = pyramid
@@ -511,8 +512,9 @@ def legacy_forward_tc(q, k, v, mask, sm_scale: Optional[float] = None, need_lse:
     return o, lse
 
 
-def legacy_backward(q, k, v, mask, o, lse, do, causal: bool, sm_scale: float, pyramid):
-    """dQ, dK, dV of the legacy kernel (_sparse_attention.backward, psa_kernel_legacy.py:947-1069)."""
+def legacy_backward(q, k, v, mask, o, lse, do, causal: bool, sm_scale: float, pyramid, impl: int = IMPL_AUTO):
+    """dQ, dK, dV of the legacy kernel (_sparse_attention.backward, psa_kernel_legacy.py:947-1069).  16-bit tensors run
+    on the tensor-core kernels unless impl == IMPL_SCALAR."""
     _need_cuda(q, k, v, mask, o, lse, do)
     do = _flat_bh(do)
     B, H, S, D = q.shape
@@ -520,8 +522,10 @@ def legacy_backward(q, k, v, mask, o, lse, do, causal: bool, sm_scale: float, py
     with torch.cuda.device(q.device):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         delta = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
-        rc = lib.psa_legacy_bwd(_ptr(q), _ptr(k), _ptr(v), _ptr(k2), _ptr(k4), _ptr(k8), _ptr(v2), _ptr(v4), _ptr(v8),
-                                _ptr(mask), _ptr(o), _ptr(lse), _ptr(do), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(delta),
-                                B * H, S, D, mask.shape[-1], float(sm_scale), int(causal), _dt(q), _stream(q))
+        use_tc = impl == IMPL_TENSOR or (impl == IMPL_AUTO and q.dtype in (torch.float16, torch.bfloat16))
+        fn = lib.psa_legacy_bwd_tc if use_tc else lib.psa_legacy_bwd
+        rc = fn(_ptr(q), _ptr(k), _ptr(v), _ptr(k2), _ptr(k4), _ptr(k8), _ptr(v2), _ptr(v4), _ptr(v8),
+                _ptr(mask), _ptr(o), _ptr(lse), _ptr(do), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(delta),
+                B * H, S, D, mask.shape[-1], float(sm_scale), int(causal), _dt(q), _stream(q))
     check(rc, "psa_legacy_bwd")
     return dq, dk, dv

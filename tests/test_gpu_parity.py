@@ -189,7 +189,7 @@ def test_causal_legacy_full_size_properties(P):
     q, k, v = (torch.randn(B, H, S, D, device=DEV, dtype=torch.bfloat16, generator=g) for _ in range(3))
     mask = C.legacy_mask(77, B, H, S, True, False).to(DEV)
     o_tc, lse_tc = P.ops.legacy_forward_tc(q, k, v, mask, causal=True)
-    o_sc, lse_sc, pyr = P.ops.legacy_forward(q, k, v, mask, True, need_lse=True)
+    o_sc, lse_sc, pyr = P.ops.legacy_forward(q, k, v, mask, True, need_lse=True, impl=P.ops.IMPL_SCALAR)
     assert int(o_tc._psa_status.item()) == 0
     assert float((o_tc.float() - o_sc.float()).abs().max()) <= 2e-2 and cosine(o_tc.float(), o_sc.float()) >= 0.999
     fin = torch.isfinite(lse_sc)
@@ -200,6 +200,11 @@ def test_causal_legacy_full_size_properties(P):
     for a, a2 in zip(grads, grads2):
         assert bool(torch.isfinite(a).all())
         assert float((a2.float() - 2 * a.float()).abs().max()) <= 1e-2 * float(a.float().abs().max())
+    # the tensor-core backward (what the calls above ran) against the scalar one
+    ref = P.ops.legacy_backward(q, k, v, mask, o_sc, lse_sc, do, True, D ** -0.5, pyr, impl=P.ops.IMPL_SCALAR)
+    for a, r in zip(grads, ref):
+        a, r = a.float(), r.float()
+        assert cosine(a, r) >= COS_OUT and float((a - r).abs().max()) <= 2e-2 * max(1.0, float(r.abs().max()))
 
 
 # ------------------------------------------------------------------ K similarity ---------------------
@@ -434,3 +439,26 @@ def test_forward_tile_image_path_vs_oracle(P, golden, case, dt):
     assert torch.equal(out, plain)               # same arithmetic, only the K/V fetch differs
     ref = O.psa_forward_newmask(q, k, v, mask, bm, bn, tn).float()
     assert float((out.float().cpu() - ref).abs().max()) <= ATOL_OUT and cosine(out.float().cpu(), ref) >= COS_OUT
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+@pytest.mark.parametrize("S,D,causal", [(700, 128, True), (700, 64, False), (1100, 128, False), (513, 64, True)])
+def test_legacy_backward_tensor_core_vs_oracle(P, dt, S, D, causal):
+    """Tensor-core backward: mixed levels on the causal diagonal (odd copy counts) and a ragged tail (pad fold), against
+    the oracle on the same 16-bit inputs and against the scalar kernels."""
+    H, B = 2, 1
+    q, k, v = C.qkv(420, B, H, S, D, C.DT[dt])
+    do = C.randn(424, (B, H, S, D), C.DT[dt])
+    mask = C.legacy_mask(425, B, H, S, causal, False)
+    o_ref, lse_ref = O.legacy_forward(q, k, v, mask, causal)
+    ref = O.legacy_backward(q, k, v, mask, o_ref, lse_ref, do, causal)
+    qd, kd, vd, md, dod = q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), do.to(DEV)
+    o, lse, pyr = P.ops.legacy_forward(qd, kd, vd, md, causal, need_lse=True)
+    assert lse is not None and pyr is not None
+    tc = P.ops.legacy_backward(qd, kd, vd, md, o, lse, dod, causal, D ** -0.5, pyr, impl=P.ops.IMPL_TENSOR)
+    sc = P.ops.legacy_backward(qd, kd, vd, md, o, lse, dod, causal, D ** -0.5, pyr, impl=P.ops.IMPL_SCALAR)
+    for g, r, s_ in zip(tc, ref, sc):
+        g, r, s_ = g.float().cpu(), r.float(), s_.float().cpu()
+        assert bool(torch.isfinite(g).all())
+        assert cosine(g, r) >= COS_OUT and float((g - r).abs().max()) <= 2e-2 * max(1.0, float(r.abs().max()))
+        assert cosine(g, s_) >= COS_OUT and float((g - s_).abs().max()) <= 2e-2 * max(1.0, float(s_.abs().max()))
