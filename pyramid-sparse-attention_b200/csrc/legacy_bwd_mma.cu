@@ -7,10 +7,10 @@
 // rounded once more when they become tensor-core operands; that only changes values where c is 3, 5, 6 or 7, i.e. on
 // the causal diagonal and in the replicate-padded tail.)
 //
-// dQ: one CTA per 128 query rows, a warp per 16 rows with its Q and dO fragments in registers; key blocks are staged
-// 32 pooled tokens at a time.  dK/dV: one CTA per 128-key block; per level the block's pooled K and V sit in shared
+// dQ: one CTA per 128 query rows, a warp per 16 rows with its Q and dO fragments in registers; the selected key blocks
+// stream through 32 pooled tokens at a time (copied asynchronously, double-buffered).  dK/dV: one CTA per 128-key block; per level the block's pooled K and V sit in shared
 // memory, a warp owns 16 pooled tokens and keeps their dK and dV in registers while the query rows of every block that
-// selected this level stream through in chunks of 32; the result is spread over the original positions in fp32 shared
+// selected this level stream through in chunks of 16 (copied asynchronously, double-buffered); the result is spread over the original positions in fp32 shared
 // memory (mean-pool backward), the replicate-padded tail is folded into the last token, one rounding at the end.
 #include "mma_sync.cuh"
 
@@ -42,6 +42,24 @@ __device__ __forceinline__ void stage_rows(unsigned short* dst, const unsigned s
   }
 }
 
+// The same with asynchronous copies (cp.async, zero fill for the rows failing ok(r)); `safe` is any valid address of the
+// source tensor.  The caller commits the group and waits for it before the rows are read.
+template <int D, typename F>
+__device__ __forceinline__ void stage_rows_async(unsigned short* dst, const unsigned short* __restrict__ src,
+                                                 const unsigned short* __restrict__ safe, int rows, F ok) {
+  constexpr int PITCH = D + 8, WPR = D / 8;
+  for (int e = threadIdx.x; e < rows * WPR; e += blockDim.x) {
+    const int r = e / WPR, c = e - r * WPR;
+    const bool v = ok(r);
+    const unsigned short* from = v ? src + (int64_t)r * D + c * 8 : safe;
+    const uint32_t to = (uint32_t)__cvta_generic_to_shared(dst + r * PITCH + c * 8);
+    const int bytes = v ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(to), "l"(from), "r"(bytes) : "memory");
+  }
+}
+__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // C = A(16 x D, rows g / g+8 of `a_rows`) . B^T(8 tokens x D, row g of `b_rows`), both [row][D+8] in shared memory.
 template <typename T, int D>
 __device__ __forceinline__ void dot_rows(float (&c)[4], const unsigned short* a_rows, const unsigned short* b_row, int tig) {
@@ -69,8 +87,8 @@ __global__ void __launch_bounds__(256) bwd_dq_mma_kernel(const T* __restrict__ q
                                                         int mq, float scale, int causal) {
   constexpr int PITCH = D + 8, KS = D / 16, ND = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  unsigned short* Ks = reinterpret_cast<unsigned short*>(smem_raw);   // [32][PITCH]
-  unsigned short* Vs = Ks + 32 * PITCH;
+  unsigned short* Ks = reinterpret_cast<unsigned short*>(smem_raw);   // [2 buffers][32][PITCH]
+  unsigned short* Vs = Ks + 2 * 32 * PITCH;
   const int m = blockIdx.x;
   const int64_t bh = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
@@ -108,53 +126,100 @@ __global__ void __launch_bounds__(256) bwd_dq_mma_kernel(const T* __restrict__ q
 
   const int32_t* mrow = mask + (bh * mq + m) * (int64_t)mask_cols;
   const int nblk = (int)(s_pad / 128);
-  for (int pb = 0; pb < nblk && pb < mask_cols; ++pb) {
-    const int level = mrow[pb];
-    int li;
-    if (level == 1) li = 0; else if (level == 2) li = 1; else if (level == 4) li = 2; else if (level == 8) li = 3; else continue;
-    if (causal && (int64_t)pb * 128 > (int64_t)m * 128 + 127) continue;   // nothing visible
-    const int P = 128 / level;
-    const unsigned short* Kl = reinterpret_cast<const unsigned short*>(lv.k[li]) + bh * lv.n[li] * D;
-    const unsigned short* Vl = reinterpret_cast<const unsigned short*>(lv.v[li]) + bh * lv.n[li] * D;
-    const int64_t l_k = level == 1 ? seq : s_pad;
-    for (int c0 = 0; c0 < P; c0 += 32) {
-      const int64_t t0 = (int64_t)pb * P + c0;
-      const int64_t n_l = lv.n[li];
-      __syncthreads();   // the previous chunk has been consumed
+  // The selected key blocks form one stream of 32-token chunks; chunk i+1 is copied (cp.async) while chunk i is used.
+  struct Chunk { int pb, c0, level, li; };
+  auto find_chunk = [&](int pb, int c0, Chunk& ch) -> bool {
+    for (; pb < nblk && pb < mask_cols; ++pb, c0 = 0) {
+      const int level = mrow[pb];
+      int li;
+      if (level == 1) li = 0; else if (level == 2) li = 1; else if (level == 4) li = 2; else if (level == 8) li = 3; else continue;
+      if (causal && (int64_t)pb * 128 > (int64_t)m * 128 + 127) continue;   // nothing visible
+      if (c0 >= 128 / level) continue;
+      ch.pb = pb; ch.c0 = c0; ch.level = level; ch.li = li;
+      return true;
+    }
+    return false;
+  };
+  auto issue = [&](const Chunk& ch, int buf) {
+    const int P = 128 / ch.level;
+    const unsigned short* Kl = reinterpret_cast<const unsigned short*>(lv.k[ch.li]) + bh * lv.n[ch.li] * D;
+    const unsigned short* Vl = reinterpret_cast<const unsigned short*>(lv.v[ch.li]) + bh * lv.n[ch.li] * D;
+    const int64_t t0 = (int64_t)ch.pb * P + ch.c0, n_l = lv.n[ch.li];
+    const int c0 = ch.c0;
+    auto tok_ok = [&](int r) { return c0 + r < P && t0 + r < n_l; };
+    stage_rows_async<D>(Ks + buf * 32 * PITCH, Kl + t0 * D, Kl, 32, tok_ok);
+    stage_rows_async<D>(Vs + buf * 32 * PITCH, Vl + t0 * D, Vl, 32, tok_ok);
+  };
+  Chunk cur, nxt;
+  bool has = find_chunk(0, 0, cur);
+  if (has) issue(cur, 0);
+  async_commit();
+  for (int buf = 0; has; buf ^= 1) {
+    const bool has_next = find_chunk(cur.pb, cur.c0 + 32, nxt);
+    async_wait_all();
+    __syncthreads();   // chunk `cur` has landed for everyone, and everyone is done with the other buffer
+    if (has_next) issue(nxt, buf ^ 1);
+    async_commit();
+    {
+      const int level = cur.level, P = 128 / level, c0 = cur.c0;
+      const int64_t l_k = level == 1 ? seq : s_pad;
+      const int64_t t0 = (int64_t)cur.pb * P + c0, n_l = lv.n[cur.li];
       auto tok_ok = [&](int r) { return c0 + r < P && t0 + r < n_l; };
-      stage_rows<D>(Ks, Kl + t0 * D, 32, tok_ok);
-      stage_rows<D>(Vs, Vl + t0 * D, 32, tok_ok);
-      __syncthreads();
+      const unsigned short* Kb = Ks + buf * 32 * PITCH;
+      const unsigned short* Vb = Vs + buf * 32 * PITCH;
+      // CTA-uniform: the chunk holds 32 existing pooled tokens whose original positions all exist and lie before the
+      // first row of this query block (or the call is not causal), and the query block has no missing rows
+      const bool whole = (!causal || cur.pb < m) && c0 + 32 <= P && t0 + 32 <= n_l && (t0 + 32) * level <= l_k &&
+                         (int64_t)m * 128 + 128 <= seq;
       // S = Q K^T and dP = dO V^T for 16 rows x 32 tokens, then ds in the accumulator layout
       uint32_t dsa[2][4];
+      // the eight products (4 token tiles x {S, dP}) advance together: independent accumulators keep the pipe busy
+      float s4[4][4], dp4[4][4];
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt) {
-        float s[4] = {0.f, 0.f, 0.f, 0.f}, dp[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-        for (int k = 0; k < KS; ++k) {
+        for (int e = 0; e < 4; ++e) { s4[nt][e] = 0.f; dp4[nt][e] = 0.f; }
+#pragma unroll
+      for (int k = 0; k < KS; ++k)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
           uint32_t b[2];
-          const unsigned short* kp = Ks + (nt * 8 + g) * PITCH + k * 16 + tig * 2;
+          const unsigned short* kp = Kb + (nt * 8 + g) * PITCH + k * 16 + tig * 2;
           b[0] = *reinterpret_cast<const uint32_t*>(kp);
           b[1] = *reinterpret_cast<const uint32_t*>(kp + 8);
-          MmaOp<T>::run(s, qa[k], b);
-          const unsigned short* vp = Vs + (nt * 8 + g) * PITCH + k * 16 + tig * 2;
+          MmaOp<T>::run(s4[nt], qa[k], b);
+          const unsigned short* vp = Vb + (nt * 8 + g) * PITCH + k * 16 + tig * 2;
           b[0] = *reinterpret_cast<const uint32_t*>(vp);
           b[1] = *reinterpret_cast<const uint32_t*>(vp + 8);
-          MmaOp<T>::run(dp, da[k], b);
+          MmaOp<T>::run(dp4[nt], da[k], b);
         }
-        float val[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int tok = nt * 8 + tig * 2 + (e & 1);
-          const bool hi = e >= 2;
-          const bool rok = hi ? ok1 : ok0;
-          const int cnt = (rok && tok_ok(tok)) ? visible_cnt((t0 + tok) * level, level, l_k, causal != 0, hi ? row1 : row0) : 0;
-          float x = 0.f;
-          if (cnt > 0) {
+      for (int nt = 0; nt < 4; ++nt) {
+        const float(&s)[4] = s4[nt];
+        const float(&dp)[4] = dp4[nt];
+        float val[4];
+        if (whole) {
+          // every copy of every token of the chunk exists and is visible to every row of this query block
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const bool hi = e >= 2;
             const float pij = expf(s[e] * scale - (hi ? lse1 : lse0));
-            x = Elem<T>::round(pij * (dp[e] - (hi ? del1 : del0))) * (float)cnt;
+            val[e] = Elem<T>::round(pij * (dp[e] - (hi ? del1 : del0))) * (float)level;
           }
-          val[e] = x;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int tok = nt * 8 + tig * 2 + (e & 1);
+            const bool hi = e >= 2;
+            const bool rok = hi ? ok1 : ok0;
+            const int cnt = (rok && tok_ok(tok)) ? visible_cnt((t0 + tok) * level, level, l_k, causal != 0, hi ? row1 : row0) : 0;
+            float x = 0.f;
+            if (cnt > 0) {
+              const float pij = expf(s[e] * scale - (hi ? lse1 : lse0));
+              x = Elem<T>::round(pij * (dp[e] - (hi ? del1 : del0))) * (float)cnt;
+            }
+            val[e] = x;
+          }
         }
         // two neighbouring 8-token tiles form the A fragment of one 16-token k-step
         dsa[nt >> 1][(nt & 1) * 2 + 0] = MmaOp<T>::pack(val[0], val[1]);
@@ -166,10 +231,12 @@ __global__ void __launch_bounds__(256) bwd_dq_mma_kernel(const T* __restrict__ q
 #pragma unroll
         for (int n = 0; n < ND; ++n) {
           uint32_t b[2];
-          ldsm_x2_trans(b, Ks + (ks * 16 + (lane & 15)) * PITCH + n * 8);
+          ldsm_x2_trans(b, Kb + (ks * 16 + (lane & 15)) * PITCH + n * 8);
           MmaOp<T>::run(acc[n], dsa[ks], b);
         }
     }
+    cur = nxt;
+    has = has_next;
   }
   unsigned short* o0 = reinterpret_cast<unsigned short*>(dq) + (bh * seq + row0) * D;
   unsigned short* o1 = reinterpret_cast<unsigned short*>(dq) + (bh * seq + row1) * D;
@@ -192,9 +259,10 @@ __global__ void __launch_bounds__(256) bwd_dkdv_mma_kernel(const T* __restrict__
   float(*dVs)[D] = dKs + 128;
   unsigned short* Kls = reinterpret_cast<unsigned short*>(dVs + 128);   // [128][PITCH] pooled K of the current level
   unsigned short* Vls = Kls + 128 * PITCH;
-  unsigned short* Qs = Vls + 128 * PITCH;                                // [32][PITCH] staged query rows
-  unsigned short* Ds = Qs + 32 * PITCH;                                  // [32][PITCH] staged dO rows
-  float* Ls = reinterpret_cast<float*>(Ds + 32 * PITCH);                 // [32] lse, [32] delta
+  constexpr int RC = 16;                                                 // query rows per staged chunk
+  unsigned short* Qs = Vls + 128 * PITCH;                                // [2 buffers][RC][PITCH] staged query rows
+  unsigned short* Ds = Qs + 2 * RC * PITCH;                              // [2 buffers][RC][PITCH] staged dO rows
+  float* Ls = reinterpret_cast<float*>(Ds + 2 * RC * PITCH);             // [2 buffers]: [RC] lse, [RC] delta
   const int pb = blockIdx.x;
   const int64_t bh = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
@@ -225,61 +293,130 @@ __global__ void __launch_bounds__(256) bwd_dkdv_mma_kernel(const T* __restrict__
 #pragma unroll
       for (int e = 0; e < 4; ++e) { aK[n][e] = 0.f; aV[n][e] = 0.f; }
 
-    for (int mm = 0; mm < mq; ++mm) {
-      if (mcol[(int64_t)mm * mask_cols] != level) continue;
-      if (causal && (int64_t)mm * 128 + 127 < (int64_t)pb * 128) continue;
-      for (int r0 = 0; r0 < 128; r0 += 32) {
-        const int64_t row0 = (int64_t)mm * 128 + r0;
-        if (row0 >= seq) break;
-        __syncthreads();   // previous rows consumed (and, first time, the level's K/V staged)
+    // The query rows of every block that selected this level form one stream of RC-row chunks; chunk i+1 is copied
+    // (cp.async) while chunk i is used.
+    struct RowChunk { int mm, r0; };
+    auto find_rows = [&](int mm, int r0, RowChunk& c) -> bool {
+      for (; mm < mq; ++mm, r0 = 0) {
+        if (mcol[(int64_t)mm * mask_cols] != level) continue;
+        if (causal && (int64_t)mm * 128 + 127 < (int64_t)pb * 128) continue;
+        if (r0 >= 128 || (int64_t)mm * 128 + r0 >= seq) continue;
+        c.mm = mm; c.r0 = r0;
+        return true;
+      }
+      return false;
+    };
+    auto issue = [&](const RowChunk& c, int buf) {
+      const int64_t row0 = (int64_t)c.mm * 128 + c.r0;
+      auto row_ok = [&](int r) { return row0 + r < seq; };
+      stage_rows_async<D>(Qs + buf * RC * PITCH, qg + row0 * D, qg, RC, row_ok);
+      stage_rows_async<D>(Ds + buf * RC * PITCH, dg + row0 * D, dg, RC, row_ok);
+      if (threadIdx.x < RC) {
+        const bool ok = row0 + threadIdx.x < seq;
+        Ls[buf * 2 * RC + threadIdx.x] = ok ? lse[bh * seq + row0 + threadIdx.x] : INFINITY;   // exp(-inf) = 0 for missing rows
+        Ls[buf * 2 * RC + RC + threadIdx.x] = ok ? delta[bh * seq + row0 + threadIdx.x] : 0.f;
+      }
+    };
+    RowChunk cur, nxt;
+    bool has = find_rows(0, 0, cur);
+    if (has) issue(cur, 0);
+    async_commit();
+    for (int buf = 0; has; buf ^= 1) {
+      const bool has_next = find_rows(cur.mm, cur.r0 + RC, nxt);
+      async_wait_all();
+      __syncthreads();   // chunk `cur` (and, first time, the level's K/V) is in place; the other buffer is free
+      if (has_next) issue(nxt, buf ^ 1);
+      async_commit();
+      if (active) {
+        const int64_t row0 = (int64_t)cur.mm * 128 + cur.r0;
         auto row_ok = [&](int r) { return row0 + r < seq; };
-        stage_rows<D>(Qs, qg + row0 * D, 32, row_ok);
-        stage_rows<D>(Ds, dg + row0 * D, 32, row_ok);
-        if (threadIdx.x < 32) {
-          const bool ok = row0 + threadIdx.x < seq;
-          Ls[threadIdx.x] = ok ? lse[bh * seq + row0 + threadIdx.x] : INFINITY;   // exp(-inf) = 0 for missing rows
-          Ls[32 + threadIdx.x] = ok ? delta[bh * seq + row0 + threadIdx.x] : 0.f;
+        const unsigned short* Qb = Qs + buf * RC * PITCH;
+        const unsigned short* Db = Ds + buf * RC * PITCH;
+        const float* Lb = Ls + buf * 2 * RC;
+        // CTA-uniform: the key block is complete (no padded positions) and lies before the query block (or the call is
+        // not causal), and the chunk has no missing rows
+        const bool whole = (!causal || cur.mm > pb) && (int64_t)pb * 128 + 128 <= seq && row0 + RC <= seq;
+        // S^T = K Q^T and dP^T = V dO^T for 16 tokens x RC query rows
+        uint32_t pa[RC / 16][4], dsa[RC / 16][4];
+        float s2[RC / 8][4], dp2[RC / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < RC / 8; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { s2[nt][e] = 0.f; dp2[nt][e] = 0.f; }
+#pragma unroll
+        for (int k0 = 0; k0 < D; k0 += 16) {
+          uint32_t ak[4], av[4];
+          const unsigned short* kp = Kls + tk0 * PITCH + k0 + tig * 2;
+          const unsigned short* vp = Vls + tk0 * PITCH + k0 + tig * 2;
+          ak[0] = *reinterpret_cast<const uint32_t*>(kp);
+          ak[1] = *reinterpret_cast<const uint32_t*>(kp + 8 * PITCH);
+          ak[2] = *reinterpret_cast<const uint32_t*>(kp + 8);
+          ak[3] = *reinterpret_cast<const uint32_t*>(kp + 8 * PITCH + 8);
+          av[0] = *reinterpret_cast<const uint32_t*>(vp);
+          av[1] = *reinterpret_cast<const uint32_t*>(vp + 8 * PITCH);
+          av[2] = *reinterpret_cast<const uint32_t*>(vp + 8);
+          av[3] = *reinterpret_cast<const uint32_t*>(vp + 8 * PITCH + 8);
+#pragma unroll
+          for (int nt = 0; nt < RC / 8; ++nt) {
+            uint32_t b[2];
+            const unsigned short* qp = Qb + (nt * 8 + g) * PITCH + k0 + tig * 2;
+            b[0] = *reinterpret_cast<const uint32_t*>(qp);
+            b[1] = *reinterpret_cast<const uint32_t*>(qp + 8);
+            MmaOp<T>::run(s2[nt], ak, b);
+            const unsigned short* dp_ = Db + (nt * 8 + g) * PITCH + k0 + tig * 2;
+            b[0] = *reinterpret_cast<const uint32_t*>(dp_);
+            b[1] = *reinterpret_cast<const uint32_t*>(dp_ + 8);
+            MmaOp<T>::run(dp2[nt], av, b);
+          }
         }
-        __syncthreads();
-        if (!active) continue;
-        // S^T = K Q^T and dP^T = V dO^T for 16 tokens x 32 query rows
-        uint32_t pa[2][4], dsa[2][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-          float s[4] = {0.f, 0.f, 0.f, 0.f}, dp[4] = {0.f, 0.f, 0.f, 0.f};
-          dot_rows<T, D>(s, Kls + tk0 * PITCH, Qs + (nt * 8 + g) * PITCH, tig);
-          dot_rows<T, D>(dp, Vls + tk0 * PITCH, Ds + (nt * 8 + g) * PITCH, tig);
+        for (int nt = 0; nt < RC / 8; ++nt) {
+          const float(&s)[4] = s2[nt];
+          const float(&dp)[4] = dp2[nt];
           float pv[4], dv_[4];
+          if (whole) {
+            // all copies of the block's tokens exist and are visible to all rows of the chunk
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int r = nt * 8 + tig * 2 + (e & 1);       // query row inside the chunk
-            const int tk = e >= 2 ? tk1 : tk0;
-            const int cnt = (tok_ok(tk) && row_ok(r)) ? visible_cnt((t0 + tk) * level, level, l_k, causal != 0, row0 + r) : 0;
-            float x = 0.f, y = 0.f;
-            if (cnt > 0) {
-              const float pij = expf(s[e] * scale - Ls[r]);
-              x = Elem<T>::round(pij) * (float)cnt;
-              y = Elem<T>::round(pij * (dp[e] - Ls[32 + r])) * (float)cnt;
+            for (int e = 0; e < 4; ++e) {
+              const int r = nt * 8 + tig * 2 + (e & 1);
+              const float pij = expf(s[e] * scale - Lb[r]);
+              pv[e] = Elem<T>::round(pij) * (float)level;
+              dv_[e] = Elem<T>::round(pij * (dp[e] - Lb[RC + r])) * (float)level;
             }
-            pv[e] = x; dv_[e] = y;
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int r = nt * 8 + tig * 2 + (e & 1);       // query row inside the chunk
+              const int tk = e >= 2 ? tk1 : tk0;
+              const int cnt = (tok_ok(tk) && row_ok(r)) ? visible_cnt((t0 + tk) * level, level, l_k, causal != 0, row0 + r) : 0;
+              float x = 0.f, y = 0.f;
+              if (cnt > 0) {
+                const float pij = expf(s[e] * scale - Lb[r]);
+                x = Elem<T>::round(pij) * (float)cnt;
+                y = Elem<T>::round(pij * (dp[e] - Lb[RC + r])) * (float)cnt;
+              }
+              pv[e] = x; dv_[e] = y;
+            }
           }
           pa[nt >> 1][(nt & 1) * 2 + 0] = MmaOp<T>::pack(pv[0], pv[1]);
           pa[nt >> 1][(nt & 1) * 2 + 1] = MmaOp<T>::pack(pv[2], pv[3]);
           dsa[nt >> 1][(nt & 1) * 2 + 0] = MmaOp<T>::pack(dv_[0], dv_[1]);
           dsa[nt >> 1][(nt & 1) * 2 + 1] = MmaOp<T>::pack(dv_[2], dv_[3]);
         }
-        // dV_l += p^T dO,  dK_l += ds^T Q  (k = the 32 query rows)
+        // dV_l += p^T dO,  dK_l += ds^T Q  (k = the RC query rows)
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks)
+        for (int ks = 0; ks < RC / 16; ++ks)
 #pragma unroll
           for (int n = 0; n < ND; ++n) {
             uint32_t b[2];
-            ldsm_x2_trans(b, Ds + (ks * 16 + (lane & 15)) * PITCH + n * 8);
+            ldsm_x2_trans(b, Db + (ks * 16 + (lane & 15)) * PITCH + n * 8);
             MmaOp<T>::run(aV[n], pa[ks], b);
-            ldsm_x2_trans(b, Qs + (ks * 16 + (lane & 15)) * PITCH + n * 8);
+            ldsm_x2_trans(b, Qb + (ks * 16 + (lane & 15)) * PITCH + n * 8);
             MmaOp<T>::run(aK[n], dsa[ks], b);
           }
       }
+      cur = nxt;
+      has = has_next;
     }
     // spread the pooled tokens' gradients over their l original positions (mean-pool backward)
     __syncthreads();
@@ -349,7 +486,7 @@ int launch_bwd_mma(const void* q, const BwdLv& lv, const int32_t* mask, const vo
   PSA_CHECK_LAUNCH("psa_legacy_bwd_tc(delta)");
   dim3 grid(mq, (unsigned)bh);
   {
-    const size_t smem = (size_t)2 * 32 * PITCH * 2;
+    const size_t smem = (size_t)2 * 2 * 32 * PITCH * 2;
     bwd_dq_mma_kernel<T, D><<<grid, 256, smem, st>>>((const T*)q, lv, mask, lse, delta, (const T*)dout, (T*)dq, seq, mask_cols, mq,
                                                       scale, causal);
     PSA_CHECK_LAUNCH("psa_legacy_bwd_tc(dq)");
