@@ -263,6 +263,7 @@ __global__ void __launch_bounds__(256) bwd_dkdv_mma_kernel(const T* __restrict__
   unsigned short* Qs = Vls + 128 * PITCH;                                // [2 buffers][RC][PITCH] staged query rows
   unsigned short* Ds = Qs + 2 * RC * PITCH;                              // [2 buffers][RC][PITCH] staged dO rows
   float* Ls = reinterpret_cast<float*>(Ds + 2 * RC * PITCH);             // [2 buffers]: [RC] lse, [RC] delta
+  unsigned char* flags = reinterpret_cast<unsigned char*>(Ls + 4 * RC);  // [mq] query blocks that use the current level
   const int pb = blockIdx.x;
   const int64_t bh = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
@@ -274,8 +275,13 @@ __global__ void __launch_bounds__(256) bwd_dkdv_mma_kernel(const T* __restrict__
 
   for (int li = 0; li < 4; ++li) {
     const int level = 1 << li, P = 128 / level;
+    // which query blocks selected this level for this key block (one pass over the mask column, kept in shared memory)
     int any = 0;
-    for (int mm = threadIdx.x; mm < mq; mm += blockDim.x) any |= (mcol[(int64_t)mm * mask_cols] == level);
+    for (int mm = threadIdx.x; mm < mq; mm += blockDim.x) {
+      const bool f = mcol[(int64_t)mm * mask_cols] == level && !(causal && (int64_t)mm * 128 + 127 < (int64_t)pb * 128);
+      flags[mm] = f ? 1 : 0;
+      any |= f ? 1 : 0;
+    }
     any = __syncthreads_or(any);
     if (!any) continue;
     const unsigned short* Kl = reinterpret_cast<const unsigned short*>(lv.k[li]) + bh * lv.n[li] * D;
@@ -298,8 +304,7 @@ __global__ void __launch_bounds__(256) bwd_dkdv_mma_kernel(const T* __restrict__
     struct RowChunk { int mm, r0; };
     auto find_rows = [&](int mm, int r0, RowChunk& c) -> bool {
       for (; mm < mq; ++mm, r0 = 0) {
-        if (mcol[(int64_t)mm * mask_cols] != level) continue;
-        if (causal && (int64_t)mm * 128 + 127 < (int64_t)pb * 128) continue;
+        if (!flags[mm]) continue;
         if (r0 >= 128 || (int64_t)mm * 128 + r0 >= seq) continue;
         c.mm = mm; c.r0 = r0;
         return true;
@@ -492,7 +497,9 @@ int launch_bwd_mma(const void* q, const BwdLv& lv, const int32_t* mask, const vo
     PSA_CHECK_LAUNCH("psa_legacy_bwd_tc(dq)");
   }
   {
-    const size_t smem = (size_t)2 * 128 * D * sizeof(float) + (size_t)(2 * 128 + 2 * 32) * PITCH * 2 + 64 * sizeof(float);
+    const size_t smem = (size_t)2 * 128 * D * sizeof(float) + (size_t)(2 * 128 + 2 * 32) * PITCH * 2 + 64 * sizeof(float) +
+                        (((size_t)mq + 15) & ~(size_t)15);
+    PSA_REQUIRE(smem <= 227 * 1024, PSA_ERR_UNSUPPORTED, "psa_legacy_bwd_tc: %d query blocks exceed the kernel's shared memory", mq);
     cudaError_t e = cudaFuncSetAttribute(bwd_dkdv_mma_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     PSA_REQUIRE(e == cudaSuccess, PSA_ERR_CUDA, "psa_legacy_bwd_tc: smem opt-in failed: %s", cudaGetErrorString(e));
     bwd_dkdv_mma_kernel<T, D><<<grid, 256, smem, st>>>((const T*)q, lv, mask, lse, delta, (const T*)dout, (T*)dk, (T*)dv, seq,
