@@ -66,6 +66,28 @@ class SparsityLog:
     def close(self):
         pass
 
+    def write_jsonl(self, path: str) -> int:
+        """One line per forward with the keys of PSALogger's sparsity.jsonl (src/psa_triton/utils/psa_logger.py:265-283,
+        minus the timestamp and the similarity statistics).  The per-(batch, head) densities were computed on the device
+        by psa_density during the run; they are brought to the host here in ONE copy, so logging costs no
+        synchronisation per layer call.  Returns the number of lines written."""
+        import json
+        import os
+        dens = [r["density"].float().mean(dim=0).reshape(-1) for r in self.records if r.get("density") is not None]
+        host = torch.stack(dens).cpu().tolist() if dens else []
+        os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+        it = iter(host)
+        with open(path, "w") as f:
+            for step, r in enumerate(self.records):
+                per_head = next(it) if r.get("density") is not None else []
+                density = sum(per_head) / len(per_head) if per_head else 1.0
+                f.write(json.dumps({
+                    "global_step": step, "layer_idx": r.get("layer_idx"), "sparsity": round(1.0 - density, 6),
+                    "density": round(density, 6), "per_head_density": [round(d, 6) for d in per_head],
+                    "sequence_length": r.get("sequence_length"), "batch_size": r.get("batch_size"),
+                    "num_heads": r.get("num_heads"), "is_warmup": bool(r.get("is_warmup", False))}) + "\n")
+        return len(self.records)
+
     def summary(self) -> dict:
         dens = [float(r["density"].mean().item()) for r in self.records if r.get("density") is not None]
         return {"calls": len(self.records), "sparse_calls": len(dens),
@@ -173,6 +195,10 @@ class PyramidSparseAttention(nn.Module):
                                      num_heads=q.shape[1], is_warmup=is_warmup)
         return self.gilbert_rearranger.reversed_rearrange(out_r) if self.use_rearrange else out_r
 
-    def close_logger(self):
+    def close_logger(self, jsonl_path: str = None):
+        """Reference name (pyramid_sparse_attention.py:408-413).  jsonl_path: also write the per-call records there
+        (SparsityLog.write_jsonl); nothing is written to disk otherwise."""
         if self.logger is not None:
+            if jsonl_path is not None:
+                self.logger.write_jsonl(jsonl_path)
             self.logger.close()

@@ -128,3 +128,19 @@ def test_topk_intervals_host_arithmetic_equals_oracle():
                 for newtype in (True, False):
                     mine = [(l, s, e) for l, s, e in topk_intervals(nk, ratios, bn, 32, newtype) if newtype or s < e]
                     assert mine == O.topk_intervals(nk, ratios, bn, 32, newtype)
+
+
+def test_sparsity_log_writes_jsonl(tmp_path):
+    """The per-call records (densities as tensors, None for warm-up calls) become one JSON line each."""
+    import json
+    from psa_b200.pyramid_sparse_attention import SparsityLog
+    log = SparsityLog()
+    log.log_sparsity(layer_idx=0, density=None, sequence_length=640, batch_size=1, num_heads=2, is_warmup=True)
+    log.log_sparsity(layer_idx=1, density=torch.tensor([[0.25, 0.75]]), sequence_length=640, batch_size=1, num_heads=2,
+                     is_warmup=False)
+    path = tmp_path / "logs" / "sparsity.jsonl"
+    assert log.write_jsonl(str(path)) == 2
+    lines = [json.loads(x) for x in path.read_text().splitlines()]
+    assert lines[0]["is_warmup"] and lines[0]["per_head_density"] == [] and lines[0]["density"] == 1.0
+    assert lines[1]["per_head_density"] == [0.25, 0.75] and lines[1]["density"] == 0.5 and lines[1]["sparsity"] == 0.5
+    assert lines[1]["global_step"] == 1 and lines[1]["layer_idx"] == 1
