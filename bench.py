@@ -38,6 +38,44 @@ BLOCK_M, BLOCK_N, TILE_N = 128, 64, 32
 CPU_SAMPLE_TOKENS = 32768
 
 
+# kernels of this library launched by one call of each entry point the benchmark uses (memsets and torch's own
+# kernels are not counted)
+KERNELS_PER_CALL = {
+    "psa_pyramid_kv_images": 1, "psa_pyramid_kv": 1, "psa_block_scores": 4, "psa_block_scores_samples": 2,
+    "psa_assign_levels": 1, "psa_fwd_images": 1, "psa_fwd": 1, "psa_fwd_images_scatter": 1, "psa_push_heads": 1,
+    "psa_push_samples": 1, "psa_pull_heads": 1, "psa_density": 1, "psa_legacy_fwd_images": 2, "psa_legacy_bwd_tc": 3,
+    "psa_legacy_bwd_tcgen05": 5,
+}
+
+
+class LaunchCounter:
+    """Counts this library's kernel launches by wrapping the C-ABI entry points (calls x kernels per call)."""
+
+    def __init__(self, lib):
+        self.lib, self.count, self.on, self.orig = lib, 0, False, {}
+        for name, per_call in KERNELS_PER_CALL.items():
+            fn = getattr(lib, name, None)
+            if fn is None:
+                continue
+            self.orig[name] = fn
+            setattr(lib, name, self._wrap(fn, per_call))
+
+    def _wrap(self, fn, per_call):
+        def call(*a):
+            if self.on:
+                self.count += per_call
+            return fn(*a)
+        return call
+
+
+# DRAM read+write bytes of one forward launch per (head x token), from ncu captures of psa_fwd_tc_kernel at the named
+# shape with a reduced head count (profiles/); the figure is about the unique bytes of Q, O and the K/V images, so it
+# scales with heads x tokens.
+FWD_TRAFFIC_PER_HEAD_TOKEN = {
+    "wan2.1-1.3b-attn-layer": (1539.0, "profiles/psa_fwd_tc_kernel__wan2.1-1.3b-shape_6heads.md"),
+}
+
+
 def load_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -109,11 +147,30 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
+def load_synthetic():
+    """The input generator, loaded by file so that the CPU arms never import the package (whose __init__ opens the CUDA
+    library)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "psa_synthetic_inputs", os.path.join(ROOT, "pyramid-sparse-attention_b200", "psa_b200", "synthetic.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def use_all_host_threads() -> int:
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the CPU arm uses every core it is given."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def oracle_sample_time(workload, ratios, steps, warmup):
     """Time the CPU restatement of the same layer on a bounded sample (head 0, first CPU_SAMPLE_TOKENS tokens).
     Returns (dense-equivalent TFLOP/s, seconds per call, description)."""
     from oracle import psa_oracle as O
-    from psa_b200 import synthetic
+    synthetic = load_synthetic()
+    use_all_host_threads()
     S = min(synthetic.seq_len(workload), CPU_SAMPLE_TOKENS)
     D = workload["head_dim"]
     q, k, v = synthetic.make_qkv(workload, 1000, torch.float32, "cpu", head_range=(0, 1), token_range=(0, S))
@@ -130,6 +187,40 @@ def oracle_sample_time(workload, ratios, steps, warmup):
     return f_dense / sec / 1e12, sec, f"head 0 of {workload['heads']}, first {S} tokens, fp32 inputs, fp64 softmax"
 
 
+def oracle_legacy_sample_time(workload, steps, warmup, tokens=4096):
+    """CPU restatement of the causal legacy forward + backward on a bounded sample: (batch 0, head 0), first `tokens`
+    tokens.  Returns (dense-equivalent TFLOP/s of forward+backward, seconds per call, description)."""
+    from oracle import psa_oracle as O
+    synthetic = load_synthetic()
+    use_all_host_threads()
+    S, D = min(synthetic.seq_len(workload), tokens), workload["head_dim"]
+    q, k, v = synthetic.make_qkv(workload, 1000, torch.float32, "cpu", head_range=(0, 1), token_range=(0, S))
+    do = torch.randn(q.shape, generator=torch.Generator().manual_seed(5))
+    mask = legacy_level_mask(77, 1, 1, S)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        o, lse = O.legacy_forward(q, k, v, mask, causal=True)
+        O.legacy_backward(q, k, v, mask, o, lse, do, causal=True)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    return 3.5 * 2.0 * S * S * D / sec / 1e12, sec, f"batch 0, head 0, first {S} tokens, fp32 inputs, fp64 math"
+
+
+def legacy_level_mask(seed, B, H, S):
+    """Random causal old-format mask [B, H, S/128, S/128] in {0,1,2,4,8} (p = 0.2/0.3/0.2/0.15/0.15), column 0 at level 1
+    so that no row is empty.  Mean token density ~0.46 of the causal triangle."""
+    import numpy as np
+    n = -(-S // 128)
+    rng = np.random.default_rng(seed)
+    m = rng.choice(np.array([0, 1, 2, 4, 8], dtype=np.int32), size=(B, H, n, n), p=[0.2, 0.3, 0.2, 0.15, 0.15])
+    m[..., 0] = 1
+    m = m * np.tril(np.ones((n, n), dtype=np.int32))
+    return torch.from_numpy(m.astype(np.int32))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -140,7 +231,7 @@ def main():
     ap.add_argument("--sparsity", default="90", choices=["90", "85"])
     ap.add_argument("--chunks", type=int, default=5, help="head chunks per rank for exchange/compute overlap (N>1)")
     ap.add_argument("--pull-blocks", type=int, default=48,
-                    help="grid cap of the full-row push that runs under the score kernels (8 GPUs: 48 -> 2.97 ms, 148 -> 3.10, 296 -> 3.14)")
+                    help="grid cap of the full-row push that runs under the score kernels")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "p2p-push", "p2p-pull", "nccl"],
                     help="N>1: our kernels over peer memory - sampled rows pushed first, full rows under the scores (p2p), all "
                          "rows pushed before the layer (p2p-push) or pulled by the head owners (p2p-pull), "
@@ -151,7 +242,7 @@ def main():
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
-    from psa_b200 import synthetic
+    synthetic = load_synthetic()
     workload = dict(synthetic.WORKLOADS[args.workload])
     if args.heads:
         workload["heads"] = args.heads
@@ -184,14 +275,21 @@ def main():
     # ------------------------------------------------------------------ our arm
     import torch.distributed as dist
     import psa_b200
-    from psa_b200 import ops
+    from psa_b200 import ops, _lib
+    launches = LaunchCounter(_lib.lib)
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-        assert H % world == 0 and S % world == 0, "heads and tokens must divide by the number of GPUs"
-    hp = H // world
-    h0 = rank * hp
+        assert S % world == 0, "tokens must divide by the number of GPUs"
+    from psa_b200.parallel import GridShard, HeadShard, PeerExchange
+    # heads that do not divide over the ranks (12 heads on 8 GPUs): head groups x query-block ranges, NCCL reshuffle
+    grid = GridShard(world, rank, H, S, D, BLOCK_M) if (world > 1 and H % world != 0) else None
+    if grid is not None:
+        args.exchange = "nccl"
+    hp = grid.heads_per_rank if grid is not None else H // world
+    h0 = grid.head_range()[0] if grid is not None else rank * hp
+    q_rows = grid.query_range() if grid is not None else (0, S)
     dtype = torch.bfloat16
     cfg = psa_b200.PSAConfig(block_m=BLOCK_M, block_n=BLOCK_N, tile_n=TILE_N, mask_ratios=ratios, mask_mode="topk")
 
@@ -226,9 +324,7 @@ def main():
         ik = ops.draw_sample_indices(1, H, BLOCK_N, BLOCK_N // 4, dev)[:, h0:h0 + hp]
         return iq.contiguous(), ik.contiguous()
 
-    from psa_b200.parallel import HeadShard, PeerExchange
-    shard = HeadShard(world, rank, H, S, D)
-    to_head_sharded, to_seq_sharded = shard.to_head_sharded, shard.to_seq_sharded
+    shard = HeadShard(world, rank, H, S, D) if grid is None else None
     peer = None
     if world > 1 and args.exchange != "nccl":
         peer = PeerExchange(H, S, D, dtype, dev)
@@ -242,7 +338,7 @@ def main():
     stage_names = ["a2a_in", "sample", "pyramid", "scores", "assign", "forward", "a2a_out"]
 
     comm_stream = torch.cuda.Stream(device=dev, priority=-1) if world > 1 else None
-    chunk_list = shard.chunks(args.chunks) if world > 1 else [(0, hp)]
+    chunk_list = shard.chunks(args.chunks) if (world > 1 and grid is None) else [(0, hp)]
 
     def timed(name, fn, rec, stream=None):
         """Run fn; when rec is a list, bracket it with CUDA events on the stream its kernels are launched on."""
@@ -273,6 +369,11 @@ def main():
         if world == 1:
             out, mask = layer_on(q, k, v, iq, ik, rec)
             return out, mask, out
+        if grid is not None:
+            qp, kk, vv = timed("a2a_in", lambda: grid.to_grid(seq_shard), rec)
+            out, mask = layer_on(qp.unsqueeze(0), kk.unsqueeze(0), vv.unsqueeze(0), iq, ik, rec)
+            out_final = timed("a2a_out", lambda: grid.to_seq(out[0]), rec)
+            return out_final, mask, out
         cur = torch.cuda.current_stream(dev)
         out_final = torch.empty((H, S // world, D), dtype=dtype, device=dev)
         comm_stream.wait_stream(cur)
@@ -305,7 +406,7 @@ def main():
     pull_buf = None
     step_no = 0
 
-    def layer_step_p2p(rec, cur):
+    def layer_step_p2p(rec, cur, v_ready=None):
         """N > 1 without a collective: q/k/v rows travel by our own copy kernel over peer memory (pushed by the token owners,
         or pulled by the head owners), the forward stores its output rows into the token owners' buffers, and the only
         cross-rank synchronisation is one barrier per step."""
@@ -322,6 +423,8 @@ def main():
             fence()
             comm_stream.wait_stream(cur)
             with torch.cuda.stream(comm_stream):
+                if v_ready is not None:
+                    comm_stream.wait_event(v_ready)          # end-to-end run: v is still on its way from the host
                 x = timed("a2a_in", lambda: peer.push(par, max_blocks=args.pull_blocks), rec, comm_stream)
                 fence()
                 e_side = ev(); e_side.record(comm_stream)
@@ -331,6 +434,8 @@ def main():
             qq, kk, vv = x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0)
         else:
             iq, ik = timed("sample", draw_indices, rec)            # data-independent: before the exchange
+            if v_ready is not None:
+                cur.wait_event(v_ready)
             if args.exchange == "p2p-push":
                 x = timed("a2a_in", lambda: peer.push(par), rec)
                 fence()
@@ -368,8 +473,10 @@ def main():
     e0, e1 = ev(), ev()
     torch.cuda.profiler.start()          # lets `ncu --profile-from-start off` see the timed region only
     e0.record()
+    launches.on = True
     for _ in range(args.steps):
-        layer_step(records)
+        out_final, mask, out = layer_step(records)
+    launches.on = False
     e1.record()
     barrier()
     torch.cuda.profiler.stop()
@@ -384,6 +491,27 @@ def main():
     for name, a, b in records:
         stage_ms[name] += a.elapsed_time(b) / args.steps
 
+    # ------------------------------------------------------------------ N > 1: one head of this rank against one GPU
+    parity = None
+    if world > 1:
+        # outside the timed region: the rank recomputes its first head from the same seeded inputs on its own GPU with the
+        # single-GPU calls, and compares with what the sharded step left for its tokens (same kernels, same sample
+        # offsets: the rows must be bit-identical)
+        launches.on = False
+        q1, k1, v1 = synthetic.make_qkv(workload, 1000, dtype, dev, head_range=(h0, h0 + 1))
+        iq_all, ik_all = draw_indices_all()
+        o1, _ = layer_on(q1, k1, v1, iq_all[:, h0:h0 + 1].contiguous(), ik_all[:, h0:h0 + 1].contiguous(), None)
+        sl = S // world
+        mine = o1[0, 0, rank * sl:(rank + 1) * sl]
+        got = peer.o[:, h0] if peer is not None else out_final[h0]
+        diff = (got.float() - mine.float()).abs()
+        worst = torch.tensor([float(diff.max()), float((diff != 0).sum())], device=dev, dtype=torch.float64)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        parity = {"what": "first head of every rank: sharded step vs single-GPU calls on the same inputs, this rank's tokens",
+                  "max_abs_diff": float(worst[0].item()), "rows_differing_max_over_ranks": int(worst[1].item()),
+                  "bit_identical": bool(worst[0].item() == 0.0)}
+        del q1, k1, v1, o1
+
     # ------------------------------------------------------------------ end to end: host buffers in, O back out
     e2e = None
     if not args.no_e2e:
@@ -393,13 +521,21 @@ def main():
             hx = seq_shard.cpu().pin_memory()
         module = psa_b200.PSAAttention(cfg)
         h_out = None
+        copy_stream = torch.cuda.Stream(device=dev) if world > 1 else None
 
         def e2e_step():
             nonlocal h_out
+            cur = torch.cuda.current_stream(dev)
             if peer is not None:
-                peer.q.copy_(hx[0], non_blocking=True); peer.k.copy_(hx[1], non_blocking=True); peer.v.copy_(hx[2], non_blocking=True)
-                layer_step()                      # barrier, pull from peers, compute, scatter into the owners' o buffers
-                dist.barrier()                    # every rank's forward has finished: this rank's o is complete
+                # q and k first (the sampled rows leave as soon as they are here); v follows on a side stream under the
+                # sample push and the scores.  No host-side wait anywhere: the ranks are ordered by stream-ordered fences.
+                peer.q.copy_(hx[0], non_blocking=True); peer.k.copy_(hx[1], non_blocking=True)
+                copy_stream.wait_stream(cur)
+                with torch.cuda.stream(copy_stream):
+                    peer.v.copy_(hx[2], non_blocking=True)
+                    v_here = ev(); v_here.record(copy_stream)
+                layer_step_p2p(None, cur, v_ready=v_here)
+                fence()                           # every rank's forward has stored its rows: this rank's o is complete
                 if h_out is None:
                     h_out = torch.empty(peer.o.shape, dtype=peer.o.dtype).pin_memory()
                 h_out.copy_(peer.o, non_blocking=True)
@@ -409,13 +545,14 @@ def main():
                 iq, ik = draw_indices()
                 h_out = psa_b200.psa_attention_host(hq, hk, hv, cfg, out=h_out, device=dev, idx_q=iq, idx_k=ik)
                 return
-            else:
-                x = to_head_sharded(hx.to(dev, non_blocking=True))
-                dq, dk, dv = x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0)
             iq, ik = draw_indices()
-            o = module(dq, dk, dv, idx_q=iq, idx_k=ik)
-            if world > 1:
-                o = to_seq_sharded(o[0])
+            xd = hx.to(dev, non_blocking=True)
+            if grid is not None:
+                qp, kk, vv = grid.to_grid(xd)
+                o = grid.to_seq(module(qp.unsqueeze(0), kk.unsqueeze(0), vv.unsqueeze(0), idx_q=iq, idx_k=ik)[0])
+            else:
+                x = shard.to_head_sharded(xd)
+                o = shard.to_seq_sharded(module(x[0].unsqueeze(0), x[1].unsqueeze(0), x[2].unsqueeze(0), idx_q=iq, idx_k=ik)[0])
             if h_out is None:
                 h_out = torch.empty(o.shape, dtype=o.dtype).pin_memory()
             h_out.copy_(o, non_blocking=True)
@@ -436,7 +573,9 @@ def main():
         per_rank_in = 3 * (S // world) * H * D * esz
         per_rank_out = (S // world) * H * D * esz
         e2e = {"value": f_dense / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": per_rank_in * world, "d2h_bytes_per_step": per_rank_out * world}
+               "h2d_bytes_per_step": per_rank_in * world, "d2h_bytes_per_step": per_rank_out * world,
+               # what the host link of one rank sustained if the whole step were copies (a lower bound on its speed)
+               "per_rank_host_link_gbs_lower_bound": (per_rank_in + per_rank_out) / (ms_e2e * 1e-3) / 1e9}
 
     if peer is not None:
         barrier()
@@ -448,33 +587,39 @@ def main():
 
     peaks = load_peaks()
     # dominant kernel: the tcgen05 forward.  Algorithmic FLOPs per launch = 4*hp*S^2*D*density (surviving blocks).
-    f_surv_launch = 4.0 * hp * float(S) * S * D * dens
+    f_surv_launch = 4.0 * hp * float(q_rows[1] - q_rows[0]) * S * D * dens
     fwd_tflops = f_surv_launch / (stage_ms["forward"] * 1e-3) / 1e12
     peak_tf = peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]
     n_elem = hp * S * D
+    per_ht = FWD_TRAFFIC_PER_HEAD_TOKEN.get(synthetic.WORKLOADS[args.workload]["name"])
+    traffic = per_ht[0] * hp * S if per_ht else None
+    traffic_source = (f"{per_ht[1]}: ncu dram bytes of one launch at this shape with fewer heads, scaled by heads"
+                      if per_ht else "no capture at this shape")
     line = {
         "metric": "psa_attn_dense_equiv_tflops", "value": f_dense / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg_json,
         "ms_per_layer": ms_step, "stage_ms": stage_ms, "density": dens, "sparsity": 1.0 - dens,
         "surviving_tflops_forward": fwd_tflops, "kernel_status": status,
-        # own kernels per chunk: pyramid images, 2 sample gathers, score GEMM, pool+normalise, level assignment, forward
-        # (+ 3 peer pulls per chunk when the exchange is ours)
-        "gpu_launches": args.steps * (10 if peer is not None else 7 * len(chunk_list)),
+        # this library's kernels launched by this rank inside the timed region, counted at the C-ABI boundary
+        "gpu_launches": launches.count,
         "exchange": (args.exchange if world > 1 else None),
         "roofline": {"bound": "tensor", "kernel": "psa_fwd_tc_kernel", "achieved": fwd_tflops, "peak": peak_tf,
                      "unit": "TFLOP/s", "frac": fwd_tflops / peak_tf,
-                     # dram read+write of one forward launch: ncu-measured 1539 B per (head x token) on the 6-head
-                     # Wan2.1-1.3B-shape capture (every byte of Q, O and the K/V images crosses HBM about once, so
-                     # the figure scales with heads x tokens)
-                     "traffic": 1539.0 * hp * S, "traffic_unit": "bytes per launch",
-                     "traffic_source": "profiles/psa_fwd_tc_kernel__wan2.1-1.3b-shape_6heads.md, scaled by heads x tokens",
+                     "traffic": traffic, "traffic_unit": "bytes per launch", "traffic_source": traffic_source,
                      "peak_source": f"{peaks['source']} (sustained bf16: kernel timed inside a long step)",
                      # tile-image pyramid: read K,V once (2 N e), write levels 1,2,4,8 of both (3.75 N e)
                      "pyramid_gbs": 5.75 * n_elem * 2 / (stage_ms["pyramid"] * 1e-3) / 1e9,
-                     "pyramid_frac_of_hbm": 5.75 * n_elem * 2 / (stage_ms["pyramid"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+                     "pyramid_frac_of_hbm": 5.75 * n_elem * 2 / (stage_ms["pyramid"] * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                     # the same on the algorithmic bytes of a pyramid (levels 2/4/8 only: 3.75 N e); the level-1 image
+                     # is this library's own extra write
+                     "pyramid_frac_algorithmic": 3.75 * n_elem * 2 / (stage_ms["pyramid"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
         "clocks": clocks, "e2e": e2e,
     }
+    if parity is not None:
+        line["parity_check"] = parity
+    if grid is not None:
+        line["config"]["parallelism"] = f"{grid.groups} head groups x {grid.parts} query-block ranges + all_to_all"
     if not args.no_cpu_baseline and world == 1:
         tf, sec, sample = oracle_sample_time(workload, ratios, 1, 1)
         line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",

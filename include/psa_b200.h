@@ -73,12 +73,14 @@ int psa_block_scores(const void* q, const void* k, const int32_t* idx_q, const i
  * Same arguments, result and kernels as psa_block_scores, minus the scratch pointer: the scratch is a built-in
  * device array of PSA_STATIC_SCRATCH_BYTES (64 MiB) that every GPU loading this library holds until the process
  * exits.  The entry point calls no cudaMalloc/cudaFree and no allocating library routine; the caller still owns
- * q, k, idx_q, idx_k and po.  A call whose psa_block_scores_scratch_bytes() exceeds the capacity is rejected with
- * PSA_ERR_ARG and a message naming both sizes (split it over fewer heads).
+ * q, k, idx_q, idx_k and po.  A call that needs more scratch than the array holds is rejected with PSA_ERR_ARG and a
+ * message naming both sizes (split it over fewer heads); the need is computed for the call's own head_dim, so it is
+ * at most psa_block_scores_scratch_bytes(), which is sized for head_dim 128.
  * The first call on a device resolves the array's device address (cudaGetSymbolAddress, with that device current);
  * make that first call outside any stream capture.  All calls on a device share the one array, which keeps the last
  * call's contents: every element a call reads it has written before, so nothing needs clearing, but two calls that
- * overlap on the GPU (different streams, or threads) race on it - serialise them. */
+ * overlap on the GPU (different streams, or threads) race on it - serialise them.  The resolved address is cached per
+ * device for the life of the process: after a cudaDeviceReset the library must be reloaded. */
 #define PSA_STATIC_SCRATCH_BYTES (64u << 20)
 size_t psa_block_scores_static_capacity(void);
 int psa_block_scores_static(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* po,

@@ -144,21 +144,6 @@ __device__ __forceinline__ bool warps_rendezvous(uint64_t* bar, int& uses, volat
 // of the row's token stream, in units of 4 tokens.
 constexpr uint32_t kItemQuirk = 1u << 14, kItemPad = 1u << 15;
 
-#ifdef PSA_FWD_PROFILE
-}  // namespace
-__device__ long long g_prof[64];
-__device__ long long g_trace[16 * 64];
-namespace {
-#define TRACE(row, t)
-#define RTRACE(row, rit) do { if (blockIdx.x == 3 && (rit) < 64) g_trace[(row) * 64 + (rit)] = clock64(); } while (0)
-#define PROF_T0() long long prof_t0 = clock64()
-#define PROF_ADD(slot) do { long long t1 = clock64(); prof_acc[slot] += t1 - prof_t0; prof_t0 = t1; } while (0)
-#else
-#define PROF_T0()
-#define PROF_ADD(slot)
-#define TRACE(row, t)
-#define RTRACE(row, rit)
-#endif
 
 // IMG = true: K/V tiles use the image layout [8-row group][slab][8 rows][128 B] and are filled by linear bulk copies from
 // the tile-image buffers; IMG = false: [slab][128 rows][128 B] filled by tensor-map TMA boxes from row-major tensors.
@@ -227,10 +212,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   // the current row are still in flight, and the first scores of the next row are computed under the epilogue.
   if (warp < kProducerWarps) {
     // ============================================================ producers
-#ifdef PSA_FWD_PROFILE
-    long long prof_acc[4] = {0, 0, 0, 0};
-#endif
-    PROF_T0();
     const uint32_t ctl_a = tc::smem_u32(ctl);
     const uint32_t k_full_a = ctl_a + (uint32_t)offsetof(Ctrl, k_full), k_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, k_empty);
     const uint32_t v_full_a = ctl_a + (uint32_t)offsetof(Ctrl, v_full), v_empty_a = ctl_a + (uint32_t)offsetof(Ctrl, v_empty);
@@ -270,7 +251,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         }
         return good;
       }
-      if (ptid == 0) RTRACE(0, rit_n);     // decode start
       uint32_t* table = sItems + (rit_n & 1) * kMaxItems;
       asm volatile("cp.async.wait_all;" ::: "memory");
       if (!warps_rendezvous(&ctl->prod_sync, syncs, abort_flag)) return false;
@@ -348,7 +328,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           row_index[rs] = R_n;
           __threadfence_block();
           tc::mbar_arrive(&ctl->row_ready[rs]);
-          RTRACE(1, rit_n);     // row published
         }
       }
       prefetch_raw(ctl->claimed[(rit_n + 1) & 1]);
@@ -404,7 +383,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             ok = tc::mbar_wait_a(k_empty_a + stage * 8, ((gt / C::NK) & 1) ^ 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            PROF_ADD(0);
             const uint32_t tile_a = sK_a + stage * C::TILE_BYTES, bar_a = k_full_a + stage * 8;
             float* bias_row = sBias + slot * 128;
             float* biasg_row = sBiasG + slot * 36;
@@ -479,15 +457,12 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
               for (int c = last_cols + lane; c < 128; c += 32) { bias_row[c] = -INFINITY; biasg_row[c >> 2] = -INFINITY; }
             const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
             if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
-            if (warp == 0 && lane == 0) TRACE(6, t);
-            PROF_ADD(1);
           }
           if (step > 0) {
             const int t = step - 1, gt = g0 + t, stage = gt % C::NV;
             ok = tc::mbar_wait_a(v_empty_a + stage * 8, ((gt / C::NV) & 1) ^ 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            PROF_ADD(2);
             const uint32_t tile_a = sV_a + stage * C::TILE_BYTES, bar_a = v_full_a + stage * 8;
             const int probe = vi + lane;
             const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sIt[probe < n_items ? probe : 0] >> 21) == t));
@@ -509,18 +484,12 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             vi += in_tile;
             const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
             if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
-            if (warp == 0 && lane == 0) TRACE(7, t);
-            PROF_ADD(3);
           }
         }
       if (ok && q_pending) fetch_q(true);
-      if (ptid == 0) RTRACE(2, rit);     // last copy of the row issued
       g0 += n_tiles;
       if (!ok) break;
     }
-#ifdef PSA_FWD_PROFILE
-    if (lane == 0 && blockIdx.x == 3) for (int i = 0; i < 4; ++i) g_prof[warp * 4 + i] = prof_acc[i];
-#endif
   } else if (warp == 3) {
     // ============================================================ MMA issuer
     if (lane == 0) {
@@ -541,10 +510,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       const uint32_t p_full_a = ctl_a + (uint32_t)offsetof(Ctrl, p_full), pv_done_a = ctl_a + (uint32_t)offsetof(Ctrl, pv_done);
       const uint32_t q_free_a = ctl_a + (uint32_t)offsetof(Ctrl, q_free), o_free_a = ctl_a + (uint32_t)offsetof(Ctrl, o_free);
       uint32_t idle = 0;
-#ifdef PSA_FWD_PROFILE
-      long long prof_acc[4] = {0, 0, 0, 0};
-#endif
-      PROF_T0();
       int g0 = 0, q_rows = 0;
       for (int rit = 0; ok; ++rit) {
         const int rslot = rit & 3;
@@ -555,10 +520,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           tc::mbar_arrive(&ctl->row_done[rslot]);
           continue;
         }
-        RTRACE(3, rit);                  // issuer: row known
         ok = tc::mbar_wait(&ctl->q_full, q_rows & 1, abort_flag);
         if (!ok) break;
-        RTRACE(4, rit);                  // issuer: query tile there
         // both accumulators are overwritten by this row's first P V products: the previous row's epilogue must have read
         // them by then (the first Q K^T products of the row do not wait for that)
         bool o_ok = q_rows == 0;
@@ -571,7 +534,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
               if (!o_ok) o_ok = tc::mbar_test_wait_a(o_free_a, (q_rows - 1) & 1);
             if (o_ok && tc::mbar_test_wait_a(p_full_a + b * 8, (gt >> 1) & 1) && tc::mbar_test_wait_a(v_full_a + stage * 8, (gt / C::NV) & 1)) {
                 tc::tc_fence_after();
-                TRACE(0, t);
                 const uint64_t vdesc = vdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
                 const uint32_t tP = tmem + b * 128;            // probabilities overwrite the scores they came from
                 const uint32_t tO = tmem + 256 + b * 128;      // even and odd tiles accumulate separately
@@ -585,10 +547,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
                 }
                 tc::umma_commit_a(v_empty_a + stage * 8);   // V tile may be refilled
                 tc::umma_commit_a(pv_done_a + b * 8);       // accumulator b is consistent again
-                TRACE(1, t);
                 ++pv_next;
                 progressed = true;
-                PROF_ADD(0);
               }
             }
             // S = Q K^T of tile t is only issued once P V of tile t-2 has been: the tensor pipe runs in issue order, so
@@ -598,13 +558,11 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
               const int t = qk_next, gt = g0 + t, b = gt & 1, stage = gt % C::NK;
               if (tc::mbar_test_wait_a(k_full_a + stage * 8, (gt / C::NK) & 1)) {
                 tc::tc_fence_after();
-                TRACE(2, t);
                 const uint64_t kdesc = kdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
                 const uint32_t idesc_qk = t == n_tiles - 1 ? tc::make_idesc(FMT, 128, last_cols, 0, 0) : idesc_qk_full;
                 const uint32_t tSb = tmem + b * 128;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
-                  constexpr int dummy = 0; (void)dummy;
                   const uint32_t qoff = (uint32_t)(((ks >> 2) * kSlabBytes + (ks & 3) * 32) >> 4);
                   const uint32_t koff = (uint32_t)(((ks >> 2) * kSlabStride + (ks & 3) * 32) >> 4);
                   tc::umma_ss(tSb, qdesc + qoff, kdesc + koff, idesc_qk, ks > 0 ? 1u : 0u);
@@ -612,10 +570,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
                 tc::umma_commit_a(k_empty_a + stage * 8);   // K tile may be refilled
                 tc::umma_commit_a(s_full_a + b * 8);
               if (t == n_tiles - 1) tc::umma_commit_a(q_free_a);   // the query tile may be replaced
-                TRACE(3, t);
                 ++qk_next;
                 progressed = true;
-                PROF_ADD(1);
               }
             }
             if (progressed) {
@@ -625,14 +581,10 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
               ok = false;
             }
           }
-        RTRACE(5, rit);                  // issuer: last product of the row issued
         if (ok) tc::mbar_arrive(&ctl->row_done[rslot]);
         ++q_rows;
         g0 += n_tiles;
       }
-#ifdef PSA_FWD_PROFILE
-      if (blockIdx.x == 3) { for (int i = 0; i < 4; ++i) g_prof[16 + i] = prof_acc[i]; g_prof[21] = g0; }
-#endif
     }
   } else {
     // ============================================================ softmax / epilogue
@@ -650,13 +602,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     const uint32_t tO_other = tmem + 256 + (g ^ 1) * 128 + lane_base;
     const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
     bool ok = true;
-#ifdef PSA_FWD_PROFILE
-    long long sprof[6] = {0, 0, 0, 0, 0, 0};
-    long long sprof_t = clock64();
-#define SPROF(i) do { long long t1_ = clock64(); sprof[i] += t1_ - sprof_t; sprof_t = t1_; } while (0)
-#else
-#define SPROF(i)
-#endif
     int g0 = 0, q_rows = 0;
     for (int rit = 0; ok; ++rit) {
       const int rslot = rit & 3;
@@ -692,16 +637,11 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       }
       float m_run = -INFINITY, l_run = 0.f;
       const int first = ((g0 & 1) == g) ? 0 : 1;    // my first tile of this row
-      if (lane == 0 && quarter == 0) RTRACE(6 + g * 5, rit);     // softmax group: row start
         for (int j = first; j < n_tiles; j += 2) {
           const int gj = g0 + j, slot = gj % kBiasSlots, it = gj >> 1;
           ok = tc::mbar_wait(&ctl->s_full[g], it & 1, abort_flag);   // scores ready (and the tile's bias words visible)
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          SPROF(0);
-          if (r == 0) TRACE(4, j);
-          if (lane == 0) TRACE(12 + quarter, j);
-          if (lane == 0 && quarter == 0 && j == first) RTRACE(7 + g * 5, rit);   // first scores seen
           tc::tc_fence_after();
           const bool ragged = j == n_tiles - 1 && last_cols < 128;   // columns the MMA did not write hold stale bits
           const float4* bias4 = reinterpret_cast<const float4*>(sBias + slot * 128);
@@ -763,7 +703,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             }
           }
           const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-          SPROF(1);
           // raise the running maximum only when it is far off (or still unset)
           float alpha = 1.f;
           const bool raise = mx > m_run + 8.f;
@@ -788,7 +727,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             }
             tc::tmem_wait_st();
           }
-          SPROF(2);
           // pass 2: probabilities (rounded to the element type) written over the scores, running sum.  Chunk c reads score
           // columns [32c, 32c+32) and writes packed columns [16c, 16c+16): always columns that were read before.
           const float m_use = m_run == -INFINITY ? 0.f : m_run;
@@ -859,11 +797,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           tc::tc_fence_before();
           __syncwarp();
           if (lane == 0) tc::mbar_arrive(&ctl->p_full[g]);   // one arrival per warp
-          if (r == 0) TRACE(5, j);
-          if (lane == 0) TRACE(8 + quarter, j);
-          SPROF(3);
         }
-      if (lane == 0 && quarter == 0) RTRACE(8 + g * 5, rit);       // last probabilities written
       // ---- epilogue: merge the two groups' partial results
       const int my_tiles = n_tiles > first ? (n_tiles - first + 1) >> 1 : 0;
       if (ok && my_tiles > 0) {
@@ -877,7 +811,6 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       xch[g * 256 + r] = m_run;
       xch[g * 256 + 128 + r] = l_run;
       if (ok) ok = warps_rendezvous(&ctl->xch_full, q_rows, abort_flag); else ++q_rows;
-      if (lane == 0 && quarter == 0) RTRACE(9 + g * 5, rit);       // both groups through their last product
       if (ok) {
         const float m_o = xch[(g ^ 1) * 256 + r], l_o = xch[(g ^ 1) * 256 + 128 + r];
         const float m_all = fmaxf(m_run, m_o);
@@ -948,13 +881,9 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         }
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&ctl->row_done[rslot]);
-        if (lane == 0 && quarter == 0) RTRACE(10 + g * 5, rit);    // output written
       }
       g0 += n_tiles;
     }
-#ifdef PSA_FWD_PROFILE
-    if (threadIdx.x == 128 && blockIdx.x == 3) for (int i = 0; i < 6; ++i) g_prof[32 + i] = sprof[i];
-#endif
   }
 
   // ---------------------------------------------------------------- teardown
@@ -1109,11 +1038,3 @@ int fwd_tc_launch(const FwdArgs& a, cudaStream_t st) {
 
 }  // namespace psa
 
-#ifdef PSA_FWD_PROFILE
-extern "C" int psa_debug_read_prof(long long* host64) {
-  return (int)cudaMemcpyFromSymbol(host64, psa::g_prof, sizeof(long long) * 64);
-}
-extern "C" int psa_debug_read_trace(long long* host512) {
-  return (int)cudaMemcpyFromSymbol(host512, psa::g_trace, sizeof(long long) * 1024);
-}
-#endif

@@ -208,15 +208,23 @@ int make_score_dims(ScoreDims& d, int64_t seq_q, int64_t seq_k, int D, int bm, i
 
 }  // namespace psa
 
-extern "C" size_t psa_block_scores_scratch_bytes(int64_t bh, int64_t seq_q, int64_t seq_k, int block_m, int block_n,
-                                                 int dtype) {
-  psa::ScoreDims d;
-  if (psa::make_score_dims(d, seq_q, seq_k, 128, block_m, block_n) != PSA_OK) return 0;   // sized for head_dim 128
+namespace psa {
+// Scratch a call really uses: R, the row maxima and (16-bit inputs) the compacted sample matrices of its head_dim.
+static size_t score_scratch_bytes(int64_t bh, int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int dtype) {
+  ScoreDims d;
+  if (make_score_dims(d, seq_q, seq_k, head_dim, block_m, block_n) != PSA_OK) return 0;
   const size_t es = dtype == PSA_F32 ? 4 : 2;
   const size_t r_bytes = ((size_t)bh * d.nq_s * d.n_d * es + 255) & ~(size_t)255;
   const size_t m_bytes = ((size_t)bh * d.nq_s * sizeof(float) + 255) & ~(size_t)255;
-  const size_t extra = dtype == PSA_F32 ? 0 : psa::scores_tc_extra_scratch(d, bh);
+  const size_t extra = dtype == PSA_F32 ? 0 : scores_tc_extra_scratch(d, bh);
   return r_bytes + m_bytes + extra;
+}
+}  // namespace psa
+
+// The public bound does not know the head_dim: it is sized for 128, the larger of the two supported widths.
+extern "C" size_t psa_block_scores_scratch_bytes(int64_t bh, int64_t seq_q, int64_t seq_k, int block_m, int block_n,
+                                                 int dtype) {
+  return psa::score_scratch_bytes(bh, seq_q, seq_k, 128, block_m, block_n, dtype);
 }
 
 extern "C" int psa_block_scores(const void* q, const void* k, const int32_t* idx_q, const int32_t* idx_k, void* po,
@@ -284,7 +292,7 @@ extern "C" int psa_block_scores_static(const void* q, const void* k, const int32
   ScoreDims d;
   int rc = make_score_dims(d, seq_q, seq_k, head_dim, block_m, block_n);
   if (rc != PSA_OK) return rc;
-  const size_t need = psa_block_scores_scratch_bytes(bh, seq_q, seq_k, block_m, block_n, dtype);
+  const size_t need = score_scratch_bytes(bh, seq_q, seq_k, head_dim, block_m, block_n, dtype);   // of this head_dim
   PSA_REQUIRE(need <= kStaticScratchBytes, PSA_ERR_ARG,
               "psa_block_scores_static: this call needs %zu bytes of scratch but the built-in scratch holds %zu; "
               "split the call over fewer heads or use psa_block_scores with caller-provided scratch",

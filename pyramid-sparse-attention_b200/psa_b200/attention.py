@@ -132,6 +132,12 @@ class PSAAttention(nn.Module):
             mask, _, _ = compute_block_mask(q, k, config, text_length=0, idx_q=idx_q, idx_k=idx_k)
         return self.sparse_attention_fn(q.contiguous(), k.contiguous(), v.contiguous(), mask, None)
 
+    @staticmethod
+    def check_status(device=None) -> None:
+        """Ask, once per run, whether any attention kernel gave up on a bounded device-side wait (its output would be
+        incomplete); raises PSAKernelError if so.  The calls themselves never synchronise with the host."""
+        ops.check_status(device)
+
 
 def psa_attention(q, k, v, *, config: PSAConfig = None, mask_ratios=None, mask_mode: str = None, block_m: int = None,
                   block_n: int = None) -> torch.Tensor:

@@ -25,9 +25,12 @@ class _LegacySparseAttention(torch.autograd.Function):
     def forward(ctx, q, k, v, block_sparse_dense, sm_scale, causal):
         need_backward = q.requires_grad or k.requires_grad or v.requires_grad
         qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
-        o, lse, pyramid = ops.legacy_forward(qc, kc, vc, block_sparse_dense, causal, sm_scale, need_lse=need_backward)
+        # the reference takes int32 or int64 masks with any strides (psa_kernel_legacy.py:1254); forward and backward
+        # both read the one normalised copy
+        mask = ops._mask32(block_sparse_dense)
+        o, lse, pyramid = ops.legacy_forward(qc, kc, vc, mask, causal, sm_scale, need_lse=need_backward)
         if need_backward:
-            ctx.save_for_backward(qc, kc, vc, block_sparse_dense, o, lse, *pyramid[0], *pyramid[1])
+            ctx.save_for_backward(qc, kc, vc, mask, o, lse, *pyramid[0], *pyramid[1])
             ctx.sm_scale = sm_scale
             ctx.causal = causal
         return o

@@ -39,6 +39,39 @@ def _flat_bh(x: torch.Tensor) -> torch.Tensor:
     return x if x.is_contiguous() else x.contiguous()
 
 
+def _mask32(mask: torch.Tensor) -> torch.Tensor:
+    """The kernels read masks as contiguous int32; the reference accepts int32 or int64 and any strides."""
+    mask = mask if mask.dtype == torch.int32 else mask.to(torch.int32)
+    return mask if mask.is_contiguous() else mask.contiguous()
+
+
+# One status word per device, shared by every launch of the tensor-core attention kernels: a kernel whose bounded
+# device-side wait expired writes PSA_ERR_TIMEOUT into it and nothing ever clears it except check_status().  Calls stay
+# free of host synchronisation; a run asks once, at the end (PSAAttention.check_status, close_logger).
+_STATUS: Dict[int, torch.Tensor] = {}
+
+
+def status_word(device) -> torch.Tensor:
+    dev = torch.device(device)
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _STATUS:
+        _STATUS[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _STATUS[idx]
+
+
+def check_status(device=None, reset: bool = True) -> None:
+    """Raise PSAKernelError if any attention kernel launched so far on `device` (default: every device used) gave up
+    on a bounded wait - its output is then incomplete.  Synchronises the device."""
+    words = list(_STATUS.items()) if device is None else [(None, status_word(device))]
+    for _, w in words:
+        code = int(w.item())
+        if code != 0:
+            if reset:
+                w.zero_()
+            raise _lib.PSAKernelError(f"a PSA kernel on {w.device} reported status {code} (bounded device-side wait expired); "
+                                      "outputs produced since the last check are incomplete")
+
+
 # ------------------------------------------------------------------------------------------------
 def pyramid_kv(k: torch.Tensor, v: torch.Tensor, block_n: int):
     """Levels 2/4/8 of the mean-pooled K and V ([B,H,S,D] -> [B,H,S_pad/l,D]) in one pass.
@@ -178,14 +211,12 @@ def psa_forward_tm(q_heads, images: KVImages, mask, out_tm, block_m: int, block_
     _need_cuda(q_heads, mask, out_tm)
     _, H, S, D = q_heads.shape
     assert out_tm.shape == (S, H, D) and out_tm.is_contiguous() and out_tm.dtype == q_heads.dtype
-    mask = _flat_bh(mask)
-    if mask.dtype != torch.int32:
-        mask = mask.to(torch.int32)
+    mask = _mask32(mask)
     out_perm = None if out_perm is None else _perm32(out_perm, S)
     if sm_scale is None:
         sm_scale = D ** -0.5
     with torch.cuda.device(q_heads.device):
-        status = torch.zeros(1, dtype=torch.int32, device=q_heads.device)
+        status = status_word(q_heads.device)
         rc = lib.psa_fwd_images_tm(_ptr(q_heads), _ptr(images.kimg), _ptr(images.vimg), _ptr(mask), _ptr(out_tm), _ptr(out_perm),
                                    H, S, D, block_m, block_n, tile_n, mask.shape[-1], float(sm_scale), int(compat_quirk),
                                    _dt(q_heads), _ptr(status), _stream(q_heads))
@@ -406,9 +437,7 @@ def psa_forward(q, k, v, mask, block_m: int, block_n: int, tile_n: int, sm_scale
     assert q.shape[-1] == k.shape[-1] == v.shape[-1]
     assert k.shape[2] == v.shape[2]
     assert q.shape[-1] in [64, 128]
-    q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _flat_bh(mask)
-    if mask.dtype != torch.int32:
-        mask = mask.to(torch.int32)
+    q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _mask32(mask)
     B, H, Sq, D = q.shape
     Sk = k.shape[2]
     if sm_scale is None:
@@ -420,7 +449,7 @@ def psa_forward(q, k, v, mask, block_m: int, block_n: int, tile_n: int, sm_scale
             pyramid = pyramid_kv_images(k, v, block_n)
         with torch.cuda.device(q.device):
             o = out if out is not None else torch.empty_like(q)
-            status = torch.zeros(1, dtype=torch.int32, device=q.device)
+            status = status_word(q.device)
             if out_perm is None:
                 rc = lib.psa_fwd_images(_ptr(q), _ptr(pyramid.kimg), _ptr(pyramid.vimg), _ptr(mask), _ptr(o), B * H, Sq, Sk, D,
                                         block_m, block_n, tile_n, mask.shape[-1], float(sm_scale), int(compat_quirk), _dt(q),
@@ -440,7 +469,7 @@ def psa_forward(q, k, v, mask, block_m: int, block_n: int, tile_n: int, sm_scale
     (k2, k4, k8), (v2, v4, v8) = pyramid
     with torch.cuda.device(q.device):
         o = out if out is not None else torch.empty_like(q)
-        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        status = status_word(q.device)
         rc = lib.psa_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(k2), _ptr(k4), _ptr(k8), _ptr(v2), _ptr(v4), _ptr(v8),
                          _ptr(mask), _ptr(o), B * H, Sq, Sk, D, block_m, block_n, tile_n, mask.shape[-1],
                          float(sm_scale), int(compat_quirk), impl, _dt(q), _ptr(status), _stream(q))
@@ -456,9 +485,7 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
     assert q.shape[-1] == k.shape[-1] == v.shape[-1]
     assert k.shape[2] == v.shape[2]
     assert q.shape[-1] in [64, 128]
-    q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _flat_bh(mask)
-    if mask.dtype != torch.int32:
-        mask = mask.to(torch.int32)
+    q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _mask32(mask)
     B, H, S, D = q.shape
     if sm_scale is None:
         sm_scale = D ** -0.5
@@ -472,7 +499,7 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
             o = torch.empty_like(q)
             lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if need_lse else None
             scratch = torch.empty(lib.psa_legacy_index_bytes(B * H, S) // 4, dtype=torch.int32, device=q.device)
-            status = torch.zeros(1, dtype=torch.int32, device=q.device)
+            status = status_word(q.device)
             rc = lib.psa_legacy_fwd_images(_ptr(q), _ptr(imgs.kimg), _ptr(imgs.vimg), _ptr(mask), _ptr(scratch), _ptr(o), _ptr(lse),
                                            B * H, S, D, mask.shape[-1], float(sm_scale), int(causal), _dt(q), _ptr(status), _stream(q))
         check(rc, "psa_legacy_fwd_images")
@@ -494,9 +521,7 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
 def legacy_forward_tc(q, k, v, mask, sm_scale: Optional[float] = None, need_lse: bool = True, causal: bool = False):
     """Legacy forward on the tcgen05 kernel (psa_legacy_fwd_images); returns (o, lse or None)."""
     _need_cuda(q, k, v, mask)
-    q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _flat_bh(mask)
-    if mask.dtype != torch.int32:
-        mask = mask.to(torch.int32)
+    q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _mask32(mask)
     B, H, S, D = q.shape
     sm_scale = D ** -0.5 if sm_scale is None else sm_scale
     imgs = pyramid_kv_images(k, v, 128)
@@ -504,7 +529,7 @@ def legacy_forward_tc(q, k, v, mask, sm_scale: Optional[float] = None, need_lse:
         o = torch.empty_like(q)
         lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if need_lse else None
         scratch = torch.empty(lib.psa_legacy_index_bytes(B * H, S) // 4, dtype=torch.int32, device=q.device)
-        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        status = status_word(q.device)
         rc = lib.psa_legacy_fwd_images(_ptr(q), _ptr(imgs.kimg), _ptr(imgs.vimg), _ptr(mask), _ptr(scratch), _ptr(o), _ptr(lse),
                                        B * H, S, D, mask.shape[-1], float(sm_scale), int(causal), _dt(q), _ptr(status), _stream(q))
     check(rc, "psa_legacy_fwd_images")
@@ -516,7 +541,7 @@ def legacy_backward(q, k, v, mask, o, lse, do, causal: bool, sm_scale: float, py
     """dQ, dK, dV of the legacy kernel (_sparse_attention.backward, psa_kernel_legacy.py:947-1069).  16-bit tensors run
     on the tensor-core kernels unless impl == IMPL_SCALAR."""
     _need_cuda(q, k, v, mask, o, lse, do)
-    do = _flat_bh(do)
+    do, mask = _flat_bh(do), _mask32(mask)
     B, H, S, D = q.shape
     (k2, k4, k8), (v2, v4, v8) = pyramid
     with torch.cuda.device(q.device):

@@ -86,6 +86,126 @@ class HeadShard:
         out.view(P, hp, sl, D)[:, first:first + count] = recv
 
 
+class GridShard:
+    """2-D partition for head counts that do not divide over the ranks (e.g. 12 heads on 8 GPUs = 4 head groups x 2
+    query ranges).  With G = gcd(heads, world) head groups of heads/G heads each and world/G query parts per group, rank
+    r works on head group r // parts and query part r % parts.  Query blocks are independent rows of the layer
+    (src/psa_triton/kernels/psa_kernel.py:173,198), so a part is just the attention call on a slice of q: it needs q
+    of its own block range only, but k and v (hence the pooled pyramid and the k samples) of ALL tokens, which are
+    rebuilt on every rank of the group.  Parts are cut on block_m boundaries, so every query block - and with it every
+    score row, mask row and output row - is the one a single GPU computes.
+
+    to_grid / to_seq are the reshuffles from and to sequence-sharded activations ([S/P, H, D] per rank), one
+    all_to_all_single each with uneven splits (NCCL on GPUs, gloo in the CPU tests)."""
+
+    def __init__(self, world: int, rank: int, heads: int, seq: int, head_dim: int, block_m: int = 128):
+        import math
+        if seq % world:
+            raise ValueError(f"{seq} tokens do not divide over {world} ranks")
+        self.world, self.rank, self.heads, self.seq, self.head_dim, self.block_m = world, rank, heads, seq, head_dim, block_m
+        self.groups = math.gcd(heads, world)
+        self.parts = world // self.groups
+        self.heads_per_rank = heads // self.groups
+        self.tokens_per_rank = seq // world
+        mq = -(-seq // block_m)
+        if self.parts > mq:
+            raise ValueError(f"{self.parts} query parts need at least as many query blocks (have {mq})")
+        per = -(-mq // self.parts)
+        self._cuts = [min(seq, p * per * block_m) for p in range(self.parts)] + [seq]     # token boundaries of the parts
+
+    def coords(self, rank: int):
+        """(head group, query part) of a rank."""
+        return rank // self.parts, rank % self.parts
+
+    def head_range(self, rank: int = None):
+        g, _ = self.coords(self.rank if rank is None else rank)
+        return g * self.heads_per_rank, (g + 1) * self.heads_per_rank
+
+    def query_range(self, rank: int = None):
+        """Token range [r0, r1) of the rank's query part; r0 is a multiple of block_m."""
+        _, part = self.coords(self.rank if rank is None else rank)
+        return self._cuts[part], self._cuts[part + 1]
+
+    def _overlap(self, token_owner: int, part_rank: int):
+        """Tokens of rank `token_owner`'s sequence shard that lie in rank `part_rank`'s query part, as a global range."""
+        t0, t1 = token_owner * self.tokens_per_rank, (token_owner + 1) * self.tokens_per_rank
+        r0, r1 = self.query_range(part_rank)
+        lo, hi = max(t0, r0), min(t1, r1)
+        return (lo, hi) if lo < hi else (lo, lo)
+
+    def to_grid(self, x: torch.Tensor):
+        """[3, S/P, H, D] (this rank's tokens of q, k, v) -> (q_part [hp, r1-r0, D], k [hp, S, D], v [hp, S, D])."""
+        n, sl, H, D = x.shape
+        assert n == 3 and sl == self.tokens_per_rank and H == self.heads
+        hp, P = self.heads_per_rank, self.world
+        t0 = self.rank * sl
+        send, send_sizes = [], []
+        for d in range(P):
+            h0, h1 = self.head_range(d)
+            lo, hi = self._overlap(self.rank, d)
+            pieces = [x[1, :, h0:h1].permute(1, 0, 2).reshape(-1), x[2, :, h0:h1].permute(1, 0, 2).reshape(-1),
+                      x[0, lo - t0:hi - t0, h0:h1].permute(1, 0, 2).reshape(-1)]
+            send.append(torch.cat(pieces))
+            send_sizes.append(int(send[-1].numel()))
+        recv_sizes = []
+        for src in range(P):
+            lo, hi = self._overlap(src, self.rank)
+            recv_sizes.append((2 * sl + (hi - lo)) * hp * D)
+        send_buf = torch.cat(send)
+        recv_buf = torch.empty(sum(recv_sizes), dtype=x.dtype, device=x.device)
+        if P == 1:
+            recv_buf.copy_(send_buf)
+        else:
+            dist.all_to_all_single(recv_buf, send_buf, output_split_sizes=recv_sizes, input_split_sizes=send_sizes)
+        r0, r1 = self.query_range()
+        k = torch.empty((hp, self.seq, D), dtype=x.dtype, device=x.device)
+        v = torch.empty_like(k)
+        q = torch.empty((hp, r1 - r0, D), dtype=x.dtype, device=x.device)
+        off = 0
+        for src in range(P):
+            lo, hi = self._overlap(src, self.rank)
+            kv = sl * hp * D
+            k[:, src * sl:(src + 1) * sl] = recv_buf[off:off + kv].view(hp, sl, D)
+            v[:, src * sl:(src + 1) * sl] = recv_buf[off + kv:off + 2 * kv].view(hp, sl, D)
+            if hi > lo:
+                q[:, lo - r0:hi - r0] = recv_buf[off + 2 * kv:off + recv_sizes[src]].view(hp, hi - lo, D)
+            off += recv_sizes[src]
+        return q, k, v
+
+    def to_seq(self, o_part: torch.Tensor) -> torch.Tensor:
+        """[hp, r1-r0, D] (output rows of this rank's query part and heads) -> [H, S/P, D] (all heads of this rank's
+        tokens)."""
+        hp, rows, D = o_part.shape
+        r0, r1 = self.query_range()
+        assert hp == self.heads_per_rank and rows == r1 - r0
+        P, sl = self.world, self.tokens_per_rank
+        send, send_sizes = [], []
+        for d in range(P):                                   # d owns tokens [d*sl, (d+1)*sl)
+            lo, hi = self._overlap(d, self.rank)
+            send.append(o_part[:, lo - r0:hi - r0].reshape(-1))
+            send_sizes.append(int(send[-1].numel()))
+        recv_sizes = []
+        for src in range(P):
+            lo, hi = self._overlap(self.rank, src)
+            recv_sizes.append((hi - lo) * hp * D)
+        send_buf = torch.cat(send)
+        recv_buf = torch.empty(sum(recv_sizes), dtype=o_part.dtype, device=o_part.device)
+        if P == 1:
+            recv_buf.copy_(send_buf)
+        else:
+            dist.all_to_all_single(recv_buf, send_buf, output_split_sizes=recv_sizes, input_split_sizes=send_sizes)
+        out = torch.empty((self.heads, sl, D), dtype=o_part.dtype, device=o_part.device)
+        t0 = self.rank * sl
+        off = 0
+        for src in range(P):
+            lo, hi = self._overlap(self.rank, src)
+            if hi > lo:
+                h0, h1 = self.head_range(src)
+                out[h0:h1, lo - t0:hi - t0] = recv_buf[off:off + recv_sizes[src]].view(hp, hi - lo, D)
+            off += recv_sizes[src]
+        return out
+
+
 # Address contract of the peer exchange (what psa_push_heads / psa_pull_heads / psa_fwd_images_scatter compute per row).
 def push_destination(rank: int, t_local: int, head: int, tokens_per_rank: int, heads_per_rank: int):
     """Row (t_local, head) of rank `rank`'s [S/P, H, D] buffer goes to -> (owner rank, local head, global token)."""
@@ -322,10 +442,10 @@ class PeerExchange:
                         first: int = 0, sm_scale: float = None, compat_quirk: bool = True) -> torch.Tensor:
         """Tile-image forward on local heads [first, first+q.shape[-3]); output rows land in the owners' `o` buffers.
         Returns the device status word of the launch."""
-        from .ops import _dt
+        from .ops import _dt, status_word
         hc, S, D = q.shape[-3], q.shape[-2], q.shape[-1]
         sm_scale = D ** -0.5 if sm_scale is None else sm_scale
-        status = torch.zeros(1, dtype=torch.int32, device=q.device)
+        status = status_word(q.device)
         stream = torch.cuda.current_stream(self.device).cuda_stream
         with torch.cuda.device(self.device):
             rc = self.lib.psa_fwd_images_scatter(q.data_ptr(), images.kimg.data_ptr(), images.vimg.data_ptr(), mask.data_ptr(),

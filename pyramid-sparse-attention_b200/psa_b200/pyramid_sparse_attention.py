@@ -196,9 +196,14 @@ class PyramidSparseAttention(nn.Module):
         return self.gilbert_rearranger.reversed_rearrange(out_r) if self.use_rearrange else out_r
 
     def close_logger(self, jsonl_path: str = None):
-        """Reference name (pyramid_sparse_attention.py:408-413).  jsonl_path: also write the per-call records there
-        (SparsityLog.write_jsonl); nothing is written to disk otherwise."""
+        """Reference name (pyramid_sparse_attention.py:408-413).  With logging enabled the per-call records go to
+        ``<config.log_dir>/sparsity.jsonl`` (the file PSALogger keeps, src/psa_triton/utils/psa_logger.py:265-283) or to
+        jsonl_path, in one host copy for the whole run.  Also the point where a run learns whether an attention kernel
+        gave up on a bounded device-side wait (ops.check_status)."""
         if self.logger is not None:
-            if jsonl_path is not None:
-                self.logger.write_jsonl(jsonl_path)
+            if self.logger.records:
+                import os
+                self.logger.write_jsonl(jsonl_path if jsonl_path is not None
+                                        else os.path.join(self.config.log_dir, "sparsity.jsonl"))
             self.logger.close()
+        ops.check_status()

@@ -17,8 +17,10 @@ WAN_1_3B = dict(name="wan2.1-1.3b-attn-layer", heads=12, head_dim=128, grid=(21,
 WAN_14B = dict(name="wan2.1-14b-attn-layer", heads=40, head_dim=128, grid=(21, 45, 80), text=0)
 COGVIDEOX_5B = dict(name="cogvideox-5b-attn-layer", heads=48, head_dim=64, grid=(13, 30, 45), text=226)
 TINY = dict(name="tiny-attn-layer", heads=2, head_dim=64, grid=(4, 32, 32), text=0)
+# causal forward + backward of the legacy kernels: batch 2 x 16 heads, 32768 tokens laid out as 8 frames of 64x64
+CAUSAL_TRAIN = dict(name="causal-legacy-fwd-bwd", heads=16, head_dim=128, grid=(8, 64, 64), text=0, batch=2)
 
-WORKLOADS = {w["name"]: w for w in (WAN_1_3B, WAN_14B, COGVIDEOX_5B, TINY)}
+WORKLOADS = {w["name"]: w for w in (WAN_1_3B, WAN_14B, COGVIDEOX_5B, TINY, CAUSAL_TRAIN)}
 
 
 def structured_field(seed: int, heads: int, head_dim: int, grid, text: int = 0, dtype=torch.bfloat16, device="cpu",

@@ -1,0 +1,188 @@
+"""GPU: the benchmark configurations at their stated token counts, a head or two each, against the CPU oracle.
+
+Every case splits the comparison the same way, so that one flipped score cannot hide behind a loose output bound:
+  scores      kernel Po vs oracle Po on the same inputs and sample offsets: fraction of cells that differ, largest
+              difference relative to the row maximum;
+  level mask  (a) the assignment kernel on the ORACLE's scores must give the oracle's mask bit for bit;
+              (b) the mask the kernels derive from their own scores: fraction of entries equal to the oracle's;
+  forward     the attention kernel on the ORACLE's mask vs the oracle's forward on that mask: max-abs, cosine.
+The measured figures are appended, one JSON line per case, to the file named by $PSA_PARITY_REPORT (if set).
+"""
+import json
+import os
+
+import pytest
+import torch
+
+import cases as C
+from oracle import psa_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+ATOL_OUT, COS_OUT = 2e-2, 0.999          # bf16 bar of the attention output: max-abs <= 2e-2, cosine >= 0.999
+
+
+@pytest.fixture(scope="module")
+def P():
+    import psa_b200
+    assert torch.cuda.is_available()
+    return psa_b200
+
+
+def cosine(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float((a @ b) / (a.norm() * b.norm() + 1e-30))
+
+
+def report(name, **figures):
+    path = os.environ.get("PSA_PARITY_REPORT")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps({"case": name, **figures}) + "\n")
+
+
+def inputs(workload, heads, dtype):
+    from psa_b200 import synthetic
+    return synthetic.make_qkv(workload, 1000, dtype, "cpu", head_range=heads)
+
+
+def score_figures(po, ref):
+    po, ref = po.float(), ref.float()
+    rel = ((po - ref).abs() / ref.amax(-1, keepdim=True)).max()
+    return float((po != ref).float().mean()), float(rel)
+
+
+def layer_case(P, name, workload, heads, dtype, block_n, ratios, po_cell_budget, mask_budget, rel_budget):
+    """One attention layer at the workload's full token count on `heads`, compared stage by stage."""
+    q, k, v = inputs(workload, heads, dtype)
+    H = q.shape[1]
+    iq, ik = C.sample_idx(41, 1, H, 128, 32), C.sample_idx(42, 1, H, block_n, block_n // 4)
+    ref_po = O.block_scores(q, k, iq, ik, 128, block_n)
+    ref_mask = O.assign_levels(ref_po, ratios, "topk_newtype", block_n, 32)
+    ref_out = O.psa_forward_newmask(q, k, v, ref_mask, 128, block_n, 32).float()
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    po = P.ops.block_scores(qd, kd, iq.to(DEV), ik.to(DEV), 128, block_n).cpu()
+    cells, rel = score_figures(po, ref_po)
+    same_in = P.ops.assign_levels(ref_po.to(DEV), ratios, "topk_newtype", block_n, 32).cpu()
+    assert torch.equal(same_in, ref_mask), "identical scores must give the identical level mask"
+    own_mask = P.ops.assign_levels(po.to(DEV), ratios, "topk_newtype", block_n, 32).cpu()
+    agree = float((own_mask == ref_mask).float().mean())
+    out = P.ops.psa_forward(qd, kd, vd, ref_mask.to(DEV), 128, block_n, 32)
+    assert int(out._psa_status.item()) == 0
+    out = out.float().cpu()
+    err, cos = float((out - ref_out).abs().max()), cosine(out, ref_out)
+    # whole layer with the kernels' own mask (what a user gets): a flipped level moves a row by the weight of one block
+    cfg = P.PSAConfig(block_n=block_n, mask_ratios=ratios)
+    e2e = P.PSAAttention(cfg)(qd, kd, vd, idx_q=iq.to(DEV), idx_k=ik.to(DEV)).float().cpu()
+    e2e_err, e2e_cos = float((e2e - ref_out).abs().max()), cosine(e2e, ref_out)
+    report(name, tokens=q.shape[2], heads=H, dtype=str(dtype), po_cells_differ=cells, po_max_rel_to_row_max=rel,
+           mask_agreement=agree, fwd_max_abs=err, fwd_cosine=cos, layer_max_abs=e2e_err, layer_cosine=e2e_cos)
+    assert cells <= po_cell_budget and rel <= rel_budget, (cells, rel)
+    assert agree >= mask_budget, agree
+    assert err <= ATOL_OUT and cos >= COS_OUT, (err, cos)
+    assert e2e_cos >= COS_OUT, e2e_cos
+
+
+def test_tiny_fp32_default_preset(P):
+    """B=1, 2 heads x 64, fp32, 4096 tokens on a 4x32x32 grid, block 64, the default preset: output and level mask."""
+    from psa_b200 import synthetic
+    q, k, v = inputs(synthetic.TINY, (0, 2), torch.float32)
+    cfg = P.PSAConfig()
+    iq, ik = C.sample_idx(41, 1, 2, cfg.block_m, cfg.block_m // 4), C.sample_idx(42, 1, 2, cfg.block_n, cfg.block_n // 4)
+    ref_out, ref_mask, ref_po = O.psa_attention(q, k, v, block_m=cfg.block_m, block_n=cfg.block_n, tile_n=cfg.tile_n,
+                                                mask_ratios=cfg.mask_ratios, mask_mode=cfg.mask_mode, idx_q=iq, idx_k=ik)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    mask, po, _ = P.compute_block_mask(qd, kd, cfg, idx_q=iq.to(DEV), idx_k=ik.to(DEV))
+    cells, rel = score_figures(po.cpu(), ref_po)
+    agree = float((mask.cpu() == ref_mask).float().mean())
+    same_in = P.ops.assign_levels(ref_po.to(DEV), cfg.mask_ratios, "topk_newtype", cfg.block_n, cfg.tile_n).cpu()
+    assert torch.equal(same_in, ref_mask)
+    out = P.PSAAttention(cfg)(qd, kd, vd, idx_q=iq.to(DEV), idx_k=ik.to(DEV)).cpu()
+    on_ref_mask = P.ops.psa_forward(qd, kd, vd, ref_mask.to(DEV), cfg.block_m, cfg.block_n, cfg.tile_n).cpu()
+    err = float((on_ref_mask - ref_out).abs().max())
+    report("tiny_fp32_default", tokens=4096, heads=2, dtype="fp32", po_cells_differ=cells, po_max_rel_to_row_max=rel,
+           mask_agreement=agree, fwd_max_abs=err, layer_max_abs=float((out - ref_out).abs().max()),
+           layer_cosine=cosine(out, ref_out))
+    assert rel <= 1e-5, rel                      # fp32 scores: summation order only
+    assert agree >= 0.999, agree
+    assert err <= 2e-5, err
+    if agree == 1.0:
+        assert float((out - ref_out).abs().max()) <= 2e-5
+
+
+def test_cogvideox_shape_bf16_with_text_tokens(P):
+    """17776 tokens (226 N(0,1) text tokens, then 13x30x45 video tokens), head_dim 64, bf16, default ratios."""
+    from psa_b200 import synthetic
+    layer_case(P, "cogvideox_5b_bf16", synthetic.COGVIDEOX_5B, (0, 2), torch.bfloat16, 64, C.DEFAULT_RATIOS,
+               po_cell_budget=0.02, mask_budget=0.98, rel_budget=0.25)
+
+
+def test_wan_1_3b_shape_bf16(P):
+    """32760 tokens (21x30x52), head_dim 128, bf16, 90 % ratios; the last query block holds 120 rows."""
+    from psa_b200 import synthetic
+    layer_case(P, "wan2.1_1.3b_bf16", synthetic.WAN_1_3B, (0, 1), torch.bfloat16, 64, C.RATIOS_90,
+               po_cell_budget=0.02, mask_budget=0.98, rel_budget=0.25)
+
+
+def test_wan_14b_token_count_stages(P):
+    """75600 tokens (21x45x80): 1182-wide index rows, a 592nd query block of 80 rows.  Pyramid bit for bit, scores,
+    assignment bit for bit on the oracle's scores, and the forward on three query blocks of one head (first, middle,
+    ragged last) against the oracle's dense masked softmax."""
+    from psa_b200 import synthetic
+    q, k, v = inputs(synthetic.WAN_14B, (0, 1), torch.bfloat16)
+    S = q.shape[2]
+    assert S == 75600
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    (k2, k4, k8), (v2, v4, v8) = P.ops.pyramid_kv(kd, vd, 64)
+    ok, ov = O.pyramid_kv(k, 64), O.pyramid_kv(v, 64)
+    for l, a, b in ((2, k2, v2), (4, k4, v4), (8, k8, v8)):
+        assert torch.equal(a.cpu(), ok[l]) and torch.equal(b.cpu(), ov[l])
+    iq, ik = C.sample_idx(41, 1, 1, 128, 32), C.sample_idx(42, 1, 1, 64, 16)
+    ref_po = O.block_scores(q, k, iq, ik, 128, 64)
+    assert ref_po.shape[-2:] == (591, 1182)
+    po = P.ops.block_scores(qd, kd, iq.to(DEV), ik.to(DEV), 128, 64).cpu()
+    cells, rel = score_figures(po, ref_po)
+    ref_mask = O.assign_levels(ref_po, C.RATIOS_90, "topk_newtype", 64, 32)
+    assert torch.equal(P.ops.assign_levels(ref_po.to(DEV), C.RATIOS_90, "topk_newtype", 64, 32).cpu(), ref_mask)
+    own = P.ops.assign_levels(po.to(DEV), C.RATIOS_90, "topk_newtype", 64, 32).cpu()
+    agree = float((own == ref_mask).float().mean())
+    out = P.ops.psa_forward(qd, kd, vd, ref_mask.to(DEV), 128, 64, 32)
+    assert int(out._psa_status.item()) == 0
+    out = out.float().cpu()
+    worst, worst_cos = 0.0, 1.0
+    for m in (0, 295, 590):
+        r0, r1 = m * 128, min((m + 1) * 128, S)
+        ref = O.psa_forward_newmask(q[:, :, r0:r1], k, v, ref_mask[:, :, m:m + 1], 128, 64, 32).float()
+        worst = max(worst, float((out[:, :, r0:r1] - ref).abs().max()))
+        worst_cos = min(worst_cos, cosine(out[:, :, r0:r1], ref))
+    report("wan2.1_14b_tokens_bf16", tokens=S, heads=1, dtype="bf16", po_cells_differ=cells, po_max_rel_to_row_max=rel,
+           mask_agreement=agree, fwd_max_abs=worst, fwd_cosine=worst_cos)
+    assert cells <= 0.02 and rel <= 0.25, (cells, rel)
+    assert agree >= 0.98, agree
+    assert worst <= ATOL_OUT and worst_cos >= COS_OUT, (worst, worst_cos)
+
+
+@pytest.mark.parametrize("variant", ["int64", "strided"])
+def test_legacy_backward_accepts_any_integer_mask_layout(P, variant):
+    """The autograd function must read int64 masks and non-contiguous views like the reference does (it converts once
+    and saves the converted mask for its backward)."""
+    B, H, S, D = 1, 2, 640, 64
+    q, k, v = C.qkv(300, B, H, S, D, torch.bfloat16)
+    do = C.randn(303, (B, H, S, D), torch.bfloat16)
+    m32 = C.legacy_mask(55, B, H, S, True, False)
+    if variant == "int64":
+        mask = m32.to(torch.int64).to(DEV)
+    else:
+        wide = torch.zeros((B, H, m32.shape[2], 2 * m32.shape[3]), dtype=torch.int32)
+        wide[..., ::2] = m32
+        mask = wide.to(DEV)[..., ::2]
+        assert not mask.is_contiguous()
+    fn = P.legacy_sparse_attention_factory(128, 32, 128, causal=True)
+    qd, kd, vd = (x.to(DEV).requires_grad_(True) for x in (q, k, v))
+    o = fn(qd, kd, vd, mask, None)
+    o.backward(do.to(DEV))
+    ro, rlse = O.legacy_forward(q, k, v, m32, causal=True)
+    ref = O.legacy_backward(q, k, v, m32, ro, rlse, do, causal=True)
+    for a, r in zip((qd.grad, kd.grad, vd.grad), ref):
+        a, r = a.float().cpu(), r.float()
+        assert cosine(a, r) >= COS_OUT and float((a - r).abs().max()) <= 2e-2 * max(1.0, float(r.abs().max()))

@@ -87,8 +87,9 @@ class _Pipe:
 def test_installer_shares_one_module_and_dense_preset_is_a_no_op():
     from psa_b200.presets import set_adaptive_sparse_attention, reset_wan_attention_to_dense
     pipe = _Pipe(4, two=True)
-    mod = set_adaptive_sparse_attention(pipe, "Wan2.2_A14B", inference_num=40, video_shape=[832, 480, 81])
-    assert mod is not None and mod.layer_num == 4 and mod.inference_num == 40
+    info = set_adaptive_sparse_attention(pipe, "Wan2.2_A14B", inference_num=40, video_shape=[832, 480, 81])
+    mod = pipe.transformer.blocks[0].attn1.inner_attention
+    assert info["type"] == "psa" and mod is not None and mod.layer_num == 4 and mod.inference_num == 40
     mods = {id(b.attn1.inner_attention) for t in (pipe.transformer, pipe.transformer_2) for b in t.blocks}
     assert mods == {id(mod)}
     assert [b.attn1.processor.layer_idx for b in pipe.transformer.blocks] == [0, 1, 2, 3]
@@ -96,7 +97,7 @@ def test_installer_shares_one_module_and_dense_preset_is_a_no_op():
     reset_wan_attention_to_dense(pipe)
     assert all(b.attn1.inner_attention is None for b in pipe.transformer.blocks)
     pipe2 = _Pipe(2)
-    assert set_adaptive_sparse_attention(pipe2, "Wan2.1_14b", video_shape=[832, 480, 81], attention_preset="baseline") is None
+    assert set_adaptive_sparse_attention(pipe2, "Wan2.1_14b", video_shape=[832, 480, 81], attention_preset="baseline")["type"] == "dense"
     assert pipe2.transformer.blocks[0].attn1.processor is None
     with pytest.raises(ValueError):
         set_adaptive_sparse_attention(pipe2, "NotAModel", video_shape=[1, 1, 1])
@@ -144,3 +145,151 @@ def test_sparsity_log_writes_jsonl(tmp_path):
     assert lines[0]["is_warmup"] and lines[0]["per_head_density"] == [] and lines[0]["density"] == 1.0
     assert lines[1]["per_head_density"] == [0.25, 0.75] and lines[1]["density"] == 0.5 and lines[1]["sparsity"] == 0.5
     assert lines[1]["global_step"] == 1 and lines[1]["layer_idx"] == 1
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# The diffusers attention processors on stand-in attention modules (linear layers, norms, a recording inner_attention).
+class _Recorder:
+    def __init__(self):
+        self.calls = []
+
+    def __call__(self, q, k, v, layer_idx):
+        self.calls.append((q.clone(), k.clone(), v.clone(), layer_idx))
+        return q + 0.5 * v          # any function of the operands: the processors must pass it on untouched
+
+
+class _RMS(torch.nn.Module):
+    def __init__(self, dim):
+        super().__init__()
+        self.weight = torch.nn.Parameter(torch.linspace(0.5, 1.5, dim))
+
+    def forward(self, x):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * self.weight
+
+
+def _stub_attn(hidden, heads, *, per_head_norm=False, fused=False, image=False, seed=0):
+    torch.manual_seed(seed)
+    a = torch.nn.Module()
+    a.heads = heads
+    a.to_q, a.to_k, a.to_v = (torch.nn.Linear(hidden, hidden) for _ in range(3))
+    a.norm_q = _RMS(hidden // heads if per_head_norm else hidden)
+    a.norm_k = _RMS(hidden // heads if per_head_norm else hidden)
+    a.to_out = torch.nn.ModuleList([torch.nn.Linear(hidden, hidden), torch.nn.Identity()])
+    a.add_k_proj = a.add_v_proj = None
+    a.is_cross_attention = False
+    a.cross_attention_dim_head = None
+    a.fused_projections = fused
+    if fused:
+        a.to_qkv = torch.nn.Linear(hidden, 3 * hidden)
+        with torch.no_grad():
+            a.to_qkv.weight.copy_(torch.cat([a.to_q.weight, a.to_k.weight, a.to_v.weight]))
+            a.to_qkv.bias.copy_(torch.cat([a.to_q.bias, a.to_k.bias, a.to_v.bias]))
+    if image:
+        a.add_k_proj, a.add_v_proj = torch.nn.Linear(hidden, hidden), torch.nn.Linear(hidden, hidden)
+        a.norm_added_k = _RMS(hidden)
+    a.inner_attention = _Recorder()
+    return a
+
+
+def _rotate_pairs(x, cos_half, sin_half):
+    """(x0 + i x1) * (cos + i sin) on neighbouring channel pairs, written with complex numbers."""
+    z = torch.view_as_complex(x.float().reshape(*x.shape[:-1], -1, 2).contiguous())
+    return torch.view_as_real(z * torch.complex(cos_half.float(), sin_half.float())).flatten(-2)
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_wan_processor_rotates_q_and_k_and_passes_head_major_views(fused):
+    from psa_b200.presets import SparseWanAttnProcessor
+    B, S, H, D = 2, 24, 3, 8
+    attn = _stub_attn(H * D, H, fused=fused)
+    x = torch.randn(B, S, H * D)
+    ang = torch.rand(1, S, 1, D // 2) * 6.28
+    # diffusers hands over full-width tables whose neighbouring entries repeat; the processor reads cos at the even
+    # and sin at the odd positions
+    freqs_cos = torch.cos(ang).repeat_interleave(2, dim=-1)
+    freqs_sin = torch.sin(ang).repeat_interleave(2, dim=-1)
+    freqs_cos[..., 1::2] += 7.0          # entries the processor must NOT read
+    freqs_sin[..., 0::2] -= 7.0
+    out = SparseWanAttnProcessor(5)(attn, x, rotary_emb=(freqs_cos, freqs_sin))
+    (q, k, v, idx), = attn.inner_attention.calls
+    assert idx == 5 and q.shape == (B, H, S, D)
+    q_lin = attn.norm_q(attn.to_q(x)).view(B, S, H, D)
+    k_lin = attn.norm_k(attn.to_k(x)).view(B, S, H, D)
+    assert torch.allclose(q.transpose(1, 2), _rotate_pairs(q_lin, torch.cos(ang), torch.sin(ang)), atol=1e-5)
+    assert torch.allclose(k.transpose(1, 2), _rotate_pairs(k_lin, torch.cos(ang), torch.sin(ang)), atol=1e-5)
+    assert not torch.allclose(q.transpose(1, 2), q_lin, atol=1e-3)          # un-rotated operands would be a silent bug
+    assert torch.allclose(v.transpose(1, 2), attn.to_v(x).view(B, S, H, D), atol=1e-6)
+    expect = attn.to_out[0]((q + 0.5 * v).transpose(1, 2).flatten(2, 3))
+    assert torch.allclose(out, expect, atol=1e-5)
+    # the module's token-major fast path recognises what the processor hands over
+    from psa_b200.attention import token_major_view
+    q_in = attn.norm_q(attn.to_q(x)).unflatten(2, (H, -1)).transpose(1, 2)
+    assert token_major_view(q_in) is not None
+
+
+def test_wan_processor_image_conditioning_branch_adds_dense_attention_over_image_keys():
+    from psa_b200.presets import SparseWanAttnProcessor
+    B, S, H, D = 1, 16, 2, 8
+    attn = _stub_attn(H * D, H, image=True)
+    seen = {}
+
+    def inner(q, k, v, layer_idx):          # cross-attention lengths differ, so this stand-in returns q alone
+        seen["k"] = k.shape
+        return q
+    attn.inner_attention = inner
+    x = torch.randn(B, S, H * D)
+    ctx = torch.randn(B, 512 + 7, H * D)                  # 7 image tokens in front of the 512 text tokens
+    out = SparseWanAttnProcessor(0)(attn, x, encoder_hidden_states=ctx)
+    assert seen["k"] == (B, H, 512, D)                    # keys/values of the sparse call come from the text context
+    k_img = attn.norm_added_k(attn.add_k_proj(ctx[:, :7])).view(B, 7, H, D).transpose(1, 2)
+    v_img = attn.add_v_proj(ctx[:, :7]).view(B, 7, H, D).transpose(1, 2)
+    q_lin = attn.norm_q(attn.to_q(x)).view(B, S, H, D).transpose(1, 2)
+    p = torch.softmax(q_lin @ k_img.transpose(-1, -2) / D ** 0.5, dim=-1)
+    img = (p @ v_img).transpose(1, 2).flatten(2, 3)
+    assert torch.allclose(out, attn.to_out[0](q_lin.transpose(1, 2).flatten(2, 3) + img), atol=1e-5)
+
+
+def test_cogvideox_processor_norms_per_head_and_rotates_video_tokens_only():
+    from psa_b200.presets import SparseCogVideoXAttnProcessor
+    B, S, T, H, D = 2, 20, 6, 2, 8
+    attn = _stub_attn(H * D, H, per_head_norm=True)
+    video, text = torch.randn(B, S, H * D), torch.randn(B, T, H * D)
+    ang = torch.rand(S, D // 2) * 6.28
+    cos, sin = torch.cos(ang).repeat_interleave(2, dim=-1), torch.sin(ang).repeat_interleave(2, dim=-1)
+    out_video, out_text = SparseCogVideoXAttnProcessor(3)(attn, video, text, image_rotary_emb=(cos, sin))
+    (q, k, v, idx), = attn.inner_attention.calls
+    assert idx == 3 and q.shape == (B, H, T + S, D)
+    x = torch.cat([text, video], dim=1)
+    q_lin = attn.norm_q(attn.to_q(x).view(B, T + S, H, D).transpose(1, 2))      # the norm sees D channels: per head
+    k_lin = attn.norm_k(attn.to_k(x).view(B, T + S, H, D).transpose(1, 2))
+    assert torch.allclose(q[:, :, :T], q_lin[:, :, :T], atol=1e-6)              # text tokens are not rotated
+    assert torch.allclose(k[:, :, :T], k_lin[:, :, :T], atol=1e-6)
+    assert torch.allclose(q[:, :, T:], _rotate_pairs(q_lin[:, :, T:], torch.cos(ang), torch.sin(ang)), atol=1e-5)
+    assert torch.allclose(k[:, :, T:], _rotate_pairs(k_lin[:, :, T:], torch.cos(ang), torch.sin(ang)), atol=1e-5)
+    full = attn.to_out[0]((q + 0.5 * v).transpose(1, 2).reshape(B, T + S, H * D))
+    assert torch.allclose(out_video, full[:, T:], atol=1e-5) and torch.allclose(out_text, full[:, :T], atol=1e-5)
+
+
+def test_installers_use_the_reference_names_and_keep_the_original_processor():
+    from psa_b200 import presets
+    for name in ("SparseWanAttnProcessor", "SparseCogVideoXAttnProcessor", "set_block_sparse_attn_wan",
+                 "set_block_sparse_attn_cogvideox", "set_adaptive_sparse_attention", "reset_wan_attention_to_dense"):
+        assert hasattr(presets, name)
+    pipe = _Pipe(3)
+    for b in pipe.transformer.blocks:
+        b.attn1.processor = "stock"
+    info = presets.set_adaptive_sparse_attention(pipe, "Wan2.1_1.3b", video_shape=[832, 480, 81], attention_preset="psa_topk")
+    assert info["name"] == "psa_topk"
+    a0 = pipe.transformer.blocks[0].attn1
+    assert isinstance(a0.processor, presets.SparseWanAttnProcessor) and a0.origin_processor == "stock"
+    presets.reset_wan_attention_to_dense(pipe)
+    assert a0.processor == "stock" and a0.inner_attention is None
+
+    class _Cog:
+        def __init__(self, n):
+            self.transformer_blocks = [_Block() for _ in range(n)]
+    cog = _Cog(2)
+    info = presets.set_adaptive_sparse_attention(cog, "CogVideo_5b", video_shape=[720, 480, 49], attention_preset="psa_balanced")
+    mod = cog.transformer_blocks[1].attn1.inner_attention
+    assert isinstance(cog.transformer_blocks[1].attn1.processor, presets.SparseCogVideoXAttnProcessor)
+    assert mod.model_type == "cogvideo" and mod.layer_num == 2 and mod.config.text_length == 226

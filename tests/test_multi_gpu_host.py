@@ -1,4 +1,4 @@
-"""CPU, world_size 2 (gloo): the sequence-sharded <-> head-sharded reshuffle used around the PSA layer."""
+"""CPU (gloo, world_size 2 to 8): the sequence-sharded <-> head-sharded reshuffles used around the PSA layer."""
 import os
 import sys
 
@@ -82,3 +82,51 @@ def test_peer_exchange_address_contract_matches_the_reshuffle():
     for r in range(world):
         assert torch.equal(pushed[r], want_head_shards[r]) and torch.equal(pulled[r], want_head_shards[r])
         assert torch.equal(outs[r], seq_shards[r] * 3.0)
+
+
+def _grid_worker(rank, world, port, H, S, D, bm, ret):
+    sys.path.insert(0, os.path.join(ROOT, "pyramid-sparse-attention_b200"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from psa_b200.parallel import GridShard
+    g = torch.Generator().manual_seed(11)
+    full = torch.randn(3, S, H, D, generator=g)
+    sl = S // world
+    local = full[:, rank * sl:(rank + 1) * sl].contiguous()
+    gs = GridShard(world, rank, H, S, D, block_m=bm)
+    q, k, v = gs.to_grid(local)
+    h0, h1 = gs.head_range()
+    r0, r1 = gs.query_range()
+    ok_in = (torch.equal(q, full[0, r0:r1, h0:h1].permute(1, 0, 2)) and torch.equal(k, full[1, :, h0:h1].permute(1, 0, 2))
+             and torch.equal(v, full[2, :, h0:h1].permute(1, 0, 2)))
+    o = q * 2.0 + v[:, r0:r1]                                     # any row-wise function of the part
+    back = gs.to_seq(o)
+    expect = (full[0] * 2.0 + full[2])[rank * sl:(rank + 1) * sl].permute(1, 0, 2)
+    ret[rank] = (ok_in, torch.equal(back, expect), r0 % bm == 0)
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world,H,S,bm", [(4, 6, 4 * 37, 16), (8, 12, 8 * 45, 32), (2, 4, 60, 16)])
+def test_grid_shard_head_groups_times_query_parts(world, H, S, bm):
+    """Head counts that do not divide the rank count: gcd(H, world) head groups x world/gcd query parts; the reshuffles
+    from and to sequence shards are exact, and the parts are cut on query-block boundaries even when a rank's token
+    shard straddles the cut."""
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 31000 + (os.getpid() + world) % 2000
+    mp.spawn(_grid_worker, args=(world, port, H, S, 4, bm, ret), nprocs=world, join=True)
+    assert all(ret[r] == (True, True, True) for r in range(world)), dict(ret)
+
+
+def test_grid_shard_layout_for_12_heads_on_8_ranks():
+    sys.path.insert(0, os.path.join(ROOT, "pyramid-sparse-attention_b200"))
+    from psa_b200.parallel import GridShard
+    parts = [GridShard(8, r, 12, 32760, 128) for r in range(8)]
+    assert parts[0].groups == 4 and parts[0].parts == 2 and parts[0].heads_per_rank == 3
+    assert [p.head_range() for p in parts] == [(0, 3), (0, 3), (3, 6), (3, 6), (6, 9), (6, 9), (9, 12), (9, 12)]
+    assert parts[0].query_range() == (0, 16384) and parts[1].query_range() == (16384, 32760)
+    # when the heads divide, it is the plain head sharding: one part covering every query block
+    plain = GridShard(8, 5, 40, 75600, 128)
+    assert plain.parts == 1 and plain.head_range() == (25, 30) and plain.query_range() == (0, 75600)

@@ -41,6 +41,35 @@ def test_static_scratch_matches_the_allocating_entry_point_twice():
         ref = ops.block_scores(q, k, iq, ik, bm, bn)
         torch.cuda.synchronize()
         assert torch.equal(po, ref)
+        # the same call again, output buffer already there: the device's free memory must not move while it runs
+        # (the driver's figure, so an allocation by any route would show)
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        stream = C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream)
+        rc = lib.psa_block_scores_static(q.data_ptr(), k.data_ptr(), iq.data_ptr(), ik.data_ptr(), po.data_ptr(), H, S, S, D,
+                                         bm, bn, ops._DT[q.dtype], 0, stream)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert rc == 0 and free_after == free_before, (free_before, free_after)
+        assert torch.equal(po, ref)
+
+
+def test_static_scratch_capacity_counts_the_calls_own_head_dim():
+    """44 heads x 8192 tokens in bf16 would need 66.3 MiB of scratch at head_dim 128 (what the public size query assumes)
+    but only ~44 MiB at head_dim 64: the allocation-free entry point must take it."""
+    from psa_b200 import _lib, ops
+    lib = _lib.lib
+    H, S, D, bm, bn = 44, 8192, 64, 128, 64
+    assert lib.psa_block_scores_scratch_bytes(H, S, S, bm, bn, 2) > lib.psa_block_scores_static_capacity()
+    g = torch.Generator(device=DEV).manual_seed(5)
+    q = torch.randn((1, H, S, D), device=DEV, dtype=torch.bfloat16, generator=g)
+    k = torch.randn((1, H, S, D), device=DEV, dtype=torch.bfloat16, generator=g)
+    iq = cases.sample_idx(3, 1, H, bm, bm // 4).to(DEV).to(torch.int32).contiguous()
+    ik = cases.sample_idx(4, 1, H, bn, bn // 4).to(DEV).to(torch.int32).contiguous()
+    rc, po = _call_static(lib, q, k, iq, ik, bm, bn)
+    assert rc == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(po, ops.block_scores(q, k, iq, ik, bm, bn))
 
 
 def test_static_scratch_rejects_oversized_calls():
