@@ -221,6 +221,162 @@ def legacy_level_mask(seed, B, H, S):
     return torch.from_numpy(m.astype(np.int32))
 
 
+def run_causal_training(args, workload, synthetic):
+    """--workload causal-legacy-fwd-bwd: one training step of the legacy (old-format mask) kernels, causal forward +
+    backward on B=2 x 16 heads x 32768 tokens x 128, bf16, random level mask (token density ~0.46 of the causal triangle),
+    dO ~ N(0,1).  The (batch, head) pairs are independent: N GPUs take 32/N of them each, no collective."""
+    import torch.distributed as dist
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    B, H, D, S = workload["batch"], workload["heads"], workload["head_dim"], synthetic.seq_len(workload)
+    if args.heads:
+        H = args.heads
+    f_dense = 3.5 * 4.0 * B * H * float(S) * S * D / 2            # forward 1 + backward 2.5, causal half
+    cfg_json = {"workload": workload["name"], "B": B, "heads": H, "head_dim": D, "seq_len": S, "grid": list(workload["grid"]),
+                "causal": True, "mask": "random levels {0,1,2,4,8} p=(.2,.3,.2,.15,.15), column 0 at level 1",
+                "block": 128, "parallelism": f"(batch, head) pairs/{world}", "l2": "inputs (q,k,v,dO) larger than L2"}
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        tf, sec, sample = oracle_legacy_sample_time(workload, args.steps, args.warmup)
+        print(json.dumps({
+            "impl": "reference", "metric": "psa_attn_dense_equiv_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": cfg_json,
+            "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    import psa_b200
+    from psa_b200 import ops, _lib
+    launches = LaunchCounter(_lib.lib)
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        assert (B * H) % world == 0, "(batch, head) pairs must divide by the number of GPUs"
+    per = B * H // world
+    mine = range(rank * per, (rank + 1) * per)
+    dtype = torch.bfloat16
+    wl = dict(workload); wl["heads"] = H
+    parts = {0: [], 1: [], 2: []}
+    for idx in mine:
+        b, h = idx // H, idx % H
+        for i, x in enumerate(synthetic.make_qkv(wl, 1000 + 7919 * b, dtype, dev, head_range=(h, h + 1))):
+            parts[i].append(x)
+    q, k, v = (torch.cat(parts[i], dim=1).contiguous() for i in range(3))                  # [1, per, S, D]
+    do = torch.randn(q.shape, device=dev, dtype=dtype, generator=torch.Generator(device=dev).manual_seed(5 + rank))
+    mask_all = legacy_level_mask(77, B, H, S).view(1, B * H, -(-S // 128), -(-S // 128))
+    mask = mask_all[:, rank * per:(rank + 1) * per].contiguous().to(dev)
+    n = mask.shape[-1]
+    dens = float(torch.where(mask > 0, 1.0 / mask.clamp(min=1).float(), torch.zeros((), device=dev)).sum() / (per * n * (n + 1) / 2))
+    scale = D ** -0.5
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def step(rec=None):
+        a, b, c = ev(), ev(), ev()
+        a.record()
+        o, lse, pooled = ops.legacy_forward(q, k, v, mask, True, scale, need_lse=True)
+        b.record()
+        grads = ops.legacy_backward(q, k, v, mask, o, lse, do, True, scale, pooled)
+        c.record()
+        if rec is not None:
+            rec.append((a, b, c))
+        return o, grads
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        o, grads = step()
+    barrier()
+    status = int(ops.status_word(dev).item())
+    rec = []
+    barrier()
+    sampler.mark_begin()
+    e0, e1 = ev(), ev()
+    torch.cuda.profiler.start()
+    e0.record()
+    launches.on = True
+    for _ in range(args.steps):
+        step(rec)
+    launches.on = False
+    e1.record()
+    barrier()
+    torch.cuda.profiler.stop()
+    sampler.mark_end()
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    fwd_ms = sum(a.elapsed_time(b) for a, b, _ in rec) / len(rec)
+    bwd_ms = sum(b.elapsed_time(c) for _, b, c in rec) / len(rec)
+
+    e2e = None
+    if not args.no_e2e:
+        host = [x.cpu().pin_memory() for x in (q, k, v, do)]
+        staged = [torch.empty_like(x) for x in (q, k, v, do)]
+        back = [torch.empty(q.shape, dtype=dtype).pin_memory() for _ in range(3)]
+
+        def e2e_step():
+            for d_, h_ in zip(staged, host):
+                d_.copy_(h_, non_blocking=True)
+            qq, kk, vv, dd = staged
+            o_, lse_, pooled_ = ops.legacy_forward(qq, kk, vv, mask, True, scale, need_lse=True)
+            g_ = ops.legacy_backward(qq, kk, vv, mask, o_, lse_, dd, True, scale, pooled_)
+            for h_, d_ in zip(back, g_):
+                h_.copy_(d_, non_blocking=True)
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        a0, a1 = ev(), ev()
+        a0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        a1.record()
+        barrier()
+        te = torch.tensor([a0.elapsed_time(a1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        ms_e2e = float(te.item()) / args.steps
+        nb = q.numel() * 2
+        e2e = {"value": f_dense / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": 4 * nb * world, "d2h_bytes_per_step": 3 * nb * world}
+    if world > 1 and rank != 0:
+        dist.destroy_process_group()
+        return
+    peaks = load_peaks()
+    peak_tf = peaks["bf16_tflops_sustained"] or peaks["bf16_tflops"]
+    f_surv_fwd = 4.0 * per * float(S) * S * D / 2 * dens            # surviving forward work of this rank
+    bwd_tf = 2.5 * f_surv_fwd / (bwd_ms * 1e-3) / 1e12
+    line = {
+        "metric": "psa_attn_dense_equiv_tflops", "value": f_dense / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": cfg_json,
+        "stage_ms": {"forward": fwd_ms, "backward": bwd_ms}, "density": dens, "kernel_status": status,
+        "gpu_launches": launches.count,
+        "surviving_tflops_forward": f_surv_fwd / (fwd_ms * 1e-3) / 1e12,
+        # the backward (dQ kernel + dK/dV kernel + small ones): 2.5x the surviving forward work; what the kernels execute on
+        # top of that (both kernels recompute S and dP; level groups of the dK/dV kernel carry unselected key blocks) is
+        # not counted
+        "roofline": {"bound": "tensor", "kernel": "bwd_dq_tc_kernel + bwd_dkdv_tc_kernel", "achieved": bwd_tf, "peak": peak_tf,
+                     "unit": "TFLOP/s", "frac": bwd_tf / peak_tf, "traffic": None,
+                     "peak_source": f"{peaks['source']} (sustained bf16: kernels timed inside a long step)"},
+        "clocks": clocks, "e2e": e2e}
+    if not args.no_cpu_baseline and world == 1:
+        tf, sec, sample = oracle_legacy_sample_time(workload, 1, 0)
+        line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": sample, "seconds": sec}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -244,6 +400,8 @@ def main():
 
     synthetic = load_synthetic()
     workload = dict(synthetic.WORKLOADS[args.workload])
+    if workload["name"] == "causal-legacy-fwd-bwd":
+        return run_causal_training(args, workload, synthetic)
     if args.heads:
         workload["heads"] = args.heads
         workload["name"] += f"-{args.heads}heads"

@@ -243,6 +243,22 @@ int psa_legacy_bwd_tc(const void* q, const void* k, const void* v, const void* k
                       const float* lse, const void* dout, void* dq, void* dk, void* dv, float* delta, int64_t bh,
                       int64_t seq, int head_dim, int mask_cols, float sm_scale, int causal, int dtype, void* stream);
 
+/* The same backward on tcgen05 tensor cores with TMEM accumulators (f16/bf16, head_dim 64/128): the kernel of a training
+ * step.  Same reference code as psa_legacy_bwd (psa_kernel_legacy.py:947-1320: driver :947-1069, dQ :1085-1156, dK/dV
+ * :1159-1234, pool/fold :1298-1320) and the same rounding rule as psa_legacy_bwd_tc.
+ * kimg/vimg: psa_pyramid_kv_images(k, v, block_n = 128), the buffers the forward psa_legacy_fwd_images read.  out/lse:
+ * the forward's results.  scratch: psa_legacy_bwd_scratch_bytes() bytes, 256-byte aligned (row statistics, the fp32 sums
+ * of the pooled rows of every level, work lists, two work counters); nothing in it needs initialising.
+ * Launches: row statistics, work list, dQ (one persistent CTA per SM: per query block the selected key blocks of all
+ * levels packed into 128-token tiles), dK/dV (per level and 128 pooled key rows: every query block that selected them),
+ * fold (pooled sums -> original positions, replicate-padded tail into the last token, one rounding).
+ * status: device int32 word, written non-zero if a bounded wait inside a kernel expired (may be NULL). */
+size_t psa_legacy_bwd_scratch_bytes(int64_t bh, int64_t seq, int head_dim);
+int psa_legacy_bwd_tcgen05(const void* q, const void* kimg, const void* vimg, const int32_t* mask, const void* out,
+                           const float* lse, const void* dout, void* dq, void* dk, void* dv, void* scratch,
+                           size_t scratch_bytes, int64_t bh, int64_t seq, int head_dim, int mask_cols, float sm_scale,
+                           int causal, int dtype, int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * Head sharding over the GPUs of one node, by peer memory instead of an all-to-all collective.  No counterpart in the
  * reference (it runs on one GPU); these calls sit where a sequence-parallel host model would otherwise call

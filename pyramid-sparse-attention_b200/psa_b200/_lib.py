@@ -68,6 +68,8 @@ SIGNATURES = {
     "psa_legacy_fwd": (_i, [_p] * 12 + [_i64, _i64, _i, _i, _f, _i, _i, _p]),
     "psa_legacy_bwd": (_i, [_p] * 17 + [_i64, _i64, _i, _i, _f, _i, _i, _p]),
     "psa_legacy_bwd_tc": (_i, [_p] * 17 + [_i64, _i64, _i, _i, _f, _i, _i, _p]),
+    "psa_legacy_bwd_scratch_bytes": (_sz, [_i64, _i64, _i]),
+    "psa_legacy_bwd_tcgen05": (_i, [_p] * 11 + [_sz, _i64, _i64, _i, _i, _f, _i, _i, _p, _p]),
 }
 for _name, (_res, _args) in SIGNATURES.items():
     _fn = getattr(lib, _name)          # AttributeError here = the library does not export a declared symbol

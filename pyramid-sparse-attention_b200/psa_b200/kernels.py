@@ -28,18 +28,18 @@ class _LegacySparseAttention(torch.autograd.Function):
         # the reference takes int32 or int64 masks with any strides (psa_kernel_legacy.py:1254); forward and backward
         # both read the one normalised copy
         mask = ops._mask32(block_sparse_dense)
-        o, lse, pyramid = ops.legacy_forward(qc, kc, vc, mask, causal, sm_scale, need_lse=need_backward)
+        o, lse, pooled = ops.legacy_forward(qc, kc, vc, mask, causal, sm_scale, need_lse=need_backward)
         if need_backward:
-            ctx.save_for_backward(qc, kc, vc, mask, o, lse, *pyramid[0], *pyramid[1])
+            ctx.save_for_backward(qc, kc, vc, mask, o, lse)
+            ctx.pooled = pooled            # the pooled K/V the forward built (not part of the graph)
             ctx.sm_scale = sm_scale
             ctx.causal = causal
         return o
 
     @staticmethod
     def backward(ctx, do):
-        q, k, v, mask, o, lse, k2, k4, k8, v2, v4, v8 = ctx.saved_tensors
-        dq, dk, dv = ops.legacy_backward(q, k, v, mask, o, lse, do.contiguous(), ctx.causal, ctx.sm_scale,
-                                         ((k2, k4, k8), (v2, v4, v8)))
+        q, k, v, mask, o, lse = ctx.saved_tensors
+        dq, dk, dv = ops.legacy_backward(q, k, v, mask, o, lse, do.contiguous(), ctx.causal, ctx.sm_scale, ctx.pooled)
         return dq, dk, dv, None, None, None
 
 

@@ -478,9 +478,36 @@ def psa_forward(q, k, v, mask, block_m: int, block_n: int, tile_n: int, sm_scale
     return o
 
 
+class LegacyKV:
+    """Pooled K/V of the legacy kernels (block 128) in the two layouts their kernels read, each built on first use: tile
+    images (tcgen05 forward and backward) and row-major levels 2/4/8 (scalar and warp-level-mma kernels)."""
+
+    def __init__(self, k: torch.Tensor, v: torch.Tensor, images: Optional[KVImages] = None, rows=None):
+        self.k, self.v, self._images, self._rows = k, v, images, rows
+
+    def images(self) -> KVImages:
+        if self._images is None:
+            self._images = pyramid_kv_images(self.k, self.v, 128)
+        return self._images
+
+    def rows(self):
+        if self._rows is None:
+            self._rows = pyramid_kv(self.k, self.v, 128)
+        return self._rows
+
+
+IMPL_WARP_MMA = 3      # legacy backward only: the warp-level mma.sync kernels
+
+
+def _legacy_tc_ok(q: torch.Tensor, sm_scale: float) -> bool:
+    return q.dtype in (torch.float16, torch.bfloat16) and -(-q.shape[2] // 128) + 5 <= 1472 and sm_scale > 0
+
+
 def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float] = None, need_lse: bool = False,
                    pyramid=None, impl: int = IMPL_AUTO):
-    """Legacy forward on the dense old-format mask (_forward, src/psa_triton/kernels/psa_kernel_legacy.py:837-938)."""
+    """Legacy forward on the dense old-format mask (_forward, src/psa_triton/kernels/psa_kernel_legacy.py:837-938).
+    Returns (o, lse or None, LegacyKV or None): a training step (need_lse) gets the log-sum-exp rows and the pooled
+    K/V for its backward."""
     _need_cuda(q, k, v, mask)
     assert q.shape[-1] == k.shape[-1] == v.shape[-1]
     assert k.shape[2] == v.shape[2]
@@ -489,12 +516,10 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
     B, H, S, D = q.shape
     if sm_scale is None:
         sm_scale = D ** -0.5
-    n128 = -(-S // 128)
-    if (pyramid is None and impl != IMPL_SCALAR and q.dtype in (torch.float16, torch.bfloat16) and n128 + 5 <= 1472
-            and sm_scale > 0):
-        # 16-bit tensors: the tcgen05 forward on tile images.  A training step (need_lse) also gets the log-sum-exp rows
-        # and the row-major pyramid its backward reads (one more pass over k and v).
-        imgs = pyramid_kv_images(k, v, 128)
+    kv = pyramid if isinstance(pyramid, LegacyKV) else LegacyKV(k, v, rows=pyramid)
+    if impl != IMPL_SCALAR and _legacy_tc_ok(q, sm_scale):
+        # 16-bit tensors: the tcgen05 forward on tile images (which the tcgen05 backward reads again)
+        imgs = kv.images()
         with torch.cuda.device(q.device):
             o = torch.empty_like(q)
             lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if need_lse else None
@@ -504,10 +529,8 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
                                            B * H, S, D, mask.shape[-1], float(sm_scale), int(causal), _dt(q), _ptr(status), _stream(q))
         check(rc, "psa_legacy_fwd_images")
         o._psa_status = status
-        return o, lse, (pyramid_kv(k, v, 128) if need_lse else None)
-    if pyramid is None:
-        pyramid = pyramid_kv(k, v, 128)
-    (k2, k4, k8), (v2, v4, v8) = pyramid
+        return o, lse, (kv if need_lse else None)
+    (k2, k4, k8), (v2, v4, v8) = kv.rows()
     with torch.cuda.device(q.device):
         o = torch.empty_like(q)
         lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if need_lse else None
@@ -515,40 +538,48 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
                                 _ptr(mask), _ptr(o), _ptr(lse), B * H, S, D, mask.shape[-1], float(sm_scale), int(causal),
                                 _dt(q), _stream(q))
     check(rc, "psa_legacy_fwd")
-    return o, lse, pyramid
+    return o, lse, kv
 
 
 def legacy_forward_tc(q, k, v, mask, sm_scale: Optional[float] = None, need_lse: bool = True, causal: bool = False):
     """Legacy forward on the tcgen05 kernel (psa_legacy_fwd_images); returns (o, lse or None)."""
     _need_cuda(q, k, v, mask)
-    q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _mask32(mask)
-    B, H, S, D = q.shape
-    sm_scale = D ** -0.5 if sm_scale is None else sm_scale
-    imgs = pyramid_kv_images(k, v, 128)
-    with torch.cuda.device(q.device):
-        o = torch.empty_like(q)
-        lse = torch.empty((B, H, S), dtype=torch.float32, device=q.device) if need_lse else None
-        scratch = torch.empty(lib.psa_legacy_index_bytes(B * H, S) // 4, dtype=torch.int32, device=q.device)
-        status = status_word(q.device)
-        rc = lib.psa_legacy_fwd_images(_ptr(q), _ptr(imgs.kimg), _ptr(imgs.vimg), _ptr(mask), _ptr(scratch), _ptr(o), _ptr(lse),
-                                       B * H, S, D, mask.shape[-1], float(sm_scale), int(causal), _dt(q), _ptr(status), _stream(q))
-    check(rc, "psa_legacy_fwd_images")
-    o._psa_status = status
+    sm_scale = q.shape[-1] ** -0.5 if sm_scale is None else sm_scale
+    if not _legacy_tc_ok(q, sm_scale):
+        raise ValueError("the tcgen05 legacy forward needs f16/bf16 tensors, at most 1467 blocks of 128 tokens and a positive scale")
+    o, lse, _ = legacy_forward(q, k, v, mask, causal, sm_scale, need_lse=need_lse, impl=IMPL_TENSOR)
     return o, lse
 
 
-def legacy_backward(q, k, v, mask, o, lse, do, causal: bool, sm_scale: float, pyramid, impl: int = IMPL_AUTO):
+def legacy_backward(q, k, v, mask, o, lse, do, causal: bool, sm_scale: float, pyramid=None, impl: int = IMPL_AUTO):
     """dQ, dK, dV of the legacy kernel (_sparse_attention.backward, psa_kernel_legacy.py:947-1069).  16-bit tensors run
-    on the tensor-core kernels unless impl == IMPL_SCALAR."""
+    on the tcgen05 kernels (impl IMPL_AUTO / IMPL_TENSOR); IMPL_WARP_MMA selects the warp-level mma kernels, IMPL_SCALAR
+    the fp32 ones (the only choice for float32 tensors).  pyramid: the LegacyKV of the forward (rebuilt if None)."""
     _need_cuda(q, k, v, mask, o, lse, do)
-    do, mask = _flat_bh(do), _mask32(mask)
+    q, k, v, o, do, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _flat_bh(o), _flat_bh(do), _mask32(mask)
     B, H, S, D = q.shape
-    (k2, k4, k8), (v2, v4, v8) = pyramid
+    kv = pyramid if isinstance(pyramid, LegacyKV) else LegacyKV(k, v, rows=pyramid)
+    half = q.dtype in (torch.float16, torch.bfloat16)
+    if impl == IMPL_AUTO:
+        impl = IMPL_TENSOR if (half and _legacy_tc_ok(q, sm_scale)) else IMPL_SCALAR
     with torch.cuda.device(q.device):
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        if impl == IMPL_TENSOR:
+            if not (half and _legacy_tc_ok(q, sm_scale)):
+                raise ValueError("the tcgen05 legacy backward needs f16/bf16 tensors, at most 1467 blocks of 128 tokens and a positive scale")
+            imgs = kv.images()
+            nbytes = lib.psa_legacy_bwd_scratch_bytes(B * H, S, D)
+            scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+            status = status_word(q.device)
+            rc = lib.psa_legacy_bwd_tcgen05(_ptr(q), _ptr(imgs.kimg), _ptr(imgs.vimg), _ptr(mask), _ptr(o), _ptr(lse), _ptr(do),
+                                            _ptr(dq), _ptr(dk), _ptr(dv), _ptr(scratch), nbytes, B * H, S, D, mask.shape[-1],
+                                            float(sm_scale), int(causal), _dt(q), _ptr(status), _stream(q))
+            check(rc, "psa_legacy_bwd_tcgen05")
+            dq._psa_status = status
+            return dq, dk, dv
+        (k2, k4, k8), (v2, v4, v8) = kv.rows()
         delta = torch.empty((B, H, S), dtype=torch.float32, device=q.device)
-        use_tc = impl == IMPL_TENSOR or (impl == IMPL_AUTO and q.dtype in (torch.float16, torch.bfloat16))
-        fn = lib.psa_legacy_bwd_tc if use_tc else lib.psa_legacy_bwd
+        fn = lib.psa_legacy_bwd_tc if impl == IMPL_WARP_MMA else lib.psa_legacy_bwd
         rc = fn(_ptr(q), _ptr(k), _ptr(v), _ptr(k2), _ptr(k4), _ptr(k8), _ptr(v2), _ptr(v4), _ptr(v8),
                 _ptr(mask), _ptr(o), _ptr(lse), _ptr(do), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(delta),
                 B * H, S, D, mask.shape[-1], float(sm_scale), int(causal), _dt(q), _stream(q))

@@ -200,11 +200,17 @@ def test_causal_legacy_full_size_properties(P):
     for a, a2 in zip(grads, grads2):
         assert bool(torch.isfinite(a).all())
         assert float((a2.float() - 2 * a.float()).abs().max()) <= 1e-2 * float(a.float().abs().max())
-    # the tensor-core backward (what the calls above ran) against the scalar one
-    ref = P.ops.legacy_backward(q, k, v, mask, o_sc, lse_sc, do, True, D ** -0.5, pyr, impl=P.ops.IMPL_SCALAR)
-    for a, r in zip(grads, ref):
-        a, r = a.float(), r.float()
-        assert cosine(a, r) >= COS_OUT and float((a - r).abs().max()) <= 2e-2 * max(1.0, float(r.abs().max()))
+    assert int(grads[0]._psa_status.item()) == 0
+    # the tcgen05 backward (what the calls above ran) is bitwise repeatable, and agrees with the warp-level mma kernels
+    # and the scalar ones (themselves checked against the oracle at small sizes)
+    again = P.ops.legacy_backward(q, k, v, mask, o_sc, lse_sc, do, True, D ** -0.5, pyr)
+    for a, b in zip(grads, again):
+        assert torch.equal(a, b)
+    for impl in (P.ops.IMPL_WARP_MMA, P.ops.IMPL_SCALAR):
+        ref = P.ops.legacy_backward(q, k, v, mask, o_sc, lse_sc, do, True, D ** -0.5, pyr, impl=impl)
+        for a, r in zip(grads, ref):
+            a, r = a.float(), r.float()
+            assert cosine(a, r) >= COS_OUT and float((a - r).abs().max()) <= 2e-2 * max(1.0, float(r.abs().max()))
 
 
 # ------------------------------------------------------------------ K similarity ---------------------
@@ -441,12 +447,16 @@ def test_forward_tile_image_path_vs_oracle(P, golden, case, dt):
     assert float((out.float().cpu() - ref).abs().max()) <= ATOL_OUT and cosine(out.float().cpu(), ref) >= COS_OUT
 
 
+@pytest.mark.parametrize("impl", ["tcgen05", "warp_mma"])
 @pytest.mark.parametrize("dt", ["bf16", "fp16"])
-@pytest.mark.parametrize("S,D,causal", [(700, 128, True), (700, 64, False), (1100, 128, False), (513, 64, True)])
-def test_legacy_backward_tensor_core_vs_oracle(P, dt, S, D, causal):
-    """Tensor-core backward: mixed levels on the causal diagonal (odd copy counts) and a ragged tail (pad fold), against
-    the oracle on the same 16-bit inputs and against the scalar kernels."""
+@pytest.mark.parametrize("S,D,causal", [(700, 128, True), (700, 64, False), (1100, 128, False), (513, 64, True), (2048, 128, True),
+                                        (1664, 64, True), (128, 128, True), (77, 64, False)])
+def test_legacy_backward_tensor_core_vs_oracle(P, dt, S, D, causal, impl):
+    """Tensor-core backward (tcgen05 kernels, and the warp-level mma kernels): mixed levels on the causal diagonal (odd
+    copy counts), ragged tails (pad fold), level groups that end inside a 128-row tile, against the oracle on the same
+    16-bit inputs and against the scalar kernels."""
     H, B = 2, 1
+    impl = P.ops.IMPL_TENSOR if impl == "tcgen05" else P.ops.IMPL_WARP_MMA
     q, k, v = C.qkv(420, B, H, S, D, C.DT[dt])
     do = C.randn(424, (B, H, S, D), C.DT[dt])
     mask = C.legacy_mask(425, B, H, S, causal, False)
@@ -455,10 +465,40 @@ def test_legacy_backward_tensor_core_vs_oracle(P, dt, S, D, causal):
     qd, kd, vd, md, dod = q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), do.to(DEV)
     o, lse, pyr = P.ops.legacy_forward(qd, kd, vd, md, causal, need_lse=True)
     assert lse is not None and pyr is not None
-    tc = P.ops.legacy_backward(qd, kd, vd, md, o, lse, dod, causal, D ** -0.5, pyr, impl=P.ops.IMPL_TENSOR)
+    tc = P.ops.legacy_backward(qd, kd, vd, md, o, lse, dod, causal, D ** -0.5, pyr, impl=impl)
+    if impl == P.ops.IMPL_TENSOR:
+        assert int(tc[0]._psa_status.item()) == 0
     sc = P.ops.legacy_backward(qd, kd, vd, md, o, lse, dod, causal, D ** -0.5, pyr, impl=P.ops.IMPL_SCALAR)
     for g, r, s_ in zip(tc, ref, sc):
         g, r, s_ = g.float().cpu(), r.float(), s_.float().cpu()
         assert bool(torch.isfinite(g).all())
         assert cosine(g, r) >= COS_OUT and float((g - r).abs().max()) <= 2e-2 * max(1.0, float(r.abs().max()))
         assert cosine(g, s_) >= COS_OUT and float((g - s_).abs().max()) <= 2e-2 * max(1.0, float(s_.abs().max()))
+
+
+def test_legacy_backward_tcgen05_sparse_and_empty_rows(P):
+    """Masks the packed streams must survive: query blocks that select nothing (dQ rows of zeros), key blocks nobody
+    selects (dK/dV rows of zeros), a single level only, and non-causal rows longer than one tile."""
+    B, H, S, D = 1, 2, 1280, 128
+    n = S // 128
+    q, k, v = C.qkv(430, B, H, S, D, torch.bfloat16)
+    do = C.randn(434, (B, H, S, D), torch.bfloat16)
+    mask = torch.zeros((B, H, n, n), dtype=torch.int32)
+    mask[0, 0, 0, :] = 8                      # head 0: only level 8, one query block
+    mask[0, 0, 3, 2] = 1
+    mask[0, 0, 5, :] = torch.tensor([1, 2, 4, 8, 0, 1, 2, 4, 8, 0], dtype=torch.int32)
+    mask[0, 1] = C.legacy_mask(9, 1, 1, S, False, False)[0, 0]
+    mask[0, 1, 4] = 0                         # an empty query block
+    mask[0, 1, :, 7] = 0                      # a key block nobody reads
+    o_ref, lse_ref = O.legacy_forward(q, k, v, mask, False)
+    ref = O.legacy_backward(q, k, v, mask, o_ref, lse_ref, do, False)
+    qd, kd, vd, md, dod = q.to(DEV), k.to(DEV), v.to(DEV), mask.to(DEV), do.to(DEV)
+    o, lse, pyr = P.ops.legacy_forward(qd, kd, vd, md, False, need_lse=True)
+    tc = P.ops.legacy_backward(qd, kd, vd, md, o, lse, dod, False, D ** -0.5, pyr, impl=P.ops.IMPL_TENSOR)
+    assert int(tc[0]._psa_status.item()) == 0
+    for g, r in zip(tc, ref):
+        g, r = g.float().cpu(), r.float()
+        assert bool(torch.isfinite(g).all())
+        assert cosine(g, r) >= COS_OUT and float((g - r).abs().max()) <= 2e-2 * max(1.0, float(r.abs().max()))
+    assert float(tc[0][0, 1, 4 * 128:5 * 128].abs().max()) == 0.0
+    assert float(tc[1][0, 1, 7 * 128:8 * 128].abs().max()) == 0.0 and float(tc[2][0, 1, 7 * 128:8 * 128].abs().max()) == 0.0
