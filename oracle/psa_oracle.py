@@ -470,7 +470,9 @@ def legacy_backward(q, k, v, mask, o, lse, do, causal: bool = False, sm_scale: f
         if causal:
             tok = tok & (pos_q[:, None] >= pos_k[None, :])
         s = qd @ kl.transpose(-1, -2) * scale
-        p = torch.exp(s - lse.double().unsqueeze(-1)) * tok
+        # pairs outside the mask are never visited by the kernels (a query block that selected nothing has lse = -inf
+        # and contributes nothing): exclude them before the exponential instead of multiplying by 0 afterwards
+        p = torch.exp((s - lse.double().unsqueeze(-1)).masked_fill(~tok, float("-inf")))
         dvl = p.transpose(-1, -2) @ dod
         dp = dod @ vl.transpose(-1, -2)
         ds = p * (dp - delta.unsqueeze(-1))

@@ -33,7 +33,8 @@ namespace psa {
 namespace {
 
 constexpr int kSlab = 128 * 128;          // 128 rows x 128 B (64 16-bit channels)
-constexpr int kThreadsBwd = 320;          // warp 0 producer, warp 1 MMA issuer, warps 2-9 element-wise (two groups)
+constexpr int kThreadsBwd = 576;          // warp 0 producer, warp 1 MMA issuer, warps 2-17 element-wise (four groups)
+constexpr int kEwWarps = 16;
 constexpr int kMaxBlocks = 1472;          // key / query blocks per head the lists are sized for
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -67,7 +68,7 @@ struct BwdParams {
   const unsigned char* kimg; // tile images (block 128) of K and V, all levels
   const unsigned char* vimg;
   ImgLevels img;
-  const float2* stat;        // [bh][s_pad]: (lse * log2 e, delta); rows >= seq: (+inf, 0)
+  const float* stat;         // [bh][s_pad / 2][4]: (-lse0, -lse1, -delta0, -delta1) of two rows, lse in log2 units; rows >= seq: (-inf, 0)
   void* dq;                  // [bh][seq][D]
   float* dkp[4];             // pooled fp32 sums per level: [bh][s_pad / l][D]
   float* dvp[4];
@@ -92,7 +93,8 @@ template <int D> struct BCfg {
   static constexpr int OFF_B0 = 2 * TILE;               // stream ring, operand 0 (Q or K): 2 stages
   static constexpr int OFF_B1 = 4 * TILE;               // stream ring, operand 1 (dO or V): 2 stages
   static constexpr int OFF_META = 6 * TILE;             // per stage 128 x 16 B (dK/dV: 128 x float2 row statistics)
-  static constexpr int OFF_LIST = OFF_META + 2 * 2048;  // work lists: 3 x kMaxBlocks words
+  static constexpr int OFF_LC = OFF_META + 2 * 2048;    // dQ: per stage 128 floats, log2(copies) of every column (-inf: none)
+  static constexpr int OFF_LIST = OFF_LC + 2 * 512;     // work lists: 3 x kMaxBlocks words
   static constexpr int OFF_CTRL = OFF_LIST + 3 * kMaxBlocks * 4;
   static constexpr int SMEM = OFF_CTRL + 512 + 1024;    // control block + alignment slack
 };
@@ -100,11 +102,11 @@ template <int D> struct BCfg {
 struct BCtrl {
   uint64_t a_full, a_free;               // stationary tiles loaded / all products that read them complete
   uint64_t b_full[2], b0_free[2], b1_free[2];
-  uint64_t s_full[2], p_full[2];         // per half: S and dP ready / 16-bit operands written
+  uint64_t s_full, p_full;               // S and dP of a tile ready / their 16-bit operands written
   uint64_t acc_full, acc_free;
   uint64_t job_ready[3], job_done[3];
   int job_id[3], job_n[3], job_last[3];  // id < 0: no more work; n = stream tiles; last = columns of the last tile (dQ) / head (dK/dV)
-  int tile_flag[2];                      // dQ: bit h = half h of the stage's tile holds the block on the causal diagonal
+  int tile_flag[2];                      // dQ: the stage's tile holds the block on the causal diagonal
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -126,10 +128,10 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dkdv_tc_kernel(const __gri
     tc::mbar_init(&ctl->a_full, 1); tc::mbar_init(&ctl->a_free, 1);
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&ctl->b_full[i], 1); tc::mbar_init(&ctl->b0_free[i], 1); tc::mbar_init(&ctl->b1_free[i], 1);
-      tc::mbar_init(&ctl->s_full[i], 1); tc::mbar_init(&ctl->p_full[i], 4);
     }
-    tc::mbar_init(&ctl->acc_full, 1); tc::mbar_init(&ctl->acc_free, 8);
-    for (int i = 0; i < 3; ++i) { tc::mbar_init(&ctl->job_ready[i], 1); tc::mbar_init(&ctl->job_done[i], 9); }
+    tc::mbar_init(&ctl->s_full, 1); tc::mbar_init(&ctl->p_full, kEwWarps);
+    tc::mbar_init(&ctl->acc_full, 1); tc::mbar_init(&ctl->acc_free, kEwWarps);
+    for (int i = 0; i < 3; ++i) { tc::mbar_init(&ctl->job_ready[i], 1); tc::mbar_init(&ctl->job_done[i], kEwWarps + 1); }
     ctl->abort_flag = 0;
     tc::fence_mbar_init();
   }
@@ -143,7 +145,7 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dkdv_tc_kernel(const __gri
   const uint32_t tmem = ctl->tmem_base;
   const int nk = p.mq;                                      // key blocks = query blocks
   const int64_t total_jobs = (int64_t)p.n_entries * p.bh;
-  // TMEM columns: dK [0,D), dV [128,128+D), S^T halves [256,320) [320,384), dP^T halves [384,448) [448,512)
+  // TMEM columns: dK [0,D), dV [128,128+D), S^T [256,384), dP^T [384,512)
   constexpr uint32_t kAccK = 0, kAccV = 128, kST = 256, kDP = 384;
 
   if (warp == 0) {
@@ -162,8 +164,9 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dkdv_tc_kernel(const __gri
         if (lane == 0) { ctl->job_id[slot] = -1; __threadfence_block(); tc::mbar_arrive(&ctl->job_ready[slot]); }
         break;
       }
-      const int2 e = p.items[job / p.bh];
-      const int64_t bh = job % p.bh;
+      // head-major order: the CTAs running at the same time stream the Q and dO rows of the same head (they stay in L2)
+      const int2 e = p.items[job % p.n_entries];
+      const int64_t bh = job / p.n_entries;
       const int li = e.x, g = e.y, l = 1 << li;
       const int n0 = g * l;                                // first key block of the group
       const int nsub = min(l, nk - n0);
@@ -212,7 +215,7 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dkdv_tc_kernel(const __gri
       ++ic;
       for (int pi = 0; pi < n_pairs && ok; ++pi, ++gp) {
         const int st = gp & 1;
-        // a stage is free when both accumulating products of its previous tile have read it (they complete together)
+        // a stage is free when both accumulating products of its previous tile have completed
         ok = tc::mbar_wait(&ctl->b0_free[st], ((gp >> 1) & 1) ^ 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -224,7 +227,7 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dkdv_tc_kernel(const __gri
             tc::tma_load_3d(sq + s * kSlab, &maps.q, &ctl->b_full[st], s * 64, m * 128, (int)bh);
             tc::tma_load_3d(sd + s * kSlab, &maps.d, &ctl->b_full[st], s * 64, m * 128, (int)bh);
           }
-          tc::bulk_load_a(tc::smem_u32(smem + C::OFF_META + st * 2048), p.stat + (bh * p.s_pad + (int64_t)m * 128), 1024,
+          tc::bulk_load_a(tc::smem_u32(smem + C::OFF_META + st * 2048), p.stat + (bh * p.s_pad + (int64_t)m * 128) * 2, 1024,
                           tc::smem_u32(&ctl->b_full[st]));
           tc::mbar_arrive_expect_tx(&ctl->b_full[st], 2 * C::TILE + 1024);
         }
@@ -234,41 +237,45 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dkdv_tc_kernel(const __gri
     // ================================================================ MMA issuer
     if (lane == 0) {
       bool ok = true;
-      const uint32_t idesc_s = tc::make_idesc(FMT, 128, 64, 0, 0);
+      const uint32_t idesc_s = tc::make_idesc(FMT, 128, 128, 0, 0);
       const uint32_t idesc_acc = tc::make_idesc(FMT, 128, D, 0, 1);
       const uint64_t kdesc = tc::make_smem_desc(tc::smem_u32(smem + C::OFF_A0), 16, C::SLABS * 1024);
       const uint64_t vdesc = tc::make_smem_desc(tc::smem_u32(smem + C::OFF_A1), 16, C::SLABS * 1024);
+      const uint64_t qk0 = tc::make_smem_desc(tc::smem_u32(smem + C::OFF_B0), 16, 1024);      // stream tiles as K-major B
+      const uint64_t dk0 = tc::make_smem_desc(tc::smem_u32(smem + C::OFF_B1), 16, 1024);
+      const uint64_t qm0 = tc::make_smem_desc(tc::smem_u32(smem + C::OFF_B0), kSlab, 1024);   // ... and as MN-major B
+      const uint64_t dm0 = tc::make_smem_desc(tc::smem_u32(smem + C::OFF_B1), kSlab, 1024);
+      const uint32_t ctl_a = tc::smem_u32(ctl);
+      const uint32_t s_full_a = ctl_a + (uint32_t)offsetof(BCtrl, s_full), p_full_a = ctl_a + (uint32_t)offsetof(BCtrl, p_full);
+      const uint32_t b_full_a = ctl_a + (uint32_t)offsetof(BCtrl, b_full);
       int gp = 0, ic = 0;
-      // S^T and dP^T of half h of the tile in stage st
-      auto issue_s = [&](int st, int h) {
-        const uint32_t qa = tc::smem_u32(smem + C::OFF_B0 + st * C::TILE) + h * 8192;
-        const uint32_t da = tc::smem_u32(smem + C::OFF_B1 + st * C::TILE) + h * 8192;
-        const uint64_t qd = tc::make_smem_desc(qa, 16, 1024), dd = tc::make_smem_desc(da, 16, 1024);
+      // S^T = K Q^T and dP^T = V dO^T of the tile in stage st (N = 128 query rows); one commit for both
+      auto issue_s = [&](int st) {
+        const uint64_t off = (uint64_t)((uint32_t)(st * C::TILE) >> 4);
+        const uint64_t qd = qk0 + off, dd = dk0 + off;
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t a_off = (uint32_t)(((ks >> 2) * 1024 + (ks & 3) * 32) >> 4);
-          const uint32_t b_off = (uint32_t)(((ks >> 2) * kSlab + (ks & 3) * 32) >> 4);
-          tc::umma_ss(tmem + kST + h * 64, kdesc + a_off, qd + b_off, idesc_s, ks > 0 ? 1u : 0u);
-        }
+        for (int ks = 0; ks < D / 16; ++ks)
+          tc::umma_ss(tmem + kST, kdesc + (uint64_t)(((ks >> 2) * 1024 + (ks & 3) * 32) >> 4),
+                      qd + (uint64_t)(((ks >> 2) * kSlab + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t a_off = (uint32_t)(((ks >> 2) * 1024 + (ks & 3) * 32) >> 4);
-          const uint32_t b_off = (uint32_t)(((ks >> 2) * kSlab + (ks & 3) * 32) >> 4);
-          tc::umma_ss(tmem + kDP + h * 64, vdesc + a_off, dd + b_off, idesc_s, ks > 0 ? 1u : 0u);
-        }
-        tc::umma_commit(&ctl->s_full[h]);
+        for (int ks = 0; ks < D / 16; ++ks)
+          tc::umma_ss(tmem + kDP, vdesc + (uint64_t)(((ks >> 2) * 1024 + (ks & 3) * 32) >> 4),
+                      dd + (uint64_t)(((ks >> 2) * kSlab + (ks & 3) * 32) >> 4), idesc_s, ks > 0 ? 1u : 0u);
+        tc::umma_commit_a(s_full_a);
       };
-      // dV += P^T dO and dK += dS^T Q over the 64 query rows of half h
-      auto issue_acc = [&](int st, int h, bool first) {
-        const uint32_t qa = tc::smem_u32(smem + C::OFF_B0 + st * C::TILE) + h * 8192;
-        const uint32_t da = tc::smem_u32(smem + C::OFF_B1 + st * C::TILE) + h * 8192;
-        const uint64_t qd = tc::make_smem_desc(qa, kSlab, 1024), dd = tc::make_smem_desc(da, kSlab, 1024);
+      // dV += P^T dO and dK += dS^T Q.  k-step ks = query rows [16 ks, 16 ks + 16); its 16-bit operand sits at column
+      // 32 (ks / 2) + 8 (ks % 2) of the buffer the fp32 values came from
+      auto issue_acc = [&](int st, bool first) {
+        const uint64_t off = (uint64_t)((uint32_t)(st * C::TILE) >> 4);
+        const uint64_t qd = qm0 + off, dd = dm0 + off;
+        tc::umma_ts(tmem + kAccV, tmem + kST, dd, idesc_acc, first ? 0u : 1u);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          tc::umma_ts(tmem + kAccV, tmem + kST + h * 64 + ks * 8, dd + (uint64_t)(ks * (2048 >> 4)), idesc_acc, (first && ks == 0) ? 0u : 1u);
+        for (int ks = 1; ks < 8; ++ks)
+          tc::umma_ts(tmem + kAccV, tmem + kST + (ks >> 1) * 32 + (ks & 1) * 8, dd + (uint64_t)(ks * (2048 >> 4)), idesc_acc, 1u);
+        tc::umma_ts(tmem + kAccK, tmem + kDP, qd, idesc_acc, first ? 0u : 1u);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          tc::umma_ts(tmem + kAccK, tmem + kDP + h * 64 + ks * 8, qd + (uint64_t)(ks * (2048 >> 4)), idesc_acc, (first && ks == 0) ? 0u : 1u);
+        for (int ks = 1; ks < 8; ++ks)
+          tc::umma_ts(tmem + kAccK, tmem + kDP + (ks >> 1) * 32 + (ks & 1) * 8, qd + (uint64_t)(ks * (2048 >> 4)), idesc_acc, 1u);
       };
       for (int it = 0; ok; ++it) {
         const int slot = it % 3;
@@ -277,28 +284,22 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dkdv_tc_kernel(const __gri
         const int n = ctl->job_n[slot];
         if (n == 0) { tc::mbar_arrive(&ctl->job_done[slot]); continue; }
         ok = tc::mbar_wait(&ctl->a_full, ic & 1, abort_flag);
-        if (ok) ok = tc::mbar_wait(&ctl->b_full[gp & 1], (gp >> 1) & 1, abort_flag);
+        if (ok) ok = tc::mbar_wait_a(b_full_a + (gp & 1) * 8, (gp >> 1) & 1, abort_flag);
         if (!ok) break;
         tc::tc_fence_after();
-        issue_s(gp & 1, 0);
-        issue_s(gp & 1, 1);
+        issue_s(gp & 1);
         for (int pi = 0; pi < n && ok; ++pi, ++gp) {
           const int st = gp & 1;
-          for (int h = 0; h < 2 && ok; ++h) {
-            ok = tc::mbar_wait(&ctl->p_full[h], gp & 1, abort_flag);
-            if (ok && pi == 0 && h == 0 && ic > 0) ok = tc::mbar_wait(&ctl->acc_free, (ic - 1) & 1, abort_flag);
+          ok = tc::mbar_wait_a(p_full_a, gp & 1, abort_flag);
+          if (ok && pi == 0 && ic > 0) ok = tc::mbar_wait(&ctl->acc_free, (ic - 1) & 1, abort_flag);
+          if (!ok) break;
+          tc::tc_fence_after();
+          issue_acc(st, pi == 0);
+          if (pi + 1 < n) {
+            ok = tc::mbar_wait_a(b_full_a + (st ^ 1) * 8, ((gp + 1) >> 1) & 1, abort_flag);
             if (!ok) break;
             tc::tc_fence_after();
-            issue_acc(st, h, pi == 0 && h == 0);
-            if (h == 1) { tc::umma_commit(&ctl->b0_free[st]); }
-            if (pi + 1 < n) {
-              if (h == 0) {
-                ok = tc::mbar_wait(&ctl->b_full[st ^ 1], ((gp + 1) >> 1) & 1, abort_flag);
-                if (!ok) break;
-                tc::tc_fence_after();
-              }
-              issue_s(st ^ 1, h);
-            }
+            issue_s(st ^ 1);      // its commit also says that both accumulating products above are complete
           }
         }
         if (!ok) break;
@@ -310,10 +311,12 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dkdv_tc_kernel(const __gri
     }
   } else {
     // ================================================================ element-wise warps: one thread per pooled key row
-    const int quarter = warp & 3, grp = (warp - 2) >> 2;     // grp = half of the query columns this thread handles
+    // four groups of four warps; group cg works on query columns [32 cg, 32 cg + 32) of the tile
+    const int quarter = warp & 3, cg = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tST = tmem + kST + grp * 64 + lane_base, tDP = tmem + kDP + grp * 64 + lane_base;
+    const uint32_t tST = tmem + kST + cg * 32 + lane_base, tDP = tmem + kDP + cg * 32 + lane_base;
+    const bool relay = warp == 2 && lane == 0;                 // tells the producer which stream stages are free again
     bool ok = true;
     int gp = 0, ic = 0;
     for (int it = 0; ok; ++it) {
@@ -325,7 +328,7 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dkdv_tc_kernel(const __gri
       if (job < 0) break;
       const int n = ctl->job_n[slot];
       const int64_t bh = ctl->job_last[slot];
-      const int2 e = p.items[job / p.bh];
+      const int2 e = p.items[job % p.n_entries];
       const int li = e.x, g = e.y, l = 1 << li;
       const int n0 = g * l;
       const int64_t n_l = p.s_pad >> li;
@@ -334,10 +337,13 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dkdv_tc_kernel(const __gri
       const int sub = (r << li) >> 7;                        // key block of the group this row belongs to
       const int64_t j0 = t * l, l_k = li == 0 ? p.seq : p.s_pad;
       const float c_static = (float)copies(j0, l, l_k, 0, 0);
-      float* dst = (grp == 0 ? p.dkp[li] : p.dvp[li]) + (bh * n_l + t) * D;
+      const float log2c = (float)li;                          // c_static is l = 2^li wherever it is not 0 (level 1: 1)
+      // the sums of this row: groups 0, 1 store the two halves of the dK channels, groups 2, 3 those of dV
+      constexpr int HD = D / 2;
+      float* dst = (cg < 2 ? p.dkp[li] : p.dvp[li]) + (bh * n_l + t) * D + (cg & 1) * HD;
       if (n == 0) {
         if (exists)
-          for (int c = 0; c < D; c += 4) *reinterpret_cast<float4*>(dst + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int c = 0; c < HD; c += 4) *reinterpret_cast<float4*>(dst + c) = make_float4(0.f, 0.f, 0.f, 0.f);
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&ctl->job_done[slot]);
         continue;
@@ -350,63 +356,80 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dkdv_tc_kernel(const __gri
         const bool act = exists && ((ent >> (16 + sub)) & 1u);
         const bool diag = p.causal && act && (n0 + sub == m);
         ok = tc::mbar_wait(&ctl->b_full[st], (gp >> 1) & 1, abort_flag);      // the row statistics of this tile
-        if (ok) ok = tc::mbar_wait(&ctl->s_full[grp], gp & 1, abort_flag);
+        if (ok) ok = tc::mbar_wait(&ctl->s_full, gp & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        // S^T and dP^T of this tile are complete, hence also both accumulating products of the previous tile: its stage
+        // may be refilled
+        if (relay && pi > 0) tc::mbar_arrive(&ctl->b0_free[st ^ 1]);
         tc::tc_fence_after();
-        const float4* stat2 = reinterpret_cast<const float4*>(smem + C::OFF_META + st * 2048) + grp * 32;   // two columns each
+        const float4* stat2 = reinterpret_cast<const float4*>(smem + C::OFF_META + st * 2048) + cg * 16;   // two columns each
         const bool slow = __any_sync(0xffffffffu, diag);
-        const int64_t qbase = (int64_t)m * 128 + grp * 64;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t sv[32], dv[32], pp[16], pd[16];
-          tc::tmem_ld32(tST + 32 * c, sv);
-          tc::tmem_ld32(tDP + 32 * c, dv);
-          tc::tmem_wait_ld();
+        const int64_t qbase = (int64_t)m * 128 + cg * 32;
+        // this thread's 32 columns in two chunks of 16 (one after the other: the element-wise warps are bound by their
+        // arithmetic, not by TMEM latency, and fewer live registers spare them spills).  The packed 16-bit results go back
+        // IN PLACE into columns this thread has read itself - chunk c into [8 c, 8 c + 8) of its group's columns - because
+        // the other groups work on the same buffers at the same time; the MMA takes every 16-element k-step from its own
+        // TMEM address, so the operand need not be contiguous.
+        uint32_t sa[16], da[16];
+        auto chunk = [&](const uint32_t (&sv)[16], const uint32_t (&dv)[16], int c) {
+          uint32_t pp[8], pd[8];
           if (!slow) {
-            // every copy that exists is visible: the count is a power of two (or 0), so one rounding after the product
-            // equals the reference's rounding before it
-            const bool on = act && c_static > 0.f;
+            // every copy that exists is visible: the count c is a power of two (or 0), so it goes into the exponent -
+            // p c = 2^(s scale - lse + log2 c), exact scaling - and one rounding after the product equals the reference's
+            // rounding before it.  c = 0 (row not selected by this query block, or no copy exists): log2 c = -inf gives
+            // p = 0 and ds = 0 * finite.  Two columns at a time on the packed fp32 pipe.
+            const float lc = (act && c_static > 0.f) ? log2c : -INFINITY;
+            const float2 lc2 = make_float2(lc, lc), sl2 = make_float2(p.scale_log2, p.scale_log2);
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              const float4 s2 = stat2[c * 16 + k];
-              const float p0 = ex2f(fmaf(__uint_as_float(sv[2 * k]), p.scale_log2, -s2.x));
-              const float p1 = ex2f(fmaf(__uint_as_float(sv[2 * k + 1]), p.scale_log2, -s2.z));
-              const float y0 = p0 * (__uint_as_float(dv[2 * k]) - s2.y), y1 = p1 * (__uint_as_float(dv[2 * k + 1]) - s2.w);
-              pp[k] = on ? pack16<FMT>(p0 * c_static, p1 * c_static) : 0u;
-              pd[k] = on ? pack16<FMT>(y0 * c_static, y1 * c_static) : 0u;
+            for (int k = 0; k < 8; ++k) {
+              const float4 s2 = stat2[c * 8 + k];                     // (-lse0, -lse1, -delta0, -delta1) of the two query columns
+              const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[2 * k]), __uint_as_float(sv[2 * k + 1])), sl2,
+                                          __fadd2_rn(lc2, make_float2(s2.x, s2.y)));
+              const float2 pc = make_float2(ex2f(x.x), ex2f(x.y));
+              const float2 y = __fmul2_rn(pc, __fadd2_rn(make_float2(__uint_as_float(dv[2 * k]), __uint_as_float(dv[2 * k + 1])),
+                                                         make_float2(s2.z, s2.w)));
+              pp[k] = pack16<FMT>(pc.x, pc.y);
+              pd[k] = pack16<FMT>(y.x, y.y);
             }
           } else {
             // a key block on the causal diagonal: the copies a query sees depend on its position
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              const float4 s2 = stat2[c * 16 + k];
-              const int64_t q0 = qbase + c * 32 + 2 * k;
+            for (int k = 0; k < 8; ++k) {
+              const float4 s2 = stat2[c * 8 + k];
+              const int64_t q0 = qbase + c * 16 + 2 * k;
               const float c0 = act ? (float)copies(j0, l, l_k, 1, q0) : 0.f, c1 = act ? (float)copies(j0, l, l_k, 1, q0 + 1) : 0.f;
-              const float p0 = ex2f(fmaf(__uint_as_float(sv[2 * k]), p.scale_log2, -s2.x));
-              const float p1 = ex2f(fmaf(__uint_as_float(sv[2 * k + 1]), p.scale_log2, -s2.z));
-              const float y0 = p0 * (__uint_as_float(dv[2 * k]) - s2.y), y1 = p1 * (__uint_as_float(dv[2 * k + 1]) - s2.w);
+              const float p0 = ex2f(fmaf(__uint_as_float(sv[2 * k]), p.scale_log2, s2.x));
+              const float p1 = ex2f(fmaf(__uint_as_float(sv[2 * k + 1]), p.scale_log2, s2.y));
+              const float y0 = p0 * (__uint_as_float(dv[2 * k]) + s2.z), y1 = p1 * (__uint_as_float(dv[2 * k + 1]) + s2.w);
               pp[k] = pack16<FMT>(c0 > 0.f ? round16<FMT>(p0) * c0 : 0.f, c1 > 0.f ? round16<FMT>(p1) * c1 : 0.f);
               pd[k] = pack16<FMT>(c0 > 0.f ? round16<FMT>(y0) * c0 : 0.f, c1 > 0.f ? round16<FMT>(y1) * c1 : 0.f);
             }
           }
-          tc::tmem_st16(tST + 16 * c, pp);
-          tc::tmem_st16(tDP + 16 * c, pd);
-        }
+          tc::tmem_st8(tST + 8 * c, pp);
+          tc::tmem_st8(tDP + 8 * c, pd);
+        };
+        tc::tmem_ld16(tST, sa); tc::tmem_ld16(tDP, da);
+        tc::tmem_wait_ld();
+        chunk(sa, da, 0);
+        tc::tmem_ld16(tST + 16, sa); tc::tmem_ld16(tDP + 16, da);
+        tc::tmem_wait_ld();
+        chunk(sa, da, 1);
         tc::tmem_wait_st();
         tc::tc_fence_before();
         __syncwarp();
-        if (lane == 0) tc::mbar_arrive(&ctl->p_full[grp]);
+        if (lane == 0) tc::mbar_arrive(&ctl->p_full);
       }
       if (!ok) break;
-      // ---- the pooled rows' sums: group 0 stores dK, group 1 dV
+      // ---- the pooled rows' sums
       ok = tc::mbar_wait(&ctl->acc_full, ic & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (relay) tc::mbar_arrive(&ctl->b0_free[(gp - 1) & 1]);   // the last tile's stage
       tc::tc_fence_after();
-      const uint32_t tAcc = tmem + (grp == 0 ? kAccK : kAccV) + lane_base;
+      const uint32_t tAcc = tmem + (cg < 2 ? kAccK : kAccV) + (cg & 1) * HD + lane_base;
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = 0; c0 < HD; c0 += 32) {
         uint32_t a[32];
         tc::tmem_ld32(tAcc + c0, a);
         tc::tmem_wait_ld();
@@ -454,11 +477,12 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dq_tc_kernel(const __grid_
   if (threadIdx.x == 0) {
     tc::mbar_init(&ctl->a_full, 1); tc::mbar_init(&ctl->a_free, 1);
     for (int i = 0; i < 2; ++i) {
-      tc::mbar_init(&ctl->b_full[i], 1); tc::mbar_init(&ctl->b0_free[i], 1); tc::mbar_init(&ctl->b1_free[i], 1);
-      tc::mbar_init(&ctl->s_full[i], 1); tc::mbar_init(&ctl->p_full[i], 4);
+      tc::mbar_init(&ctl->b_full[i], 2);            // one arrival for the V copies of the tile, one for its K copies
+      tc::mbar_init(&ctl->b0_free[i], 1); tc::mbar_init(&ctl->b1_free[i], 1);
     }
-    tc::mbar_init(&ctl->acc_full, 1); tc::mbar_init(&ctl->acc_free, 8);
-    for (int i = 0; i < 3; ++i) { tc::mbar_init(&ctl->job_ready[i], 1); tc::mbar_init(&ctl->job_done[i], 9); }
+    tc::mbar_init(&ctl->s_full, 1); tc::mbar_init(&ctl->p_full, kEwWarps);
+    tc::mbar_init(&ctl->acc_full, 1); tc::mbar_init(&ctl->acc_free, kEwWarps);
+    for (int i = 0; i < 3; ++i) { tc::mbar_init(&ctl->job_ready[i], 1); tc::mbar_init(&ctl->job_done[i], kEwWarps + 1); }
     ctl->abort_flag = 0;
     tc::fence_mbar_init();
   }
@@ -472,8 +496,8 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dq_tc_kernel(const __grid_
   const uint32_t tmem = ctl->tmem_base;
   const int nk = p.mq;
   const int64_t total_rows = (int64_t)p.mq * p.bh;
-  // TMEM columns: dQ [0,D), S halves [128,192) [192,256), dP halves [256,320) [320,384)
-  constexpr uint32_t kAcc = 0, kS = 128, kDP = 256;
+  // TMEM columns: dQ [0,D), S of even tiles [128,256), S of odd tiles [256,384), dP [384,512)
+  constexpr uint32_t kAcc = 0, kS = 128, kDP = 384;
   constexpr int kGroup = C::SLABS * 1024;          // 8 rows of a tile image
 
   if (warp == 0) {
@@ -492,9 +516,10 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dq_tc_kernel(const __grid_
         if (lane == 0) { ctl->job_id[slot] = -1; __threadfence_block(); tc::mbar_arrive(&ctl->job_ready[slot]); }
         break;
       }
-      // heavy rows first: causal rows are walked from the last query block down
-      const int m = p.causal ? p.mq - 1 - (int)(R / p.bh) : (int)(R % p.mq);
-      const int64_t bh = p.causal ? R % p.bh : R / p.mq;
+      // head-major order (the CTAs running at the same time stream the K/V images of the same head: they stay in L2);
+      // within a head the causal rows are walked from the last query block down, the long ones first
+      const int m = p.causal ? p.mq - 1 - (int)(R % p.mq) : (int)(R % p.mq);
+      const int64_t bh = R / p.mq;
       // the row's blocks, level by level (ordered compaction of the dense level row); entry: block | level index << 12 |
       // first column (in units of 16 tokens) << 16
       const int32_t* mrow = p.mask + (bh * p.mq + m) * (int64_t)p.mask_cols;
@@ -540,28 +565,32 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dq_tc_kernel(const __grid_
       int ki = 0;
       for (int t = 0; t < n_tiles && ok; ++t, ++gt) {
         const int st = gt & 1;
-        // K is read last (by dQ += dS K): its release also says that the metadata of the stage are no longer needed
-        ok = tc::mbar_wait(&ctl->b0_free[st], ((gt >> 1) & 1) ^ 1, abort_flag);
-        if (ok) ok = tc::mbar_wait(&ctl->b1_free[st], ((gt >> 1) & 1) ^ 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
         const int probe = ki + lane;
         const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(items[probe < n_items ? probe : 0] >> 19) == t));
-        int4* meta = reinterpret_cast<int4*>(smem + C::OFF_META + st * 2048);
         const uint32_t x = lane < in_tile ? items[ki + lane] : 0u;
         const int li = (x >> 12) & 3, blk = x & 0xfff, P = 128 >> li, col = ((int)(x >> 16) << 4) & 127;
-        uint32_t my_bytes = 0;
-        if (lane < in_tile) {
-          const int64_t off = p.img.off[li] + (((int64_t)bh * p.img.groups[li] + (((int64_t)blk * P) >> 3)) * C::SLABS << 10);
-          const uint32_t dstoff = (uint32_t)(col >> 3) * kGroup;
-          tc::bulk_load_a(tc::smem_u32(smem + C::OFF_B0 + st * C::TILE) + dstoff, p.kimg + off, (uint32_t)(P * D * 2),
-                          tc::smem_u32(&ctl->b_full[st]));
-          tc::bulk_load_a(tc::smem_u32(smem + C::OFF_B1 + st * C::TILE) + dstoff, p.vimg + off, (uint32_t)(P * D * 2),
-                          tc::smem_u32(&ctl->b_full[st]));
-          my_bytes = 2u * (uint32_t)(P * D * 2);
-        }
+        const int64_t off = p.img.off[li] + (((int64_t)bh * p.img.groups[li] + (((int64_t)blk * P) >> 3)) * C::SLABS << 10);
+        const uint32_t dstoff = (uint32_t)(col >> 3) * kGroup;
+        const uint32_t my_bytes = lane < in_tile ? (uint32_t)(P * D * 2) : 0u;
+        const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
+        // V of the stage's previous tile is free as soon as its dP is complete: the V copies leave first
+        ok = tc::mbar_wait(&ctl->b1_free[st], ((gt >> 1) & 1) ^ 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane < in_tile)
+          tc::bulk_load_a(tc::smem_u32(smem + C::OFF_B1 + st * C::TILE) + dstoff, p.vimg + off, my_bytes, tc::smem_u32(&ctl->b_full[st]));
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive_expect_tx(&ctl->b_full[st], bytes);
+        // K is read last (by dQ += dS K): its release also says that the metadata of the stage are no longer needed
+        ok = tc::mbar_wait(&ctl->b0_free[st], ((gt >> 1) & 1) ^ 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane < in_tile)
+          tc::bulk_load_a(tc::smem_u32(smem + C::OFF_B0 + st * C::TILE) + dstoff, p.kimg + off, my_bytes, tc::smem_u32(&ctl->b_full[st]));
         // per-column metadata, written by the whole warp block after block: (first original position, positions that
         // exist from there, level, copies when nothing hides them); absent columns: zeros
+        int4* meta = reinterpret_cast<int4*>(smem + C::OFF_META + st * 2048);
+        float* lcol = reinterpret_cast<float*>(smem + C::OFF_LC + st * 512);
         int flag_diag = 0;
         for (int b = 0; b < in_tile; ++b) {
           const int b_li = __shfl_sync(0xffffffffu, li, b), b_blk = __shfl_sync(0xffffffffu, blk, b);
@@ -572,16 +601,16 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dq_tc_kernel(const __grid_
             const int64_t j0 = ((int64_t)b_blk * b_P + c) * b_l;
             const int64_t avail = l_k - j0;
             const int cs = avail < 0 ? 0 : (avail > b_l ? b_l : (int)avail);
-            meta[b_col + c] = make_int4((int)j0, (int)min(avail, (int64_t)1 << 30), b_l, __float_as_int((float)cs));
+            meta[b_col + c] = make_int4((int)j0, (int)min(avail, (int64_t)1 << 30), b_l, 0);
+            lcol[b_col + c] = cs > 0 ? (float)b_li : -INFINITY;      // cs is 0 or the level 2^li
           }
-          if (p.causal && b_blk == m) flag_diag |= (b_col < 64 ? 1 : 0) | (b_col + b_P > 64 ? 2 : 0);
+          if (p.causal && b_blk == m) flag_diag = 1;
         }
         const int used = t == n_tiles - 1 ? last_cols : 128;
-        for (int c = used + lane; c < 128; c += 32) meta[c] = make_int4(0, 0, 0, 0);
+        for (int c = used + lane; c < 128; c += 32) { meta[c] = make_int4(0, 0, 0, 0); lcol[c] = -INFINITY; }
         if (lane == 0) ctl->tile_flag[st] = flag_diag;
         ki += in_tile;
         __syncwarp();
-        const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
         if (lane == 0) tc::mbar_arrive_expect_tx(&ctl->b_full[st], bytes);
       }
     }
@@ -590,40 +619,50 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dq_tc_kernel(const __grid_
     if (lane == 0) {
       bool ok = true;
       const uint32_t idesc_acc = tc::make_idesc(FMT, 128, D, 0, 1);
+      const uint32_t idesc_full = tc::make_idesc(FMT, 128, 128, 0, 0);
       const uint64_t qdesc = tc::make_smem_desc(tc::smem_u32(smem + C::OFF_A0), 16, 1024);
       const uint64_t ddesc = tc::make_smem_desc(tc::smem_u32(smem + C::OFF_A1), 16, 1024);
-      int gt = 0, rc = 0;
-      auto cols_of = [](int used, int h) { const int c = used - 64 * h; return c < 0 ? 0 : (c > 64 ? 64 : c); };
-      // S and dP of half h (columns [64h, 64h+cols)) of the tile in stage st
-      auto issue_s = [&](int st, int h, int cols) {
-        if (cols > 0) {
-          const uint32_t ka = tc::smem_u32(smem + C::OFF_B0 + st * C::TILE) + h * 8 * kGroup;
-          const uint32_t va = tc::smem_u32(smem + C::OFF_B1 + st * C::TILE) + h * 8 * kGroup;
-          const uint64_t kd = tc::make_smem_desc(ka, 16, kGroup), vd = tc::make_smem_desc(va, 16, kGroup);
-          const uint32_t idesc = tc::make_idesc(FMT, 128, cols, 0, 0);
+      const uint64_t kk0 = tc::make_smem_desc(tc::smem_u32(smem + C::OFF_B0), 16, kGroup);     // stream tiles as K-major B
+      const uint64_t vk0 = tc::make_smem_desc(tc::smem_u32(smem + C::OFF_B1), 16, kGroup);
+      const uint64_t km0 = tc::make_smem_desc(tc::smem_u32(smem + C::OFF_B0), 1024, kGroup);   // K tile as MN-major B
+      const uint32_t ctl_a = tc::smem_u32(ctl);
+      const uint32_t s_full_a = ctl_a + (uint32_t)offsetof(BCtrl, s_full), p_full_a = ctl_a + (uint32_t)offsetof(BCtrl, p_full);
+      const uint32_t b_full_a = ctl_a + (uint32_t)offsetof(BCtrl, b_full);
+      int g0 = 0, rc = 0;                                   // stream tiles of the rows before this one / rows with work
+      // S = Q K^T of tile u of the row (stage and score buffer by the running tile count), N = its columns
+      auto issue_S = [&](int gu, int cols) {
+        const uint64_t kd = kk0 + (uint64_t)((uint32_t)((gu & 1) * C::TILE) >> 4);
+        const uint32_t idesc = cols == 128 ? idesc_full : tc::make_idesc(FMT, 128, cols, 0, 0);
+        const uint32_t ts = tmem + kS + (gu & 1) * 128;
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t a_off = (uint32_t)(((ks >> 2) * kSlab + (ks & 3) * 32) >> 4);
-            const uint32_t b_off = (uint32_t)(((ks >> 2) * 1024 + (ks & 3) * 32) >> 4);
-            tc::umma_ss(tmem + kS + h * 64, qdesc + a_off, kd + b_off, idesc, ks > 0 ? 1u : 0u);
-          }
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint32_t a_off = (uint32_t)(((ks >> 2) * kSlab + (ks & 3) * 32) >> 4);
-            const uint32_t b_off = (uint32_t)(((ks >> 2) * 1024 + (ks & 3) * 32) >> 4);
-            tc::umma_ss(tmem + kDP + h * 64, ddesc + a_off, vd + b_off, idesc, ks > 0 ? 1u : 0u);
-          }
-        }
-        tc::umma_commit(&ctl->s_full[h]);
-        if (h == 1) tc::umma_commit(&ctl->b1_free[st]);      // V has been read by both halves
+        for (int ks = 0; ks < D / 16; ++ks)
+          tc::umma_ss(ts, qdesc + (uint64_t)(((ks >> 2) * kSlab + (ks & 3) * 32) >> 4),
+                      kd + (uint64_t)(((ks >> 2) * 1024 + (ks & 3) * 32) >> 4), idesc, ks > 0 ? 1u : 0u);
       };
-      // dQ += dS K over the columns of half h
-      auto issue_acc = [&](int st, int h, int cols, bool first) {
-        const uint32_t ka = tc::smem_u32(smem + C::OFF_B0 + st * C::TILE) + h * 8 * kGroup;
-        const uint64_t kd = tc::make_smem_desc(ka, 1024, kGroup);
-        for (int ks = 0; ks < cols / 16; ++ks)
-          tc::umma_ts(tmem + kAcc, tmem + kDP + h * 64 + ks * 8, kd + (uint64_t)(ks * ((2 * kGroup) >> 4)), idesc_acc,
-                      (first && ks == 0) ? 0u : 1u);
+      // dP = dO V^T of the same tile; its commit covers every product issued before it
+      auto issue_dP = [&](int gu, int cols) {
+        const uint64_t vd = vk0 + (uint64_t)((uint32_t)((gu & 1) * C::TILE) >> 4);
+        const uint32_t idesc = cols == 128 ? idesc_full : tc::make_idesc(FMT, 128, cols, 0, 0);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks)
+          tc::umma_ss(tmem + kDP, ddesc + (uint64_t)(((ks >> 2) * kSlab + (ks & 3) * 32) >> 4),
+                      vd + (uint64_t)(((ks >> 2) * 1024 + (ks & 3) * 32) >> 4), idesc, ks > 0 ? 1u : 0u);
+        tc::umma_commit_a(s_full_a);
+      };
+      // dQ += dS K; k-step ks = columns [16 ks, 16 ks + 16) of the tile, whose 16-bit operand sits at column
+      // 32 (ks / 2) + 8 (ks % 2) of the dP buffer
+      auto issue_acc = [&](int gu, int cols, bool first) {
+        const uint64_t kd = km0 + (uint64_t)((uint32_t)((gu & 1) * C::TILE) >> 4);
+        if (cols == 128) {
+          tc::umma_ts(tmem + kAcc, tmem + kDP, kd, idesc_acc, first ? 0u : 1u);
+#pragma unroll
+          for (int ks = 1; ks < 8; ++ks)
+            tc::umma_ts(tmem + kAcc, tmem + kDP + (ks >> 1) * 32 + (ks & 1) * 8, kd + (uint64_t)(ks * ((2 * kGroup) >> 4)), idesc_acc, 1u);
+        } else {
+          for (int ks = 0; ks < cols / 16; ++ks)
+            tc::umma_ts(tmem + kAcc, tmem + kDP + (ks >> 1) * 32 + (ks & 1) * 8, kd + (uint64_t)(ks * ((2 * kGroup) >> 4)), idesc_acc,
+                        (first && ks == 0) ? 0u : 1u);
+        }
       };
       for (int it = 0; ok; ++it) {
         const int slot = it % 3;
@@ -631,34 +670,50 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dq_tc_kernel(const __grid_
         if (!ok || ctl->job_id[slot] < 0) break;
         const int n = ctl->job_n[slot], last_cols = ctl->job_last[slot];
         if (n == 0) { tc::mbar_arrive(&ctl->job_done[slot]); continue; }
+        auto cols_of = [&](int u) { return u == n - 1 ? last_cols : 128; };
         ok = tc::mbar_wait(&ctl->a_full, rc & 1, abort_flag);
-        if (ok) ok = tc::mbar_wait(&ctl->b_full[gt & 1], (gt >> 1) & 1, abort_flag);
+        if (ok) ok = tc::mbar_wait_a(b_full_a + (g0 & 1) * 8, (g0 >> 1) & 1, abort_flag);
         if (!ok) break;
         tc::tc_fence_after();
-        {
-          const int used = n == 1 ? last_cols : 128;
-          issue_s(gt & 1, 0, cols_of(used, 0));
-          issue_s(gt & 1, 1, cols_of(used, 1));
-        }
-        for (int t = 0; t < n && ok; ++t, ++gt) {
-          const int st = gt & 1;
-          const int used = t == n - 1 ? last_cols : 128;
-          const int used_next = t + 1 == n - 1 ? last_cols : 128;
-          for (int h = 0; h < 2 && ok; ++h) {
-            ok = tc::mbar_wait(&ctl->p_full[h], gt & 1, abort_flag);
-            if (ok && t == 0 && h == 0 && rc > 0) ok = tc::mbar_wait(&ctl->acc_free, (rc - 1) & 1, abort_flag);
-            if (!ok) break;
+        issue_S(g0, cols_of(0));
+        issue_dP(g0, cols_of(0));
+        // S of tile u+1 is issued as soon as its operands are there, dQ of tile u and dP of tile u+1 when the element-wise
+        // warps are done with tile u: the issuer polls for whichever comes first
+        int s_issued = 1, t = 0;
+        uint32_t idle = 0;
+        while (ok && t < n) {
+          bool progressed = false;
+          if (s_issued < n && s_issued <= t + 1 && tc::mbar_test_wait_a(b_full_a + ((g0 + s_issued) & 1) * 8, ((g0 + s_issued) >> 1) & 1)) {
             tc::tc_fence_after();
-            issue_acc(st, h, cols_of(used, h), t == 0 && h == 0);
-            if (h == 1) tc::umma_commit(&ctl->b0_free[st]);
+            issue_S(g0 + s_issued, cols_of(s_issued));
+            ++s_issued;
+            progressed = true;
+          }
+          if (tc::mbar_test_wait_a(p_full_a, (g0 + t) & 1)) {
+            if (t == 0 && rc > 0) {
+              ok = tc::mbar_wait(&ctl->acc_free, (rc - 1) & 1, abort_flag);
+              if (!ok) break;
+            }
+            tc::tc_fence_after();
+            issue_acc(g0 + t, cols_of(t), t == 0);
             if (t + 1 < n) {
-              if (h == 0) {
-                ok = tc::mbar_wait(&ctl->b_full[st ^ 1], ((gt + 1) >> 1) & 1, abort_flag);
+              if (s_issued == t + 1) {      // its K/V stage has not landed yet
+                ok = tc::mbar_wait_a(b_full_a + ((g0 + t + 1) & 1) * 8, ((g0 + t + 1) >> 1) & 1, abort_flag);
                 if (!ok) break;
                 tc::tc_fence_after();
+                issue_S(g0 + t + 1, cols_of(t + 1));
+                ++s_issued;
               }
-              issue_s(st ^ 1, h, cols_of(used_next, h));
+              issue_dP(g0 + t + 1, cols_of(t + 1));
             }
+            ++t;
+            progressed = true;
+          }
+          if (progressed) {
+            idle = 0;
+          } else if (++idle > (1u << 24) || ((idle & 1023) == 1023 && *abort_flag)) {
+            *abort_flag = 1;
+            ok = false;
           }
         }
         if (!ok) break;
@@ -666,14 +721,17 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dq_tc_kernel(const __grid_
         tc::umma_commit(&ctl->a_free);
         tc::mbar_arrive(&ctl->job_done[slot]);
         ++rc;
+        g0 += n;
       }
     }
   } else {
     // ================================================================ element-wise warps: one thread per query row
-    const int quarter = warp & 3, grp = (warp - 2) >> 2;     // grp = half of the tile's columns this thread handles
+    // four groups of four warps; group cg works on columns [32 cg, 32 cg + 32) of the tile
+    const int quarter = warp & 3, cg = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tS = tmem + kS + grp * 64 + lane_base, tDP = tmem + kDP + grp * 64 + lane_base;
+    const uint32_t tDP = tmem + kDP + cg * 32 + lane_base;
+    const bool relay = warp == 2 && lane == 0;                 // tells the producer which stream stages are free again
     bool ok = true;
     int gt = 0, rc = 0;
     for (int it = 0; ok; ++it) {
@@ -684,82 +742,102 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dq_tc_kernel(const __grid_
       const int64_t R = ctl->job_id[slot];
       if (R < 0) break;
       const int n = ctl->job_n[slot], last_cols = ctl->job_last[slot];
-      const int m = p.causal ? p.mq - 1 - (int)(R / p.bh) : (int)(R % p.mq);
-      const int64_t bh = p.causal ? R % p.bh : R / p.mq;
+      const int m = p.causal ? p.mq - 1 - (int)(R % p.mq) : (int)(R % p.mq);
+      const int64_t bh = R / p.mq;
       const int64_t qpos = (int64_t)m * 128 + r;
-      constexpr int HALF = D / 2;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.dq) + ((int64_t)bh * p.seq + qpos) * D + grp * HALF;
+      constexpr int QD = D / 4;                               // channels of the row each group stores
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.dq) + ((int64_t)bh * p.seq + qpos) * D + cg * QD;
       if (n == 0) {
         if (qpos < p.seq)
-          for (int c = 0; c < HALF; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0u, 0u, 0u, 0u);
+          for (int c = 0; c < QD; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0u, 0u, 0u, 0u);
         __syncwarp();
         if (lane == 0) tc::mbar_arrive(&ctl->job_done[slot]);
         continue;
       }
-      const float2 my = p.stat[bh * p.s_pad + qpos];          // (lse * log2 e, delta); +inf for rows past the end
+      // (-lse * log2 e, -delta) of this row; -inf for rows past the end
+      const float* my_pair = p.stat + ((bh * p.s_pad + qpos) >> 1) * 4 + (qpos & 1);
+      const float2 my = make_float2(my_pair[0], my_pair[2]);
       for (int t = 0; t < n && ok; ++t, ++gt) {
         const int st = gt & 1;
         const int used = t == n - 1 ? last_cols : 128;
-        const int cols = max(0, min(64, used - 64 * grp));
-        ok = tc::mbar_wait(&ctl->s_full[grp], gt & 1, abort_flag);
+        ok = tc::mbar_wait(&ctl->s_full, gt & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (cols > 0) {
+        // S and dP of this tile are complete, and so is dQ of the previous tile: V of this tile and K of the previous one
+        // may be replaced
+        if (relay) {
+          tc::mbar_arrive(&ctl->b1_free[st]);
+          if (t > 0) tc::mbar_arrive(&ctl->b0_free[st ^ 1]);
+        }
+        if (cg * 32 < used) {
           tc::tc_fence_after();
-          const int4* meta = reinterpret_cast<const int4*>(smem + C::OFF_META + st * 2048) + grp * 64;
-          const int flag = ctl->tile_flag[st];
-          const bool slow = (flag >> grp) & 1;
-#pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            uint32_t sv[32], dv[32], pd[16];
-            tc::tmem_ld32(tS + 32 * c, sv);
-            tc::tmem_ld32(tDP + 32 * c, dv);
-            tc::tmem_wait_ld();
+          const uint32_t tS = tmem + kS + st * 128 + cg * 32 + lane_base;
+          const int4* meta = reinterpret_cast<const int4*>(smem + C::OFF_META + st * 2048) + cg * 32;
+          const float2* lc2 = reinterpret_cast<const float2*>(smem + C::OFF_LC + st * 512) + cg * 16;
+          const bool slow = ctl->tile_flag[st] != 0;
+          const float2 sl2 = make_float2(p.scale_log2, p.scale_log2), nlse2 = make_float2(my.x, my.x), ndel2 = make_float2(my.y, my.y);
+          uint32_t sa[16], da[16];
+          auto chunk = [&](const uint32_t (&sv)[16], const uint32_t (&dv)[16], int c) {
+            uint32_t pd[8];
             if (!slow) {
+              // the copy count of a column is a power of two (or 0): it goes into the exponent, p c = 2^(s scale - lse +
+              // log2 c), so one rounding after the product equals the reference's rounding before it; log2 c = -inf
+              // (no copy exists) gives 0.  Two columns at a time on the packed fp32 pipe.
 #pragma unroll
-              for (int k = 0; k < 16; ++k) {
-                const float c0 = __int_as_float(meta[c * 32 + 2 * k].w), c1 = __int_as_float(meta[c * 32 + 2 * k + 1].w);
-                const float p0 = ex2f(fmaf(__uint_as_float(sv[2 * k]), p.scale_log2, -my.x));
-                const float p1 = ex2f(fmaf(__uint_as_float(sv[2 * k + 1]), p.scale_log2, -my.x));
-                const float y0 = p0 * (__uint_as_float(dv[2 * k]) - my.y), y1 = p1 * (__uint_as_float(dv[2 * k + 1]) - my.y);
-                pd[k] = pack16<FMT>(c0 > 0.f ? y0 * c0 : 0.f, c1 > 0.f ? y1 * c1 : 0.f);
+              for (int k = 0; k < 8; ++k) {
+                const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[2 * k]), __uint_as_float(sv[2 * k + 1])), sl2,
+                                            __fadd2_rn(lc2[c * 8 + k], nlse2));
+                const float2 pc = make_float2(ex2f(x.x), ex2f(x.y));
+                const float2 y = __fmul2_rn(pc, __fadd2_rn(make_float2(__uint_as_float(dv[2 * k]), __uint_as_float(dv[2 * k + 1])), ndel2));
+                pd[k] = pack16<FMT>(y.x, y.y);
               }
             } else {
 #pragma unroll
-              for (int k = 0; k < 16; ++k) {
-                const int4 m0 = meta[c * 32 + 2 * k], m1 = meta[c * 32 + 2 * k + 1];
+              for (int k = 0; k < 8; ++k) {
+                const int4 m0 = meta[c * 16 + 2 * k], m1 = meta[c * 16 + 2 * k + 1];
                 const int v0 = min(m0.y, (int)min(qpos + 1 - (int64_t)m0.x, (int64_t)1 << 30));
                 const int v1 = min(m1.y, (int)min(qpos + 1 - (int64_t)m1.x, (int64_t)1 << 30));
                 const float c0 = (float)max(0, min(v0, m0.z)), c1 = (float)max(0, min(v1, m1.z));
-                const float p0 = ex2f(fmaf(__uint_as_float(sv[2 * k]), p.scale_log2, -my.x));
-                const float p1 = ex2f(fmaf(__uint_as_float(sv[2 * k + 1]), p.scale_log2, -my.x));
-                const float y0 = p0 * (__uint_as_float(dv[2 * k]) - my.y), y1 = p1 * (__uint_as_float(dv[2 * k + 1]) - my.y);
+                const float p0 = ex2f(fmaf(__uint_as_float(sv[2 * k]), p.scale_log2, my.x));
+                const float p1 = ex2f(fmaf(__uint_as_float(sv[2 * k + 1]), p.scale_log2, my.x));
+                const float y0 = p0 * (__uint_as_float(dv[2 * k]) + my.y), y1 = p1 * (__uint_as_float(dv[2 * k + 1]) + my.y);
                 pd[k] = pack16<FMT>(c0 > 0.f ? round16<FMT>(y0) * c0 : 0.f, c1 > 0.f ? round16<FMT>(y1) * c1 : 0.f);
               }
             }
-            tc::tmem_st16(tDP + 16 * c, pd);
-          }
+            tc::tmem_st8(tDP + 8 * c, pd);
+          };
+          // this thread's 32 columns in two chunks of 16, one after the other; the packed results go back in place into
+          // columns of the dP buffer the thread has read itself (chunk c into [8 c, 8 c + 8) of its group's columns),
+          // because the other groups work on the same buffer at the same time.  Columns past the tile's end hold stale
+          // bits and are never read by a product.
+          tc::tmem_ld16(tS, sa); tc::tmem_ld16(tDP, da);
+          tc::tmem_wait_ld();
+          chunk(sa, da, 0);
+          tc::tmem_ld16(tS + 16, sa); tc::tmem_ld16(tDP + 16, da);
+          tc::tmem_wait_ld();
+          chunk(sa, da, 1);
           tc::tmem_wait_st();
           tc::tc_fence_before();
         }
         __syncwarp();
-        if (lane == 0) tc::mbar_arrive(&ctl->p_full[grp]);
+        if (lane == 0) tc::mbar_arrive(&ctl->p_full);
       }
       if (!ok) break;
-      // ---- dQ rows: each group stores half of the channels
+      // ---- dQ rows: each group stores a quarter of the channels
       ok = tc::mbar_wait(&ctl->acc_full, rc & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (relay) tc::mbar_arrive(&ctl->b0_free[(gt - 1) & 1]);   // K of the row's last tile
       tc::tc_fence_after();
-      const uint32_t tAcc = tmem + kAcc + grp * HALF + lane_base;
+      const uint32_t tAcc = tmem + kAcc + cg * QD + lane_base;
 #pragma unroll
-      for (int c0 = 0; c0 < HALF; c0 += 32) {
-        uint32_t a[32];
-        tc::tmem_ld32(tAcc + c0, a);
+      for (int c0 = 0; c0 < QD; c0 += 16) {
+        uint32_t a[16];
+        tc::tmem_ld16(tAcc + c0, a);
         tc::tmem_wait_ld();
         if (qpos < p.seq) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8)
+          for (int i = 0; i < 16; i += 8)
             *reinterpret_cast<uint4*>(orow + c0 + i) =
                 make_uint4(pack16<FMT>(__uint_as_float(a[i]) * p.scale, __uint_as_float(a[i + 1]) * p.scale),
                            pack16<FMT>(__uint_as_float(a[i + 2]) * p.scale, __uint_as_float(a[i + 3]) * p.scale),
@@ -793,13 +871,14 @@ __global__ void __launch_bounds__(kThreadsBwd, 1) bwd_dq_tc_kernel(const __grid_
 // ------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) bwd_stat_kernel(const T* __restrict__ o, const T* __restrict__ dout, const float* __restrict__ lse,
-                                                       float2* __restrict__ stat, int64_t bh, int64_t seq, int64_t s_pad, int D) {
+                                                       float* __restrict__ stat, int64_t bh, int64_t seq, int64_t s_pad, int D) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + warp;       // over bh * s_pad
   if (row >= bh * s_pad) return;
   const int64_t b = row / s_pad, t = row - b * s_pad;
+  float* dst = stat + (row >> 1) * 4 + (row & 1);           // per pair of rows: (-lse0, -lse1, -delta0, -delta1)
   if (t >= seq) {
-    if (lane == 0) stat[row] = make_float2(INFINITY, 0.f);
+    if (lane == 0) { dst[0] = -INFINITY; dst[2] = 0.f; }
     return;
   }
   const int64_t src = (b * seq + t) * D;
@@ -812,7 +891,8 @@ __global__ void __launch_bounds__(256) bwd_stat_kernel(const T* __restrict__ o, 
   if (lane == 0) {
     const float l = lse[b * seq + t];
     // a row that saw no key has lse = -inf; its probabilities are taken as 0 (the reference leaves them undefined)
-    stat[row] = make_float2(l == -INFINITY ? INFINITY : l * 1.4426950408889634f, acc);
+    dst[0] = l == -INFINITY ? -INFINITY : -l * 1.4426950408889634f;
+    dst[2] = -acc;
   }
 }
 
@@ -889,7 +969,7 @@ int launch_bwd_tc(const void* q, const void* kimg, const void* vimg, const int32
   BwdParams p;
   p.mask = mask; p.kimg = (const unsigned char*)kimg; p.vimg = (const unsigned char*)vimg;
   p.img = make_img_levels(bh, seq, D, 128);
-  p.stat = reinterpret_cast<const float2*>(scratch + L.stat);
+  p.stat = reinterpret_cast<const float*>(scratch + L.stat);
   p.dq = dq;
   for (int i = 0; i < 4; ++i) {
     p.dkp[i] = reinterpret_cast<float*>(scratch + L.pooled[i]);
@@ -906,7 +986,7 @@ int launch_bwd_tc(const void* q, const void* kimg, const void* vimg, const int32
   PSA_REQUIRE(e == cudaSuccess, PSA_ERR_CUDA, "psa_legacy_bwd_tcgen05: cudaMemsetAsync failed: %s", cudaGetErrorString(e));
 
   bwd_stat_kernel<T><<<(unsigned)cdiv64(bh * s_pad, 8), 256, 0, st>>>((const T*)out, (const T*)dout, lse,
-                                                                     reinterpret_cast<float2*>(scratch + L.stat), bh, seq, s_pad, D);
+                                                                     reinterpret_cast<float*>(scratch + L.stat), bh, seq, s_pad, D);
   PSA_CHECK_LAUNCH("psa_legacy_bwd_tcgen05(row statistics)");
   bwd_items_kernel<<<1, 32, 0, st>>>(reinterpret_cast<int2*>(scratch + L.items), nk);
   PSA_CHECK_LAUNCH("psa_legacy_bwd_tcgen05(work list)");
