@@ -78,9 +78,16 @@ def test_block_scores_oracle(P, dt, S, D, bm, bn, impl):
     # 16-bit: R is rounded to the element type before exp2, so a dot product whose fp32 sum lands on the other side
     # of a rounding boundary (summation order) moves that cell by one ulp of R, i.e. up to 2^(ulp) in the score:
     # rare (bounded below) but as large as 3% (fp16) / 25% (bf16) of the row scale when it happens.
-    eps = {"fp32": 1e-6, "fp16": 3e-2, "bf16": 0.25}[dt]
-    assert float(((po - ref).abs() / ref.amax(-1, keepdim=True)).max()) <= eps
-    assert float((po != ref).float().mean()) < (0.02 if dt != "fp32" else 1.0)
+    rel, cells = float(((po - ref).abs() / ref.amax(-1, keepdim=True)).max()), float((po != ref).float().mean())
+    import json, os
+    if os.environ.get("PSA_PARITY_REPORT"):
+        with open(os.environ["PSA_PARITY_REPORT"], "a") as f:
+            f.write(json.dumps({"case": f"scores_{dt}_{S}_{D}_{bm}_{bn}_{impl}", "po_cells_differ": cells, "po_max_rel_to_row_max": rel}) + "\n")
+    # measured on a B200 over these cases: no cell differs in most of them; worst fp16 (S=5000, tcgen05 path) 1.2 % of the
+    # cells by at most 0.4 % of the row maximum, worst bf16 0.023 % of the cells by at most 0.14 %
+    eps = {"fp32": 1e-6, "fp16": 1e-2, "bf16": 5e-2}[dt]
+    assert rel <= eps
+    assert cells < {"fp32": 1.0, "fp16": 0.02, "bf16": 2e-3}[dt]
 
 
 # ------------------------------------------------------------------ level assignment: bit exact --------
@@ -226,7 +233,9 @@ def test_ksim_golden(P, golden, case):
 # ------------------------------------------------------------------ plug-and-play call -----------------
 @pytest.mark.parametrize("case", C.E2E_CASES, ids=lambda c: c[0])
 def test_end_to_end_golden(P, golden, case):
-    """PSAAttention with the oracle's sample offsets: mask vs the reference's mask, output vs its output."""
+    """PSAAttention with the oracle's sample offsets.  The reference's module returns no mask, so the fixture's
+    `<case>_mask` is the ORACLE's mask for these inputs (the oracle's assignment is itself pinned bit for bit against
+    the reference's transfer_attn_to_mask); `<case>_out` is the reference's own output."""
     name, S, D, H, kw, seed = case
     kw = dict(kw)
     if "mask_ratios" in kw:
@@ -239,7 +248,11 @@ def test_end_to_end_golden(P, golden, case):
     mask, po, _ = P.compute_block_mask(q.to(DEV), k.to(DEV), cfg, idx_q=iq.to(DEV), idx_k=ik.to(DEV))
     ref_mask = t(golden[f"{name}_mask"])
     agree = float((mask.cpu() == ref_mask).float().mean())
-    assert agree > 0.98, f"mask agreement {agree}"     # fp32 scores differ in the last bits (summation order)
+    import json, os
+    if os.environ.get("PSA_PARITY_REPORT"):
+        with open(os.environ["PSA_PARITY_REPORT"], "a") as f:
+            f.write(json.dumps({"case": f"e2e_{name}", "mask_agreement": agree}) + "\n")
+    assert agree >= 0.998, f"mask agreement {agree}"   # measured 1.0 in all four cases; fp32 scores differ in the last bits only
     out = P.PSAAttention(cfg)(q.to(DEV), k.to(DEV), v.to(DEV), idx_q=iq.to(DEV), idx_k=ik.to(DEV)).cpu()
     if agree == 1.0:
         assert float((C.sub(out) - t(golden[f"{name}_out"])).abs().max()) < 2e-5
