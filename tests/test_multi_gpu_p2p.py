@@ -120,3 +120,64 @@ def test_pull_and_scatter_match_the_collective(H, S, D):
     for p in procs:
         p.join(timeout=60)
     assert results == {0: "ok", 1: "ok"}, results
+
+
+def _grid_worker(rank: int, world: int, port: int, H: int, S: int, D: int, q):
+    try:
+        import torch.distributed as dist
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        import psa_b200
+        from psa_b200 import ops
+        from psa_b200.parallel import GridShard
+        import cases as C
+
+        dtype = torch.bfloat16
+        sl = S // world
+        full = [C.randn(700 + i, (H, S, D), dtype, smooth=8 if i < 2 else 0) for i in range(3)]      # q, k, v: [H, S, D]
+        mine = torch.stack([x[:, rank * sl:(rank + 1) * sl].permute(1, 0, 2) for x in full]).contiguous().to(dev)   # [3, S/P, H, D]
+        grid = GridShard(world, rank, H, S, D, 128)
+        qp, kk, vv = grid.to_grid(mine)
+        h0, h1 = grid.head_range()
+        r0, r1 = grid.query_range()
+        assert r0 % 128 == 0
+        cfg = psa_b200.PSAConfig(mask_ratios=C.DEFAULT_RATIOS)
+        torch.manual_seed(5)                                       # the same draw on every rank, sliced by head group
+        iq = ops.draw_sample_indices(1, H, 128, 32, dev)
+        ik = ops.draw_sample_indices(1, H, 64, 16, dev)
+        mod = psa_b200.PSAAttention(cfg)
+        part = mod(qp.unsqueeze(0), kk.unsqueeze(0), vv.unsqueeze(0), idx_q=iq[:, h0:h1].contiguous(), idx_k=ik[:, h0:h1].contiguous())
+        back = grid.to_seq(part[0])                                # [H, S/P, D]: all heads of this rank's tokens
+        # the same layer on one GPU, whole heads and all query blocks
+        whole = mod(full[0].unsqueeze(0).to(dev), full[1].unsqueeze(0).to(dev), full[2].unsqueeze(0).to(dev), idx_q=iq, idx_k=ik)
+        want = whole[0, :, rank * sl:(rank + 1) * sl]
+        assert torch.equal(back, want), "2-D partition differs from the single-GPU layer"
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001 - the parent reports it
+        import traceback
+        q.put((rank, "".join(traceback.format_exception(type(e), e, e.__traceback__))[-3000:]))
+
+
+@pytest.mark.parametrize("H,S,D", [(3, 2 * 1000, 128), (1, 2 * 700, 64)])
+def test_head_group_times_query_range_split_is_bit_identical_to_one_gpu(H, S, D):
+    """Head counts that do not divide the GPU count: gcd(H, 2) = 1 head group x 2 query-block ranges (the cut falls inside
+    rank 1's token shard).  Each rank attends its query range against all keys; the reassembled output must equal the
+    single-GPU layer bit for bit."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_grid_worker, args=(r, 2, port, H, S, D, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = {}
+    for _ in procs:
+        r, msg = q.get(timeout=240)
+        results[r] = msg
+    for p in procs:
+        p.join(timeout=60)
+    assert results == {0: "ok", 1: "ok"}, results
