@@ -20,7 +20,7 @@
 //               O += P V with P read from TMEM and V read MN-major from its swizzled tile.  Descriptors are built once;
 //               per MMA only an immediate is added.  It polls (non-blocking) for whichever product is ready and issues in
 //               the fixed order QK0 QK1 PV0 QK2 PV1 ...; the tensor pipe runs in issue order, so "S of tile t ready" also
-//               says that P V of tile t-2 is done with the buffer.  The first scores of the next row are computed while
+//               says that P V of tile t-2 is done with the buffer and with the accumulator.  The first scores of the next row are computed while
 //               the softmax warps are still in the epilogue of the current one.
 //   warps 4-11  softmax: two groups of four warps, ONE thread per query row.  Group g owns the tiles whose running index
 //               is g (mod 2), with its own running maximum, running sum and output accumulator (a split-KV inside the
@@ -546,7 +546,9 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
                     tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, (t > 1 || ks > 0) ? 1u : 0u);
                 }
                 tc::umma_commit_a(v_empty_a + stage * 8);   // V tile may be refilled
-                tc::umma_commit_a(pv_done_a + b * 8);       // accumulator b is consistent again
+                // a tcgen05.commit costs this thread 100-500 cycles: "accumulator b is final" is only signalled for its last
+                // tile of the row (in between, the scores of tile t+2 - issued after this product - say the same)
+                if (t >= n_tiles - 2) tc::umma_commit_a(pv_done_a + b * 8);
                 ++pv_next;
                 progressed = true;
               }
@@ -602,7 +604,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     const uint32_t tO_other = tmem + 256 + (g ^ 1) * 128 + lane_base;
     const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
     bool ok = true;
-    int g0 = 0, q_rows = 0;
+    int g0 = 0, q_rows = 0, pv_rows = 0;
     for (int rit = 0; ok; ++rit) {
       const int rslot = rit & 3;
       ok = tc::mbar_wait(&ctl->row_ready[rslot], (rit >> 2) & 1, abort_flag);
@@ -642,6 +644,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           ok = tc::mbar_wait(&ctl->s_full[g], it & 1, abort_flag);   // scores ready (and the tile's bias words visible)
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
+          // The scores of running tile gj were issued after P V of tile gj-2 (same group), so that product is complete
+          // and the accumulator may be rescaled below.
           tc::tc_fence_after();
           const bool ragged = j == n_tiles - 1 && last_cols < 128;   // columns the MMA did not write hold stale bits
           const float4* bias4 = reinterpret_cast<const float4*>(sBias + slot * 128);
@@ -712,11 +716,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             l_run *= alpha;
           }
           if (j >= 2 && __any_sync(0xffffffffu, raise)) {
-            // the accumulator may only be touched between two of its P V products: wait for the one of tile j-2
-            ok = tc::mbar_wait(&ctl->pv_done[g], (it - 1) & 1, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc::tc_fence_after();
+            // the accumulator may only be touched between two of its P V products: the one of tile j-2 is complete (see
+            // above), the one of tile j waits for the probabilities written below
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 32) {
               tc::tmem_ld32(tO + c0, vb);
@@ -801,9 +802,10 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       // ---- epilogue: merge the two groups' partial results
       const int my_tiles = n_tiles > first ? (n_tiles - first + 1) >> 1 : 0;
       if (ok && my_tiles > 0) {
-        const int last_it = (g0 + first + 2 * (my_tiles - 1)) >> 1;
-        ok = tc::mbar_wait(&ctl->pv_done[g], last_it & 1, abort_flag);
+        // signalled once per row in which this group has tiles: after the last of them
+        ok = tc::mbar_wait(&ctl->pv_done[g], pv_rows & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
+        ++pv_rows;
       }
       // group g publishes (maximum, sum); after the barrier both groups' last products are complete.  An aborting group
       // still joins the barrier so that the other one is not left waiting.
