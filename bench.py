@@ -44,7 +44,8 @@ KERNELS_PER_CALL = {
     "psa_pyramid_kv_images": 1, "psa_pyramid_kv": 1, "psa_block_scores": 4, "psa_block_scores_samples": 2,
     "psa_assign_levels": 1, "psa_fwd_images": 1, "psa_fwd": 1, "psa_fwd_images_scatter": 1, "psa_push_heads": 1,
     "psa_push_samples": 1, "psa_pull_heads": 1, "psa_density": 1, "psa_legacy_fwd_images": 2, "psa_legacy_bwd_tc": 3,
-    "psa_legacy_bwd_tcgen05": 5,
+    "psa_legacy_bwd_tcgen05": 5, "psa_ksim": 1, "psa_ksim_perm": 1, "psa_legacy_fwd_images_perm": 2, "psa_gather_rows": 1,
+    "psa_pyramid_kv_images_perm": 1, "psa_block_scores_perm": 4,
 }
 
 
@@ -378,6 +379,72 @@ def run_causal_training(args, workload, synthetic):
         dist.destroy_process_group()
 
 
+def run_preset_layer(args, workload, synthetic):
+    """--workload wan2.1-1.3b-default-preset: one call of the plug-and-play module (PyramidSparseAttention) configured by
+    the pipeline's default preset of attention_config.yaml - old mask format, block 128, cumulative-mass thresholds,
+    similarity cap, Gilbert token order - on the Wan2.1-1.3B attention shape (single GPU).  Reports the layer with the
+    reordering folded into the kernels and, beside it, with the reference's four reordering copies."""
+    import psa_b200
+    from psa_b200 import ops, _lib
+    from psa_b200.presets import WanAttentionConfigLoader
+    from psa_b200.pyramid_sparse_attention import AttentionConfig, PyramidSparseAttention
+    assert int(os.environ.get("WORLD_SIZE", "1")) == 1, "this workload runs on one GPU"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    launches = LaunchCounter(_lib.lib)
+    H, D, S = workload["heads"], workload["head_dim"], synthetic.seq_len(workload)
+    info = WanAttentionConfigLoader().get_attention_config(workload["model"], None, list(workload["video_shape"]))
+    params = dict(info["params"]); params["warmup_steps"] = 0; params["verbose"] = False
+    cfg = AttentionConfig(**params)
+    module = PyramidSparseAttention(cfg, inference_num=50, layer_num=30, model_type=workload["model"])
+    q, k, v = synthetic.make_qkv(workload, 1000, torch.bfloat16, dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    with torch.no_grad():
+        assert module._rows_in_place_old_format(q, k)
+        sampler = ClockSampler(0)
+        sampler.start()
+        for _ in range(args.warmup):
+            module(q, k, v, 0)
+        torch.cuda.synchronize()
+        sampler.mark_begin()
+        launches.on = True
+        ms = timed(lambda: module(q, k, v, 0), args.steps, 0)
+        launches.on = False
+        sampler.mark_end()
+        clocks = sampler.stop()
+        dens = float(module.logger.records[-1]["density"].mean().item())
+        module.logger.records.clear()
+        folded = PyramidSparseAttention._rows_in_place_old_format
+        PyramidSparseAttention._rows_in_place_old_format = lambda self, q_, k_: False      # the copy route, for comparison
+        ms_copies = timed(lambda: module(q, k, v, 0), args.steps, args.warmup)
+        PyramidSparseAttention._rows_in_place_old_format = folded
+    ops.check_status(dev)
+    f_dense = 4.0 * H * float(S) * S * D
+    print(json.dumps({
+        "metric": "psa_attn_dense_equiv_tflops", "value": f_dense / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload["name"], "B": 1, "heads": H, "head_dim": D, "seq_len": S, "grid": list(workload["grid"]),
+                   "preset": info["name"], "attn_impl": cfg.attn_impl, "block": [cfg.block_m, cfg.block_n, cfg.tile_n],
+                   "mask_mode": cfg.mask_mode, "use_sim_mask": cfg.use_sim_mask, "rearrange": cfg.rearrange_method,
+                   "l2": "inputs (q,k,v) larger than L2"},
+        "ms_per_layer": ms, "ms_per_layer_with_reordering_copies": ms_copies, "density": dens, "gpu_launches": launches.count,
+        "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -403,6 +470,8 @@ def main():
     workload = dict(synthetic.WORKLOADS[args.workload])
     if workload["name"] == "causal-legacy-fwd-bwd":
         return run_causal_training(args, workload, synthetic)
+    if workload["name"] == "wan2.1-1.3b-default-preset":
+        return run_preset_layer(args, workload, synthetic)
     if args.heads:
         workload["heads"] = args.heads
         workload["name"] += f"-{args.heads}heads"

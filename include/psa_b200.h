@@ -158,6 +158,16 @@ int psa_fwd_images_perm(const void* q, const void* kimg, const void* vimg, const
                         const int32_t* out_perm, int64_t bh, int64_t seq_q, int64_t seq_k, int head_dim, int block_m,
                         int block_n, int tile_n, int mask_width, float sm_scale, int compat_quirk, int dtype, int32_t* status,
                         void* stream);
+/* The same for the presets with the old mask format and the similarity cap (every shipped `attn_impl: old_mask_type`
+ * preset reorders too, src/psa_triton/pyramid_sparse_attention.py:340-406):
+ *   psa_ksim_perm:               psa_ksim of the reordered k (calc_k_similarity_triton after rearrange)
+ *   psa_legacy_fwd_images_perm:  psa_legacy_fwd_images (not causal, no lse) with q already reordered, kimg/vimg from
+ *                                psa_pyramid_kv_images_perm(block_n = 128), output row t stored at row out_perm[t] */
+int psa_ksim_perm(const void* k, const int32_t* perm, int32_t* out, int64_t bh, int64_t seq, int head_dim, int block_n, float t2,
+                  float t4, float t8, int dtype, void* stream);
+int psa_legacy_fwd_images_perm(const void* q, const void* kimg, const void* vimg, const int32_t* mask, int32_t* index_scratch,
+                               void* out, const int32_t* out_perm, int64_t bh, int64_t seq, int head_dim, int mask_cols,
+                               float sm_scale, int dtype, int32_t* status, void* stream);
 
 /* Token-major tensors.  Replaces the three transpose(1, 2) of q, k, v in front of the attention call and the
  * transpose(1, 2).flatten(2, 3) behind it in the diffusers processors, modify_diffusers.py:302-307 and :357-371 (each

@@ -8,8 +8,8 @@
 namespace psa {
 
 template <typename T>
-__global__ void __launch_bounds__(128) ksim_kernel(const T* __restrict__ k, int32_t* __restrict__ out, int64_t seq,
-                                                   int D, int bn, int nblk, float t2, float t4, float t8) {
+__global__ void __launch_bounds__(128) ksim_kernel(const T* __restrict__ k, const int32_t* __restrict__ perm, int32_t* __restrict__ out,
+                                                   int64_t seq, int D, int bn, int nblk, float t2, float t4, float t8) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int blk = blockIdx.x * 4 + warp;
   if (blk >= nblk) return;
@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(128) ksim_kernel(const T* __restrict__ k, int3
       for (int t = 0; t < 8; ++t) {
         int64_t tok = (int64_t)blk * bn + g0 + t;
         tok = tok < seq ? tok : seq - 1;
+        if (perm) tok = perm[tok];              // token `tok` of the reordered sequence is stored row perm[tok]
         x[t] = Elem<T>::to_f(kh[tok * D + c]);
         nn[t] = fmaf(x[t], x[t], nn[t]);
       }
@@ -67,8 +68,8 @@ __global__ void __launch_bounds__(128) ksim_kernel(const T* __restrict__ k, int3
 
 }  // namespace psa
 
-extern "C" int psa_ksim(const void* k, int32_t* out, int64_t bh, int64_t seq, int head_dim, int block_n, float t2,
-                        float t4, float t8, int dtype, void* stream) {
+static int ksim_launch(const void* k, const int32_t* perm, int32_t* out, int64_t bh, int64_t seq, int head_dim, int block_n, float t2,
+                       float t4, float t8, int dtype, void* stream) {
   using namespace psa;
   PSA_REQUIRE(k && out, PSA_ERR_ARG, "psa_ksim: null pointer");
   PSA_REQUIRE(bh > 0 && bh < 65536 && seq > 0, PSA_ERR_ARG, "psa_ksim: bad shape");
@@ -76,7 +77,18 @@ extern "C" int psa_ksim(const void* k, int32_t* out, int64_t bh, int64_t seq, in
   const int nblk = (int)cdiv64(seq, block_n);
   dim3 grid((nblk + 3) / 4, (unsigned)bh);
   cudaStream_t st = (cudaStream_t)stream;
-  PSA_DISPATCH_DTYPE(dtype, T, (ksim_kernel<T><<<grid, 128, 0, st>>>((const T*)k, out, seq, head_dim, block_n, nblk, t2, t4, t8)));
+  PSA_DISPATCH_DTYPE(dtype, T, (ksim_kernel<T><<<grid, 128, 0, st>>>((const T*)k, perm, out, seq, head_dim, block_n, nblk, t2, t4, t8)));
   PSA_CHECK_LAUNCH("psa_ksim");
   return PSA_OK;
+}
+
+extern "C" int psa_ksim(const void* k, int32_t* out, int64_t bh, int64_t seq, int head_dim, int block_n, float t2,
+                        float t4, float t8, int dtype, void* stream) {
+  return ksim_launch(k, nullptr, out, bh, seq, head_dim, block_n, t2, t4, t8, dtype, stream);
+}
+
+extern "C" int psa_ksim_perm(const void* k, const int32_t* perm, int32_t* out, int64_t bh, int64_t seq, int head_dim, int block_n,
+                             float t2, float t4, float t8, int dtype, void* stream) {
+  PSA_REQUIRE(perm, PSA_ERR_ARG, "psa_ksim_perm: null pointer");
+  return ksim_launch(k, perm, out, bh, seq, head_dim, block_n, t2, t4, t8, dtype, stream);
 }

@@ -44,9 +44,9 @@ extern "C" size_t psa_legacy_index_bytes(int64_t bh, int64_t seq) {
   return (size_t)(bh * n * (n + 5) * (int64_t)sizeof(int32_t));
 }
 
-extern "C" int psa_legacy_fwd_images(const void* q, const void* kimg, const void* vimg, const int32_t* mask, int32_t* index_scratch,
-                                     void* out, float* lse, int64_t bh, int64_t seq, int head_dim, int mask_cols, float sm_scale,
-                                     int causal, int dtype, int32_t* status, void* stream) {
+static int legacy_fwd_images(const void* q, const void* kimg, const void* vimg, const int32_t* mask, int32_t* index_scratch,
+                             void* out, float* lse, const int32_t* out_perm, int64_t bh, int64_t seq, int head_dim, int mask_cols,
+                             float sm_scale, int causal, int dtype, int32_t* status, void* stream) {
   using namespace psa;
   PSA_REQUIRE(q && kimg && vimg && mask && index_scratch && out, PSA_ERR_ARG, "psa_legacy_fwd_images: null pointer");
   PSA_REQUIRE(bh > 0 && bh < 65536 && seq > 0, PSA_ERR_ARG, "psa_legacy_fwd_images: bad shape");
@@ -64,7 +64,23 @@ extern "C" int psa_legacy_fwd_images(const void* q, const void* kimg, const void
   a.bh = bh; a.seq_q = seq; a.seq_k = seq; a.D = head_dim; a.bm = 128; a.bn = 128; a.tn = 32;
   a.width = nk + 5; a.scale = sm_scale; a.quirk = 0; a.dtype = dtype;
   a.lse = lse; a.legacy = 1; a.causal = causal ? 1 : 0;
+  a.scatter.row_perm = out_perm;
   PSA_REQUIRE(fwd_tc_supported(a), PSA_ERR_UNSUPPORTED,
               "psa_legacy_fwd_images: needs f16/bf16, head_dim 64/128 and at most 1467 key blocks");
   return fwd_tc_launch(a, st);
+}
+
+extern "C" int psa_legacy_fwd_images(const void* q, const void* kimg, const void* vimg, const int32_t* mask, int32_t* index_scratch,
+                                     void* out, float* lse, int64_t bh, int64_t seq, int head_dim, int mask_cols, float sm_scale,
+                                     int causal, int dtype, int32_t* status, void* stream) {
+  return legacy_fwd_images(q, kimg, vimg, mask, index_scratch, out, lse, nullptr, bh, seq, head_dim, mask_cols, sm_scale, causal, dtype,
+                           status, stream);
+}
+
+extern "C" int psa_legacy_fwd_images_perm(const void* q, const void* kimg, const void* vimg, const int32_t* mask, int32_t* index_scratch,
+                                          void* out, const int32_t* out_perm, int64_t bh, int64_t seq, int head_dim, int mask_cols,
+                                          float sm_scale, int dtype, int32_t* status, void* stream) {
+  PSA_REQUIRE(out_perm, PSA_ERR_ARG, "psa_legacy_fwd_images_perm: null pointer");
+  return legacy_fwd_images(q, kimg, vimg, mask, index_scratch, out, nullptr, out_perm, bh, seq, head_dim, mask_cols, sm_scale, 0, dtype,
+                           status, stream);
 }

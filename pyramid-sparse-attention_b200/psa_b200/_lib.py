@@ -64,6 +64,8 @@ SIGNATURES = {
     "psa_assign_levels": (_i, [_p, _p, _i64, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _i, _i, _p]),
     "psa_density": (_i, [_p, _p, _i64, _i64, _i, _i, _p]),
     "psa_ksim": (_i, [_p, _p, _i64, _i64, _i, _i, _f, _f, _f, _i, _p]),
+    "psa_ksim_perm": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _f, _f, _f, _i, _p]),
+    "psa_legacy_fwd_images_perm": (_i, [_p] * 7 + [_i64, _i64, _i, _i, _f, _i, _p, _p]),
     "psa_fwd": (_i, [_p] * 11 + [_i64, _i64, _i64, _i, _i, _i, _i, _i, _f, _i, _i, _i, _p, _p]),
     "psa_legacy_fwd": (_i, [_p] * 12 + [_i64, _i64, _i, _i, _f, _i, _i, _p]),
     "psa_legacy_bwd": (_i, [_p] * 17 + [_i64, _i64, _i, _i, _f, _i, _i, _p]),

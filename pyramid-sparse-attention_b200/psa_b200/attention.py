@@ -53,15 +53,13 @@ def compute_block_mask(q, k, config, text_length: int = 0, idx_q=None, idx_k=Non
     """Scores -> level mask (-> similarity cap), the no-grad half of PSAAttention.forward
     (src/psa_triton/attention.py:178-223, 276-299).  Returns (mask, scores, sim_mask).
     The sample offsets are drawn from torch's generator of q's device, Q first and K second, exactly as
-    the reference does; tests may pass them in instead.  perm (int32 [S], no similarity cap): the mask of
-    q[..., perm, :], k[..., perm, :] with the rows read in place."""
+    the reference does; tests may pass them in instead.  perm (int32 [S]): the mask of q[..., perm, :],
+    k[..., perm, :] with the rows read in place."""
     B, H = q.shape[0], q.shape[1]
     sim = None
-    if perm is not None and config.use_sim_mask:
-        raise ValueError("the similarity cap reads k row-major: reorder k first instead of passing perm")
     if config.use_sim_mask:
         sim = ops.k_similarity(k, config.block_n, float(config.sim_2x_threshold), float(config.sim_4x_threshold),
-                               float(config.sim_8x_threshold))
+                               float(config.sim_8x_threshold), perm=perm)
     if idx_q is None:
         idx_q = ops.draw_sample_indices(B, H, config.block_m, config.block_m // 4, q.device)
     if idx_k is None:

@@ -413,16 +413,21 @@ def density(mask: torch.Tensor, newtype: bool) -> torch.Tensor:
     return out
 
 
-def k_similarity(k: torch.Tensor, block_n: int, t2: float, t4: float, t8: float) -> torch.Tensor:
+def k_similarity(k: torch.Tensor, block_n: int, t2: float, t4: float, t8: float, perm: Optional[torch.Tensor] = None) -> torch.Tensor:
     """[B,H,ceil(S/block_n)] int32 in {1,2,4,8}; calc_k_similarity_triton on the replicate-padded K
-    (src/psa_triton/kernels/calc_ksim_kernel.py:160-225, src/psa_triton/attention.py:196-204)."""
+    (src/psa_triton/kernels/calc_ksim_kernel.py:160-225, src/psa_triton/attention.py:196-204).  perm: the cap of
+    k[..., perm, :], read in place."""
     _need_cuda(k)
     k = _flat_bh(k)
     B, H, S, D = k.shape
     assert block_n % 8 == 0, "blocksize must be divisible by 8"
     with torch.cuda.device(k.device):
         out = torch.empty((B, H, -(-S // block_n)), dtype=torch.int32, device=k.device)
-        rc = lib.psa_ksim(_ptr(k), _ptr(out), B * H, S, D, block_n, t2, t4, t8, _dt(k), _stream(k))
+        if perm is None:
+            rc = lib.psa_ksim(_ptr(k), _ptr(out), B * H, S, D, block_n, t2, t4, t8, _dt(k), _stream(k))
+        else:
+            perm = _perm32(perm, S)
+            rc = lib.psa_ksim_perm(_ptr(k), _ptr(perm), _ptr(out), B * H, S, D, block_n, t2, t4, t8, _dt(k), _stream(k))
     check(rc, "psa_ksim")
     return out
 
@@ -539,6 +544,31 @@ def legacy_forward(q, k, v, mask, causal: bool = False, sm_scale: Optional[float
                                 _dt(q), _stream(q))
     check(rc, "psa_legacy_fwd")
     return o, lse, kv
+
+
+def legacy_forward_reordered(q, k, v, mask, perm: torch.Tensor, sm_scale: Optional[float] = None) -> torch.Tensor:
+    """The legacy forward (not causal, inference) of q[..., perm, :], k[..., perm, :], v[..., perm, :] with the result put
+    back in the stored order - without reordered copies of k, v or the output: the tile images are built through perm,
+    only q is gathered, and the forward stores output row t at row perm[t].  mask: the level mask of the reordered
+    sequence (old format)."""
+    _need_cuda(q, k, v, mask, perm)
+    q, k, v, mask = _flat_bh(q), _flat_bh(k), _flat_bh(v), _mask32(mask)
+    B, H, S, D = q.shape
+    sm_scale = D ** -0.5 if sm_scale is None else sm_scale
+    if not _legacy_tc_ok(q, sm_scale):
+        raise ValueError("the reordered legacy forward needs f16/bf16 tensors, at most 1467 blocks of 128 tokens and a positive scale")
+    perm = _perm32(perm, S)
+    imgs = pyramid_kv_images(k, v, 128, perm=perm)
+    q_r = gather_rows(q, perm)
+    with torch.cuda.device(q.device):
+        o = torch.empty_like(q)
+        scratch = torch.empty(lib.psa_legacy_index_bytes(B * H, S) // 4, dtype=torch.int32, device=q.device)
+        status = status_word(q.device)
+        rc = lib.psa_legacy_fwd_images_perm(_ptr(q_r), _ptr(imgs.kimg), _ptr(imgs.vimg), _ptr(mask), _ptr(scratch), _ptr(o), _ptr(perm),
+                                            B * H, S, D, mask.shape[-1], float(sm_scale), _dt(q), _ptr(status), _stream(q))
+    check(rc, "psa_legacy_fwd_images_perm")
+    o._psa_status = status
+    return o
 
 
 def legacy_forward_tc(q, k, v, mask, sm_scale: Optional[float] = None, need_lse: bool = True, causal: bool = False):

@@ -142,12 +142,32 @@ class PyramidSparseAttention(nn.Module):
 
     def _rows_in_place(self, q, k) -> bool:
         """Whether the Gilbert order can be folded into the kernels (k, v, the output and the sampled q rows are never
-        copied): 16-bit tensors on the tcgen05 kernels, separator-format mask, no similarity cap."""
+        copied): 16-bit tensors on the tcgen05 kernels, separator-format mask without the similarity cap."""
         c = self.config
         return (self.use_rearrange and c.attn_impl == "new_mask_type" and not c.use_sim_mask and q.is_cuda
                 and q.shape[2] == k.shape[2] == self.gilbert_rearranger.total_elements + self.gilbert_rearranger.text_length
                 and ops.images_supported(k, c.block_m, c.block_n, c.tile_n)
                 and -(-k.shape[2] // c.block_n) + 5 <= 1472)
+
+    def _rows_in_place_old_format(self, q, k) -> bool:
+        """The same for the old mask format (with or without the similarity cap; block 128): inference only, the
+        differentiable route keeps the copies."""
+        c = self.config
+        return (self.use_rearrange and c.attn_impl == "old_mask_type" and q.is_cuda
+                and not (torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or self._v_requires_grad))
+                and q.dtype in (torch.float16, torch.bfloat16) and c.block_m == 128 and c.block_n == 128 and c.tile_n == 32
+                and q.shape[-1] in (64, 128) and -(-q.shape[2] // 128) + 5 <= 1472
+                and q.shape[2] == k.shape[2] == self.gilbert_rearranger.total_elements + self.gilbert_rearranger.text_length)
+
+    _v_requires_grad = False      # set per call by forward()
+
+    def _forward_old_format_in_place(self, q, k, v, compute_stats):
+        c = self.config
+        perm = self.gilbert_rearranger.source_rows(q.device)
+        mask, _, _ = compute_block_mask(q, k, c, text_length=c.text_length, perm=perm)
+        out = ops.legacy_forward_reordered(q, k, v, mask, perm)
+        dens = ops.density(mask, False) if compute_stats else None
+        return out, dens
 
     def _forward_rows_in_place(self, q, k, v, compute_stats):
         c = self.config
@@ -164,6 +184,14 @@ class PyramidSparseAttention(nn.Module):
         is_warmup = self.get_current_time() < self.config.warmup_steps
         compute_stats = self.config.verbose or self.logger is not None
         dens = None
+        self._v_requires_grad = v.requires_grad
+        if not is_warmup and self._rows_in_place_old_format(q, k):
+            out, dens = self._forward_old_format_in_place(q, k, v, compute_stats)
+            self.sparsity_counter += 1
+            if self.logger is not None:
+                self.logger.log_sparsity(layer_idx=layer_idx, density=dens, sequence_length=q.shape[2],
+                                         batch_size=q.shape[0], num_heads=q.shape[1], is_warmup=False)
+            return out
         if not is_warmup and self._rows_in_place(q, k):
             tm = [token_major_view(x) for x in (q, k, v)]
             if all(t is not None for t in tm):

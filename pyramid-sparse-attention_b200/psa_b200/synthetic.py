@@ -20,7 +20,12 @@ TINY = dict(name="tiny-attn-layer", heads=2, head_dim=64, grid=(4, 32, 32), text
 # causal forward + backward of the legacy kernels: batch 2 x 16 heads, 32768 tokens laid out as 8 frames of 64x64
 CAUSAL_TRAIN = dict(name="causal-legacy-fwd-bwd", heads=16, head_dim=128, grid=(8, 64, 64), text=0, batch=2)
 
-WORKLOADS = {w["name"]: w for w in (WAN_1_3B, WAN_14B, COGVIDEOX_5B, TINY, CAUSAL_TRAIN)}
+# the Wan2.1-1.3B layer through the plug-and-play module with the pipeline's DEFAULT preset (old mask format, block 128,
+# cumulative-mass thresholds, similarity cap, Gilbert order)
+WAN_1_3B_PRESET = dict(name="wan2.1-1.3b-default-preset", heads=12, head_dim=128, grid=(21, 30, 52), text=0,
+                       model="Wan2.1_1.3b", video_shape=(832, 480, 81))
+
+WORKLOADS = {w["name"]: w for w in (WAN_1_3B, WAN_14B, COGVIDEOX_5B, TINY, CAUSAL_TRAIN, WAN_1_3B_PRESET)}
 
 
 def structured_field(seed: int, heads: int, head_dim: int, grid, text: int = 0, dtype=torch.bfloat16, device="cpu",

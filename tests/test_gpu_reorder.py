@@ -113,6 +113,56 @@ def test_module_reorders_in_place(P, text):
     assert mod.logger.records[0]["density"].shape == (1, H)
 
 
+def test_similarity_cap_through_a_row_table(P):
+    """psa_ksim_perm: the cap of k[..., perm, :] read in place equals the cap of the reordered copy (thresholds at 0, where
+    the mean cosines of these keys fall on both sides)."""
+    S, H, D = 1000, 3, 64
+    k = C.randn(17, (1, H, S, D), torch.bfloat16, smooth=4).to(DEV)
+    perm = _perm(9, S).to(DEV)
+    for bn in (128, 64, 32):
+        a = P.ops.k_similarity(k, bn, 0.0, 0.0, 0.0, perm=perm)
+        b = P.ops.k_similarity(k[:, :, perm.long()].contiguous(), bn, 0.0, 0.0, 0.0)
+        assert torch.equal(a, b)
+        assert len(torch.unique(b)) > 1
+
+
+@pytest.mark.parametrize("text,sim", [(0, True), (37, True), (226, False)])
+def test_module_reorders_in_place_old_format(P, text, sim):
+    """The presets with the old mask format (block 128, thresholdbound, similarity cap - the default preset of the Wan
+    2.1 1.3B pipeline) also skip the four reordering copies: the similarity cap, the scores and the tile images read k
+    through the row table, only q is gathered, the legacy forward stores its rows back through the table.  Bit-identical
+    to the copy route; and the oracle's legacy forward on the reordered inputs agrees."""
+    from psa_b200.attention import compute_block_mask
+    from psa_b200.pyramid_sparse_attention import AttentionConfig, PyramidSparseAttention
+    W, Hh, T, H, D = 12, 8, 9, 2, 128
+    cfg = AttentionConfig(width=W, height=Hh, depth=T, text_length=text, use_rearrange=True, rearrange_method="Gilbert",
+                          block_m=128, block_n=128, tile_n=32, use_sim_mask=sim, mask_ratios=C.RATIOS_THR, mask_mode="thresholdbound",
+                          warmup_steps=0, attn_impl="old_mask_type", sim_2x_threshold=0.7, sim_4x_threshold=0.65,
+                          sim_8x_threshold=0.6)
+    mod = PyramidSparseAttention(cfg, inference_num=10, layer_num=1, model_type="wan")
+    S = W * Hh * T + text
+    q, k, v = C.qkv(993, 1, H, S, D, torch.bfloat16, smooth=16)
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    assert mod._rows_in_place_old_format(qd, kd)
+    torch.manual_seed(77)
+    fused = mod(qd, kd, vd, 0)
+    assert int(fused._psa_status.item()) == 0
+    # the same layer with explicit copies
+    torch.manual_seed(77)
+    qr, kr, vr = mod.gilbert_rearranger.rearrange(qd, kd, vd)
+    mask, _, simm = compute_block_mask(qr.contiguous(), kr.contiguous(), cfg, text_length=text)
+    o, _, _ = P.ops.legacy_forward(qr.contiguous(), kr.contiguous(), vr.contiguous(), mask, False)
+    copied = mod.gilbert_rearranger.reversed_rearrange(o)
+    assert torch.equal(fused, copied)
+    assert (simm is not None) == sim
+    qc, kc, vc = mod.gilbert_rearranger.rearrange(q, k, v)
+    oo, _ = O.legacy_forward(qc, kc, vc, mask.cpu(), False)
+    ref = mod.gilbert_rearranger.reversed_rearrange(oo.float())
+    assert float((fused.float().cpu() - ref).abs().max()) <= 2e-2
+    a, b = fused.float().cpu().double().flatten(), ref.double().flatten()
+    assert float((a @ b) / (a.norm() * b.norm())) >= 0.999
+
+
 # ------------------------------------------------------------------ token-major tensors ----------------
 @pytest.mark.parametrize("with_perm", [False, True])
 def test_gather_heads(P, with_perm):
