@@ -633,6 +633,25 @@ def main():
 
     pull_buf = None
     step_no = 0
+    draw_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+    pending_draw = None
+
+    def launch_draw():
+        with torch.cuda.stream(draw_stream):
+            idx = draw_indices_all()
+            e = ev(); e.record(draw_stream)
+        return idx, e
+
+    def prefetched_draw(cur):
+        nonlocal pending_draw
+        if pending_draw is None:
+            pending_draw = launch_draw()
+        idx, e = pending_draw
+        cur.wait_event(e)
+        for t_ in idx:
+            t_.record_stream(cur)
+        pending_draw = launch_draw()
+        return idx
 
     def layer_step_p2p(rec, cur, v_ready=None):
         """N > 1 without a collective: q/k/v rows travel by our own copy kernel over peer memory (pushed by the token owners,
@@ -646,7 +665,9 @@ def main():
             # block scores and the level assignment run from them while, on a second stream, every rank stores its full
             # rows into the owners' receive buffers (alternating between steps) and a second barrier follows; (4) images
             # and forward wait for that.
-            iq_all, ik_all = timed("sample", draw_indices_all, rec)
+            # the sample offsets do not depend on the data: the draw of the NEXT step runs on a side stream under this step
+            # (same generator consumption, one draw per step), this step waits only for the one made during the previous step
+            iq_all, ik_all = timed("sample", lambda: prefetched_draw(cur), rec)
             timed("a2a_in", lambda: peer.push_samples(par, iq_all, ik_all), rec)
             fence()
             comm_stream.wait_stream(cur)

@@ -121,7 +121,13 @@ int psa_ksim(const void* k, int32_t* out, int64_t bh, int64_t seq, int head_dim,
  * level-4, -1, level-8, -1, rest ignored.  compat_quirk != 0 reproduces the reference's handling of levels
  * whose pooled block is narrower than half a tile (:261-278): each merged pair also attends pooled tokens
  * [2P, tile_n) of that level.  impl: 0 = pick, 1 = scalar kernel, 2 = tcgen05 kernel (f16/bf16, block_m 128).
- * status: device int32 word, written non-zero if a bounded wait inside the kernel expired (may be NULL). */
+ * status: device int32 word, written non-zero if a bounded wait inside the kernel expired (may be NULL).
+ * The tcgen05 kernel is persistent: its CTAs claim query blocks from a counter.  The counters are a ring of 256 device
+ * words inside the library (one per launch, zeroed on the launching stream right before the kernel); the first
+ * tcgen05 launch on a device resolves the ring's address (cudaGetSymbolAddress) - make it outside any stream capture -
+ * and more than 256 launches of this family in flight at once on one device would share counters (a captured graph pins
+ * its slot for every replay: do not replay such graphs while more than 255 other launches overlap them).  This holds
+ * for every psa_fwd* / psa_legacy_fwd_images* entry point. */
 int psa_fwd(const void* q, const void* k, const void* v, const void* k2, const void* k4, const void* k8,
             const void* v2, const void* v4, const void* v8, const int32_t* mask, void* out, int64_t bh,
             int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width,
