@@ -198,6 +198,25 @@ int psa_fwd_images_tm(const void* q, const void* kimg, const void* vimg, const i
                       int heads, int64_t seq, int head_dim, int block_m, int block_n, int tile_n, int mask_width, float sm_scale,
                       int compat_quirk, int dtype, int32_t* status, void* stream);
 
+/* The same three loads with the rotary embedding of the diffusion transformers applied on the way, so that the
+ * processors (modify_diffusers.py:260-281 Wan, :363-369 CogVideoX) need not write rotated copies of q and k: every
+ * kernel that touches a q or k row rotates it as it reads it.  rope_a, rope_b: fp32 device tables [seq - rope_first]
+ * [head_dim], 16-byte aligned; stored token s >= rope_first uses table row s - rope_first (CogVideoX leaves its leading
+ * text tokens alone), tokens before it pass unchanged.  Channel pair (x0, x1) becomes
+ *     (x0*a[even] - x1*b[even],  x1*a[odd] + x0*b[odd]),
+ * each product and sum rounded to fp32 separately and the result rounded once to the element type: bit for bit the
+ * element-wise formulation of both processors (Wan: a = cos at the even entries, b = sin at the odd entries, both
+ * repeated over the pair; CogVideoX: a = cos, b = sin).  Values are never rotated. */
+int psa_gather_heads_rope(const void* src, const int32_t* perm, const float* rope_a, const float* rope_b, int64_t rope_first,
+                          void* dst, int heads, int64_t seq, int head_dim, int dtype, void* stream);
+int psa_pyramid_kv_images_tm_rope(const void* k, const void* v, const int32_t* perm, const float* rope_a, const float* rope_b,
+                                  int64_t rope_first, void* kimg, void* vimg, int heads, int64_t seq, int head_dim, int block_n,
+                                  int dtype, void* stream);
+int psa_block_scores_tm_rope(const void* q, const void* k, const int32_t* perm, const float* rope_a, const float* rope_b,
+                             int64_t rope_first, const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch,
+                             size_t scratch_bytes, int heads, int64_t seq, int head_dim, int block_m, int block_n, int dtype,
+                             void* stream);
+
 /* Antidiagonal block-importance estimate of the causal (vision-language) call site.  Replaces estimate_block_importance
  * with select_mode "inverse", softmax, kdb 1 - and its Triton kernels flat_group_gemm_fuse_reshape /
  * softmax_fuse_block_sum - qwen2.5-vl-example/src/attention/PSA_casual/utils/block_importance.py:282-562,

@@ -1,5 +1,7 @@
 // Argument bundle and dispatch hooks of the attention forward kernels.
 #pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -42,6 +44,11 @@ struct OutScatter {
 // batch): token t of local head h is row (t % tokens_per_rank) of peer t / tokens_per_rank, whose buffer is laid out
 // [tokens_per_rank][heads_total][D]; kernels read it with plain loads.  perm != null: the operand is read in a reordered
 // token sequence, token t of the sequence being row perm[t] of the stored tensor (int32 [seq]).
+// rope_a != null (16-bit operands only): rows are rotated while they are read, as the attention processors of the
+// diffusion transformers do before the attention call (modify_diffusers.py:260-281 for Wan, :363-369 for CogVideoX).
+// Stored token s >= rope_first uses row s - rope_first of the two fp32 tables [.., D]; channel pair (x0, x1) becomes
+// (x0*a[even] - x1*b[even], x1*a[odd] + x0*b[odd]), every product and sum rounded to fp32 on its own (no fused
+// multiply-add) and the result rounded once to the element type - bit for bit what the framework's element-wise ops give.
 struct RowSource {
   const void* base;
   const void* peer[kMaxPeers];
@@ -49,6 +56,10 @@ struct RowSource {
   int heads_total, head0;
   int64_t tokens_per_rank;
   const int32_t* perm;
+  const float* rope_a;
+  const float* rope_b;
+  int64_t rope_first;
+  int rope_bf16;   // element type of the rows when rope_a is set: 1 bf16, 0 f16
 };
 
 inline RowSource local_rows(const void* base) {
@@ -64,6 +75,54 @@ __device__ __forceinline__ const uint4* row_word(const RowSource& s, int64_t bh,
   if (s.n_peers == 0) return reinterpret_cast<const uint4*>(s.base) + (bh * seq + tok) * row16 + c;
   const int64_t owner = tok / s.tokens_per_rank, local = tok - owner * s.tokens_per_rank;
   return reinterpret_cast<const uint4*>(s.peer[owner]) + (local * s.heads_total + s.head0 + bh) * row16 + c;
+}
+
+// Eight 16-bit channels (four pairs) turned by the table entries a[0..7], b[0..7].
+__device__ __forceinline__ uint4 rotate_word(uint4 w, const float* __restrict__ a, const float* __restrict__ b, bool bf16) {
+  const float4 a0 = *reinterpret_cast<const float4*>(a), a1 = *reinterpret_cast<const float4*>(a + 4);
+  const float4 b0 = *reinterpret_cast<const float4*>(b), b1 = *reinterpret_cast<const float4*>(b + 4);
+  const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+  const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+  uint32_t in[4] = {w.x, w.y, w.z, w.w}, out[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float x0, x1;
+    if (bf16) {
+      x0 = __uint_as_float(in[i] << 16);
+      x1 = __uint_as_float(in[i] & 0xffff0000u);
+    } else {
+      const __half2 h = *reinterpret_cast<const __half2*>(&in[i]);
+      x0 = __low2float(h);
+      x1 = __high2float(h);
+    }
+    const float y0 = __fsub_rn(__fmul_rn(x0, av[2 * i]), __fmul_rn(x1, bv[2 * i]));
+    const float y1 = __fadd_rn(__fmul_rn(x1, av[2 * i + 1]), __fmul_rn(x0, bv[2 * i + 1]));
+    if (bf16) {
+      const __nv_bfloat162 o = __floats2bfloat162_rn(y0, y1);
+      out[i] = *reinterpret_cast<const uint32_t*>(&o);
+    } else {
+      const __half2 o = __floats2half2_rn(y0, y1);
+      out[i] = *reinterpret_cast<const uint32_t*>(&o);
+    }
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// 16-byte word `c` of the row of token `tok` of local head `bh`, rotated if the source says so.
+__device__ __forceinline__ uint4 load_row_word(const RowSource& s, int64_t bh, int64_t seq, int64_t tok, int row16, int c) {
+  if (s.perm) tok = s.perm[tok];
+  uint4 w;
+  if (s.n_peers == 0) {
+    w = *(reinterpret_cast<const uint4*>(s.base) + (bh * seq + tok) * row16 + c);
+  } else {
+    const int64_t owner = tok / s.tokens_per_rank, local = tok - owner * s.tokens_per_rank;
+    w = *(reinterpret_cast<const uint4*>(s.peer[owner]) + (local * s.heads_total + s.head0 + bh) * row16 + c);
+  }
+  if (s.rope_a && tok >= s.rope_first) {
+    const int64_t off = ((tok - s.rope_first) * row16 + c) * 8;    // row16 * 8 channels per table row
+    w = rotate_word(w, s.rope_a + off, s.rope_b + off, s.rope_bf16 != 0);
+  }
+  return w;
 }
 #endif
 

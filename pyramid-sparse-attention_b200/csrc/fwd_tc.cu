@@ -654,16 +654,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           const uchar4* minrow4 = reinterpret_cast<const uchar4*>(sMinRow + slot * 128);
           // Fast path: the bias is uniform inside every aligned group of 4 columns (blocks are at least 4 wide), so the
           // maximum is taken on raw scores per group and the bias enters once per group.  A tile with a block that ends
-          // inside a group takes the per-column path.  The unwritten columns of a ragged last tile (a multiple of 16, bias
-          // -inf) are cleared in registers, so that stale bits can never read as NaN.
-          const bool slow = (flagw[0] | flagw[1] | flagw[2]) != 0;
-#define PSA_CLEAR_STALE(v, c)                                                                                                \
-  do {                                                                                                                       \
-    if (ragged) {                                                                                                            \
-      _Pragma("unroll") for (int i = 0; i < 32; ++i)                                                                         \
-        if (32 * (c) + i >= last_cols) v[i] = 0u;                                                                            \
-    }                                                                                                                        \
-  } while (0)
+          // inside a group, or with unwritten columns, takes the per-column path.
+          const bool slow = ragged || (flagw[0] | flagw[1] | flagw[2]) != 0;
           uint32_t va[32], vb[32];      // two chunks of 32 score columns in flight
           float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
           if (!slow) {
@@ -682,7 +674,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     mx3 = fmaxf(mx3, fmaf(fmaxf(fmaxf(f[28], f[29]), fmaxf(f[30], f[31])), p.scale_log2, gb.w));                             \
   } while (0)
             tc::tmem_ld32(tS, va);
-            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 32, vb); PSA_MAX_CHUNK(va, 0);   // NaN-safe: fmaxf drops a NaN operand
+            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 32, vb); PSA_MAX_CHUNK(va, 0);
             tc::tmem_wait_ld(); tc::tmem_ld32(tS + 64, va); PSA_MAX_CHUNK(vb, 1);
             tc::tmem_wait_ld(); tc::tmem_ld32(tS + 96, vb); PSA_MAX_CHUNK(va, 2);
             tc::tmem_wait_ld(); tc::tmem_ld32(tS, va);      PSA_MAX_CHUNK(vb, 3);   // chunk 0 again, for pass 2
@@ -762,12 +754,11 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     PSA_EXP_GROUP(f, gb.z - m_use, 6, ls_a); PSA_EXP_GROUP(f, gb.w - m_use, 7, ls_b);                                        \
     tc::tmem_st16(tS + 16 * (c), pk);                                                                                        \
   } while (0)
-            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 32, vb); PSA_CLEAR_STALE(va, 0); PSA_EXP_CHUNK(va, 0);
-            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 64, va); PSA_CLEAR_STALE(vb, 1); PSA_EXP_CHUNK(vb, 1);
-            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 96, vb); PSA_CLEAR_STALE(va, 2); PSA_EXP_CHUNK(va, 2);
-            tc::tmem_wait_ld();                             PSA_CLEAR_STALE(vb, 3); PSA_EXP_CHUNK(vb, 3);
+            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 32, vb); PSA_EXP_CHUNK(va, 0);
+            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 64, va); PSA_EXP_CHUNK(vb, 1);
+            tc::tmem_wait_ld(); tc::tmem_ld32(tS + 96, vb); PSA_EXP_CHUNK(va, 2);
+            tc::tmem_wait_ld();                             PSA_EXP_CHUNK(vb, 3);
 #undef PSA_EXP_CHUNK
-#undef PSA_CLEAR_STALE
 #undef PSA_EXP_GROUP
           } else {
 #pragma unroll 1

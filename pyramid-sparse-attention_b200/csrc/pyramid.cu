@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(256) pyramid_img_kernel(const RowSource k, con
     for (int t = 0; t < 8; ++t) {
       int64_t tok = j * 8 + t;
       tok = tok < S ? tok : S - 1;
-      r[t] = *row_word(x, head, S, tok, cpr, c);
+      r[t] = load_row_word(x, head, S, tok, cpr, c);
     }
     uint4 a[4], b[2], d;
 #pragma unroll
@@ -216,8 +216,9 @@ extern "C" int psa_pyramid_kv_images_perm(const void* k, const void* v, const in
   return launch_pyramid_images(ks, vs, kimg, vimg, bh, seq, head_dim, block_n, dtype, 0, (cudaStream_t)stream);
 }
 
-extern "C" int psa_pyramid_kv_images_tm(const void* k, const void* v, const int32_t* perm, void* kimg, void* vimg, int heads,
-                                        int64_t seq, int head_dim, int block_n, int dtype, void* stream) {
+static int pyramid_kv_images_tm(const void* k, const void* v, const int32_t* perm, const float* rope_a, const float* rope_b,
+                                int64_t rope_first, void* kimg, void* vimg, int heads, int64_t seq, int head_dim, int block_n,
+                                int dtype, void* stream) {
   using namespace psa;
   PSA_REQUIRE(k && v && kimg && vimg, PSA_ERR_ARG, "psa_pyramid_kv_images_tm: null pointer");
   PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "psa_pyramid_kv_images_tm: 16-bit element types only");
@@ -232,7 +233,26 @@ extern "C" int psa_pyramid_kv_images_tm(const void* k, const void* v, const int3
   ks.heads_total = vs.heads_total = heads;
   ks.tokens_per_rank = vs.tokens_per_rank = seq;
   ks.perm = vs.perm = perm;
+  ks.rope_a = rope_a;      // keys are rotated while they are read; values never are
+  ks.rope_b = rope_b;
+  ks.rope_first = rope_first;
+  ks.rope_bf16 = dtype == PSA_BF16;
   return launch_pyramid_images(ks, vs, kimg, vimg, heads, seq, head_dim, block_n, dtype, 0, (cudaStream_t)stream);
+}
+
+extern "C" int psa_pyramid_kv_images_tm(const void* k, const void* v, const int32_t* perm, void* kimg, void* vimg, int heads,
+                                        int64_t seq, int head_dim, int block_n, int dtype, void* stream) {
+  return pyramid_kv_images_tm(k, v, perm, nullptr, nullptr, 0, kimg, vimg, heads, seq, head_dim, block_n, dtype, stream);
+}
+
+extern "C" int psa_pyramid_kv_images_tm_rope(const void* k, const void* v, const int32_t* perm, const float* rope_a,
+                                             const float* rope_b, int64_t rope_first, void* kimg, void* vimg, int heads, int64_t seq,
+                                             int head_dim, int block_n, int dtype, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(rope_a && rope_b && rope_first >= 0 && rope_first <= seq, PSA_ERR_ARG, "psa_pyramid_kv_images_tm_rope: bad rotary tables");
+  PSA_REQUIRE((((uintptr_t)rope_a | (uintptr_t)rope_b) & 15) == 0, PSA_ERR_ARG,
+              "psa_pyramid_kv_images_tm_rope: tables must be 16-byte aligned");
+  return pyramid_kv_images_tm(k, v, perm, rope_a, rope_b, rope_first, kimg, vimg, heads, seq, head_dim, block_n, dtype, stream);
 }
 
 extern "C" int psa_pyramid_kv_images_peers(const void* const* peer_k, const void* const* peer_v, int n_peers, int64_t tokens_per_rank,

@@ -329,9 +329,10 @@ extern "C" int psa_block_scores_perm(const void* q, const void* k, const int32_t
   return launch_scores<__nv_bfloat16>(qs, ks, idx_q, idx_k, po, scratch, d, bh, 2, st);
 }
 
-extern "C" int psa_block_scores_tm(const void* q, const void* k, const int32_t* perm, const int32_t* idx_q, const int32_t* idx_k,
-                                   void* po, void* scratch, size_t scratch_bytes, int heads, int64_t seq, int head_dim, int block_m,
-                                   int block_n, int dtype, void* stream) {
+static int block_scores_tm(const void* q, const void* k, const int32_t* perm, const float* rope_a, const float* rope_b,
+                           int64_t rope_first, const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch,
+                           size_t scratch_bytes, int heads, int64_t seq, int head_dim, int block_m, int block_n, int dtype,
+                           void* stream) {
   using namespace psa;
   PSA_REQUIRE(q && k && idx_q && idx_k && po && scratch, PSA_ERR_ARG, "psa_block_scores_tm: null pointer");
   PSA_REQUIRE(heads > 0 && heads < 65536 && seq > 0 && seq < ((int64_t)1 << 31), PSA_ERR_ARG, "psa_block_scores_tm: bad shape");
@@ -350,9 +351,31 @@ extern "C" int psa_block_scores_tm(const void* q, const void* k, const int32_t* 
   qs.heads_total = ks.heads_total = heads;
   qs.tokens_per_rank = ks.tokens_per_rank = seq;
   qs.perm = ks.perm = perm;
+  qs.rope_a = ks.rope_a = rope_a;
+  qs.rope_b = ks.rope_b = rope_b;
+  qs.rope_first = ks.rope_first = rope_first;
+  qs.rope_bf16 = ks.rope_bf16 = dtype == PSA_BF16;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == PSA_F16) return launch_scores<__half>(qs, ks, idx_q, idx_k, po, scratch, d, heads, 2, st);
   return launch_scores<__nv_bfloat16>(qs, ks, idx_q, idx_k, po, scratch, d, heads, 2, st);
+}
+
+extern "C" int psa_block_scores_tm(const void* q, const void* k, const int32_t* perm, const int32_t* idx_q, const int32_t* idx_k,
+                                   void* po, void* scratch, size_t scratch_bytes, int heads, int64_t seq, int head_dim, int block_m,
+                                   int block_n, int dtype, void* stream) {
+  return block_scores_tm(q, k, perm, nullptr, nullptr, 0, idx_q, idx_k, po, scratch, scratch_bytes, heads, seq, head_dim, block_m,
+                         block_n, dtype, stream);
+}
+
+extern "C" int psa_block_scores_tm_rope(const void* q, const void* k, const int32_t* perm, const float* rope_a, const float* rope_b,
+                                        int64_t rope_first, const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch,
+                                        size_t scratch_bytes, int heads, int64_t seq, int head_dim, int block_m, int block_n,
+                                        int dtype, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(rope_a && rope_b && rope_first >= 0 && rope_first <= seq, PSA_ERR_ARG, "psa_block_scores_tm_rope: bad rotary tables");
+  PSA_REQUIRE((((uintptr_t)rope_a | (uintptr_t)rope_b) & 15) == 0, PSA_ERR_ARG, "psa_block_scores_tm_rope: tables must be 16-byte aligned");
+  return block_scores_tm(q, k, perm, rope_a, rope_b, rope_first, idx_q, idx_k, po, scratch, scratch_bytes, heads, seq, head_dim,
+                         block_m, block_n, dtype, stream);
 }
 
 extern "C" int psa_block_scores_peers(const void* const* peer_q, const void* const* peer_k, int n_peers, int64_t tokens_per_rank,

@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(256) gather_samples_kernel(const RowSource x, 
     const int ic = i < n_valid ? i : n_valid - 1;
     int64_t tok = (int64_t)(ic / keep) * block + idx[bh * keep + (ic % keep)];
     tok = tok < seq ? tok : seq - 1;
-    dst[(int64_t)i * cpr + c] = *row_word(x, bh, seq, tok, cpr, c);
+    dst[(int64_t)i * cpr + c] = load_row_word(x, bh, seq, tok, cpr, c);
   }
 }
 

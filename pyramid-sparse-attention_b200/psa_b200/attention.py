@@ -84,11 +84,14 @@ def token_major_view(x: torch.Tensor):
     return t if t.is_contiguous() else None
 
 
-def psa_attention_token_major(q, k, v, config, perm=None, text_length: int = 0, idx_q=None, idx_k=None):
+def psa_attention_token_major(q, k, v, config, perm=None, text_length: int = 0, idx_q=None, idx_k=None, rope=None):
     """The PSA layer on token-major tensors: q, k, v [B, S, H, D] contiguous (16-bit, separator-format mask, no
     similarity cap), perm an optional int32 [S] row table (attention token t = stored token perm[t]).  Returns
     (out [B, S, H, D], mask).  No transposed or reordered copy of k, v or the output is made; the result equals
-    PSAAttention on q.transpose(1, 2)[:, :, perm] ... put back, bit for bit (same sample offsets)."""
+    PSAAttention on q.transpose(1, 2)[:, :, perm] ... put back, bit for bit (same sample offsets).
+    rope (ops.RotaryTables): q and k are given UNROTATED and every kernel that reads one of their rows rotates it on
+    the way - the result equals rotating q and k first (as the processors of modify_diffusers.py do) bit for bit,
+    without the two rotated copies."""
     B, S, H, D = q.shape
     if config.use_sim_mask or config.attn_impl != "new_mask_type":
         raise ValueError("the token-major route covers new_mask_type without the similarity cap")
@@ -99,14 +102,14 @@ def psa_attention_token_major(q, k, v, config, perm=None, text_length: int = 0, 
     if idx_k is None:
         idx_k = ops.draw_sample_indices(B, H, config.block_n, config.block_n // 4, q.device)
     with torch.no_grad():
-        po = torch.cat([ops.block_scores_tm(q[b], k[b], idx_q[b], idx_k[b], config.block_m, config.block_n, perm=perm)
-                        for b in range(B)], dim=0)
+        po = torch.cat([ops.block_scores_tm(q[b], k[b], idx_q[b], idx_k[b], config.block_m, config.block_n, perm=perm,
+                                            rope=rope) for b in range(B)], dim=0)
         mask = ops.assign_levels(po, config.mask_ratios, f"{config.mask_mode}_newtype", config.block_n, config.tile_n,
                                  text_length=text_length)
     out = torch.empty_like(q)
     for b in range(B):
-        images = ops.pyramid_kv_images_tm(k[b], v[b], config.block_n, perm=perm)
-        q_heads = ops.gather_heads(q[b], perm)
+        images = ops.pyramid_kv_images_tm(k[b], v[b], config.block_n, perm=perm, rope=rope)
+        q_heads = ops.gather_heads(q[b], perm, rope=rope)
         ops.psa_forward_tm(q_heads, images, mask[b], out[b], config.block_m, config.block_n, config.tile_n, out_perm=perm)
     return out, mask
 

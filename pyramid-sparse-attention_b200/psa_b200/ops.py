@@ -156,19 +156,59 @@ def _tm_check(*ts):
     return x.shape
 
 
-def gather_heads(x: torch.Tensor, perm: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """[S, H, D] -> [1, H, S, D] with out[0, h, t] = x[perm[t], h] (perm None: a plain transpose copy)."""
+class RotaryTables:
+    """Rotary embedding applied by the kernels while they read q and k rows (token-major route).  a, b: fp32 [S - first,
+    D] on the device; stored token s >= first uses row s - first, channel pair (x0, x1) becomes
+    (x0*a[even] - x1*b[even], x1*a[odd] + x0*b[odd]) with every product and sum rounded separately."""
+
+    def __init__(self, a: torch.Tensor, b: torch.Tensor, first: int = 0):
+        assert a.shape == b.shape and a.dim() == 2, "rotary tables are [tokens, head_dim]"
+        self.a = a.to(torch.float32).contiguous()
+        self.b = b.to(torch.float32).contiguous()
+        self.first = int(first)
+
+    def check(self, S: int, D: int, device) -> None:
+        _need_cuda(self.a, self.b)
+        if self.a.device != device or tuple(self.a.shape) != (S - self.first, D) or not 0 <= self.first <= S:
+            raise ValueError(f"rotary tables of shape {tuple(self.a.shape)} on {self.a.device} do not fit {S} tokens "
+                             f"(first rotated token {self.first}), head_dim {D} on {device}")
+
+
+def rotate_rows(x: torch.Tensor, rope: RotaryTables) -> torch.Tensor:
+    """What the fused loads compute, with the framework's element-wise operations: x [B, H, S, D] -> rotated copy.
+    (The route for tensors the token-major kernels do not take, and the yardstick of their tests.)"""
+    S, D = x.shape[2], x.shape[3]
+    a, b = rope.a.to(x.device), rope.b.to(x.device)
+    assert tuple(a.shape) == (S - rope.first, D)
+    head, tail = x[:, :, :rope.first], x[:, :, rope.first:].float()
+    x0, x1 = tail[..., 0::2], tail[..., 1::2]
+    out = torch.empty_like(tail)
+    out[..., 0::2] = x0 * a[:, 0::2] - x1 * b[:, 0::2]
+    out[..., 1::2] = x1 * a[:, 1::2] + x0 * b[:, 1::2]
+    return torch.cat([head, out.to(x.dtype)], dim=2)
+
+
+def gather_heads(x: torch.Tensor, perm: Optional[torch.Tensor] = None, rope: Optional[RotaryTables] = None) -> torch.Tensor:
+    """[S, H, D] -> [1, H, S, D] with out[0, h, t] = x[perm[t], h] (perm None: a plain transpose copy), rotated on the
+    way if rope is given."""
     S, H, D = _tm_check(x)
     perm = None if perm is None else _perm32(perm, S)
     with torch.cuda.device(x.device):
         out = torch.empty((1, H, S, D), dtype=x.dtype, device=x.device)
-        rc = lib.psa_gather_heads(_ptr(x), _ptr(perm), _ptr(out), H, S, D, x.element_size(), _stream(x))
+        if rope is None:
+            rc = lib.psa_gather_heads(_ptr(x), _ptr(perm), _ptr(out), H, S, D, x.element_size(), _stream(x))
+        else:
+            rope.check(S, D, x.device)
+            rc = lib.psa_gather_heads_rope(_ptr(x), _ptr(perm), _ptr(rope.a), _ptr(rope.b), rope.first, _ptr(out), H, S, D,
+                                           _dt(x), _stream(x))
     check(rc, "psa_gather_heads")
     return out
 
 
-def pyramid_kv_images_tm(k: torch.Tensor, v: torch.Tensor, block_n: int, perm: Optional[torch.Tensor] = None) -> KVImages:
-    """pyramid_kv_images of k, v given token-major ([S, H, D]), optionally read through a row table."""
+def pyramid_kv_images_tm(k: torch.Tensor, v: torch.Tensor, block_n: int, perm: Optional[torch.Tensor] = None,
+                         rope: Optional[RotaryTables] = None) -> KVImages:
+    """pyramid_kv_images of k, v given token-major ([S, H, D]), optionally read through a row table, the keys
+    optionally rotated as they are read."""
     S, H, D = _tm_check(k, v)
     perm = None if perm is None else _perm32(perm, S)
     nbytes = lib.psa_kv_image_bytes(H, S, D, block_n)
@@ -177,14 +217,21 @@ def pyramid_kv_images_tm(k: torch.Tensor, v: torch.Tensor, block_n: int, perm: O
     with torch.cuda.device(k.device):
         kimg = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
         vimg = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
-        rc = lib.psa_pyramid_kv_images_tm(_ptr(k), _ptr(v), _ptr(perm), _ptr(kimg), _ptr(vimg), H, S, D, block_n, _dt(k),
-                                          _stream(k))
+        if rope is None:
+            rc = lib.psa_pyramid_kv_images_tm(_ptr(k), _ptr(v), _ptr(perm), _ptr(kimg), _ptr(vimg), H, S, D, block_n, _dt(k),
+                                              _stream(k))
+        else:
+            rope.check(S, D, k.device)
+            rc = lib.psa_pyramid_kv_images_tm_rope(_ptr(k), _ptr(v), _ptr(perm), _ptr(rope.a), _ptr(rope.b), rope.first,
+                                                   _ptr(kimg), _ptr(vimg), H, S, D, block_n, _dt(k), _stream(k))
     check(rc, "psa_pyramid_kv_images_tm")
     return KVImages(kimg, vimg, block_n)
 
 
-def block_scores_tm(q, k, idx_q, idx_k, block_m: int, block_n: int, perm: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """block_scores of q, k given token-major ([S, H, D]); idx_q [H, block_m/4], idx_k [H, block_n/4].  -> [1, H, Mq, Nk]."""
+def block_scores_tm(q, k, idx_q, idx_k, block_m: int, block_n: int, perm: Optional[torch.Tensor] = None,
+                    rope: Optional[RotaryTables] = None) -> torch.Tensor:
+    """block_scores of q, k given token-major ([S, H, D]); idx_q [H, block_m/4], idx_k [H, block_n/4].  -> [1, H, Mq, Nk].
+    With rope the sampled rows of q and k are rotated as they are gathered."""
     S, H, D = _tm_check(q, k)
     _need_cuda(idx_q, idx_k)
     assert idx_q.shape == (H, block_m // 4) and idx_k.shape == (H, block_n // 4)
@@ -198,8 +245,14 @@ def block_scores_tm(q, k, idx_q, idx_k, block_m: int, block_n: int, perm: Option
         if nbytes == 0:
             raise ValueError(f"psa_block_scores_tm: unsupported block sizes m={block_m} n={block_n}")
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
-        rc = lib.psa_block_scores_tm(_ptr(q), _ptr(k), _ptr(perm), _ptr(iq), _ptr(ik), _ptr(po), _ptr(scratch), nbytes, H, S, D,
-                                     block_m, block_n, _dt(q), _stream(q))
+        if rope is None:
+            rc = lib.psa_block_scores_tm(_ptr(q), _ptr(k), _ptr(perm), _ptr(iq), _ptr(ik), _ptr(po), _ptr(scratch), nbytes, H,
+                                         S, D, block_m, block_n, _dt(q), _stream(q))
+        else:
+            rope.check(S, D, q.device)
+            rc = lib.psa_block_scores_tm_rope(_ptr(q), _ptr(k), _ptr(perm), _ptr(rope.a), _ptr(rope.b), rope.first, _ptr(iq),
+                                              _ptr(ik), _ptr(po), _ptr(scratch), nbytes, H, S, D, block_m, block_n, _dt(q),
+                                              _stream(q))
     check(rc, "psa_block_scores_tm")
     return po
 

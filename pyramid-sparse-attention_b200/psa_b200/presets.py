@@ -122,6 +122,37 @@ def rope_real_pairs(x: torch.Tensor, image_rotary_emb) -> torch.Tensor:
     return (x.float() * cos + turned.float() * sin).to(x.dtype)
 
 
+_rotary_cache = {}
+
+
+def _rotary_tables(kind: str, cos: torch.Tensor, sin: torch.Tensor, first: int):
+    """ops.RotaryTables for the fused loads, built once per (cos, sin) pair - every layer of a step passes the same
+    tables.  kind "wan": cos/sin broadcastable to [1, S, 1, D], cosine read at the even entries and sine at the odd
+    ones (rope_interleaved_pairs); kind "real": cos/sin [S, D] (rope_real_pairs).  None if the tables carry a batch."""
+    from . import ops
+    key = (kind, cos.data_ptr(), sin.data_ptr(), tuple(cos.shape), cos.device, first, cos._version, sin._version)
+    hit = _rotary_cache.get(key)
+    if hit is not None:
+        return hit
+    if kind == "wan":
+        D = cos.shape[-1]
+        plain = cos.dim() == 2 or (cos.dim() == 4 and cos.shape[0] == 1 and cos.shape[2] == 1)
+        if not plain or cos.shape != sin.shape:
+            return None
+        c2, s2 = cos.reshape(-1, D).float(), sin.reshape(-1, D).float()
+        a = c2[:, 0::2].repeat_interleave(2, dim=1)
+        b = s2[:, 1::2].repeat_interleave(2, dim=1)
+    else:
+        if cos.dim() != 2:
+            return None
+        a, b = cos.float(), sin.float()
+    tables = ops.RotaryTables(a, b, first)
+    if len(_rotary_cache) > 8:
+        _rotary_cache.clear()
+    _rotary_cache[key] = tables
+    return tables
+
+
 class SparseWanAttnProcessor:
     """Attention processor of the Wan 2.1 / 2.2 transformer blocks with the sparse module in place of the dense
     attention (modify_diffusers.py:192-315): separate or fused projections, q/k norms on the full hidden width,
@@ -165,9 +196,14 @@ class SparseWanAttnProcessor:
             k = attn.norm_k(k)
         H = attn.heads
         q, k, v = (x.unflatten(2, (H, -1)) for x in (q, k, v))                  # [B, S, H, D]
+        fused = None
         if rotary_emb is not None:
-            q = rope_interleaved_pairs(q, *rotary_emb)
-            k = rope_interleaved_pairs(k, *rotary_emb)
+            # a module that rotates inside its kernels gets q and k as they are (self-attention: same length, same tables)
+            if getattr(attn.inner_attention, "fuses_rotary", False) and q.is_cuda and q.shape[1] == k.shape[1]:
+                fused = _rotary_tables("wan", rotary_emb[0], rotary_emb[1], 0)
+            if fused is None:
+                q = rope_interleaved_pairs(q, *rotary_emb)
+                k = rope_interleaved_pairs(k, *rotary_emb)
         from_image = None
         if image_context is not None:
             k_img, v_img = self._project_image(attn, image_context)
@@ -175,7 +211,10 @@ class SparseWanAttnProcessor:
             k_img, v_img = k_img.unflatten(2, (H, -1)), v_img.unflatten(2, (H, -1))
             from_image = torch.nn.functional.scaled_dot_product_attention(
                 q.transpose(1, 2), k_img.transpose(1, 2), v_img.transpose(1, 2)).transpose(1, 2).flatten(2, 3).type_as(q)
-        out = attn.inner_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), self.layer_idx)
+        if fused is not None:
+            out = attn.inner_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), self.layer_idx, rotary=fused)
+        else:
+            out = attn.inner_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), self.layer_idx)
         out = out.transpose(1, 2).flatten(2, 3).type_as(q)
         if from_image is not None:
             out = out + from_image
@@ -203,11 +242,19 @@ class SparseCogVideoXAttnProcessor:
             q = attn.norm_q(q).to(dtype=v.dtype)
         if getattr(attn, "norm_k", None) is not None:
             k = attn.norm_k(k).to(dtype=v.dtype)
+        fused = None
         if image_rotary_emb is not None:
-            q = torch.cat([q[:, :, :n_text], rope_real_pairs(q[:, :, n_text:], image_rotary_emb)], dim=2)
-            if not getattr(attn, "is_cross_attention", False):
-                k = torch.cat([k[:, :, :n_text], rope_real_pairs(k[:, :, n_text:], image_rotary_emb)], dim=2)
-        out = attn.inner_attention(q, k, v, self.layer_idx)
+            if (getattr(attn.inner_attention, "fuses_rotary", False) and q.is_cuda
+                    and not getattr(attn, "is_cross_attention", False)):
+                fused = _rotary_tables("real", image_rotary_emb[0], image_rotary_emb[1], n_text)
+            if fused is None:
+                q = torch.cat([q[:, :, :n_text], rope_real_pairs(q[:, :, n_text:], image_rotary_emb)], dim=2)
+                if not getattr(attn, "is_cross_attention", False):
+                    k = torch.cat([k[:, :, :n_text], rope_real_pairs(k[:, :, n_text:], image_rotary_emb)], dim=2)
+        if fused is not None:
+            out = attn.inner_attention(q, k, v, self.layer_idx, rotary=fused)
+        else:
+            out = attn.inner_attention(q, k, v, self.layer_idx)
         out = out.transpose(1, 2).reshape(B, -1, H * D)
         out = attn.to_out[1](attn.to_out[0](out))
         return out[:, n_text:], out[:, :n_text]

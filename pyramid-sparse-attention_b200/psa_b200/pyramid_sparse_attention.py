@@ -180,8 +180,17 @@ class PyramidSparseAttention(nn.Module):
         dens = ops.density(mask, True) if compute_stats else None
         return out.view(q.shape), dens
 
-    def forward(self, q, k, v, layer_idx):
+    fuses_rotary = True       # forward() takes rotary=..., so a processor may hand over unrotated q and k
+
+    def forward(self, q, k, v, layer_idx, rotary=None):
+        """q, k, v [B, H, S, D].  rotary (ops.RotaryTables, optional): q and k arrive unrotated; on the token-major route
+        the kernels rotate the rows as they read them, on every other route they are rotated here first."""
         is_warmup = self.get_current_time() < self.config.warmup_steps
+        if rotary is not None:
+            tm = [token_major_view(x) for x in (q, k, v)]
+            if is_warmup or not (self._rows_in_place(q, k) and all(t is not None for t in tm)):
+                q, k = ops.rotate_rows(q, rotary), ops.rotate_rows(k, rotary)
+                rotary = None
         compute_stats = self.config.verbose or self.logger is not None
         dens = None
         self._v_requires_grad = v.requires_grad
@@ -198,7 +207,7 @@ class PyramidSparseAttention(nn.Module):
                 # the processors hand over transposed views of [B, S, H, D] tensors: read those where they lie and return
                 # the same kind of view, so that the caller's transpose(1, 2).flatten(2, 3) costs nothing
                 out_tm, mask = psa_attention_token_major(*tm, self.config, perm=self.gilbert_rearranger.source_rows(q.device),
-                                                         text_length=self.config.text_length)
+                                                         text_length=self.config.text_length, rope=rotary)
                 out = out_tm.transpose(1, 2)
                 dens = ops.density(mask, True) if compute_stats else None
             else:

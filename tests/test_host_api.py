@@ -293,3 +293,23 @@ def test_installers_use_the_reference_names_and_keep_the_original_processor():
     mod = cog.transformer_blocks[1].attn1.inner_attention
     assert isinstance(cog.transformer_blocks[1].attn1.processor, presets.SparseCogVideoXAttnProcessor)
     assert mod.model_type == "cogvideo" and mod.layer_num == 2 and mod.config.text_length == 226
+
+
+def test_rotary_tables_of_the_fused_loads_reproduce_both_processor_formulas():
+    """ops.rotate_rows (the element-wise statement of what the rotating loads compute) against the two rotary
+    formulations of the processors, bit for bit on bf16: Wan (interleaved pairs, cosine at even / sine at odd table
+    entries) and CogVideoX (real tables, video tokens only)."""
+    from psa_b200 import ops
+    from psa_b200.presets import _rotary_tables, rope_interleaved_pairs, rope_real_pairs
+    B, H, S, D, n_text = 2, 3, 50, 16, 7
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(B, H, S, D, generator=g).to(torch.bfloat16)
+    ang = torch.rand(1, S, 1, D, generator=g) * 6.28
+    cos, sin = torch.cos(ang), torch.sin(ang)                  # entries differ between the two channels of a pair
+    wan = rope_interleaved_pairs(x.transpose(1, 2), cos, sin).transpose(1, 2)
+    assert torch.equal(ops.rotate_rows(x, _rotary_tables("wan", cos, sin, 0)), wan)
+    ang2 = torch.rand(S - n_text, D // 2, generator=g).repeat_interleave(2, -1) * 6.28
+    c2, s2 = torch.cos(ang2), torch.sin(ang2)
+    cog = torch.cat([x[:, :, :n_text], rope_real_pairs(x[:, :, n_text:], (c2, s2))], dim=2)
+    assert torch.equal(ops.rotate_rows(x, _rotary_tables("real", c2, s2, n_text)), cog)
+    assert _rotary_tables("wan", cos.expand(2, S, 1, D), sin.expand(2, S, 1, D), 0) is None   # per-sample tables: not fused
