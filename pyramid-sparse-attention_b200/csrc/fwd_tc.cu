@@ -85,6 +85,11 @@ template <int D> struct Cfg {
   static constexpr int SLABS = D / 64;
   static constexpr int NK = D == 64 ? 4 : 3;   // K-tile ring
   static constexpr int NV = D == 64 ? 4 : 2;   // V-tile ring
+  // Score buffers in TMEM.  At D = 128 the two accumulators leave room for two; at D = 64 for three, and the third one
+  // lets Q K^T run two tiles ahead of P V, so that a softmax group finds its next scores ready when it is done with a tile.
+  static constexpr int NSB = D == 64 ? 3 : 2;
+  static constexpr int O_BASE = NSB * 128;          // first TMEM column of the accumulators
+  static constexpr int O_STRIDE = NSB == 3 ? 64 : 128;
   static constexpr int TILE_BYTES = SLABS * kSlabBytes;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + TILE_BYTES;
@@ -100,8 +105,13 @@ template <int D> struct Cfg {
 };
 
 struct Ctrl {
-  uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
-  uint64_t s_full[2], p_full[2], pv_done[2], q_full;
+  uint64_t k_full[4], v_full[4];
+  // "stage may be refilled": two barriers per stage, used by alternate fills.  Only the warp that fills a tile arrives on
+  // its full barrier, so a producer warp that was held up can find a stage two fills ahead of the one it is waiting
+  // for - with one barrier per stage that looks exactly like "not yet" to a parity wait, and the warp (which owns one of
+  // the next tiles) would block for good.  With two, a waiter may be up to three fills behind.
+  uint64_t k_empty[8], v_empty[8];
+  uint64_t s_full[3], p_full[2], pv_done[2], q_full;
   uint64_t row_ready[4], row_done[4], q_free, o_free;   // hand-over of query rows between the roles of a persistent CTA
   uint64_t prod_sync, xch_full;                         // bounded rendezvous of the producer warps / of the softmax warps
   int row_tiles[4], row_last_cols[4], row_index[4];   // row_index >= total_rows: no more rows
@@ -169,12 +179,15 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
   // ---------------------------------------------------------------- setup (once per CTA)
   if (threadIdx.x == 0) {
     for (int i = 0; i < 4; ++i) {
-      tc::mbar_init(&ctl->k_full[i], kProducerWarps); tc::mbar_init(&ctl->k_empty[i], 1);
-      tc::mbar_init(&ctl->v_full[i], kProducerWarps); tc::mbar_init(&ctl->v_empty[i], 1);
+      tc::mbar_init(&ctl->k_full[i], 1);   // one producer warp fills a whole tile
+      tc::mbar_init(&ctl->v_full[i], 1);
+      tc::mbar_init(&ctl->k_empty[2 * i], 1); tc::mbar_init(&ctl->k_empty[2 * i + 1], 1);
+      tc::mbar_init(&ctl->v_empty[2 * i], 1); tc::mbar_init(&ctl->v_empty[2 * i + 1], 1);
     }
     ctl->abort_flag = 0;
     tc::fence_mbar_init();
   } else if (threadIdx.x == 32) {
+    tc::mbar_init(&ctl->s_full[2], 1);
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&ctl->s_full[i], 1);
       tc::mbar_init(&ctl->p_full[i], 4);   // one arrival per softmax warp of the group
@@ -380,16 +393,24 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           if (!ok) break;
           if (step < n_tiles) {
             const int t = step, gt = g0 + t, stage = gt % C::NK, slot = gt % kBiasSlots;
-            ok = tc::mbar_wait_a(k_empty_a + stage * 8, ((gt / C::NK) & 1) ^ 1, abort_flag);
+            if (gt >= C::NK) {      // fill number f of the stage waits for the scores of fill f-1
+              const int f = gt / C::NK - 1;
+              ok = tc::mbar_wait_a(k_empty_a + (stage * 2 + (f & 1)) * 8, (f >> 1) & 1, abort_flag);
+            }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            const int probe = ki + lane;
+            const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sIt[probe < n_items ? probe : 0] >> 21) == t));
+            // Every producer warp waits for every tile's stage, in order (a parity wait is only valid for a waiter at most
+            // one phase ahead of its barrier), but ONE warp gathers the whole tile and the warps take turns: an mbarrier
+            // arrive costs its thread ~250 cycles and a wait ~170, so three warps that each handle a third of every tile
+            // spend far longer per tile than one warp that handles all of it while the others work on the next ones.
+            if ((2 * gt) % kProducerWarps == warp) {
             const uint32_t tile_a = sK_a + stage * C::TILE_BYTES, bar_a = k_full_a + stage * 8;
             float* bias_row = sBias + slot * 128;
             float* biasg_row = sBiasG + slot * 36;
-            const int probe = ki + lane;
-            const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sIt[probe < n_items ? probe : 0] >> 21) == t));
-            const bool active = 3 * lane + warp < in_tile;
-            const uint32_t x = active ? sIt[ki + 3 * lane + warp] : 0u;
+            const bool active = lane < in_tile;
+            const uint32_t x = active ? sIt[ki + lane] : 0u;
             const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = ((int)(x >> 16) << 2) & 127, row0 = blk * P;
             // logit bias of the block's columns
             const int nl = li == 0 ? n0 : (li == 1 ? n1 : (li == 2 ? n2 : n3));
@@ -427,7 +448,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             // per-column path of the softmax
             const bool odd_edge = active && ((nvalid > 0 && nvalid < P && (nvalid & 3) != 0) || diag);
             const bool any_odd = __any_sync(0xffffffffu, odd_edge);
-            if (lane == 0) reinterpret_cast<int*>(biasg_row)[32 + warp] = any_odd ? 1 : 0;
+            if (lane < 3) reinterpret_cast<int*>(biasg_row)[32 + lane] = (lane == 0 && any_odd) ? 1 : 0;
             // wide blocks (at most 4 per tile): the whole warp writes the bias, 4 columns per lane
             unsigned wide = __ballot_sync(0xffffffffu, active && P > 16);
             while (wide) {
@@ -450,25 +471,30 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
                 }
               }
             }
-            ki += in_tile;
             // the bias of this tile must be complete before the tile is announced: the softmax warps read it once the
             // scores are ready, and "scores ready" follows "K tile full" through the MMA issuer
-            if (t == n_tiles - 1 && warp == 0)
+            if (t == n_tiles - 1)
               for (int c = last_cols + lane; c < 128; c += 32) { bias_row[c] = -INFINITY; biasg_row[c >> 2] = -INFINITY; }
             const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
             if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
+            }
+            ki += in_tile;
           }
           if (step > 0) {
             const int t = step - 1, gt = g0 + t, stage = gt % C::NV;
-            ok = tc::mbar_wait_a(v_empty_a + stage * 8, ((gt / C::NV) & 1) ^ 1, abort_flag);
+            if (gt >= C::NV) {
+              const int f = gt / C::NV - 1;
+              ok = tc::mbar_wait_a(v_empty_a + (stage * 2 + (f & 1)) * 8, (f >> 1) & 1, abort_flag);
+            }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            const uint32_t tile_a = sV_a + stage * C::TILE_BYTES, bar_a = v_full_a + stage * 8;
             const int probe = vi + lane;
             const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sIt[probe < n_items ? probe : 0] >> 21) == t));
-            const int mine = vi + 3 * lane + warp;
+            if ((2 * gt + 1) % kProducerWarps == warp) {
+            const uint32_t tile_a = sV_a + stage * C::TILE_BYTES, bar_a = v_full_a + stage * 8;
+            const int mine = vi + lane;
             uint32_t my_bytes = 0;
-            if (3 * lane + warp < in_tile) {
+            if (lane < in_tile) {
               const uint32_t x = sIt[mine];
               const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = ((int)(x >> 16) << 2) & 127;
               if (IMG) {
@@ -481,9 +507,10 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
               }
               my_bytes = (uint32_t)C::SLABS * P * 128u;
             }
-            vi += in_tile;
             const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
             if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
+            }
+            vi += in_tile;
           }
         }
       if (ok && q_pending) fetch_q(true);
@@ -535,8 +562,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             if (o_ok && tc::mbar_test_wait_a(p_full_a + b * 8, (gt >> 1) & 1) && tc::mbar_test_wait_a(v_full_a + stage * 8, (gt / C::NV) & 1)) {
                 tc::tc_fence_after();
                 const uint64_t vdesc = vdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
-                const uint32_t tP = tmem + b * 128;            // probabilities overwrite the scores they came from
-                const uint32_t tO = tmem + 256 + b * 128;      // even and odd tiles accumulate separately
+                const uint32_t tP = tmem + (gt % C::NSB) * 128;              // probabilities overwrite the scores they came from
+                const uint32_t tO = tmem + C::O_BASE + b * C::O_STRIDE;      // even and odd tiles accumulate separately
                 if (t < n_tiles - 1 || last_cols == 128) {
                   tc::umma_ts(tO, tP, vdesc, idesc_pv, t > 1 ? 1u : 0u);
 #pragma unroll
@@ -545,32 +572,34 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
                   for (int ks = 0; ks < last_cols / 16; ++ks)
                     tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, (t > 1 || ks > 0) ? 1u : 0u);
                 }
-                tc::umma_commit_a(v_empty_a + stage * 8);   // V tile may be refilled
+                tc::umma_commit_a(v_empty_a + (stage * 2 + ((gt / C::NV) & 1)) * 8);   // V tile may be refilled
                 // a tcgen05.commit costs this thread 100-500 cycles: "accumulator b is final" is only signalled for its last
                 // tile of the row (in between, the scores of tile t+2 - issued after this product - say the same)
-                if (t >= n_tiles - 2) tc::umma_commit_a(pv_done_a + b * 8);
+                // With three score buffers the next scores of this group may be issued before this product, so every product
+                // is signalled (the softmax waits for it before it rescales the accumulator).
+                if (C::NSB == 3 || t >= n_tiles - 2) tc::umma_commit_a(pv_done_a + b * 8);
                 ++pv_next;
                 progressed = true;
               }
             }
-            // S = Q K^T of tile t is only issued once P V of tile t-2 has been: the tensor pipe runs in issue order, so
-            // "S_t ready" then also means that P V of tile t-2 has finished reading the probabilities that were written over
-            // the scores of buffer t&1
-            if (qk_next < n_tiles && qk_next <= pv_next + 1) {
-              const int t = qk_next, gt = g0 + t, b = gt & 1, stage = gt % C::NK;
+            // S = Q K^T of tile t is only issued once P V of tile t-NSB has been (NSB score buffers): the tensor pipe runs in
+            // issue order, so "S_t ready" then also means that P V of tile t-NSB has finished reading the probabilities that
+            // were written over the scores of buffer t mod NSB
+            if (qk_next < n_tiles && qk_next <= pv_next + C::NSB - 1) {
+              const int t = qk_next, gt = g0 + t, stage = gt % C::NK;
               if (tc::mbar_test_wait_a(k_full_a + stage * 8, (gt / C::NK) & 1)) {
                 tc::tc_fence_after();
                 const uint64_t kdesc = kdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
                 const uint32_t idesc_qk = t == n_tiles - 1 ? tc::make_idesc(FMT, 128, last_cols, 0, 0) : idesc_qk_full;
-                const uint32_t tSb = tmem + b * 128;
+                const uint32_t tSb = tmem + (gt % C::NSB) * 128;
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                   const uint32_t qoff = (uint32_t)(((ks >> 2) * kSlabBytes + (ks & 3) * 32) >> 4);
                   const uint32_t koff = (uint32_t)(((ks >> 2) * kSlabStride + (ks & 3) * 32) >> 4);
                   tc::umma_ss(tSb, qdesc + qoff, kdesc + koff, idesc_qk, ks > 0 ? 1u : 0u);
                 }
-                tc::umma_commit_a(k_empty_a + stage * 8);   // K tile may be refilled
-                tc::umma_commit_a(s_full_a + b * 8);
+                tc::umma_commit_a(k_empty_a + (stage * 2 + ((gt / C::NK) & 1)) * 8);   // K tile may be refilled
+                tc::umma_commit_a(s_full_a + (gt % C::NSB) * 8);
               if (t == n_tiles - 1) tc::umma_commit_a(q_free_a);   // the query tile may be replaced
                 ++qk_next;
                 progressed = true;
@@ -599,9 +628,9 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     const int g = (warp - 4) >> 2;                // softmax group = tile parity = score buffer = accumulator
     const int r = quarter * 32 + lane;            // row inside the query block
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tS = tmem + g * 128 + lane_base;         // scores of my tiles; probabilities go back in place
-    const uint32_t tO = tmem + 256 + g * 128 + lane_base;   // my accumulator
-    const uint32_t tO_other = tmem + 256 + (g ^ 1) * 128 + lane_base;
+    const uint32_t tS_mine = tmem + g * 128 + lane_base;    // scores of my tiles (two score buffers); probabilities go back in place
+    const uint32_t tO = tmem + C::O_BASE + g * C::O_STRIDE + lane_base;   // my accumulator
+    const uint32_t tO_other = tmem + C::O_BASE + (g ^ 1) * C::O_STRIDE + lane_base;
     const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
     bool ok = true;
     int g0 = 0, q_rows = 0, pv_rows = 0;
@@ -641,12 +670,15 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       const int first = ((g0 & 1) == g) ? 0 : 1;    // my first tile of this row
         for (int j = first; j < n_tiles; j += 2) {
           const int gj = g0 + j, slot = gj % kBiasSlots, it = gj >> 1;
-          ok = tc::mbar_wait(&ctl->s_full[g], it & 1, abort_flag);   // scores ready (and the tile's bias words visible)
+          // scores ready (and the tile's bias words visible)
+          if (C::NSB == 2) ok = tc::mbar_wait(&ctl->s_full[g], it & 1, abort_flag);
+          else ok = tc::mbar_wait(&ctl->s_full[gj % 3], (gj / 3) & 1, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          // The scores of running tile gj were issued after P V of tile gj-2 (same group), so that product is complete
-          // and the accumulator may be rescaled below.
+          // Two score buffers: the scores of running tile gj were issued after P V of tile gj-2 (same group), so that product
+          // is complete and the accumulator may be rescaled below.  Three: see the wait before the rescale.
           tc::tc_fence_after();
+          const uint32_t tS = C::NSB == 2 ? tS_mine : tmem + (uint32_t)(gj % 3) * 128 + lane_base;
           const bool ragged = j == n_tiles - 1 && last_cols < 128;   // columns the MMA did not write hold stale bits
           const float4* bias4 = reinterpret_cast<const float4*>(sBias + slot * 128);
           const float4* bg4 = reinterpret_cast<const float4*>(sBiasG + slot * 36);     // one bias word per 4 columns
@@ -714,6 +746,16 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             alpha = m_run == -INFINITY ? 0.f : ex2(m_run - mx);
             m_run = mx;
             l_run *= alpha;
+          }
+          if (C::NSB == 3 && j >= 2) {
+            // Every product of this group is signalled; each signal is waited for exactly once and in order (here for the
+            // product of tile j-2, in the epilogue for the last one), so the waiter is never more than one phase behind.
+            // By now - a whole maximum pass after the scores were found ready - it has normally long completed.
+            ok = tc::mbar_wait(&ctl->pv_done[g], pv_rows & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ++pv_rows;
+            tc::tc_fence_after();
           }
           if (j >= 2 && __any_sync(0xffffffffu, raise)) {
             // the accumulator may only be touched between two of its P V products: the one of tile j-2 is complete (see
