@@ -9,19 +9,21 @@
 //               the selected K/V blocks of every pyramid level into 128-token tiles, PACKING blocks of different levels
 //               into the same tile.  A block is P = block_n/level contiguous pooled rows.  From tile images it is ONE
 //               linear bulk copy per operand; from row-major tensors one TMA box {64 ch, P rows} per 64-channel slab
-//               (128-byte swizzle).  Never multicast.  A copy costs its issuing thread 150-200 cycles whatever its size,
-//               so the blocks of a tile are spread over the lanes of all three warps (lane l of warp w takes block 3l+w),
-//               which decode and issue side by side.  K tiles and V tiles live in separate rings (K is released after
-//               S = Q K^T, V after O += P V) and K runs one tile ahead of V.  The producers also write the logit bias of
+//               (128-byte swizzle).  Never multicast.  A copy costs its issuing thread ~100 cycles whatever its size, an
+//               mbarrier arrive ~250 and a wait ~170, so the blocks of a tile are spread over the lanes of ONE warp and the
+//               three warps take turns (K tile t is job 2t, V tile t job 2t+1, job J belongs to warp J mod 3); every warp
+//               still waits for every tile's stage, in order.  K tiles and V tiles live in separate rings (K is released
+//               after S = Q K^T, V after O += P V) and K runs one tile ahead of V.  The producers also write the logit bias of
 //               the tile's columns (log2 of the level, -inf for columns that do not exist), per column and per group of
 //               4 columns, publish every row (tile count) to the other roles and fetch its query tile as soon as the
 //               previous row's last Q K^T has read the old one.
-//   warp 3      MMA issuer (one thread): S = Q K^T (operands in shared memory) into one of two TMEM score buffers, and
+//   warp 3      MMA issuer (one thread): S = Q K^T (operands in shared memory) into one of the TMEM score buffers, and
 //               O += P V with P read from TMEM and V read MN-major from its swizzled tile.  Descriptors are built once;
 //               per MMA only an immediate is added.  It polls (non-blocking) for whichever product is ready and issues in
 //               the fixed order QK0 QK1 PV0 QK2 PV1 ...; the tensor pipe runs in issue order, so "S of tile t ready" also
-//               says that P V of tile t-2 is done with the buffer and with the accumulator.  The first scores of the next row are computed while
-//               the softmax warps are still in the epilogue of the current one.
+//               says that P V of tile t-2 is done with the buffer and with the accumulator (two score buffers; with three,
+//               at head_dim 64, Q K^T runs up to two tiles ahead of P V and every P V is signalled instead).  The first
+//               scores of the next row are computed while the softmax warps are still in the epilogue of the current one.
 //   warps 4-11  softmax: two groups of four warps, ONE thread per query row.  Group g owns the tiles whose running index
 //               is g (mod 2), with its own running maximum, running sum and output accumulator (a split-KV inside the
 //               CTA), so no thread needs another thread's partial result and the two warps on a scheduler work on
@@ -30,7 +32,8 @@
 //               The running maximum is only raised when the new one exceeds it by more than 2^8 ("lazy" rescale of the
 //               accumulator).  Epilogue of a row: the groups exchange (max, sum), every thread reads BOTH accumulators of
 //               its row from TMEM, and after an 8x8 transpose by warp shuffles 8 lanes store one row's 128 contiguous bytes.
-// TMEM (512 columns): S0/P0 [0,128), S1/P1 [128,256), O of even tiles [256,256+D), O of odd tiles [384,384+D).
+// TMEM (512 columns), head_dim 128: S0/P0 [0,128), S1/P1 [128,256), O of even tiles [256,384), O of odd tiles [384,512);
+// head_dim 64: three score buffers [0,384), O of even tiles [384,448), O of odd tiles [448,512).
 //
 // Every wait is bounded - mbarrier waits, the issuer's polling loop and the warp-group rendezvous (mbarriers, never
 // bar.sync, inside the role loops); on expiry the CTA records PSA_ERR_TIMEOUT in the status word, lets copies in
