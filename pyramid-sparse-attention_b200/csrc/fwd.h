@@ -44,11 +44,6 @@ struct OutScatter {
 // batch): token t of local head h is row (t % tokens_per_rank) of peer t / tokens_per_rank, whose buffer is laid out
 // [tokens_per_rank][heads_total][D]; kernels read it with plain loads.  perm != null: the operand is read in a reordered
 // token sequence, token t of the sequence being row perm[t] of the stored tensor (int32 [seq]).
-// rope_a != null (16-bit operands only): rows are rotated while they are read, as the attention processors of the
-// diffusion transformers do before the attention call (modify_diffusers.py:260-281 for Wan, :363-369 for CogVideoX).
-// Stored token s >= rope_first uses row s - rope_first of the two fp32 tables [.., D]; channel pair (x0, x1) becomes
-// (x0*a[even] - x1*b[even], x1*a[odd] + x0*b[odd]), every product and sum rounded to fp32 on its own (no fused
-// multiply-add) and the result rounded once to the element type - bit for bit what the framework's element-wise ops give.
 struct RowSource {
   const void* base;
   const void* peer[kMaxPeers];
@@ -56,10 +51,19 @@ struct RowSource {
   int heads_total, head0;
   int64_t tokens_per_rank;
   const int32_t* perm;
-  const float* rope_a;
-  const float* rope_b;
-  int64_t rope_first;
-  int rope_bf16;   // element type of the rows when rope_a is set: 1 bf16, 0 f16
+};
+
+// Rotary tables for rows that are rotated while they are read (16-bit operands), as the attention processors of the
+// diffusion transformers do before the attention call (modify_diffusers.py:260-281 for Wan, :363-369 for CogVideoX).
+// Stored token s >= first uses row s - first of the two fp32 tables [.., D]; channel pair (x0, x1) becomes
+// (x0*a[even] - x1*b[even], x1*a[odd] + x0*b[odd]), every product and sum rounded to fp32 on its own (no fused
+// multiply-add) and the result rounded once to the element type - bit for bit what the framework's element-wise ops give.
+// a == null: no rotation (kernels are then instantiated without the rotary code).
+struct RopeTables {
+  const float* a;
+  const float* b;
+  int64_t first;
+  int bf16;   // element type of the rows: 1 bf16, 0 f16
 };
 
 inline RowSource local_rows(const void* base) {
@@ -108,19 +112,16 @@ __device__ __forceinline__ uint4 rotate_word(uint4 w, const float* __restrict__ 
   return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
-// 16-byte word `c` of the row of token `tok` of local head `bh`, rotated if the source says so.
-__device__ __forceinline__ uint4 load_row_word(const RowSource& s, int64_t bh, int64_t seq, int64_t tok, int row16, int c) {
-  if (s.perm) tok = s.perm[tok];
-  uint4 w;
-  if (s.n_peers == 0) {
-    w = *(reinterpret_cast<const uint4*>(s.base) + (bh * seq + tok) * row16 + c);
-  } else {
-    const int64_t owner = tok / s.tokens_per_rank, local = tok - owner * s.tokens_per_rank;
-    w = *(reinterpret_cast<const uint4*>(s.peer[owner]) + (local * s.heads_total + s.head0 + bh) * row16 + c);
-  }
-  if (s.rope_a && tok >= s.rope_first) {
-    const int64_t off = ((tok - s.rope_first) * row16 + c) * 8;    // row16 * 8 channels per table row
-    w = rotate_word(w, s.rope_a + off, s.rope_b + off, s.rope_bf16 != 0);
+// 16-byte word `c` of the row of token `tok` of local head `bh`; with ROPE, rotated by the tables (if they are set).
+template <bool ROPE>
+__device__ __forceinline__ uint4 load_row_word(const RowSource& s, const RopeTables& rope, int64_t bh, int64_t seq, int64_t tok,
+                                               int row16, int c) {
+  if (!ROPE) return *row_word(s, bh, seq, tok, row16, c);
+  const int64_t stored = s.perm ? (int64_t)s.perm[tok] : tok;
+  uint4 w = *row_word(s, bh, seq, tok, row16, c);
+  if (rope.a && stored >= rope.first) {
+    const int64_t off = ((stored - rope.first) * row16 + c) * 8;    // row16 * 8 channels per table row
+    w = rotate_word(w, rope.a + off, rope.b + off, rope.bf16 != 0);
   }
   return w;
 }

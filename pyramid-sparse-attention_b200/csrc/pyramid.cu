@@ -122,10 +122,10 @@ __device__ __forceinline__ void img_store(unsigned char* base, int64_t bh, int64
   *reinterpret_cast<uint4*>(p) = val;
 }
 
-template <typename T>
+template <typename T, bool ROPE>
 __global__ void __launch_bounds__(256) pyramid_img_kernel(const RowSource k, const RowSource v, unsigned char* __restrict__ kimg,
                                                           unsigned char* __restrict__ vimg, ImgLevels L, int64_t bh, int64_t S, int64_t n8,
-                                                          int cpr) {
+                                                          int cpr, const RopeTables rope) {
   const RowSource& x = blockIdx.y ? v : k;
   unsigned char* img = blockIdx.y ? vimg : kimg;
   const int slabs = cpr / 8;
@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(256) pyramid_img_kernel(const RowSource k, con
     for (int t = 0; t < 8; ++t) {
       int64_t tok = j * 8 + t;
       tok = tok < S ? tok : S - 1;
-      r[t] = load_row_word(x, head, S, tok, cpr, c);
+      r[t] = (ROPE && blockIdx.y == 0) ? load_row_word<true>(x, rope, head, S, tok, cpr, c) : *row_word(x, head, S, tok, cpr, c);
     }
     uint4 a[4], b[2], d;
 #pragma unroll
@@ -168,7 +168,7 @@ extern "C" size_t psa_kv_image_bytes(int64_t bh, int64_t seq, int head_dim, int 
 
 namespace psa {
 static int launch_pyramid_images(const RowSource& k, const RowSource& v, void* kimg, void* vimg, int64_t bh, int64_t seq, int head_dim,
-                                 int block_n, int dtype, int max_blocks, cudaStream_t st) {
+                                 int block_n, int dtype, int max_blocks, cudaStream_t st, const RopeTables& rope = RopeTables{}) {
   const ImgLevels L = make_img_levels(bh, seq, head_dim, block_n);
   const int64_t s_pad = cdiv64(seq, block_n) * block_n;
   const int64_t n8 = s_pad / 8;
@@ -177,10 +177,13 @@ static int launch_pyramid_images(const RowSource& k, const RowSource& v, void* k
   const int64_t cap = max_blocks > 0 ? max_blocks : 148 * 16;
   if (blocks > cap) blocks = cap;
   dim3 grid((unsigned)blocks, 2);
-  if (dtype == PSA_F16)
-    pyramid_img_kernel<__half><<<grid, 256, 0, st>>>(k, v, (unsigned char*)kimg, (unsigned char*)vimg, L, bh, seq, n8, cpr);
-  else
-    pyramid_img_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(k, v, (unsigned char*)kimg, (unsigned char*)vimg, L, bh, seq, n8, cpr);
+  if (dtype == PSA_F16) {
+    if (rope.a) pyramid_img_kernel<__half, true><<<grid, 256, 0, st>>>(k, v, (unsigned char*)kimg, (unsigned char*)vimg, L, bh, seq, n8, cpr, rope);
+    else pyramid_img_kernel<__half, false><<<grid, 256, 0, st>>>(k, v, (unsigned char*)kimg, (unsigned char*)vimg, L, bh, seq, n8, cpr, rope);
+  } else {
+    if (rope.a) pyramid_img_kernel<__nv_bfloat16, true><<<grid, 256, 0, st>>>(k, v, (unsigned char*)kimg, (unsigned char*)vimg, L, bh, seq, n8, cpr, rope);
+    else pyramid_img_kernel<__nv_bfloat16, false><<<grid, 256, 0, st>>>(k, v, (unsigned char*)kimg, (unsigned char*)vimg, L, bh, seq, n8, cpr, rope);
+  }
   PSA_CHECK_LAUNCH("psa_pyramid_kv_images");
   return PSA_OK;
 }
@@ -233,11 +236,8 @@ static int pyramid_kv_images_tm(const void* k, const void* v, const int32_t* per
   ks.heads_total = vs.heads_total = heads;
   ks.tokens_per_rank = vs.tokens_per_rank = seq;
   ks.perm = vs.perm = perm;
-  ks.rope_a = rope_a;      // keys are rotated while they are read; values never are
-  ks.rope_b = rope_b;
-  ks.rope_first = rope_first;
-  ks.rope_bf16 = dtype == PSA_BF16;
-  return launch_pyramid_images(ks, vs, kimg, vimg, heads, seq, head_dim, block_n, dtype, 0, (cudaStream_t)stream);
+  const RopeTables rope = {rope_a, rope_b, rope_first, dtype == PSA_BF16};   // applied to the keys only
+  return launch_pyramid_images(ks, vs, kimg, vimg, heads, seq, head_dim, block_n, dtype, 0, (cudaStream_t)stream, rope);
 }
 
 extern "C" int psa_pyramid_kv_images_tm(const void* k, const void* v, const int32_t* perm, void* kimg, void* vimg, int heads,

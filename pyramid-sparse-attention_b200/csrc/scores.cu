@@ -162,7 +162,8 @@ __global__ void __launch_bounds__(256) scores_pool_normalise(const T* __restrict
 
 template <typename T>
 static int launch_scores(const RowSource& q, const RowSource& k, const int32_t* idx_q, const int32_t* idx_k, void* po,
-                         void* scratch, const ScoreDims& d, int64_t bh, int impl, cudaStream_t st) {
+                         void* scratch, const ScoreDims& d, int64_t bh, int impl, cudaStream_t st,
+                         const RopeTables& rope = RopeTables{}) {
   T* R = (T*)scratch;
   const size_t r_bytes = ((size_t)bh * d.nq_s * d.n_d * sizeof(T) + 255) & ~(size_t)255;
   float* rowmax = (float*)((char*)scratch + r_bytes);
@@ -171,10 +172,10 @@ static int launch_scores(const RowSource& q, const RowSource& k, const int32_t* 
   bool use_tc = (impl == 2) || (impl == 0 && sizeof(T) == 2 && scores_tc_supported(d));
   if (use_tc) {
     int rc = launch_scores_cellmax_tc(q, k, idx_q, idx_k, R, rowmax, extra, d, bh, sizeof(T) == 4 ? PSA_F32 :
-                                      (std::is_same<T, __half>::value ? PSA_F16 : PSA_BF16), st);
+                                      (std::is_same<T, __half>::value ? PSA_F16 : PSA_BF16), st, rope);
     if (rc != PSA_OK) return rc;
   } else {
-    PSA_REQUIRE(q.n_peers == 0 && k.n_peers == 0, PSA_ERR_UNSUPPORTED, "the scalar score kernel reads local tensors only");
+    PSA_REQUIRE(q.n_peers == 0 && k.n_peers == 0 && !rope.a, PSA_ERR_UNSUPPORTED, "the scalar score kernel reads local tensors only");
     dim3 grid((unsigned)cdiv64(d.nq_s, 64), (unsigned)bh);
     scores_cellmax_simt<T><<<grid, 256, 0, st>>>((const T*)q.base, (const T*)k.base, idx_q, idx_k, R, rowmax, d);
     PSA_CHECK_LAUNCH("psa_block_scores(stage A)");
@@ -351,13 +352,10 @@ static int block_scores_tm(const void* q, const void* k, const int32_t* perm, co
   qs.heads_total = ks.heads_total = heads;
   qs.tokens_per_rank = ks.tokens_per_rank = seq;
   qs.perm = ks.perm = perm;
-  qs.rope_a = ks.rope_a = rope_a;
-  qs.rope_b = ks.rope_b = rope_b;
-  qs.rope_first = ks.rope_first = rope_first;
-  qs.rope_bf16 = ks.rope_bf16 = dtype == PSA_BF16;
+  const RopeTables rope = {rope_a, rope_b, rope_first, dtype == PSA_BF16};
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == PSA_F16) return launch_scores<__half>(qs, ks, idx_q, idx_k, po, scratch, d, heads, 2, st);
-  return launch_scores<__nv_bfloat16>(qs, ks, idx_q, idx_k, po, scratch, d, heads, 2, st);
+  if (dtype == PSA_F16) return launch_scores<__half>(qs, ks, idx_q, idx_k, po, scratch, d, heads, 2, st, rope);
+  return launch_scores<__nv_bfloat16>(qs, ks, idx_q, idx_k, po, scratch, d, heads, 2, st, rope);
 }
 
 extern "C" int psa_block_scores_tm(const void* q, const void* k, const int32_t* perm, const int32_t* idx_q, const int32_t* idx_k,

@@ -26,7 +26,8 @@ bool scores_tc_supported(const ScoreDims& d);
 // bytes of scratch the tcgen05 path needs beyond R and rowmax (compacted sample matrices)
 size_t scores_tc_extra_scratch(const ScoreDims& d, int64_t bh);
 int launch_scores_cellmax_tc(const RowSource& q, const RowSource& k, const int32_t* idx_q, const int32_t* idx_k, void* R,
-                             float* rowmax, void* extra, const ScoreDims& d, int64_t bh, int dtype, cudaStream_t st);
+                             float* rowmax, void* extra, const ScoreDims& d, int64_t bh, int dtype, cudaStream_t st,
+                             const RopeTables& rope = RopeTables{});
 
 // the same stage A on sample matrices that are already compacted: qs [bh][nq_s][D], ks [bh][nk_cols][D]
 int launch_scores_cellmax_tc_samples(const void* qs, const void* ks, void* R, float* rowmax, const ScoreDims& d, int64_t bh,

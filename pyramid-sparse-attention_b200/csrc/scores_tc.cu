@@ -24,10 +24,10 @@ constexpr int kSlabBytes = 128 * 128;
 constexpr int kThreads = 192;
 constexpr int kStages = 2;
 
-template <typename T>
+template <typename T, bool ROPE>
 __global__ void __launch_bounds__(256) gather_samples_kernel(const RowSource x, const int32_t* __restrict__ idx,
                                                              T* __restrict__ out, int64_t seq, int D, int block, int keep,
-                                                             int n_valid, int n_out) {
+                                                             int n_valid, int n_out, const RopeTables rope) {
   const int cpr = D * (int)sizeof(T) / 16;
   const int64_t bh = blockIdx.y;
   uint4* dst = reinterpret_cast<uint4*>(out + bh * (int64_t)n_out * D);
@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(256) gather_samples_kernel(const RowSource x, 
     const int ic = i < n_valid ? i : n_valid - 1;
     int64_t tok = (int64_t)(ic / keep) * block + idx[bh * keep + (ic % keep)];
     tok = tok < seq ? tok : seq - 1;
-    dst[(int64_t)i * cpr + c] = load_row_word(x, bh, seq, tok, cpr, c);
+    dst[(int64_t)i * cpr + c] = load_row_word<ROPE>(x, rope, bh, seq, tok, cpr, c);
   }
 }
 
@@ -289,7 +289,8 @@ size_t scores_tc_extra_scratch(const ScoreDims& d, int64_t bh) {
 }
 
 int launch_scores_cellmax_tc(const RowSource& q, const RowSource& k, const int32_t* idx_q, const int32_t* idx_k, void* R,
-                             float* rowmax, void* extra, const ScoreDims& d, int64_t bh, int dtype, cudaStream_t st) {
+                             float* rowmax, void* extra, const ScoreDims& d, int64_t bh, int dtype, cudaStream_t st,
+                             const RopeTables& rope) {
   PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "the tcgen05 score kernel needs f16/bf16 inputs");
   PSA_REQUIRE(scores_tc_supported(d), PSA_ERR_UNSUPPORTED, "the tcgen05 score kernel does not cover this block size");
   const size_t qb = ((size_t)bh * d.nq_s * d.D * 2 + 255) & ~(size_t)255;
@@ -299,10 +300,13 @@ int launch_scores_cellmax_tc(const RowSource& q, const RowSource& k, const int32
     const int cpr = d.D * 2 / 16;
     dim3 gq((unsigned)std::min<int64_t>(cdiv64((int64_t)d.nq_s * cpr, 256), 148 * 8), (unsigned)bh);
     dim3 gk((unsigned)std::min<int64_t>(cdiv64((int64_t)d.nk_cols * cpr, 256), 148 * 8), (unsigned)bh);
-    gather_samples_kernel<uint16_t><<<gq, 256, 0, st>>>(q, idx_q, (uint16_t*)qs, d.seq_q, d.D, d.bm, d.kq,
-                                                         d.nq_s, d.nq_s);
-    gather_samples_kernel<uint16_t><<<gk, 256, 0, st>>>(k, idx_k, (uint16_t*)ks, d.seq_k, d.D, d.bn, d.kk,
-                                                         d.nk_s, d.nk_cols);
+    if (rope.a) {
+      gather_samples_kernel<uint16_t, true><<<gq, 256, 0, st>>>(q, idx_q, (uint16_t*)qs, d.seq_q, d.D, d.bm, d.kq, d.nq_s, d.nq_s, rope);
+      gather_samples_kernel<uint16_t, true><<<gk, 256, 0, st>>>(k, idx_k, (uint16_t*)ks, d.seq_k, d.D, d.bn, d.kk, d.nk_s, d.nk_cols, rope);
+    } else {
+      gather_samples_kernel<uint16_t, false><<<gq, 256, 0, st>>>(q, idx_q, (uint16_t*)qs, d.seq_q, d.D, d.bm, d.kq, d.nq_s, d.nq_s, rope);
+      gather_samples_kernel<uint16_t, false><<<gk, 256, 0, st>>>(k, idx_k, (uint16_t*)ks, d.seq_k, d.D, d.bn, d.kk, d.nk_s, d.nk_cols, rope);
+    }
     PSA_CHECK_LAUNCH("psa_block_scores(gather)");
   }
   const int fmt = dtype == PSA_BF16;
