@@ -225,10 +225,16 @@ int psa_block_scores_tm_rope(const void* q, const void* k, const int32_t* perm, 
  * in groups of `stride`; logit(i, j) = sum_s q[i*stride + stride-1-s] . k[j*stride + s] / sqrt(D) / stride; causal: group
  * i sees groups j <= i, else all groups of the padded length; out [BH, nb, nb] (dtype), nb = ceil(seq/block_size) =
  * softmax mass per (query block, key block).  block_size/stride must be a power of two in 2..32.
- * scratch: psa_antidiag_scratch_bytes() bytes (the fp32 logits), 16-byte aligned. */
+ * scratch: psa_antidiag_scratch_bytes() bytes (the fp32 logits), 16-byte aligned.
+ * psa_antidiag_scores_impl: impl 0 = pick (the tcgen05 kernel when seq is a multiple of stride, else the warp-level
+ * mma.sync kernel), 2 = tcgen05 (PSA_ERR_UNSUPPORTED otherwise), 3 = mma.sync; status (may be NULL): device word that
+ * receives PSA_ERR_TIMEOUT if a bounded wait of the tcgen05 kernel expires (the output is then incomplete). */
 size_t psa_antidiag_scratch_bytes(int64_t bh, int64_t seq, int head_dim, int block_size, int stride, int chunk_size);
 int psa_antidiag_scores(const void* q, const void* k, void* out, void* scratch, size_t scratch_bytes, int64_t bh, int64_t seq,
                         int head_dim, int block_size, int stride, int chunk_size, int causal, int dtype, void* stream);
+int psa_antidiag_scores_impl(const void* q, const void* k, void* out, void* scratch, size_t scratch_bytes, int64_t bh, int64_t seq,
+                             int head_dim, int block_size, int stride, int chunk_size, int causal, int dtype, int impl,
+                             int32_t* status, void* stream);
 
 /* Level assignment of the causal call site.  Replaces transfer_attn_to_mask,
  * qwen2.5-vl-example/src/attention/PSA_casual/PyramidAdaptiveBlockSparseAttn.py:85-168.

@@ -6,14 +6,18 @@
 // channels of a group row is 128 contiguous bytes of one token of q or k.  Then a row softmax (causal: groups j <= i)
 // and the sum of the probabilities over (block/stride x block/stride) cells give the mass per (query block, key block).
 //
-// Kernel 1 (tensor cores, legacy mma.sync path: a tcgen05 version is future work): 128x128 logit tiles, 8 warps of
-// 32x64, K streamed in chunks of 64 through registers into padded shared-memory tiles; logits are written as fp32,
-// already multiplied by log2(e)/sqrt(D)/stride.  Causal launches skip the tiles above the diagonal.
+// Kernel 1, tcgen05 (antidiag_tc.cu; lengths that are a multiple of the stride): TMA boxes over a 4-D view of q and k,
+// one accumulator tile per 128x128 logits in TMEM.  Kernel 1, warp-level mma.sync (this file; any length): 128x128 logit
+// tiles, 8 warps of 32x64, K streamed in chunks of 64 through registers into padded shared-memory tiles.  Both write the
+// logits as fp32, already multiplied by log2(e)/sqrt(D)/stride, and skip the tiles above the diagonal when causal.
 // Kernel 2 (HBM-bound: reads the logits once per pass): one CTA per query block, a warp per group row: maximum, sum
 // of exp2, then the cell sums, accumulated per warp in shared memory in a fixed order (deterministic).
 #include "mma_sync.cuh"
 
 namespace psa {
+bool antidiag_tc_supported(int64_t seq, int head_dim, int stride, int dtype);
+int launch_antidiag_logits_tc(const void* q, const void* k, float* logits, int64_t bh, int64_t seq, int head_dim, int stride, int n,
+                              int n_valid, int causal, float scale_log2, int dtype, int32_t* status, cudaStream_t st);
 namespace {
 
 constexpr int kTile = 128;       // groups per CTA tile, both ways
@@ -205,8 +209,16 @@ extern "C" size_t psa_antidiag_scratch_bytes(int64_t bh, int64_t seq, int head_d
 extern "C" int psa_antidiag_scores(const void* q, const void* k, void* out, void* scratch, size_t scratch_bytes, int64_t bh,
                                    int64_t seq, int head_dim, int block_size, int stride, int chunk_size, int causal, int dtype,
                                    void* stream) {
+  return psa_antidiag_scores_impl(q, k, out, scratch, scratch_bytes, bh, seq, head_dim, block_size, stride, chunk_size, causal, dtype,
+                                  0, nullptr, stream);
+}
+
+extern "C" int psa_antidiag_scores_impl(const void* q, const void* k, void* out, void* scratch, size_t scratch_bytes, int64_t bh,
+                                        int64_t seq, int head_dim, int block_size, int stride, int chunk_size, int causal, int dtype,
+                                        int impl, int32_t* status, void* stream) {
   using namespace psa;
   PSA_REQUIRE(q && k && out && scratch, PSA_ERR_ARG, "psa_antidiag_scores: null pointer");
+  PSA_REQUIRE(impl == 0 || impl == 2 || impl == 3, PSA_ERR_ARG, "psa_antidiag_scores: impl=%d (0 pick, 2 tcgen05, 3 mma.sync)", impl);
   PSA_REQUIRE(bh > 0 && bh < 65536, PSA_ERR_ARG, "psa_antidiag_scores: bh=%lld out of range", (long long)bh);
   PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "psa_antidiag_scores: f16/bf16 only");
   PSA_REQUIRE((((uintptr_t)q | (uintptr_t)k | (uintptr_t)scratch) & 15) == 0, PSA_ERR_ARG,
@@ -225,13 +237,26 @@ extern "C" int psa_antidiag_scores(const void* q, const void* k, void* out, void
   dim3 grid((unsigned)col_tiles, (unsigned)row_tiles, (unsigned)bh);
   const size_t smem = (size_t)8 * (d.n / d.rb) * sizeof(float);
   dim3 grid2((unsigned)d.nb, (unsigned)bh);
+  const bool tc_ok = antidiag_tc_supported(seq, head_dim, stride, dtype);
+  PSA_REQUIRE(impl != 2 || tc_ok, PSA_ERR_UNSUPPORTED,
+              "psa_antidiag_scores: the tcgen05 kernel needs a length that is a multiple of the stride (seq=%lld, stride=%d)",
+              (long long)seq, stride);
+  const bool use_tc = tc_ok && impl != 3;
+  if (use_tc) {
+    rc = launch_antidiag_logits_tc(q, k, (float*)scratch, bh, seq, head_dim, stride, d.n, d.n_valid, p.causal, p.scale_log2, dtype, status, st);
+    if (rc != PSA_OK) return rc;
+  }
   if (dtype == PSA_F16) {
-    antidiag_logits_kernel<__half><<<grid, 256, 0, st>>>((const __half*)q, (const __half*)k, (float*)scratch, p);
-    PSA_CHECK_LAUNCH("psa_antidiag_scores(logits)");
+    if (!use_tc) {
+      antidiag_logits_kernel<__half><<<grid, 256, 0, st>>>((const __half*)q, (const __half*)k, (float*)scratch, p);
+      PSA_CHECK_LAUNCH("psa_antidiag_scores(logits)");
+    }
     antidiag_softmax_cells_kernel<__half><<<grid2, 256, smem, st>>>((const float*)scratch, (__half*)out, d.n, d.n_valid, d.rb, d.nb, p.causal);
   } else {
-    antidiag_logits_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (float*)scratch, p);
-    PSA_CHECK_LAUNCH("psa_antidiag_scores(logits)");
+    if (!use_tc) {
+      antidiag_logits_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (float*)scratch, p);
+      PSA_CHECK_LAUNCH("psa_antidiag_scores(logits)");
+    }
     antidiag_softmax_cells_kernel<__nv_bfloat16><<<grid2, 256, smem, st>>>((const float*)scratch, (__nv_bfloat16*)out, d.n, d.n_valid, d.rb,
                                                                             d.nb, p.causal);
   }

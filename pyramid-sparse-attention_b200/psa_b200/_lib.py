@@ -45,6 +45,7 @@ SIGNATURES = {
     "psa_block_scores_tm_rope": (_i, [_p] * 5 + [_i64] + [_p] * 4 + [_sz, _i, _i64, _i, _i, _i, _i, _p]),
     "psa_antidiag_scratch_bytes": (_sz, [_i64, _i64, _i, _i, _i, _i]),
     "psa_antidiag_scores": (_i, [_p, _p, _p, _p, _sz, _i64, _i64, _i, _i, _i, _i, _i, _i, _p]),
+    "psa_antidiag_scores_impl": (_i, [_p, _p, _p, _p, _sz, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _p, _p]),
     "psa_assign_levels_causal": (_i, [_p, _p, _i64, _i, _i, _i, _i, _i, _p, _p, _p, _p, _p, _i, _p]),
     "psa_legacy_index_bytes": (_sz, [_i64, _i64]),
     "psa_legacy_fwd_images": (_i, [_p] * 7 + [_i64, _i64, _i, _i, _f, _i, _i, _p, _p]),

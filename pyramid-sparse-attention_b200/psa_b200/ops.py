@@ -394,9 +394,11 @@ def assign_levels(po: torch.Tensor, mask_ratios: Dict[int, Tuple[float, float]],
     return mask
 
 
-def antidiag_block_scores(q, k, block_size: int, stride: int, chunk_size: int, causal: bool = True) -> torch.Tensor:
+def antidiag_block_scores(q, k, block_size: int, stride: int, chunk_size: int, causal: bool = True,
+                          impl: int = 0) -> torch.Tensor:
     """Antidiagonal block-importance estimate [B, H, nb, nb] (q.dtype), nb = ceil(L/block_size): estimate_block_importance
-    with select_mode='inverse' (qwen2.5-vl-example/src/attention/PSA_casual/utils/block_importance.py:282-562)."""
+    with select_mode='inverse' (qwen2.5-vl-example/src/attention/PSA_casual/utils/block_importance.py:282-562).
+    impl: 0 pick (tcgen05 GEMM when L is a multiple of stride), IMPL_TENSOR, IMPL_WARP_MMA."""
     _need_cuda(q, k)
     q, k = _flat_bh(q), _flat_bh(k)
     B, H, L, D = q.shape
@@ -409,9 +411,11 @@ def antidiag_block_scores(q, k, block_size: int, stride: int, chunk_size: int, c
     with torch.cuda.device(q.device):
         out = torch.empty((B, H, nb, nb), dtype=q.dtype, device=q.device)
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
-        rc = lib.psa_antidiag_scores(_ptr(q), _ptr(k), _ptr(out), _ptr(scratch), nbytes, B * H, L, D, block_size, stride,
-                                     chunk_size, int(causal), _dt(q), _stream(q))
+        status = status_word(q.device)
+        rc = lib.psa_antidiag_scores_impl(_ptr(q), _ptr(k), _ptr(out), _ptr(scratch), nbytes, B * H, L, D, block_size, stride,
+                                          chunk_size, int(causal), _dt(q), impl, _ptr(status), _stream(q))
     check(rc, "psa_antidiag_scores")
+    out._psa_status = status
     return out
 
 

@@ -76,6 +76,45 @@ def test_antidiagonal_estimate_vs_oracle(P, golden_causal, case, dt):
     assert float((got.sum(-1) - rows).abs().max()) <= 0.05 * rb
 
 
+TC_CASES = [  # L (a multiple of the stride), D, H, block, stride, chunk, causal
+    (1024, 128, 2, 128, 16, 1024, True),       # one chunk, n = 64 groups: a single partial tile
+    (1008, 64, 2, 128, 16, 1024, True),        # 63 valid groups of 64: the last group row is padding
+    (4096 + 512, 128, 1, 128, 8, 4096, True),  # two chunks, 576 valid of 1024 groups, 5 row tiles, K = 1024
+    (2304, 64, 3, 128, 16, 1024, False),       # not causal: every column tile of the padded length
+    (3072, 128, 1, 64, 16, 1024, True),        # 4 groups per block
+]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "fp16"])
+@pytest.mark.parametrize("case", TC_CASES, ids=lambda c: f"L{c[0]}_d{c[1]}_s{c[4]}_{'c' if c[6] else 'n'}")
+def test_antidiagonal_estimate_tcgen05_vs_oracle_and_warp_mma(P, case, dt):
+    """The tcgen05 GEMM (TMA boxes over a 4-D view of q and k) against the oracle on the same 16-bit inputs, and against
+    the warp-level mma.sync kernel: both accumulate the same products in fp32, so the rounded masses may differ by one
+    unit in the last place of the 16-bit result at most."""
+    L, D, H, block, stride, chunk, causal = case
+    q, k, _ = C.qkv(510, 1, H, L, D, C.DT[dt])
+    qd, kd = q.to(DEV), k.to(DEV)
+    tc = P.ops.antidiag_block_scores(qd, kd, block, stride, chunk, causal, impl=P.ops.IMPL_TENSOR)
+    assert int(tc._psa_status.item()) == 0
+    mma = P.ops.antidiag_block_scores(qd, kd, block, stride, chunk, causal, impl=P.ops.IMPL_WARP_MMA)
+    auto = P.ops.antidiag_block_scores(qd, kd, block, stride, chunk, causal)
+    assert torch.equal(auto, tc)                                   # a length that divides picks the tcgen05 kernel
+    ref = O.antidiag_block_scores(q, k, block, stride, causal, chunk)
+    rb = block // stride
+    got = tc.float().cpu().double()
+    assert got.shape == ref.shape
+    assert float((got - ref).abs().max()) <= rb * 2.0 ** -8
+    ulp = 2.0 ** -8 if dt == "bf16" else 2.0 ** -11
+    assert float((got - mma.float().cpu().double()).abs().max()) <= rb * ulp
+    assert torch.equal(P.ops.antidiag_block_scores(qd, kd, block, stride, chunk, causal, impl=P.ops.IMPL_TENSOR), tc)   # repeatable
+
+
+def test_antidiagonal_estimate_tcgen05_needs_whole_groups(P):
+    q, k, _ = C.qkv(500, 1, 1, 1000, 64, torch.bfloat16)
+    with pytest.raises(ValueError):
+        P.ops.antidiag_block_scores(q.to(DEV), k.to(DEV), 128, 16, 1024, True, impl=P.ops.IMPL_TENSOR)
+
+
 def test_antidiagonal_estimate_rejects_fp32(P):
     q, k, _ = C.qkv(500, 1, 1, 256, 64, torch.float32)
     with pytest.raises(ValueError):
