@@ -45,7 +45,7 @@ KERNELS_PER_CALL = {
     "psa_assign_levels": 1, "psa_fwd_images": 1, "psa_fwd": 1, "psa_fwd_images_scatter": 1, "psa_push_heads": 1,
     "psa_push_samples": 1, "psa_pull_heads": 1, "psa_density": 1, "psa_legacy_fwd_images": 2, "psa_legacy_bwd_tc": 3,
     "psa_legacy_bwd_tcgen05": 5, "psa_ksim": 1, "psa_ksim_perm": 1, "psa_legacy_fwd_images_perm": 2, "psa_gather_rows": 1,
-    "psa_pyramid_kv_images_perm": 1, "psa_block_scores_perm": 4,
+    "psa_pyramid_kv_images_perm": 1, "psa_block_scores_perm": 4, "psa_antidiag_scores_impl": 2, "psa_assign_levels_causal": 1,
 }
 
 
@@ -445,6 +445,73 @@ def run_preset_layer(args, workload, synthetic):
         "clocks": clocks}))
 
 
+def run_causal_prefill(args, workload, synthetic):
+    """--workload qwen2.5-vl-causal-layer: the causal (vision-language prefill) call site on one GPU - antidiagonal
+    block-importance estimate, causal level mask, similarity cap, legacy causal forward - through the module that mirrors
+    PyramidAdaptiveBlockSparseAttnTrain, with the stages timed one by one as well."""
+    import psa_b200
+    from psa_b200 import ops, _lib
+    from psa_b200.causal import AttentionConfig, PyramidAdaptiveBlockSparseAttnTrain, transfer_attn_to_mask, x_block_imp_estimate
+    assert int(os.environ.get("WORLD_SIZE", "1")) == 1, "this workload runs on one GPU"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    launches = LaunchCounter(_lib.lib)
+    H = args.heads or workload["heads"]
+    D, S = workload["head_dim"], synthetic.seq_len(workload)
+    wl = dict(workload); wl["heads"] = H
+    q, k, v = synthetic.make_qkv(wl, 1000, torch.bfloat16, dev)
+    cfg = AttentionConfig(text_length=0)
+    module = PyramidAdaptiveBlockSparseAttnTrain(cfg, layer_idx=0)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, steps):
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(steps):
+            r = fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps, r
+
+    with torch.no_grad():
+        for _ in range(args.warmup):
+            module(q, k, v)
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        sampler.mark_begin()
+        torch.cuda.profiler.start()
+        launches.on = True
+        ms, _ = timed(lambda: module(q, k, v), args.steps)
+        launches.on = False
+        torch.cuda.profiler.stop()
+        sampler.mark_end()
+        clocks = sampler.stop()
+        est_kw = dict(block_size=cfg.query_block, stride=cfg.xattn_stride, chunk_size=cfg.xattn_chunk_size, causal=True)
+        ms_est, est = timed(lambda: x_block_imp_estimate(q, k, **est_kw), args.steps)
+        ms_mask, mask = timed(lambda: transfer_attn_to_mask(est, cfg.mask_ratios, 0, cfg.mask_mode, block_size=cfg.query_block,
+                                                            causal=True), args.steps)
+    ops.check_status(dev)
+    n = S // cfg.xattn_stride
+    f_est = 2.0 * H * n * n * cfg.xattn_stride * D * 0.5 * (1.0 + 128.0 / n)      # lower triangle of 128x128 tiles
+    f_dense = 4.0 * H * float(S) * S * D * 0.5
+    peaks = load_peaks()
+    print(json.dumps({
+        "metric": "psa_attn_dense_equiv_tflops", "value": f_dense / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload["name"] + (f"-{H}heads" if args.heads else ""), "B": 1, "heads": H, "head_dim": D,
+                   "seq_len": S, "block": 128, "stride": cfg.xattn_stride, "chunk": cfg.xattn_chunk_size, "mask_mode": cfg.mask_mode,
+                   "causal": True, "dense_equiv": "causal triangle: 2*H*S^2*D", "l2": "inputs (q,k,v) larger than L2"},
+        "ms_per_layer": ms, "stage_ms": {"estimate": ms_est, "level_mask": ms_mask},
+        "estimate_gemm_tflops": f_est / (ms_est * 1e-3) / 1e12,
+        "roofline": {"bound": "tensor", "kernel": "antidiag_logits_tc_kernel + antidiag_softmax_cells_kernel (the estimate stage)",
+                     "achieved": f_est / (ms_est * 1e-3) / 1e12, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": f_est / (ms_est * 1e-3) / 1e12 / peaks["bf16_tflops"], "traffic": None,
+                     "peak_source": peaks["source"] + " (burst bf16: a sub-millisecond stage)"},
+        "gpu_launches": launches.count, "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -472,6 +539,8 @@ def main():
         return run_causal_training(args, workload, synthetic)
     if workload["name"] == "wan2.1-1.3b-default-preset":
         return run_preset_layer(args, workload, synthetic)
+    if workload["name"] == "qwen2.5-vl-causal-layer":
+        return run_causal_prefill(args, workload, synthetic)
     if args.heads:
         workload["heads"] = args.heads
         workload["name"] += f"-{args.heads}heads"

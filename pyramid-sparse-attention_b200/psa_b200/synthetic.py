@@ -25,7 +25,9 @@ CAUSAL_TRAIN = dict(name="causal-legacy-fwd-bwd", heads=16, head_dim=128, grid=(
 WAN_1_3B_PRESET = dict(name="wan2.1-1.3b-default-preset", heads=12, head_dim=128, grid=(21, 30, 52), text=0,
                        model="Wan2.1_1.3b", video_shape=(832, 480, 81))
 
-WORKLOADS = {w["name"]: w for w in (WAN_1_3B, WAN_14B, COGVIDEOX_5B, TINY, CAUSAL_TRAIN, WAN_1_3B_PRESET)}
+# the causal (vision-language prefill) call site: 28 query heads x 128 channels as in Qwen2.5-VL-7B, 32768 tokens
+CAUSAL_PREFILL = dict(name="qwen2.5-vl-causal-layer", heads=28, head_dim=128, grid=(8, 64, 64), text=0)
+WORKLOADS = {w["name"]: w for w in (WAN_1_3B, WAN_14B, COGVIDEOX_5B, TINY, CAUSAL_TRAIN, WAN_1_3B_PRESET, CAUSAL_PREFILL)}
 
 
 def structured_field(seed: int, heads: int, head_dim: int, grid, text: int = 0, dtype=torch.bfloat16, device="cpu",
