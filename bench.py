@@ -505,7 +505,7 @@ def run_causal_prefill(args, workload, synthetic):
                    "causal": True, "dense_equiv": "causal triangle: 2*H*S^2*D", "l2": "inputs (q,k,v) larger than L2"},
         "ms_per_layer": ms, "stage_ms": {"estimate": ms_est, "level_mask": ms_mask},
         "estimate_gemm_tflops": f_est / (ms_est * 1e-3) / 1e12,
-        "roofline": {"bound": "tensor", "kernel": "antidiag_logits_tc_kernel + antidiag_softmax_cells_kernel (the estimate stage)",
+        "roofline": {"bound": "tensor", "kernel": "antidiag_logits_tc_kernel + antidiag_combine_kernel (the estimate stage)",
                      "achieved": f_est / (ms_est * 1e-3) / 1e12, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": f_est / (ms_est * 1e-3) / 1e12 / peaks["bf16_tflops"], "traffic": None,
                      "peak_source": peaks["source"] + " (burst bf16: a sub-millisecond stage)"},

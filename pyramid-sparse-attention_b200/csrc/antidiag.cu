@@ -6,18 +6,19 @@
 // channels of a group row is 128 contiguous bytes of one token of q or k.  Then a row softmax (causal: groups j <= i)
 // and the sum of the probabilities over (block/stride x block/stride) cells give the mass per (query block, key block).
 //
-// Kernel 1, tcgen05 (antidiag_tc.cu; lengths that are a multiple of the stride): TMA boxes over a 4-D view of q and k,
-// one accumulator tile per 128x128 logits in TMEM.  Kernel 1, warp-level mma.sync (this file; any length): 128x128 logit
-// tiles, 8 warps of 32x64, K streamed in chunks of 64 through registers into padded shared-memory tiles.  Both write the
-// logits as fp32, already multiplied by log2(e)/sqrt(D)/stride, and skip the tiles above the diagonal when causal.
+// Lengths that are a multiple of the stride take the tcgen05 route (antidiag_tc.cu: GEMM with a partial softmax in its
+// epilogue + a combine kernel, no logits in HBM).  Other lengths run the two kernels of this file:
+// Kernel 1, warp-level mma.sync: 128x128 logit
+// tiles, 8 warps of 32x64, K streamed in chunks of 64 through registers into padded shared-memory tiles; it writes the
+// logits as fp32, already multiplied by log2(e)/sqrt(D)/stride, and skips the tiles above the diagonal when causal.
 // Kernel 2 (HBM-bound: reads the logits once per pass): one CTA per query block, a warp per group row: maximum, sum
 // of exp2, then the cell sums, accumulated per warp in shared memory in a fixed order (deterministic).
 #include "mma_sync.cuh"
 
 namespace psa {
-bool antidiag_tc_supported(int64_t seq, int head_dim, int stride, int dtype);
-int launch_antidiag_logits_tc(const void* q, const void* k, float* logits, int64_t bh, int64_t seq, int head_dim, int stride, int n,
-                              int n_valid, int causal, float scale_log2, int dtype, int32_t* status, cudaStream_t st);
+bool antidiag_tc_supported(int64_t seq, int head_dim, int stride, int n, int dtype);
+int launch_antidiag_tc(const void* q, const void* k, void* out, float* scratch, int64_t bh, int64_t seq, int head_dim, int stride, int n,
+                       int n_valid, int rb, int nb, int causal, float scale_log2, int dtype, int32_t* status, cudaStream_t st);
 namespace {
 
 constexpr int kTile = 128;       // groups per CTA tile, both ways
@@ -200,10 +201,19 @@ int make_dims(AdDims& d, int64_t seq, int head_dim, int block_size, int stride, 
 }  // namespace
 }  // namespace psa
 
+// bytes either route needs: the fp32 logits (mma.sync route), or per row one maximum per column tile and one sum per key
+// block of whole tiles (tcgen05 route)
+static size_t antidiag_scratch_need(int64_t bh, const psa::AdDims& d) {
+  const size_t logits = (size_t)bh * d.n * d.n * sizeof(float);
+  const size_t tiles = (size_t)(d.n + 127) / 128;
+  const size_t partial = (size_t)bh * d.n * tiles * (1 + 128 / d.rb) * sizeof(float);
+  return logits > partial ? logits : partial;
+}
+
 extern "C" size_t psa_antidiag_scratch_bytes(int64_t bh, int64_t seq, int head_dim, int block_size, int stride, int chunk_size) {
   psa::AdDims d;
   if (bh <= 0 || psa::make_dims(d, seq, head_dim, block_size, stride, chunk_size) != PSA_OK) return 0;
-  return (size_t)bh * d.n * d.n * sizeof(float);
+  return antidiag_scratch_need(bh, d);
 }
 
 extern "C" int psa_antidiag_scores(const void* q, const void* k, void* out, void* scratch, size_t scratch_bytes, int64_t bh,
@@ -226,7 +236,7 @@ extern "C" int psa_antidiag_scores_impl(const void* q, const void* k, void* out,
   AdDims d;
   int rc = make_dims(d, seq, head_dim, block_size, stride, chunk_size);
   if (rc != PSA_OK) return rc;
-  PSA_REQUIRE(scratch_bytes >= (size_t)bh * d.n * d.n * sizeof(float), PSA_ERR_ARG, "psa_antidiag_scores: scratch too small (%zu bytes)",
+  PSA_REQUIRE(scratch_bytes >= antidiag_scratch_need(bh, d), PSA_ERR_ARG, "psa_antidiag_scores: scratch too small (%zu bytes)",
               scratch_bytes);
   AdParams p;
   p.seq = seq; p.n = d.n; p.stride = stride; p.D = head_dim; p.causal = causal ? 1 : 0;
@@ -237,26 +247,21 @@ extern "C" int psa_antidiag_scores_impl(const void* q, const void* k, void* out,
   dim3 grid((unsigned)col_tiles, (unsigned)row_tiles, (unsigned)bh);
   const size_t smem = (size_t)8 * (d.n / d.rb) * sizeof(float);
   dim3 grid2((unsigned)d.nb, (unsigned)bh);
-  const bool tc_ok = antidiag_tc_supported(seq, head_dim, stride, dtype);
+  const bool tc_ok = antidiag_tc_supported(seq, head_dim, stride, d.n, dtype);
   PSA_REQUIRE(impl != 2 || tc_ok, PSA_ERR_UNSUPPORTED,
               "psa_antidiag_scores: the tcgen05 kernel needs a length that is a multiple of the stride (seq=%lld, stride=%d)",
               (long long)seq, stride);
   const bool use_tc = tc_ok && impl != 3;
-  if (use_tc) {
-    rc = launch_antidiag_logits_tc(q, k, (float*)scratch, bh, seq, head_dim, stride, d.n, d.n_valid, p.causal, p.scale_log2, dtype, status, st);
-    if (rc != PSA_OK) return rc;
-  }
+  if (use_tc)      // GEMM with a partial softmax in its epilogue, then a small combine kernel: no logits in HBM
+    return launch_antidiag_tc(q, k, out, (float*)scratch, bh, seq, head_dim, stride, d.n, d.n_valid, d.rb, d.nb, p.causal, p.scale_log2,
+                              dtype, status, st);
   if (dtype == PSA_F16) {
-    if (!use_tc) {
-      antidiag_logits_kernel<__half><<<grid, 256, 0, st>>>((const __half*)q, (const __half*)k, (float*)scratch, p);
-      PSA_CHECK_LAUNCH("psa_antidiag_scores(logits)");
-    }
+    antidiag_logits_kernel<__half><<<grid, 256, 0, st>>>((const __half*)q, (const __half*)k, (float*)scratch, p);
+    PSA_CHECK_LAUNCH("psa_antidiag_scores(logits)");
     antidiag_softmax_cells_kernel<__half><<<grid2, 256, smem, st>>>((const float*)scratch, (__half*)out, d.n, d.n_valid, d.rb, d.nb, p.causal);
   } else {
-    if (!use_tc) {
-      antidiag_logits_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (float*)scratch, p);
-      PSA_CHECK_LAUNCH("psa_antidiag_scores(logits)");
-    }
+    antidiag_logits_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (float*)scratch, p);
+    PSA_CHECK_LAUNCH("psa_antidiag_scores(logits)");
     antidiag_softmax_cells_kernel<__nv_bfloat16><<<grid2, 256, smem, st>>>((const float*)scratch, (__nv_bfloat16*)out, d.n, d.n_valid, d.rb,
                                                                             d.nb, p.causal);
   }

@@ -1,6 +1,7 @@
-// Antidiagonal logits of the causal call site on tcgen05 tensor cores (f16/bf16, lengths that are a multiple of the
-// stride).  Replaces the GEMM half of flat_group_gemm_fuse_reshape
-// (qwen2.5-vl-example/src/attention/PSA_casual/kernels/block_importance_kernels.py:255-323).
+// Antidiagonal block-importance estimate of the causal call site on tcgen05 tensor cores (f16/bf16, lengths that are a
+// multiple of the stride).  Replaces flat_group_gemm_fuse_reshape and softmax_fuse_block_sum
+// (qwen2.5-vl-example/src/attention/PSA_casual/kernels/block_importance_kernels.py:255-323, 6-192); the fp32 logits
+// never reach HBM.
 //
 // logit(i, j) = sum_s q[i*stride + stride-1-s] . k[j*stride + s]: one GEMM of the two [n, stride*D] group matrices.
 // Neither matrix is materialised: q and k are described to TMA as 4-D tensors {channel, token in group, group,
@@ -11,8 +12,12 @@
 // Persistent CTAs (one per SM) walk the 128x128 logit tiles (tiles above the diagonal are skipped when causal):
 //   warp 0   producer: per K-chunk two boxes (A, B) into a 4-stage ring (32 KB per stage)
 //   warp 1   MMA issuer: stride*D/16 tcgen05.mma (M = N = 128, K = 16) per tile into one of two TMEM accumulators
-//   warps 2-5 epilogue (thread = row): accumulator -> registers -> * log2(e)/sqrt(D)/stride -> fp32 logits, while the
-//            issuer already works on the next tile's accumulator
+//   warps 2-5 epilogue (thread = group row): the 128 logits of the row go to registers (the accumulator is released at
+//            once, so the issuer already works on the next tile), then the row's maximum over the tile's visible columns
+//            and, per key block (block/stride columns), the sum of exp2(logit - maximum): a partial softmax.
+// antidiag_combine_kernel then merges the partial results of a row (its maximum over all tiles, the normaliser, the
+// rescaled block sums) and adds the rows of a query block: the softmax mass per (query block, key block).
+// Per row the first kernel writes n/128 maxima and n/(block/stride) sums instead of n logits.
 // Tensor-bound: 2*BH*n^2*stride*D flops (half when causal).  Every mbarrier wait is bounded; on expiry the CTA sets the
 // abort flag, lets copies in flight land, frees its TMEM and returns PSA_ERR_TIMEOUT through the status word.
 #include <cmath>
@@ -36,8 +41,11 @@ struct Ctrl {
 };
 
 struct Params {
-  float* logits;       // [bh][n][n]
-  int n;               // groups of the padded length (row pitch of the logits)
+  float* tile_max;     // [bh][n][n / 128]: maximum of the row's visible logits inside a column tile
+  float* block_sum;    // [bh][n][col_tiles * 128 / rb]: sum of exp2(logit - that maximum) over a key block's columns
+  int n;               // groups of the padded length
+  int n_valid;         // groups that hold a valid query token
+  int rb;              // groups per block (power of two, 2..32)
   int row_tiles;       // tiles that hold a valid query group
   int col_tiles;       // non-causal: tiles per row
   int stride;
@@ -46,6 +54,12 @@ struct Params {
   float scale_log2;
   int32_t* status;
 };
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
   asm volatile(
@@ -161,24 +175,60 @@ __global__ void __launch_bounds__(kThreads, 1) antidiag_logits_tc_kernel(const _
       if (!ok) break;
       tc::tc_fence_after();
       const int row = it * 128 + r;
-      float* out = p.logits + ((int64_t)bh * p.n + row) * p.n + (int64_t)jt * 128;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t v[32];
-        tc::tmem_ld32(tmem + b * 128 + lane_base + c0, v);
-        tc::tmem_wait_ld();
-        if (row < p.n) {
+      uint32_t v[4][32];
+      tc::tmem_ld32(tmem + b * 128 + lane_base, v[0]);
+      tc::tmem_ld32(tmem + b * 128 + lane_base + 32, v[1]);
+      tc::tmem_ld32(tmem + b * 128 + lane_base + 64, v[2]);
+      tc::tmem_ld32(tmem + b * 128 + lane_base + 96, v[3]);
+      tc::tmem_wait_ld();
+      tc::tc_fence_before();
+      tc::mbar_arrive(&ctl->acc_empty[b]);          // the accumulator may be overwritten: the row lives in registers now
+      if (row >= p.n_valid) continue;               // group rows without a valid query token contribute nothing
+      // visible columns: all of the tile, or (causal, diagonal tile) those up to the row's own group
+      int last = (p.causal && jt == it) ? r : 127;
+      if (jt * 128 + last >= p.n) last = p.n - 1 - jt * 128;      // columns past the padded length do not exist
+      float m = -INFINITY;
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            if (jt * 128 + c0 + i < p.n)            // n is a multiple of 4 (block/stride >= 2 and whole chunks)
-              *reinterpret_cast<float4*>(out + c0 + i) =
-                  make_float4(__uint_as_float(v[i]) * p.scale_log2, __uint_as_float(v[i + 1]) * p.scale_log2,
-                              __uint_as_float(v[i + 2]) * p.scale_log2, __uint_as_float(v[i + 3]) * p.scale_log2);
-          }
+      for (int c = 0; c < 128; ++c)
+        if (c <= last) m = fmaxf(m, __uint_as_float(v[c >> 5][c & 31]));
+      m *= p.scale_log2;                            // the scale is positive
+      const int nbt = 128 / p.rb;                   // key blocks per tile: 4 .. 64
+      const int64_t rowi = (int64_t)bh * p.n + row;
+      p.tile_max[rowi * p.col_tiles + jt] = m;
+      float* sums = p.block_sum + rowi * ((int64_t)p.col_tiles * nbt) + (int64_t)jt * nbt;
+      // sums of groups of 2 columns first, then merged up to the block width (a power of two)
+      float part[64];
+#pragma unroll
+      for (int c = 0; c < 128; c += 2) {
+        const float e0 = c <= last ? ex2(fmaf(__uint_as_float(v[c >> 5][c & 31]), p.scale_log2, -m)) : 0.f;
+        const float e1 = c + 1 <= last ? ex2(fmaf(__uint_as_float(v[(c + 1) >> 5][(c + 1) & 31]), p.scale_log2, -m)) : 0.f;
+        part[c >> 1] = e0 + e1;
+      }
+      if (p.rb == 2) {
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) *reinterpret_cast<float4*>(sums + i) = make_float4(part[i], part[i + 1], part[i + 2], part[i + 3]);
+      } else if (p.rb == 4) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          *reinterpret_cast<float4*>(sums + i) = make_float4(part[2 * i] + part[2 * i + 1], part[2 * i + 2] + part[2 * i + 3],
+                                                              part[2 * i + 4] + part[2 * i + 5], part[2 * i + 6] + part[2 * i + 7]);
+      } else {
+        float q4[16];                               // sums of 8 columns
+#pragma unroll
+        for (int i = 0; i < 16; ++i) q4[i] = (part[4 * i] + part[4 * i + 1]) + (part[4 * i + 2] + part[4 * i + 3]);
+        if (p.rb == 8) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 4) *reinterpret_cast<float4*>(sums + i) = make_float4(q4[i], q4[i + 1], q4[i + 2], q4[i + 3]);
+        } else if (p.rb == 16) {
+#pragma unroll
+          for (int i = 0; i < 8; i += 4)
+            *reinterpret_cast<float4*>(sums + i) = make_float4(q4[2 * i] + q4[2 * i + 1], q4[2 * i + 2] + q4[2 * i + 3],
+                                                                q4[2 * i + 4] + q4[2 * i + 5], q4[2 * i + 6] + q4[2 * i + 7]);
+        } else {
+          *reinterpret_cast<float4*>(sums) = make_float4((q4[0] + q4[1]) + (q4[2] + q4[3]), (q4[4] + q4[5]) + (q4[6] + q4[7]),
+                                                          (q4[8] + q4[9]) + (q4[10] + q4[11]), (q4[12] + q4[13]) + (q4[14] + q4[15]));
         }
       }
-      tc::tc_fence_before();
-      tc::mbar_arrive(&ctl->acc_empty[b]);
     }
   }
 
@@ -193,6 +243,48 @@ __global__ void __launch_bounds__(kThreads, 1) antidiag_logits_tc_kernel(const _
     __syncwarp();
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem, 256);
+  }
+}
+
+// One CTA per query block (rb group rows), a warp per row: the row's maximum over its column tiles, its normaliser,
+// then the rescaled block sums, accumulated per warp in shared memory in a fixed order (deterministic) and added up.
+// part: [8 warps][n / rb] floats.
+template <int FMT>
+__global__ void __launch_bounds__(256) antidiag_combine_kernel(const float* __restrict__ tile_max, const float* __restrict__ block_sum,
+                                                              uint16_t* __restrict__ out, int n, int n_valid, int rb, int nb, int causal) {
+  extern __shared__ float part[];
+  const int qb = blockIdx.x;
+  const int64_t bh = blockIdx.y;
+  const int nkb = n / rb, tiles = (n + 127) / 128, nbt = 128 / rb;
+  const int pitch = tiles * nbt;                       // row pitch of block_sum (whole tiles)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int e = threadIdx.x; e < 8 * nkb; e += blockDim.x) part[e] = 0.f;
+  __syncthreads();
+  float* mine = part + warp * nkb;
+  for (int r = warp; r < rb; r += 8) {
+    const int i = qb * rb + r;
+    if (i >= n_valid) continue;
+    const int nt = causal ? i / 128 + 1 : tiles;        // column tiles the row has
+    const int nblk = causal ? i / rb + 1 : nkb;         // key blocks with a visible column
+    const float* tm = tile_max + (bh * n + i) * (int64_t)tiles;
+    const float* bs = block_sum + (bh * n + i) * (int64_t)pitch;
+    float m = -INFINITY;
+    for (int j = lane; j < nt; j += 32) m = fmaxf(m, tm[j]);
+    for (int off = 16; off; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    float l = 0.f;
+    for (int b = lane; b < nblk; b += 32) l += bs[b] * ex2(tm[b / nbt] - m);
+    for (int off = 16; off; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+    const float inv = 1.0f / l;
+    for (int b = lane; b < nblk; b += 32) mine[b] += bs[b] * ex2(tm[b / nbt] - m) * inv;
+    __syncwarp();
+  }
+  __syncthreads();
+  uint16_t* dst = out + (bh * nb + qb) * (int64_t)nb;
+  for (int c = threadIdx.x; c < nb; c += blockDim.x) {
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) sum += part[w * nkb + c];
+    dst[c] = FMT ? __bfloat16_as_ushort(__float2bfloat16_rn(sum)) : __half_as_ushort(__float2half_rn(sum));
   }
 }
 
@@ -223,15 +315,17 @@ int encode_groups_4d(CUtensorMap* map, const void* base, int is_bf16, int D, int
 }
 
 template <int D, int FMT>
-int launch(const void* q, const void* k, float* logits, int64_t bh, int64_t seq, int stride, int n, int n_valid, int causal,
-           float scale_log2, int32_t* status, cudaStream_t st) {
+int launch(const void* q, const void* k, void* out, float* scratch, int64_t bh, int64_t seq, int stride, int n, int n_valid, int rb,
+           int nb, int causal, float scale_log2, int32_t* status, cudaStream_t st) {
   CUtensorMap tq, tk;
   int rc = encode_groups_4d(&tq, q, FMT, D, stride, seq, bh);
   if (rc != PSA_OK) return rc;
   rc = encode_groups_4d(&tk, k, FMT, D, stride, seq, bh);
   if (rc != PSA_OK) return rc;
   Params p;
-  p.logits = logits; p.n = n; p.stride = stride; p.causal = causal; p.bh = bh; p.scale_log2 = scale_log2; p.status = status;
+  p.tile_max = scratch;
+  p.block_sum = scratch + (size_t)bh * n * ((n + 127) / 128);
+  p.n = n; p.n_valid = n_valid; p.rb = rb; p.stride = stride; p.causal = causal; p.bh = bh; p.scale_log2 = scale_log2; p.status = status;
   p.row_tiles = (n_valid + 127) / 128;
   p.col_tiles = (n + 127) / 128;
   const int smem = kStages * kStageBytes + 256 + 1024;
@@ -245,24 +339,31 @@ int launch(const void* q, const void* k, float* logits, int64_t bh, int64_t seq,
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
   antidiag_logits_tc_kernel<D, FMT><<<grid, kThreads, smem, st>>>(tq, tk, p);
   PSA_CHECK_LAUNCH("psa_antidiag_scores(tcgen05 logits)");
+  dim3 grid2((unsigned)nb, (unsigned)bh);
+  antidiag_combine_kernel<FMT><<<grid2, 256, (size_t)8 * (n / rb) * sizeof(float), st>>>(p.tile_max, p.block_sum, (uint16_t*)out, n, n_valid,
+                                                                                         rb, nb, causal);
+  PSA_CHECK_LAUNCH("psa_antidiag_scores(combine)");
   return PSA_OK;
 }
 
 }  // namespace
 
-bool antidiag_tc_supported(int64_t seq, int head_dim, int stride, int dtype) {
+bool antidiag_tc_supported(int64_t seq, int head_dim, int stride, int n, int dtype) {
+  (void)n;
   return (dtype == PSA_F16 || dtype == PSA_BF16) && (head_dim == 64 || head_dim == 128) && stride >= 1 && seq % stride == 0 &&
          seq / stride >= 1;
 }
 
-int launch_antidiag_logits_tc(const void* q, const void* k, float* logits, int64_t bh, int64_t seq, int head_dim, int stride, int n,
-                              int n_valid, int causal, float scale_log2, int dtype, int32_t* status, cudaStream_t st) {
+// Whole estimate: out [bh][nb][nb] in the element type.  scratch: bh * n * ceil(n/128) * (1 + 128/rb) floats (at most
+// bh * n * n for rb >= 2 and n >= 256; the caller's buffer holds bh * n * n).
+int launch_antidiag_tc(const void* q, const void* k, void* out, float* scratch, int64_t bh, int64_t seq, int head_dim, int stride, int n,
+                       int n_valid, int rb, int nb, int causal, float scale_log2, int dtype, int32_t* status, cudaStream_t st) {
   const int fmt = dtype == PSA_BF16;
   if (head_dim == 64)
-    return fmt ? launch<64, 1>(q, k, logits, bh, seq, stride, n, n_valid, causal, scale_log2, status, st)
-               : launch<64, 0>(q, k, logits, bh, seq, stride, n, n_valid, causal, scale_log2, status, st);
-  return fmt ? launch<128, 1>(q, k, logits, bh, seq, stride, n, n_valid, causal, scale_log2, status, st)
-             : launch<128, 0>(q, k, logits, bh, seq, stride, n, n_valid, causal, scale_log2, status, st);
+    return fmt ? launch<64, 1>(q, k, out, scratch, bh, seq, stride, n, n_valid, rb, nb, causal, scale_log2, status, st)
+               : launch<64, 0>(q, k, out, scratch, bh, seq, stride, n, n_valid, rb, nb, causal, scale_log2, status, st);
+  return fmt ? launch<128, 1>(q, k, out, scratch, bh, seq, stride, n, n_valid, rb, nb, causal, scale_log2, status, st)
+             : launch<128, 0>(q, k, out, scratch, bh, seq, stride, n, n_valid, rb, nb, causal, scale_log2, status, st);
 }
 
 }  // namespace psa
