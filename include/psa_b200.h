@@ -216,6 +216,18 @@ int psa_block_scores_tm_rope(const void* q, const void* k, const int32_t* perm, 
                              int64_t rope_first, const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch,
                              size_t scratch_bytes, int heads, int64_t seq, int head_dim, int block_m, int block_n, int dtype,
                              void* stream);
+/* The same for head-major tensors [bh][seq][head_dim] (what the CogVideoX processor holds after its per-head norms,
+ * modify_diffusers.py:357-369): psa_gather_rows / psa_pyramid_kv_images_perm / psa_block_scores_perm with the rows
+ * rotated as they are read.  perm may be NULL (stored order); self-attention (one length, one table pair). */
+int psa_gather_rows_rope(const void* src, const int32_t* perm, const float* rope_a, const float* rope_b, int64_t rope_first,
+                         void* dst, int64_t bh, int64_t seq, int head_dim, int dtype, void* stream);
+int psa_pyramid_kv_images_perm_rope(const void* k, const void* v, const int32_t* perm, const float* rope_a, const float* rope_b,
+                                    int64_t rope_first, void* kimg, void* vimg, int64_t bh, int64_t seq, int head_dim, int block_n,
+                                    int dtype, void* stream);
+int psa_block_scores_perm_rope(const void* q, const void* k, const int32_t* perm, const float* rope_a, const float* rope_b,
+                               int64_t rope_first, const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch,
+                               size_t scratch_bytes, int64_t bh, int64_t seq, int head_dim, int block_m, int block_n, int dtype,
+                               void* stream);
 
 /* Antidiagonal block-importance estimate of the causal (vision-language) call site.  Replaces estimate_block_importance
  * with select_mode "inverse", softmax, kdb 1 - and its Triton kernels flat_group_gemm_fuse_reshape /

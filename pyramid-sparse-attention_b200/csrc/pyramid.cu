@@ -219,6 +219,23 @@ extern "C" int psa_pyramid_kv_images_perm(const void* k, const void* v, const in
   return launch_pyramid_images(ks, vs, kimg, vimg, bh, seq, head_dim, block_n, dtype, 0, (cudaStream_t)stream);
 }
 
+extern "C" int psa_pyramid_kv_images_perm_rope(const void* k, const void* v, const int32_t* perm, const float* rope_a,
+                                               const float* rope_b, int64_t rope_first, void* kimg, void* vimg, int64_t bh, int64_t seq,
+                                               int head_dim, int block_n, int dtype, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(k && v && kimg && vimg && rope_a && rope_b, PSA_ERR_ARG, "psa_pyramid_kv_images_perm_rope: null pointer");
+  PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "psa_pyramid_kv_images_perm_rope: 16-bit element types only");
+  PSA_REQUIRE(seq < ((int64_t)1 << 31) && rope_first >= 0 && rope_first <= seq, PSA_ERR_ARG, "psa_pyramid_kv_images_perm_rope: bad shape");
+  PSA_REQUIRE(psa_kv_image_bytes(bh, seq, head_dim, block_n) > 0, PSA_ERR_ARG,
+              "psa_pyramid_kv_images_perm_rope: needs head_dim 64/128 and block_n a multiple of 64 (got %d, %d)", head_dim, block_n);
+  PSA_REQUIRE((((uintptr_t)k | (uintptr_t)v | (uintptr_t)kimg | (uintptr_t)vimg | (uintptr_t)rope_a | (uintptr_t)rope_b) & 15) == 0,
+              PSA_ERR_ARG, "psa_pyramid_kv_images_perm_rope: k, v, the images and the tables must be 16-byte aligned");
+  RowSource ks = local_rows(k), vs = local_rows(v);
+  ks.perm = vs.perm = perm;      // may be null: stored order
+  const RopeTables rope = {rope_a, rope_b, rope_first, dtype == PSA_BF16};   // applied to the keys only
+  return launch_pyramid_images(ks, vs, kimg, vimg, bh, seq, head_dim, block_n, dtype, 0, (cudaStream_t)stream, rope);
+}
+
 static int pyramid_kv_images_tm(const void* k, const void* v, const int32_t* perm, const float* rope_a, const float* rope_b,
                                 int64_t rope_first, void* kimg, void* vimg, int heads, int64_t seq, int head_dim, int block_n,
                                 int dtype, void* stream) {

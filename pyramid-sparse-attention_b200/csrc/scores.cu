@@ -306,12 +306,11 @@ extern "C" int psa_block_scores_static(const void* q, const void* k, const int32
   return PSA_OK;
 }
 
-extern "C" int psa_block_scores_perm(const void* q, const void* k, const int32_t* perm_q, const int32_t* perm_k,
-                                     const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch, size_t scratch_bytes,
-                                     int64_t bh, int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int dtype,
-                                     void* stream) {
+static int block_scores_perm(const void* q, const void* k, const int32_t* perm_q, const int32_t* perm_k, const psa::RopeTables& rope,
+                             const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch, size_t scratch_bytes, int64_t bh,
+                             int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int dtype, void* stream) {
   using namespace psa;
-  PSA_REQUIRE(q && k && perm_q && perm_k && idx_q && idx_k && po && scratch, PSA_ERR_ARG, "psa_block_scores_perm: null pointer");
+  PSA_REQUIRE(q && k && (rope.a || (perm_q && perm_k)) && idx_q && idx_k && po && scratch, PSA_ERR_ARG, "psa_block_scores_perm: null pointer");
   PSA_REQUIRE(bh > 0 && bh < 65536, PSA_ERR_ARG, "psa_block_scores_perm: bh=%lld out of range", (long long)bh);
   PSA_REQUIRE(dtype == PSA_F16 || dtype == PSA_BF16, PSA_ERR_UNSUPPORTED, "psa_block_scores_perm: f16/bf16 only");
   PSA_REQUIRE(((uintptr_t)scratch & 255) == 0 && (((uintptr_t)q | (uintptr_t)k) & 15) == 0, PSA_ERR_ARG,
@@ -326,8 +325,28 @@ extern "C" int psa_block_scores_perm(const void* q, const void* k, const int32_t
   qs.perm = perm_q;
   ks.perm = perm_k;
   cudaStream_t st = (cudaStream_t)stream;
-  if (dtype == PSA_F16) return launch_scores<__half>(qs, ks, idx_q, idx_k, po, scratch, d, bh, 2, st);
-  return launch_scores<__nv_bfloat16>(qs, ks, idx_q, idx_k, po, scratch, d, bh, 2, st);
+  if (dtype == PSA_F16) return launch_scores<__half>(qs, ks, idx_q, idx_k, po, scratch, d, bh, 2, st, rope);
+  return launch_scores<__nv_bfloat16>(qs, ks, idx_q, idx_k, po, scratch, d, bh, 2, st, rope);
+}
+
+extern "C" int psa_block_scores_perm(const void* q, const void* k, const int32_t* perm_q, const int32_t* perm_k,
+                                     const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch, size_t scratch_bytes,
+                                     int64_t bh, int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int dtype,
+                                     void* stream) {
+  return block_scores_perm(q, k, perm_q, perm_k, psa::RopeTables{}, idx_q, idx_k, po, scratch, scratch_bytes, bh, seq_q, seq_k, head_dim,
+                           block_m, block_n, dtype, stream);
+}
+
+extern "C" int psa_block_scores_perm_rope(const void* q, const void* k, const int32_t* perm, const float* rope_a, const float* rope_b,
+                                          int64_t rope_first, const int32_t* idx_q, const int32_t* idx_k, void* po, void* scratch,
+                                          size_t scratch_bytes, int64_t bh, int64_t seq, int head_dim, int block_m, int block_n,
+                                          int dtype, void* stream) {
+  using namespace psa;
+  PSA_REQUIRE(rope_a && rope_b && rope_first >= 0 && rope_first <= seq, PSA_ERR_ARG, "psa_block_scores_perm_rope: bad rotary tables");
+  PSA_REQUIRE((((uintptr_t)rope_a | (uintptr_t)rope_b) & 15) == 0, PSA_ERR_ARG, "psa_block_scores_perm_rope: tables must be 16-byte aligned");
+  const RopeTables rope = {rope_a, rope_b, rope_first, dtype == PSA_BF16};
+  return block_scores_perm(q, k, perm, perm, rope, idx_q, idx_k, po, scratch, scratch_bytes, bh, seq, seq, head_dim, block_m, block_n,
+                           dtype, stream);
 }
 
 static int block_scores_tm(const void* q, const void* k, const int32_t* perm, const float* rope_a, const float* rope_b,

@@ -43,6 +43,9 @@ SIGNATURES = {
     "psa_gather_heads_rope": (_i, [_p, _p, _p, _p, _i64, _p, _i, _i64, _i, _i, _p]),
     "psa_pyramid_kv_images_tm_rope": (_i, [_p] * 5 + [_i64, _p, _p, _i, _i64, _i, _i, _i, _p]),
     "psa_block_scores_tm_rope": (_i, [_p] * 5 + [_i64] + [_p] * 4 + [_sz, _i, _i64, _i, _i, _i, _i, _p]),
+    "psa_gather_rows_rope": (_i, [_p, _p, _p, _p, _i64, _p, _i64, _i64, _i, _i, _p]),
+    "psa_pyramid_kv_images_perm_rope": (_i, [_p] * 5 + [_i64, _p, _p, _i64, _i64, _i, _i, _i, _p]),
+    "psa_block_scores_perm_rope": (_i, [_p] * 5 + [_i64] + [_p] * 4 + [_sz, _i64, _i64, _i, _i, _i, _i, _p]),
     "psa_antidiag_scratch_bytes": (_sz, [_i64, _i64, _i, _i, _i, _i]),
     "psa_antidiag_scores": (_i, [_p, _p, _p, _p, _sz, _i64, _i64, _i, _i, _i, _i, _i, _i, _p]),
     "psa_antidiag_scores_impl": (_i, [_p, _p, _p, _p, _sz, _i64, _i64, _i, _i, _i, _i, _i, _i, _i, _p, _p]),

@@ -49,12 +49,13 @@ class PSAConfig:
                     f"Got block_n={self.block_n}.")
 
 
-def compute_block_mask(q, k, config, text_length: int = 0, idx_q=None, idx_k=None, perm=None):
+def compute_block_mask(q, k, config, text_length: int = 0, idx_q=None, idx_k=None, perm=None, rope=None):
     """Scores -> level mask (-> similarity cap), the no-grad half of PSAAttention.forward
     (src/psa_triton/attention.py:178-223, 276-299).  Returns (mask, scores, sim_mask).
     The sample offsets are drawn from torch's generator of q's device, Q first and K second, exactly as
     the reference does; tests may pass them in instead.  perm (int32 [S]): the mask of q[..., perm, :],
-    k[..., perm, :] with the rows read in place."""
+    k[..., perm, :] with the rows read in place.  rope (ops.RotaryTables; no similarity cap): q and k are given
+    unrotated and the sampled rows are rotated as they are gathered."""
     B, H = q.shape[0], q.shape[1]
     sim = None
     if config.use_sim_mask:
@@ -64,7 +65,8 @@ def compute_block_mask(q, k, config, text_length: int = 0, idx_q=None, idx_k=Non
         idx_q = ops.draw_sample_indices(B, H, config.block_m, config.block_m // 4, q.device)
     if idx_k is None:
         idx_k = ops.draw_sample_indices(B, H, config.block_n, config.block_n // 4, q.device)
-    po = ops.block_scores(q, k, idx_q, idx_k, config.block_m, config.block_n, perm_q=perm, perm_k=perm)
+    assert rope is None or not config.use_sim_mask, "the similarity cap reads unrotated keys"
+    po = ops.block_scores(q, k, idx_q, idx_k, config.block_m, config.block_n, perm_q=perm, perm_k=perm, rope=rope)
     if config.attn_impl == "old_mask_type":
         mode = config.mask_mode
     else:

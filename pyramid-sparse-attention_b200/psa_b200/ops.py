@@ -108,23 +108,30 @@ def _perm32(perm: torch.Tensor, seq: int) -> torch.Tensor:
     return perm.contiguous()
 
 
-def gather_rows(x: torch.Tensor, perm: torch.Tensor) -> torch.Tensor:
+def gather_rows(x: torch.Tensor, perm: Optional[torch.Tensor], rope=None) -> torch.Tensor:
     """x[..., perm, :] for [B,H,S,D] tensors (the q copy of a reordered layer; GilbertRearranger.rearrange_single,
-    src/psa_triton/utils/rearranger.py:97-115, with the text move folded into perm)."""
-    _need_cuda(x, perm)
+    src/psa_triton/utils/rearranger.py:97-115, with the text move folded into perm).  rope (RotaryTables): the rows are
+    rotated on the way (16-bit tensors); perm may then be None (stored order)."""
+    _need_cuda(x)
     x = _flat_bh(x)
     B, H, S, D = x.shape
-    perm = _perm32(perm, S)
+    perm = None if perm is None else _perm32(perm, S)
     with torch.cuda.device(x.device):
         out = torch.empty_like(x)
-        rc = lib.psa_gather_rows(_ptr(x), _ptr(perm), _ptr(out), B * H, S, D, x.element_size(), _stream(x))
+        if rope is None:
+            rc = lib.psa_gather_rows(_ptr(x), _ptr(perm), _ptr(out), B * H, S, D, x.element_size(), _stream(x))
+        else:
+            rope.check(S, D, x.device)
+            rc = lib.psa_gather_rows_rope(_ptr(x), _ptr(perm), _ptr(rope.a), _ptr(rope.b), rope.first, _ptr(out), B * H, S, D,
+                                          _dt(x), _stream(x))
     check(rc, "psa_gather_rows")
     return out
 
 
-def pyramid_kv_images(k: torch.Tensor, v: torch.Tensor, block_n: int, perm: Optional[torch.Tensor] = None) -> KVImages:
+def pyramid_kv_images(k: torch.Tensor, v: torch.Tensor, block_n: int, perm: Optional[torch.Tensor] = None, rope=None) -> KVImages:
     """One pass over K and V -> tile images of levels 1/2/4/8 (f16/bf16, block_n 64/128).  perm: build the images of
-    k[..., perm, :], v[..., perm, :] without materialising them."""
+    k[..., perm, :], v[..., perm, :] without materialising them.  rope (RotaryTables): the keys are rotated as they are
+    read."""
     _need_cuda(k, v)
     assert k.shape == v.shape and k.dtype == v.dtype
     k, v = _flat_bh(k), _flat_bh(v)
@@ -135,7 +142,12 @@ def pyramid_kv_images(k: torch.Tensor, v: torch.Tensor, block_n: int, perm: Opti
     with torch.cuda.device(k.device):
         kimg = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
         vimg = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
-        if perm is None:
+        if rope is not None:
+            rope.check(S, D, k.device)
+            perm = None if perm is None else _perm32(perm, S)
+            rc = lib.psa_pyramid_kv_images_perm_rope(_ptr(k), _ptr(v), _ptr(perm), _ptr(rope.a), _ptr(rope.b), rope.first,
+                                                     _ptr(kimg), _ptr(vimg), B * H, S, D, block_n, _dt(k), _stream(k))
+        elif perm is None:
             rc = lib.psa_pyramid_kv_images(_ptr(k), _ptr(v), _ptr(kimg), _ptr(vimg), B * H, S, D, block_n, _dt(k), _stream(k))
         else:
             perm = _perm32(perm, S)
@@ -285,9 +297,11 @@ def draw_sample_indices(B: int, H: int, block: int, keep: int, device) -> torch.
     return idx.view(B, H, keep)
 
 
-def block_scores(q, k, idx_q, idx_k, block_m: int, block_n: int, impl: int = IMPL_AUTO, perm_q=None, perm_k=None) -> torch.Tensor:
+def block_scores(q, k, idx_q, idx_k, block_m: int, block_n: int, impl: int = IMPL_AUTO, perm_q=None, perm_k=None,
+                 rope=None) -> torch.Tensor:
     """Block-importance scores Po [B,H,Mq,Nk] (q.dtype).  idx_q [B,H,block_m/4], idx_k [B,H,block_n/4].
-    perm_q / perm_k (both or neither): the scores of q[..., perm_q, :], k[..., perm_k, :], read in place (f16/bf16)."""
+    perm_q / perm_k (both or neither): the scores of q[..., perm_q, :], k[..., perm_k, :], read in place (f16/bf16).
+    rope (RotaryTables; self-attention, perm_q is perm_k or both None): the sampled rows are rotated as they are gathered."""
     _need_cuda(q, k, idx_q, idx_k)
     q, k = _flat_bh(q), _flat_bh(k)
     B, H, Sq, D = q.shape
@@ -302,7 +316,14 @@ def block_scores(q, k, idx_q, idx_k, block_m: int, block_n: int, impl: int = IMP
         if nbytes == 0:
             raise ValueError(f"psa_block_scores: unsupported block sizes m={block_m} n={block_n}")
         scratch = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
-        if perm_q is None and perm_k is None:
+        if rope is not None:
+            assert Sq == Sk and perm_q is perm_k, "the rotating score kernel serves self-attention with one row table"
+            rope.check(Sq, D, q.device)
+            perm = None if perm_q is None else _perm32(perm_q, Sq)
+            rc = lib.psa_block_scores_perm_rope(_ptr(q), _ptr(k), _ptr(perm), _ptr(rope.a), _ptr(rope.b), rope.first, _ptr(iq),
+                                                _ptr(ik), _ptr(po), _ptr(scratch), nbytes, B * H, Sq, D, block_m, block_n,
+                                                _dt(q), _stream(q))
+        elif perm_q is None and perm_k is None:
             rc = lib.psa_block_scores(_ptr(q), _ptr(k), _ptr(iq), _ptr(ik), _ptr(po), _ptr(scratch), nbytes, B * H, Sq, Sk,
                                       D, block_m, block_n, _dt(q), impl, _stream(q))
         else:

@@ -169,13 +169,13 @@ class PyramidSparseAttention(nn.Module):
         dens = ops.density(mask, False) if compute_stats else None
         return out, dens
 
-    def _forward_rows_in_place(self, q, k, v, compute_stats):
+    def _forward_rows_in_place(self, q, k, v, compute_stats, rope=None):
         c = self.config
         perm = self.gilbert_rearranger.source_rows(q.device)
         with torch.no_grad():
-            mask, _, _ = compute_block_mask(q, k, c, text_length=c.text_length, perm=perm)
-        images = ops.pyramid_kv_images(k.contiguous(), v.contiguous(), c.block_n, perm=perm)
-        q_r = ops.gather_rows(q.contiguous(), perm)
+            mask, _, _ = compute_block_mask(q, k, c, text_length=c.text_length, perm=perm, rope=rope)
+        images = ops.pyramid_kv_images(k.contiguous(), v.contiguous(), c.block_n, perm=perm, rope=rope)
+        q_r = ops.gather_rows(q.contiguous(), perm, rope=rope)
         out = ops.psa_forward(q_r, k, v, mask, c.block_m, c.block_n, c.tile_n, None, pyramid=images, out_perm=perm)
         dens = ops.density(mask, True) if compute_stats else None
         return out.view(q.shape), dens
@@ -187,8 +187,8 @@ class PyramidSparseAttention(nn.Module):
         the kernels rotate the rows as they read them, on every other route they are rotated here first."""
         is_warmup = self.get_current_time() < self.config.warmup_steps
         if rotary is not None:
-            tm = [token_major_view(x) for x in (q, k, v)]
-            if is_warmup or not (self._rows_in_place(q, k) and all(t is not None for t in tm)):
+            # the in-place routes (token-major views or head-major tensors) rotate inside their loads
+            if is_warmup or not self._rows_in_place(q, k):
                 q, k = ops.rotate_rows(q, rotary), ops.rotate_rows(k, rotary)
                 rotary = None
         compute_stats = self.config.verbose or self.logger is not None
@@ -211,7 +211,7 @@ class PyramidSparseAttention(nn.Module):
                 out = out_tm.transpose(1, 2)
                 dens = ops.density(mask, True) if compute_stats else None
             else:
-                out, dens = self._forward_rows_in_place(q, k, v, compute_stats)
+                out, dens = self._forward_rows_in_place(q, k, v, compute_stats, rope=rotary)
             self.sparsity_counter += 1
             if self.logger is not None:
                 self.logger.log_sparsity(layer_idx=layer_idx, density=dens, sequence_length=q.shape[2],

@@ -84,3 +84,53 @@ def test_wan_processor_hands_unrotated_rows_to_a_module_that_rotates_in_its_kern
     ops.check_status()
     assert fused_calls == [True, False], fused_calls
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("first,reorder", [(0, False), (226, True)])
+def test_head_major_rotating_loads_equal_rotated_copies(first, reorder):
+    """The same three loads for head-major tensors [B, H, S, D] (what the CogVideoX processor holds after its per-head
+    norms): rows read through an optional order table and rotated on the way."""
+    from psa_b200 import ops
+    B, H, D = 1, 3, 64
+    S = 1000 + first
+    q, k, v = (C.randn(60 + i, (B, H, S, D), torch.bfloat16, smooth=4).to(DEV) for i in range(3))
+    a, b = _tables(S, first, D, 17)
+    rope = ops.RotaryTables(a, b, first)
+    perm = torch.randperm(S, generator=torch.Generator().manual_seed(5)).to(torch.int32).to(DEV) if reorder else None
+    q_r, k_r = ops.rotate_rows(q, rope), ops.rotate_rows(k, rope)
+    want_q = ops.gather_rows(q_r, perm) if reorder else q_r
+    assert torch.equal(ops.gather_rows(q, perm, rope=rope), want_q)
+    fused, plain = ops.pyramid_kv_images(k, v, 64, perm=perm, rope=rope), ops.pyramid_kv_images(k_r, v, 64, perm=perm)
+    assert torch.equal(fused.kimg, plain.kimg) and torch.equal(fused.vimg, plain.vimg)
+    iq, ik = C.sample_idx(41, B, H, 128, 32).to(DEV), C.sample_idx(42, B, H, 64, 16).to(DEV)
+    assert torch.equal(ops.block_scores(q, k, iq, ik, 128, 64, perm_q=perm, perm_k=perm, rope=rope),
+                       ops.block_scores(q_r, k_r, iq, ik, 128, 64, perm_q=perm, perm_k=perm))
+
+
+def test_cogvideox_processor_hands_unrotated_head_major_rows_to_the_module(monkeypatch):
+    """CogVideoX: text tokens first, per-head norms (head-major q, k), rotary tables for the video tokens only.  With the
+    module's `fuses_rotary` visible the processor passes q, k unrotated; behind a plain wrapper it rotates them itself."""
+    from psa_b200 import ops
+    from psa_b200.presets import SparseCogVideoXAttnProcessor
+    from test_gpu_processors import _Tap, _attn, _module
+    B, H, D, grid, n_text = 1, 2, 64, (16, 16, 8), 226
+    S = grid[0] * grid[1] * grid[2]
+    attn = _attn(H * D, H, per_head_norm=True)
+    module = _module(grid, n_text, True)
+    hidden = C.randn(71, (B, S, H * D), torch.bfloat16, smooth=8).to(DEV)
+    text = C.randn(72, (B, n_text, H * D), torch.bfloat16).to(DEV)
+    ang = (torch.rand(S, D // 2, generator=torch.Generator().manual_seed(9)) * 6.28).repeat_interleave(2, -1)
+    rot = (torch.cos(ang).to(DEV), torch.sin(ang).to(DEV))
+    fused_calls = []
+    real = ops.gather_rows
+    monkeypatch.setattr(ops, "gather_rows", lambda t, perm, rope=None: (fused_calls.append(rope is not None), real(t, perm, rope=rope))[1])
+    proc = SparseCogVideoXAttnProcessor(0)
+    outs = []
+    for inner in (module, _Tap(module)):
+        attn.inner_attention = inner
+        torch.manual_seed(123)
+        with torch.no_grad():
+            outs.append(proc(attn, hidden, text, image_rotary_emb=rot))
+    ops.check_status()
+    assert fused_calls == [True, False], fused_calls
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
