@@ -65,7 +65,7 @@ def compute_block_mask(q, k, config, text_length: int = 0, idx_q=None, idx_k=Non
         idx_q = ops.draw_sample_indices(B, H, config.block_m, config.block_m // 4, q.device)
     if idx_k is None:
         idx_k = ops.draw_sample_indices(B, H, config.block_n, config.block_n // 4, q.device)
-    assert rope is None or not config.use_sim_mask, "the similarity cap reads unrotated keys"
+    assert rope is None or not config.use_sim_mask, "the similarity cap would see unrotated keys"
     po = ops.block_scores(q, k, idx_q, idx_k, config.block_m, config.block_n, perm_q=perm, perm_k=perm, rope=rope)
     if config.attn_impl == "old_mask_type":
         mode = config.mask_mode
