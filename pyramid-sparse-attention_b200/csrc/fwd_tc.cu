@@ -93,6 +93,11 @@ template <int D> struct Cfg {
   static constexpr int NSB = D == 64 ? 3 : 2;
   static constexpr int O_BASE = NSB * 128;          // first TMEM column of the accumulators
   static constexpr int O_STRIDE = NSB == 3 ? 64 : 128;
+  // head_dim 128: ONE tcgen05.commit per tile.  "Scores of tile t complete" (the barrier that frees t's K stage) is also what
+  // the softmax waits for and what frees the V stage of tile t-NSB, whose product was issued before these scores - the
+  // tensor pipe runs in issue order, and a commit costs the issuing thread more than an MMA.  At head_dim 64 the V ring is
+  // deeper than the score buffers, the late release costs more than the commits save, and the three signals stay apart.
+  static constexpr bool ONE_SIGNAL = D == 128;
   static constexpr int TILE_BYTES = SLABS * kSlabBytes;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + TILE_BYTES;
@@ -113,7 +118,7 @@ struct Ctrl {
   // its full barrier, so a producer warp that was held up can find a stage two fills ahead of the one it is waiting
   // for - with one barrier per stage that looks exactly like "not yet" to a parity wait, and the warp (which owns one of
   // the next tiles) would block for good.  With two, a waiter may be up to three fills behind.
-  uint64_t k_empty[8], v_empty[8];
+  uint64_t k_empty[8], v_empty[8];      // k_empty doubles as "scores ready" when there is one signal per tile
   uint64_t s_full[3], p_full[2], pv_done[2], q_full;
   uint64_t row_ready[4], row_done[4], q_free, o_free;   // hand-over of query rows between the roles of a persistent CTA
   uint64_t prod_sync, xch_full;                         // bounded rendezvous of the producer warps / of the softmax warps
@@ -486,8 +491,13 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           if (step > 0) {
             const int t = step - 1, gt = g0 + t, stage = gt % C::NV;
             if (gt >= C::NV) {
-              const int f = gt / C::NV - 1;
-              ok = tc::mbar_wait_a(v_empty_a + (stage * 2 + (f & 1)) * 8, (f >> 1) & 1, abort_flag);
+              if (C::ONE_SIGNAL) {      // the scores of tile u were issued after P V of tile gt-NV, which held this stage
+                const int u = gt - C::NV + C::NSB, fu = u / C::NK;
+                ok = tc::mbar_wait_a(k_empty_a + ((u % C::NK) * 2 + (fu & 1)) * 8, (fu >> 1) & 1, abort_flag);
+              } else {
+                const int f = gt / C::NV - 1;
+                ok = tc::mbar_wait_a(v_empty_a + (stage * 2 + (f & 1)) * 8, (f >> 1) & 1, abort_flag);
+              }
             }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -575,7 +585,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
                   for (int ks = 0; ks < last_cols / 16; ++ks)
                     tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, (t > 1 || ks > 0) ? 1u : 0u);
                 }
-                tc::umma_commit_a(v_empty_a + (stage * 2 + ((gt / C::NV) & 1)) * 8);   // V tile may be refilled
+                if (!C::ONE_SIGNAL) tc::umma_commit_a(v_empty_a + (stage * 2 + ((gt / C::NV) & 1)) * 8);   // V tile may be refilled
                 // a tcgen05.commit costs this thread 100-500 cycles: "accumulator b is final" is only signalled for its last
                 // tile of the row (in between, the scores of tile t+2 - issued after this product - say the same)
                 // With three score buffers the next scores of this group may be issued before this product, so every product
@@ -601,8 +611,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
                   const uint32_t koff = (uint32_t)(((ks >> 2) * kSlabStride + (ks & 3) * 32) >> 4);
                   tc::umma_ss(tSb, qdesc + qoff, kdesc + koff, idesc_qk, ks > 0 ? 1u : 0u);
                 }
-                tc::umma_commit_a(k_empty_a + (stage * 2 + ((gt / C::NK) & 1)) * 8);   // K tile may be refilled
-                tc::umma_commit_a(s_full_a + (gt % C::NSB) * 8);
+                tc::umma_commit_a(k_empty_a + (stage * 2 + ((gt / C::NK) & 1)) * 8);   // K tile may be refilled (ONE_SIGNAL: scores ready)
+                if (!C::ONE_SIGNAL) tc::umma_commit_a(s_full_a + (gt % C::NSB) * 8);
               if (t == n_tiles - 1) tc::umma_commit_a(q_free_a);   // the query tile may be replaced
                 ++qk_next;
                 progressed = true;
@@ -674,7 +684,9 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         for (int j = first; j < n_tiles; j += 2) {
           const int gj = g0 + j, slot = gj % kBiasSlots, it = gj >> 1;
           // scores ready (and the tile's bias words visible)
-          if (C::NSB == 2) ok = tc::mbar_wait(&ctl->s_full[g], it & 1, abort_flag);
+          if (C::ONE_SIGNAL)
+            ok = tc::mbar_wait(&ctl->k_empty[(gj % C::NK) * 2 + ((gj / C::NK) & 1)], ((gj / C::NK) >> 1) & 1, abort_flag);
+          else if (C::NSB == 2) ok = tc::mbar_wait(&ctl->s_full[g], it & 1, abort_flag);
           else ok = tc::mbar_wait(&ctl->s_full[gj % 3], (gj / 3) & 1, abort_flag);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
