@@ -177,7 +177,13 @@ def psa_attention_host(q, k, v, config: PSAConfig = None, out=None, device=None,
     module = PSAAttention(config)
     if out is None:
         out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
-    hc = heads_per_chunk if heads_per_chunk > 0 else max(1, -(-H // 8))
+    if heads_per_chunk > 0:
+        hc = heads_per_chunk
+    else:
+        # about fourteen chunks (the first one's copy and the last one's compute and copy back are not overlapped with
+        # anything), but no chunk below ~32 MB of input: smaller copies and kernels cost more than they hide
+        per_head = 3 * B * L * D * q.element_size()
+        hc = min(H, max(-(-H // 14), -(-(32 << 20) // per_head)))
     chunks = [(h0, min(H, h0 + hc)) for h0 in range(0, H, hc)]
     with torch.cuda.device(dev):
         main = torch.cuda.current_stream()
@@ -200,19 +206,27 @@ def psa_attention_host(q, k, v, config: PSAConfig = None, out=None, device=None,
             with torch.cuda.stream(s_in):
                 if computed[b] is not None:
                     s_in.wait_event(computed[b])
-                for dst, src in zip(stage[b], (q, k, v)):
+                # q and k first: the scores and the level mask need nothing else, v is only read by the attention kernel
+                for dst, src in zip(stage[b][:2], (q, k)):
                     dst[:, :n].copy_(src[:, h0:h1], non_blocking=True)
-                arrived = torch.cuda.Event()
-                arrived.record(s_in)
-            main.wait_event(arrived)
-            if drained[b] is not None:
-                main.wait_event(drained[b])
-            dq, dk, dv = (t[:, :n] for t in stage[b])
+                arrived_qk = torch.cuda.Event()
+                arrived_qk.record(s_in)
+                stage[b][2][:, :n].copy_(v[:, h0:h1], non_blocking=True)
+                arrived_v = torch.cuda.Event()
+                arrived_v.record(s_in)
+            main.wait_event(arrived_qk)
+            dq, dk = (t[:, :n] for t in stage[b][:2])
             if n != hc:
-                dq, dk, dv = dq.contiguous(), dk.contiguous(), dv.contiguous()
+                dq, dk = dq.contiguous(), dk.contiguous()
             with torch.no_grad():
                 mask, _, _ = compute_block_mask(dq, dk, config, idx_q=idx_q[:, h0:h1].contiguous(),
                                                 idx_k=idx_k[:, h0:h1].contiguous())
+            main.wait_event(arrived_v)
+            if drained[b] is not None:
+                main.wait_event(drained[b])
+            dv = stage[b][2][:, :n]
+            if n != hc:
+                dv = dv.contiguous()
             o = module.sparse_attention_fn(dq, dk, dv, mask, None)
             outs[b][:, :n].copy_(o)
             computed[b] = torch.cuda.Event()
