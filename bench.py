@@ -42,7 +42,9 @@ CPU_SAMPLE_TOKENS = 32768
 # kernels are not counted)
 KERNELS_PER_CALL = {
     "psa_pyramid_kv_images": 1, "psa_pyramid_kv": 1, "psa_block_scores": 4, "psa_block_scores_samples": 2,
-    "psa_assign_levels": 1, "psa_fwd_images": 1, "psa_fwd": 1, "psa_fwd_images_scatter": 1, "psa_push_heads": 1,
+    # bf16 forward: the fixed-reference kernel and, right behind it, the exact kernel that returns at once unless the first
+    # one raised its guard word
+    "psa_assign_levels": 1, "psa_fwd_images": 2, "psa_fwd": 2, "psa_fwd_images_scatter": 2, "psa_push_heads": 1,
     "psa_push_samples": 1, "psa_pull_heads": 1, "psa_density": 1, "psa_legacy_fwd_images": 2, "psa_legacy_bwd_tc": 3,
     "psa_legacy_bwd_tcgen05": 5, "psa_ksim": 1, "psa_ksim_perm": 1, "psa_legacy_fwd_images_perm": 2, "psa_gather_rows": 1,
     "psa_pyramid_kv_images_perm": 1, "psa_block_scores_perm": 4, "psa_antidiag_scores_impl": 2, "psa_assign_levels_causal": 1,

@@ -35,6 +35,16 @@
 // TMEM (512 columns), head_dim 128: S0/P0 [0,128), S1/P1 [128,256), O of even tiles [256,384), O of odd tiles [384,512);
 // head_dim 64: three score buffers [0,384), O of even tiles [384,448), O of odd tiles [448,512).
 //
+// bf16 without the causal rule runs the FIXED-REFERENCE variant of the same kernel: the exponent that the probabilities of
+// a query row are taken relative to is the maximum of the row's FIRST tile (the group that owns that tile leaves it in
+// shared memory for the other one) and is never raised.  A bf16 probability has the exponent range of fp32, so later scores
+// may exceed the reference by dozens of octaves without losing a bit; the sum stays in fp32.  That removes the maximum
+// pass from every tile but the first and the rescaling of the accumulator, so both groups add into ONE accumulator
+// ([384, 384 + head_dim)), a third score buffer fits at head_dim 128 as well, and the row's end needs only the two sums.
+// A row whose sum of probabilities exceeds 2^90 (or is NaN) sets a guard word; the exact kernel is launched right behind
+// on the same stream and returns at once unless that word is set, in which case it redoes the call.  fp16 probabilities
+// (range 2^-24 .. 2^15) and the causal variants always take the exact kernel.
+//
 // Every wait is bounded - mbarrier waits, the issuer's polling loop and the warp-group rendezvous (mbarriers, never
 // bar.sync, inside the role loops); on expiry the CTA records PSA_ERR_TIMEOUT in the status word, lets copies in
 // flight land, frees its TMEM and returns.
@@ -82,22 +92,32 @@ struct TcParams {
   float* lse;           // optional log-sum-exp output
   int legacy;           // rows without a visible key give 0 / -inf instead of 0/0
   int causal;           // legacy causal rule on the diagonal block (index rows hold no block beyond the diagonal)
+  int* guard;           // fixed-reference variant: set when a row's probabilities left the safe exponent range
+  const int* only_if;   // run only if this word is non-zero (the exact kernel as the fixed-reference variant's fallback)
 };
 
-template <int D> struct Cfg {
+// FIXED (bf16, head_dim 128, no causal rule): the reference exponent of a query row is the maximum of its FIRST tile and
+// is never raised - bf16 probabilities have the exponent range of fp32, so later scores may exceed it by dozens of
+// octaves without harm (a guard word reports rows that came near the range; the exact kernel then redoes the call).
+// No maximum pass after the first tile, no rescaling of the accumulator, hence ONE accumulator for both softmax groups
+// and room for a third score buffer.
+template <int D, bool FIXED = false> struct Cfg {
   static constexpr int SLABS = D / 64;
   static constexpr int NK = D == 64 ? 4 : 3;   // K-tile ring
   static constexpr int NV = D == 64 ? 4 : 2;   // V-tile ring
   // Score buffers in TMEM.  At D = 128 the two accumulators leave room for two; at D = 64 for three, and the third one
   // lets Q K^T run two tiles ahead of P V, so that a softmax group finds its next scores ready when it is done with a tile.
-  static constexpr int NSB = D == 64 ? 3 : 2;
+  static constexpr int NSB = (D == 64 || FIXED) ? 3 : 2;
   static constexpr int O_BASE = NSB * 128;          // first TMEM column of the accumulators
-  static constexpr int O_STRIDE = NSB == 3 ? 64 : 128;
+  static constexpr int O_STRIDE = FIXED ? 0 : (NSB == 3 ? 64 : 128);
   // head_dim 128: ONE tcgen05.commit per tile.  "Scores of tile t complete" (the barrier that frees t's K stage) is also what
   // the softmax waits for and what frees the V stage of tile t-NSB, whose product was issued before these scores - the
   // tensor pipe runs in issue order, and a commit costs the issuing thread more than an MMA.  At head_dim 64 the V ring is
   // deeper than the score buffers, the late release costs more than the commits save, and the three signals stay apart.
   static constexpr bool ONE_SIGNAL = D == 128;
+  // The V stage of tile t is free when P V of tile t is complete.  With as many score buffers as V stages the scores of
+  // tile t+NV say so; with more score buffers than V stages no later score does, and the product is signalled itself.
+  static constexpr bool V_SIGNAL = !ONE_SIGNAL || NSB > NV;
   static constexpr int TILE_BYTES = SLABS * kSlabBytes;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + TILE_BYTES;
@@ -106,7 +126,7 @@ template <int D> struct Cfg {
   static constexpr int OFF_BIASG = OFF_BIAS + kBiasSlots * 128 * 4;   // one bias word per 4 columns + per-warp tile flags
   static constexpr int OFF_MINROW = OFF_BIASG + kBiasSlots * (32 + 4) * 4;   // causal: first query row that sees a column
   static constexpr int OFF_XCH = OFF_MINROW + kBiasSlots * 128;
-  static constexpr int OFF_ROW = OFF_XCH + 2 * 2 * 2 * 128 * 4;   // (max, sum) of both groups, two rows in flight
+  static constexpr int OFF_ROW = OFF_XCH + 2 * 2 * 2 * 128 * 4 + 4 * 128 * 4;   // (max, sum) of both groups, two rows in flight; reference exponents of four rows
   static constexpr int OFF_RAW = OFF_ROW + 2 * kMaxItems * 4;      // raw index list of the row being decoded
   static constexpr int OFF_CTRL = OFF_RAW + kMaxWidth * 4;
   static constexpr int SMEM_BYTES = OFF_CTRL + 1024 + 1024;   // control block + alignment slack
@@ -119,7 +139,7 @@ struct Ctrl {
   // for - with one barrier per stage that looks exactly like "not yet" to a parity wait, and the warp (which owns one of
   // the next tiles) would block for good.  With two, a waiter may be up to three fills behind.
   uint64_t k_empty[8], v_empty[8];      // k_empty doubles as "scores ready" when there is one signal per tile
-  uint64_t s_full[3], p_full[2], pv_done[2], q_full;
+  uint64_t s_full[3], p_full[2], pv_done[2], q_full, mref_full[4];
   uint64_t row_ready[4], row_done[4], q_free, o_free;   // hand-over of query rows between the roles of a persistent CTA
   uint64_t prod_sync, xch_full;                         // bounded rendezvous of the producer warps / of the softmax warps
   int row_tiles[4], row_last_cols[4], row_index[4];   // row_index >= total_rows: no more rows
@@ -165,9 +185,11 @@ constexpr uint32_t kItemQuirk = 1u << 14, kItemPad = 1u << 15;
 
 // IMG = true: K/V tiles use the image layout [8-row group][slab][8 rows][128 B] and are filled by linear bulk copies from
 // the tile-image buffers; IMG = false: [slab][128 rows][128 B] filled by tensor-map TMA boxes from row-major tensors.
-template <int D, int FMT, bool IMG, bool CAUSAL>
+template <int D, int FMT, bool IMG, bool CAUSAL, bool FIXED>
 __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_constant__ TmapPack maps, const TcParams p) {
-  using C = Cfg<D>;
+  using C = Cfg<D, FIXED>;
+  static_assert(!FIXED || (FMT == 1 && !CAUSAL), "the fixed reference needs bf16 probabilities and a first tile that every row sees");
+  if (p.only_if && *p.only_if == 0) return;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   unsigned char* sQ = smem + C::OFF_Q;
@@ -202,6 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       tc::mbar_init(&ctl->pv_done[i], 1);
     }
     tc::mbar_init(&ctl->q_full, 1);
+    for (int i = 0; i < 4; ++i) tc::mbar_init(&ctl->mref_full[i], 4);   // the four warps of the group that owns a row's first tile
     tc::mbar_init(&ctl->q_free, 1);
     tc::mbar_init(&ctl->o_free, 8);        // one arrival per softmax warp
     tc::fence_mbar_init();
@@ -491,7 +514,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           if (step > 0) {
             const int t = step - 1, gt = g0 + t, stage = gt % C::NV;
             if (gt >= C::NV) {
-              if (C::ONE_SIGNAL) {      // the scores of tile u were issued after P V of tile gt-NV, which held this stage
+              if (!C::V_SIGNAL) {      // the scores of tile u were issued after P V of tile gt-NV, which held this stage
                 const int u = gt - C::NV + C::NSB, fu = u / C::NK;
                 ok = tc::mbar_wait_a(k_empty_a + ((u % C::NK) * 2 + (fu & 1)) * 8, (fu >> 1) & 1, abort_flag);
               } else {
@@ -578,19 +601,21 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
                 const uint32_t tP = tmem + (gt % C::NSB) * 128;              // probabilities overwrite the scores they came from
                 const uint32_t tO = tmem + C::O_BASE + b * C::O_STRIDE;      // even and odd tiles accumulate separately
                 if (t < n_tiles - 1 || last_cols == 128) {
-                  tc::umma_ts(tO, tP, vdesc, idesc_pv, t > 1 ? 1u : 0u);
+                  tc::umma_ts(tO, tP, vdesc, idesc_pv, t > (FIXED ? 0 : 1) ? 1u : 0u);
 #pragma unroll
                   for (int ks = 1; ks < 8; ++ks) tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, 1u);
                 } else {
                   for (int ks = 0; ks < last_cols / 16; ++ks)
-                    tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, (t > 1 || ks > 0) ? 1u : 0u);
+                    tc::umma_ts(tO, tP + ks * 8, vdesc + (uint64_t)(ks * ((2 * kGroupStride) >> 4)), idesc_pv, (t > (FIXED ? 0 : 1) || ks > 0) ? 1u : 0u);
                 }
-                if (!C::ONE_SIGNAL) tc::umma_commit_a(v_empty_a + (stage * 2 + ((gt / C::NV) & 1)) * 8);   // V tile may be refilled
+                if (C::V_SIGNAL) tc::umma_commit_a(v_empty_a + (stage * 2 + ((gt / C::NV) & 1)) * 8);   // V tile may be refilled
                 // a tcgen05.commit costs this thread 100-500 cycles: "accumulator b is final" is only signalled for its last
                 // tile of the row (in between, the scores of tile t+2 - issued after this product - say the same)
                 // With three score buffers the next scores of this group may be issued before this product, so every product
                 // is signalled (the softmax waits for it before it rescales the accumulator).
-                if (C::NSB == 3 || t >= n_tiles - 2) tc::umma_commit_a(pv_done_a + b * 8);
+                if (FIXED) {      // one accumulator, never touched between products: only the row's last product is signalled
+                  if (t == n_tiles - 1) tc::umma_commit_a(pv_done_a);
+                } else if (C::NSB == 3 || t >= n_tiles - 2) tc::umma_commit_a(pv_done_a + b * 8);
                 ++pv_next;
                 progressed = true;
               }
@@ -647,6 +672,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
     bool ok = true;
     int g0 = 0, q_rows = 0, pv_rows = 0;
+    float* sMref = sXch + 1024;                   // fixed reference: [row & 3][128], behind the exchange area
     for (int rit = 0; ok; ++rit) {
       const int rslot = rit & 3;
       ok = tc::mbar_wait(&ctl->row_ready[rslot], (rit >> 2) & 1, abort_flag);
@@ -681,6 +707,9 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       }
       float m_run = -INFINITY, l_run = 0.f;
       const int first = ((g0 & 1) == g) ? 0 : 1;    // my first tile of this row
+      bool have_ref = false;                        // fixed reference: m_run holds the row's reference exponent
+      const int ne = q_rows;                        // rows with tiles before this one
+      const int ref_slot = ne & 3;
         for (int j = first; j < n_tiles; j += 2) {
           const int gj = g0 + j, slot = gj % kBiasSlots, it = gj >> 1;
           // scores ready (and the tile's bias words visible)
@@ -705,7 +734,10 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           const bool slow = ragged || (flagw[0] | flagw[1] | flagw[2]) != 0;
           uint32_t va[32], vb[32];      // two chunks of 32 score columns in flight
           float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-          if (!slow) {
+          const bool ref_tile = !FIXED || j == 0;      // fixed reference: only a row's first tile takes the maximum pass
+          if (!ref_tile) {
+            if (!slow) tc::tmem_ld32(tS, va);          // chunk 0 for pass 2
+          } else if (!slow) {
             // pass 1: running maximum; the load of the next chunk is issued before the current one is used
 #define PSA_MAX_CHUNK(v, c)                                                                                                  \
   do {                                                                                                                       \
@@ -756,13 +788,31 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
           // raise the running maximum only when it is far off (or still unset)
           float alpha = 1.f;
-          const bool raise = mx > m_run + 8.f;
-          if (raise) {
-            alpha = m_run == -INFINITY ? 0.f : ex2(m_run - mx);
-            m_run = mx;
-            l_run *= alpha;
+          bool raise = false;
+          if (FIXED) {
+            if (j == 0) {
+              // the group that owns the row's first tile sets the reference for both groups
+              m_run = mx == -INFINITY ? 0.f : mx;
+              sMref[ref_slot * 128 + r] = m_run;
+              __syncwarp();
+              if (lane == 0) tc::mbar_arrive(&ctl->mref_full[ref_slot]);
+              have_ref = true;
+            } else if (!have_ref) {
+              ok = tc::mbar_wait(&ctl->mref_full[ref_slot], (ne >> 2) & 1, abort_flag);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) break;
+              m_run = sMref[ref_slot * 128 + r];
+              have_ref = true;
+            }
+          } else {
+            raise = mx > m_run + 8.f;
+            if (raise) {
+              alpha = m_run == -INFINITY ? 0.f : ex2(m_run - mx);
+              m_run = mx;
+              l_run *= alpha;
+            }
           }
-          if (C::NSB == 3 && j >= 2) {
+          if (!FIXED && C::NSB == 3 && j >= 2) {
             // Every product of this group is signalled; each signal is waited for exactly once and in order (here for the
             // product of tile j-2, in the epilogue for the last one), so the waiter is never more than one phase behind.
             // By now - a whole maximum pass after the scores were found ready - it has normally long completed.
@@ -772,7 +822,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             ++pv_rows;
             tc::tc_fence_after();
           }
-          if (j >= 2 && __any_sync(0xffffffffu, raise)) {
+          if (!FIXED && j >= 2 && __any_sync(0xffffffffu, raise)) {
             // the accumulator may only be touched between two of its P V products: the one of tile j-2 is complete (see
             // above), the one of tile j waits for the probabilities written below
 #pragma unroll 1
@@ -858,7 +908,17 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
         }
       // ---- epilogue: merge the two groups' partial results
       const int my_tiles = n_tiles > first ? (n_tiles - first + 1) >> 1 : 0;
-      if (ok && my_tiles > 0) {
+      if (FIXED) {
+        if (ok && !have_ref) {      // a group without tiles in this row still passes the phase (and needs the reference for lse)
+          ok = tc::mbar_wait(&ctl->mref_full[ref_slot], (ne >> 2) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (ok) m_run = sMref[ref_slot * 128 + r];
+        }
+        if (ok) {                   // the row's last product: the one accumulator is final
+          ok = tc::mbar_wait(&ctl->pv_done[0], ne & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+        }
+      } else if (ok && my_tiles > 0) {
         // signalled once per row in which this group has tiles: after the last of them
         ok = tc::mbar_wait(&ctl->pv_done[g], pv_rows & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
@@ -872,27 +932,30 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       if (ok) ok = warps_rendezvous(&ctl->xch_full, q_rows, abort_flag); else ++q_rows;
       if (ok) {
         const float m_o = xch[(g ^ 1) * 256 + r], l_o = xch[(g ^ 1) * 256 + 128 + r];
-        const float m_all = fmaxf(m_run, m_o);
-        const float w_me = m_run == -INFINITY ? 0.f : ex2(m_run - m_all);
-        const float w_ot = m_o == -INFINITY ? 0.f : ex2(m_o - m_all);
+        const float m_all = FIXED ? m_run : fmaxf(m_run, m_o);      // fixed reference: both groups used the same exponent
+        const float w_me = FIXED ? 1.f : (m_run == -INFINITY ? 0.f : ex2(m_run - m_all));
+        const float w_ot = FIXED ? 1.f : (m_o == -INFINITY ? 0.f : ex2(m_o - m_all));
         const float l_all = l_run * w_me + l_o * w_ot;
-        const bool dead = p.legacy && m_all == -INFINITY;         // legacy kernel: no visible key -> 0, lse -inf
+        // legacy kernel: no visible key -> 0, lse -inf (fixed reference: every row sees its first tile, so "no key" = sum 0)
+        const bool dead = p.legacy && (FIXED ? l_all == 0.f : m_all == -INFINITY);
         const float inv = dead ? 0.f : 1.0f / l_all;              // otherwise an empty row is 0/0 like the reference
         const float w = w_me * inv, wo = w_ot * inv;
+        if (FIXED && p.guard && !(l_all < 1.2e27f) && qrow < p.seq_q) *p.guard = 1;   // 2^90: near the end of the exponent range (or NaN)
         if (p.lse && g == 0 && qrow < p.seq_q)
           p.lse[(int64_t)bh * p.seq_q + qrow] = dead ? -INFINITY : (m_all + log2f(l_all)) * 0.6931471805599453f;
-        const bool other_has = n_tiles - my_tiles > 0;
+        const bool other_has = !FIXED && n_tiles - my_tiles > 0;
+        const bool mine_has = FIXED || my_tiles > 0;
         tc::tc_fence_after();
         float f[HALF];
 #pragma unroll
         for (int c0 = 0; c0 < HALF; c0 += 32) {
           uint32_t va[32], vb[32];
-          if (my_tiles > 0) tc::tmem_ld32(tO + g * HALF + c0, va);
+          if (mine_has) tc::tmem_ld32(tO + g * HALF + c0, va);
           if (other_has) tc::tmem_ld32(tO_other + g * HALF + c0, vb);
           tc::tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            f[c0 + i] = (my_tiles > 0 ? __uint_as_float(va[i]) * w : 0.f) + (other_has ? __uint_as_float(vb[i]) * wo : 0.f);
+            f[c0 + i] = (mine_has ? __uint_as_float(va[i]) * w : 0.f) + (other_has ? __uint_as_float(vb[i]) * wo : 0.f);
         }
         // the accumulators may be overwritten by the next row from here on
         tc::tc_fence_before();
@@ -1036,9 +1099,9 @@ static int next_row_counter(int** out, cudaStream_t st) {
   return PSA_OK;
 }
 
-template <int D, int FMT, bool IMG, bool CAUSAL = false>
-static int launch_tc(const FwdArgs& a, cudaStream_t st) {
-  using C = Cfg<D>;
+template <int D, int FMT, bool IMG, bool CAUSAL = false, bool FIXED = false>
+static int launch_tc(const FwdArgs& a, cudaStream_t st, int* guard = nullptr, const int* only_if = nullptr) {
+  using C = Cfg<D, FIXED>;
   TmapPack maps;
   const int is_bf16 = FMT == 1;
   int rc = encode_tmap_3d(&maps.q, a.q, 2, is_bf16, D, a.seq_q, a.bh, 128);
@@ -1060,7 +1123,8 @@ static int launch_tc(const FwdArgs& a, cudaStream_t st) {
   p.img = make_img_levels(a.bh, a.seq_k, D, IMG ? a.bn : 64);
   p.scatter = a.scatter;
   p.lse = a.lse; p.legacy = a.legacy; p.causal = a.causal;
-  cudaError_t e = cudaFuncSetAttribute(psa_fwd_tc_kernel<D, FMT, IMG, CAUSAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+  p.guard = guard; p.only_if = only_if;
+  cudaError_t e = cudaFuncSetAttribute(psa_fwd_tc_kernel<D, FMT, IMG, CAUSAL, FIXED>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
   PSA_REQUIRE(e == cudaSuccess, PSA_ERR_CUDA, "psa_fwd: shared-memory opt-in (%d B) failed: %s", C::SMEM_BYTES,
               cudaGetErrorString(e));
   // persistent: one CTA per SM (221 KB of shared memory and all 512 TMEM columns each), rows dealt round-robin so that
@@ -1072,9 +1136,21 @@ static int launch_tc(const FwdArgs& a, cudaStream_t st) {
   const unsigned grid = (unsigned)(p.total_rows < sms ? p.total_rows : sms);
   rc = next_row_counter(&p.row_counter, st);
   if (rc != PSA_OK) return rc;
-  psa_fwd_tc_kernel<D, FMT, IMG, CAUSAL><<<grid, kThreads, C::SMEM_BYTES, st>>>(maps, p);
+  psa_fwd_tc_kernel<D, FMT, IMG, CAUSAL, FIXED><<<grid, kThreads, C::SMEM_BYTES, st>>>(maps, p);
   PSA_CHECK_LAUNCH("psa_fwd(tcgen05)");
   return PSA_OK;
+}
+
+// bf16 without the causal rule: the fixed-reference kernel, then the exact one, which returns at once unless the first one
+// raised its guard word (a row whose probabilities came near the end of the exponent range) - no host round trip.
+template <int D, bool IMG>
+static int launch_fixed_then_exact(const FwdArgs& a, cudaStream_t st) {
+  int* guard = nullptr;
+  int rc = next_row_counter(&guard, st);      // a zeroed device word of this launch
+  if (rc != PSA_OK) return rc;
+  rc = launch_tc<D, 1, IMG, false, true>(a, st, guard, nullptr);
+  if (rc != PSA_OK) return rc;
+  return launch_tc<D, 1, IMG, false, false>(a, st, nullptr, guard);
 }
 
 int fwd_tc_launch(const FwdArgs& a, cudaStream_t st) {
@@ -1087,13 +1163,12 @@ int fwd_tc_launch(const FwdArgs& a, cudaStream_t st) {
       if (a.D == 64) return fmt ? launch_tc<64, 1, true, true>(a, st) : launch_tc<64, 0, true, true>(a, st);
       return fmt ? launch_tc<128, 1, true, true>(a, st) : launch_tc<128, 0, true, true>(a, st);
     }
-    if (a.D == 64) return fmt ? launch_tc<64, 1, true>(a, st) : launch_tc<64, 0, true>(a, st);
-    return fmt ? launch_tc<128, 1, true>(a, st) : launch_tc<128, 0, true>(a, st);
+    if (a.D == 64) return fmt ? launch_fixed_then_exact<64, true>(a, st) : launch_tc<64, 0, true>(a, st);
+    return fmt ? launch_fixed_then_exact<128, true>(a, st) : launch_tc<128, 0, true>(a, st);
   }
   PSA_REQUIRE(!a.causal, PSA_ERR_UNSUPPORTED, "the causal rule needs the tile-image path");
-  if (a.D == 64) return fmt ? launch_tc<64, 1, false>(a, st) : launch_tc<64, 0, false>(a, st);
-  return fmt ? launch_tc<128, 1, false>(a, st) : launch_tc<128, 0, false>(a, st);
+  if (a.D == 64) return fmt ? launch_fixed_then_exact<64, false>(a, st) : launch_tc<64, 0, false>(a, st);
+  return fmt ? launch_fixed_then_exact<128, false>(a, st) : launch_tc<128, 0, false>(a, st);
 }
 
 }  // namespace psa
-

@@ -515,3 +515,38 @@ def test_legacy_backward_tcgen05_sparse_and_empty_rows(P):
         assert cosine(g, r) >= COS_OUT and float((g - r).abs().max()) <= 2e-2 * max(1.0, float(r.abs().max()))
     assert float(tc[0][0, 1, 4 * 128:5 * 128].abs().max()) == 0.0
     assert float(tc[1][0, 1, 7 * 128:8 * 128].abs().max()) == 0.0 and float(tc[2][0, 1, 7 * 128:8 * 128].abs().max()) == 0.0
+
+
+# ------------------------------------------------------------------ fixed reference exponent (bf16) --------
+@pytest.mark.parametrize("images", [True, False], ids=["images", "row_major"])
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("key_gain", [12.0, 40.0], ids=["60_octaves_above", "200_octaves_above"])
+def test_scores_far_above_a_rows_first_tile(P, D, images, key_gain):
+    """bf16 rows take their probabilities relative to the maximum of their FIRST tile.  A key in a later tile whose score
+    lies 60 octaves above that stays inside the exponent range of a bf16 probability and of the fp32 sum; one that lies
+    200 octaves above does not: the kernel's guard word must hand the call to the exact kernel.  Both must give the
+    oracle's rows (which are then almost exactly the value row of that one key)."""
+    S, bn = 1024, 64
+    nb = S // bn
+    g = torch.Generator().manual_seed(77)
+    q = (0.1 * torch.randn(1, 2, S, D, generator=g))
+    k = (0.1 * torch.randn(1, 2, S, D, generator=g))
+    v = torch.randn(1, 2, S, D, generator=g)
+    q[..., 0] = 40.0
+    k[0, 0, 900, 0] = key_gain            # head 0: token 900 sits in the row's eighth tile; head 1 has no such key
+    q, k, v = (x.to(torch.bfloat16) for x in (q, k, v))
+    row = list(range(nb)) + [-1, -1, -1, -1]
+    mask = torch.tensor(row, dtype=torch.int32).view(1, 1, 1, -1).expand(1, 2, S // 128, len(row)).contiguous()
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    pyr = P.ops.pyramid_kv_images(kd, vd, bn) if images else None
+    if images:
+        out = P.ops.psa_forward(qd, kd, vd, mask.to(DEV), 128, bn, 32, pyramid=pyr)
+    else:
+        out = P.ops.psa_forward(qd, kd, vd, mask.to(DEV), 128, bn, 32, impl=P.ops.IMPL_TENSOR)
+    assert int(out._psa_status.item()) == 0
+    ref = O.psa_forward_newmask(q, k, v, mask, 128, bn, 32).float()
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    assert float((got - ref).abs().max()) <= ATOL_OUT and cosine(got, ref) >= COS_OUT
+    # head 0 is the value row of the one key, head 1 an ordinary average
+    assert float((got[0, 0] - v[0, 0, 900].float()).abs().max()) <= ATOL_OUT
