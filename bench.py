@@ -76,7 +76,7 @@ class LaunchCounter:
 # scales with heads x tokens.
 FWD_TRAFFIC_PER_HEAD_TOKEN = {
     "wan2.1-1.3b-attn-layer": (1539.0, "profiles/psa_fwd_tc_kernel__wan2.1-1.3b-shape_6heads.md"),
-    "wan2.1-14b-attn-layer": (2904.0, "profiles/psa_fwd_tc_kernel__wan2.1-14b-shape_5heads_dram.md"),
+    "wan2.1-14b-attn-layer": (2837.0, "profiles/psa_fwd_tc_kernel__wan2.1-14b-shape_5heads_dram.md"),
 }
 
 
