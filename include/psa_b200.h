@@ -127,7 +127,14 @@ int psa_ksim(const void* k, int32_t* out, int64_t bh, int64_t seq, int head_dim,
  * tcgen05 launch on a device resolves the ring's address (cudaGetSymbolAddress) - make it outside any stream capture -
  * and more than 256 launches of this family in flight at once on one device would share counters (a captured graph pins
  * its slot for every replay: do not replay such graphs while more than 255 other launches overlap them).  This holds
- * for every psa_fwd* / psa_legacy_fwd_images* entry point. */
+ * for every psa_fwd* / psa_legacy_fwd_images* entry point.
+ * bf16 without the causal rule is TWO launches of the tcgen05 kernel.  The first takes the probabilities of a query row
+ * relative to the maximum of the row's first tile instead of a running maximum (same result: the factor cancels against
+ * the row sum; bf16 probabilities and the fp32 sum have the exponent range for it), which saves the maximum pass and
+ * the rescaling; a row whose sum leaves the safe range sets a guard word (another slot of the counter ring).  The
+ * second launch is the running-maximum kernel: it reads the guard word, returns at once if it is zero and recomputes
+ * the call otherwise.  Both are ordered on `stream`; nothing is read back by the host.  fp16 calls and the causal
+ * variants are one launch of the running-maximum kernel. */
 int psa_fwd(const void* q, const void* k, const void* v, const void* k2, const void* k4, const void* k8,
             const void* v2, const void* v4, const void* v8, const int32_t* mask, void* out, int64_t bh,
             int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width,
