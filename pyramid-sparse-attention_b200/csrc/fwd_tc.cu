@@ -139,7 +139,11 @@ struct Ctrl {
   // for - with one barrier per stage that looks exactly like "not yet" to a parity wait, and the warp (which owns one of
   // the next tiles) would block for good.  With two, a waiter may be up to three fills behind.
   uint64_t k_empty[8], v_empty[8];      // k_empty doubles as "scores ready" when there is one signal per tile
-  uint64_t s_full[3], p_full[2], pv_done[2], q_full, mref_full[4];
+  uint64_t s_full[3], pv_done[2], q_full, mref_full[4];
+  // probabilities of a tile written: two barriers per group, used by the group's alternate tiles.  With three score
+  // buffers a group can finish its NEXT tile before the issuer has seen this one (P V also waits for the V tile), and a
+  // parity wait must never fall two phases behind its barrier.
+  uint64_t p_full[4];
   uint64_t row_ready[4], row_done[4], q_free, o_free;   // hand-over of query rows between the roles of a persistent CTA
   uint64_t prod_sync, xch_full;                         // bounded rendezvous of the producer warps / of the softmax warps
   int row_tiles[4], row_last_cols[4], row_index[4];   // row_index >= total_rows: no more rows
@@ -220,7 +224,8 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
     tc::mbar_init(&ctl->s_full[2], 1);
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&ctl->s_full[i], 1);
-      tc::mbar_init(&ctl->p_full[i], 4);   // one arrival per softmax warp of the group
+      tc::mbar_init(&ctl->p_full[2 * i], 4);   // one arrival per softmax warp of the group
+      tc::mbar_init(&ctl->p_full[2 * i + 1], 4);
       tc::mbar_init(&ctl->pv_done[i], 1);
     }
     tc::mbar_init(&ctl->q_full, 1);
@@ -595,7 +600,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             if (pv_next < qk_next) {
               const int t = pv_next, gt = g0 + t, b = gt & 1, stage = gt % C::NV;
               if (!o_ok) o_ok = tc::mbar_test_wait_a(o_free_a, (q_rows - 1) & 1);
-            if (o_ok && tc::mbar_test_wait_a(p_full_a + b * 8, (gt >> 1) & 1) && tc::mbar_test_wait_a(v_full_a + stage * 8, (gt / C::NV) & 1)) {
+            if (o_ok && tc::mbar_test_wait_a(p_full_a + (b * 2 + ((gt >> 1) & 1)) * 8, (gt >> 2) & 1) && tc::mbar_test_wait_a(v_full_a + stage * 8, (gt / C::NV) & 1)) {
                 tc::tc_fence_after();
                 const uint64_t vdesc = vdesc0 + (uint64_t)(stage * (C::TILE_BYTES >> 4));
                 const uint32_t tP = tmem + (gt % C::NSB) * 128;              // probabilities overwrite the scores they came from
@@ -904,7 +909,7 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
           tc::tmem_wait_st();
           tc::tc_fence_before();
           __syncwarp();
-          if (lane == 0) tc::mbar_arrive(&ctl->p_full[g]);   // one arrival per warp
+          if (lane == 0) tc::mbar_arrive(&ctl->p_full[g * 2 + (it & 1)]);   // one arrival per warp
         }
       // ---- epilogue: merge the two groups' partial results
       const int my_tiles = n_tiles > first ? (n_tiles - first + 1) >> 1 : 0;
