@@ -12,8 +12,10 @@
 //               (128-byte swizzle).  Never multicast.  A copy costs its issuing thread ~100 cycles whatever its size, an
 //               mbarrier arrive ~250 and a wait ~170, so the blocks of a tile are spread over the lanes of ONE warp and the
 //               three warps take turns (K tile t is job 2t, V tile t job 2t+1, job J belongs to warp J mod 3); every warp
-//               still waits for every tile's stage, in order.  K tiles and V tiles live in separate rings (K is released
-//               after S = Q K^T, V after O += P V) and K runs one tile ahead of V.  The producers also write the logit bias of
+//               still passes every tile's stage barrier, in order.  K tiles and V tiles live in separate rings (K is
+//               released after S = Q K^T, V after O += P V) and every warp walks them with two cursors, whichever stage
+//               is free first: a V stage is released late, a K stage early, and in one fixed order every K gather
+//               queued behind the wait for a V stage.  The producers also write the logit bias of
 //               the tile's columns (log2 of the level, -inf for columns that do not exist), per column and per group of
 //               4 columns, publish every row (tile count) to the other roles and fetch its query tile as soon as the
 //               previous row's last Q K^T has read the old one.
@@ -422,19 +424,73 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
       if (q_pending) fetch_q(false);
       if (n_tiles > 0) ++q_rows;
       int ki = 0, vi = 0;              // first item of the next K tile / V tile
-        // step s gathers K tile s and then V tile s-1: K runs one tile ahead of V
-        for (int step = 0; ok && step <= n_tiles; ++step) {
-          if (q_pending) fetch_q(step >= C::NK - 1);   // latest before the copy that needs the previous row's last tile gone
-          if (ok && step == decode_step) ok = decode_row(rit + 1);
-          if (!ok) break;
-          if (step < n_tiles) {
-            const int t = step, gt = g0 + t, stage = gt % C::NK, slot = gt % kBiasSlots;
-            if (gt >= C::NK) {      // fill number f of the stage waits for the scores of fill f-1
-              const int f = gt / C::NK - 1;
-              ok = tc::mbar_wait_a(k_empty_a + (stage * 2 + (f & 1)) * 8, (f >> 1) & 1, abort_flag);
+        // Two cursors per warp: the next V tile and the next K tile of the row.  A V stage is released late (by the completion
+        // of a P V product), a K stage early (by the scores of the tile three before); walking them in one fixed order
+        // made every K gather queue behind the wait for a V stage.  Every warp still passes every stage's barrier in
+        // order (per cursor), the tile's owner gathers it; the row bookkeeping (query tile, decode of the next row) is
+        // keyed to the K cursor.
+        int kt = 0, vt = 0;
+        bool decoded = false;
+        uint32_t spins = 0;
+        while (ok && (vt < n_tiles || !decoded)) {
+          bool progressed = false;
+          if (vt < kt) {
+            const int t = vt, gt = g0 + t, stage = gt % C::NV;
+            bool ready = true;
+            if (gt >= C::NV) {
+              if (!C::V_SIGNAL) {      // the scores of tile u were issued after P V of tile gt-NV, which held this stage
+                const int u = gt - C::NV + C::NSB, fu = u / C::NK;
+                ready = tc::mbar_test_wait_a(k_empty_a + ((u % C::NK) * 2 + (fu & 1)) * 8, (fu >> 1) & 1);
+              } else {
+                const int f = gt / C::NV - 1;
+                ready = tc::mbar_test_wait_a(v_empty_a + (stage * 2 + (f & 1)) * 8, (f >> 1) & 1);
+              }
             }
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            ready = __all_sync(0xffffffffu, ready);
+            if (ready) {
+            const int probe = vi + lane;
+            const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sIt[probe < n_items ? probe : 0] >> 21) == t));
+            if ((2 * gt + 1) % kProducerWarps == warp) {
+            const uint32_t tile_a = sV_a + stage * C::TILE_BYTES, bar_a = v_full_a + stage * 8;
+            const int mine = vi + lane;
+            uint32_t my_bytes = 0;
+            if (lane < in_tile) {
+              const uint32_t x = sIt[mine];
+              const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = ((int)(x >> 16) << 2) & 127;
+              if (IMG) {
+                const unsigned char* src = p.vimg + p.img.off[li] + (((int64_t)bh * p.img.groups[li] + ((blk * P) >> 3)) * C::SLABS << 10);
+                tc::bulk_load_a(tile_a + (col >> 3) * (C::SLABS * 1024), src, (uint32_t)(P * D * 2), bar_a);
+              } else {
+#pragma unroll
+                for (int sl = 0; sl < C::SLABS; ++sl)
+                  tc::tma_load_3d_a(tile_a + sl * kSlabBytes + col * 128, vmap0 + (uint64_t)li * sizeof(CUtensorMap), bar_a, sl * 64, blk * P, bh);
+              }
+              my_bytes = (uint32_t)C::SLABS * P * 128u;
+            }
+            const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
+            if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
+            }
+            vi += in_tile;
+              ++vt;
+              progressed = true;
+            }
+          }
+          if (kt < n_tiles || !decoded) {
+            if (q_pending) fetch_q(kt >= C::NK - 1);   // latest before the copy that needs the previous row's last tile gone
+            if (ok && !decoded && kt == decode_step) {
+              ok = decode_row(rit + 1);
+              decoded = true;
+              progressed = true;
+            }
+            if (ok && kt < n_tiles) {
+              const int t = kt, gt = g0 + t, stage = gt % C::NK, slot = gt % kBiasSlots;
+              bool ready = true;
+              if (gt >= C::NK) {      // fill number f of the stage waits for the scores of fill f-1
+                const int f = gt / C::NK - 1;
+                ready = tc::mbar_test_wait_a(k_empty_a + (stage * 2 + (f & 1)) * 8, (f >> 1) & 1);
+              }
+              ready = __all_sync(0xffffffffu, ready);
+              if (ready) {
             const int probe = ki + lane;
             const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sIt[probe < n_items ? probe : 0] >> 21) == t));
             // Every producer warp waits for every tile's stage, in order (a parity wait is only valid for a waiter at most
@@ -515,43 +571,16 @@ __global__ void __launch_bounds__(kThreads, 1) psa_fwd_tc_kernel(const __grid_co
             if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
             }
             ki += in_tile;
+                ++kt;
+                progressed = true;
+              }
+            }
           }
-          if (step > 0) {
-            const int t = step - 1, gt = g0 + t, stage = gt % C::NV;
-            if (gt >= C::NV) {
-              if (!C::V_SIGNAL) {      // the scores of tile u were issued after P V of tile gt-NV, which held this stage
-                const int u = gt - C::NV + C::NSB, fu = u / C::NK;
-                ok = tc::mbar_wait_a(k_empty_a + ((u % C::NK) * 2 + (fu & 1)) * 8, (fu >> 1) & 1, abort_flag);
-              } else {
-                const int f = gt / C::NV - 1;
-                ok = tc::mbar_wait_a(v_empty_a + (stage * 2 + (f & 1)) * 8, (f >> 1) & 1, abort_flag);
-              }
-            }
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            const int probe = vi + lane;
-            const int in_tile = __popc(__ballot_sync(0xffffffffu, probe < n_items && (int)(sIt[probe < n_items ? probe : 0] >> 21) == t));
-            if ((2 * gt + 1) % kProducerWarps == warp) {
-            const uint32_t tile_a = sV_a + stage * C::TILE_BYTES, bar_a = v_full_a + stage * 8;
-            const int mine = vi + lane;
-            uint32_t my_bytes = 0;
-            if (lane < in_tile) {
-              const uint32_t x = sIt[mine];
-              const int li = (x >> 12) & 3, blk = x & 0xfff, P = p.bn >> li, col = ((int)(x >> 16) << 2) & 127;
-              if (IMG) {
-                const unsigned char* src = p.vimg + p.img.off[li] + (((int64_t)bh * p.img.groups[li] + ((blk * P) >> 3)) * C::SLABS << 10);
-                tc::bulk_load_a(tile_a + (col >> 3) * (C::SLABS * 1024), src, (uint32_t)(P * D * 2), bar_a);
-              } else {
-#pragma unroll
-                for (int sl = 0; sl < C::SLABS; ++sl)
-                  tc::tma_load_3d_a(tile_a + sl * kSlabBytes + col * 128, vmap0 + (uint64_t)li * sizeof(CUtensorMap), bar_a, sl * 64, blk * P, bh);
-              }
-              my_bytes = (uint32_t)C::SLABS * P * 128u;
-            }
-            const uint32_t bytes = __reduce_add_sync(0xffffffffu, my_bytes);
-            if (lane == 0) tc::mbar_arrive_expect_tx_a(bar_a, bytes);
-            }
-            vi += in_tile;
+          if (progressed) {
+            spins = 0;
+          } else if (++spins > (1u << 24) || ((spins & 255) == 255 && *abort_flag)) {
+            *abort_flag = 1;
+            ok = false;
           }
         }
       if (ok && q_pending) fetch_q(true);
