@@ -188,16 +188,18 @@ def test_legacy_backward_accepts_any_integer_mask_layout(P, variant):
         assert cosine(a, r) >= COS_OUT and float((a - r).abs().max()) <= 2e-2 * max(1.0, float(r.abs().max()))
 
 
-@pytest.mark.parametrize("workload,heads", [("COGVIDEOX_5B", 24), ("WAN_1_3B", 12)])
-def test_forward_many_launches_complete_and_repeat(P, workload, heads):
+@pytest.mark.parametrize("workload,heads,dt,launches", [("COGVIDEOX_5B", 24, "bf16", 120), ("WAN_1_3B", 12, "bf16", 120),
+                                                        ("WAN_1_3B", 6, "fp16", 60), ("WAN_14B", 4, "bf16", 40)])
+def test_forward_many_launches_complete_and_repeat(P, workload, heads, dt, launches):
     """The persistent forward hands tiles between its producer, issuer and softmax warps through mbarriers whose waits
-    are bounded; a protocol slip shows up as a rare expired wait (status word) rather than a wrong number.  120 launches
-    back to back at a full token count (head_dim 64 with three score buffers, head_dim 128 with two) must all complete
-    and give the bits of the first one."""
+    are bounded; a protocol slip shows up as a rare expired wait (status word) rather than a wrong number.  Many launches
+    back to back at full token counts - bf16 (fixed reference exponent, three score buffers) at head_dim 64 and 128,
+    fp16 (running maximum, two score buffers at head_dim 128), and the 59-tile rows of the 75600-token shape - must
+    all complete and give the bits of the first one."""
     from psa_b200 import synthetic
     wl = dict(getattr(synthetic, workload))
     wl["heads"] = heads
-    q, k, v = synthetic.make_qkv(wl, 1000, torch.bfloat16, DEV)
+    q, k, v = synthetic.make_qkv(wl, 1000, C.DT[dt], DEV)
     cfg = P.PSAConfig(block_m=128, block_n=64, tile_n=32, mask_ratios=C.RATIOS_90, mask_mode="topk")
     torch.manual_seed(2000)
     mask, _, _ = P.compute_block_mask(q, k, cfg)
@@ -205,7 +207,7 @@ def test_forward_many_launches_complete_and_repeat(P, workload, heads):
     first = P.ops.psa_forward(q, k, v, mask, 128, 64, 32, pyramid=images).clone()
     assert not torch.isnan(first).any()
     differing = 0
-    for i in range(120):
+    for i in range(launches):
         out = P.ops.psa_forward(q, k, v, mask, 128, 64, 32, pyramid=images)
         if i % 8 == 7:
             differing += int(not torch.equal(out, first))
