@@ -134,7 +134,8 @@ int psa_ksim(const void* k, int32_t* out, int64_t bh, int64_t seq, int head_dim,
  * the rescaling; a row whose sum leaves the safe range sets a guard word (another slot of the counter ring).  The
  * second launch is the running-maximum kernel: it reads the guard word, returns at once if it is zero and recomputes
  * the call otherwise.  Both are ordered on `stream`; nothing is read back by the host.  fp16 calls and the causal
- * variants are one launch of the running-maximum kernel. */
+ * variants are one launch of the running-maximum kernel.  A bf16 call therefore takes THREE words of the ring (two row
+ * counters and the guard word): about 85 such calls may be in flight on one device before words are shared. */
 int psa_fwd(const void* q, const void* k, const void* v, const void* k2, const void* k4, const void* k8,
             const void* v2, const void* v4, const void* v8, const int32_t* mask, void* out, int64_t bh,
             int64_t seq_q, int64_t seq_k, int head_dim, int block_m, int block_n, int tile_n, int mask_width,
